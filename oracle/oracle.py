@@ -1,0 +1,329 @@
+"""ctypes front-end for the CPU checker (TEST INFRASTRUCTURE ONLY).
+
+``Oracle`` wraps ``liboracle.so`` (the C restatement in ``oracle_ops.c``); ``Reference`` wraps
+the reference's own operator headers compiled into ``oracle/_ref`` (see ``build_oracle.py``).
+Only the tests, the smoke entry and the benchmark's CPU-baseline leg may import this module;
+the shipped package never does.
+
+All arrays are C-contiguous numpy arrays; fp32 data, int32 token ids (uint16 for the
+reference wrappers, which keep the reference's token type).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+_f32p = C.POINTER(C.c_float)
+_i32p = C.POINTER(C.c_int32)
+_u16p = C.POINTER(C.c_uint16)
+
+
+def _fp(a: np.ndarray):
+    assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"], (a.dtype, a.flags)
+    return a.ctypes.data_as(_f32p)
+
+
+def _ip(a: np.ndarray):
+    assert a.dtype == np.int32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(_i32p)
+
+
+def _up(a: np.ndarray):
+    assert a.dtype == np.uint16 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(_u16p)
+
+
+def ensure_built() -> None:
+    need = [os.path.join(HERE, "liboracle.so"), os.path.join(HERE, "liboracle_fast.so")]
+    if not all(os.path.exists(p) for p in need):
+        from . import build_oracle  # noqa: WPS433 (local import: builds on demand)
+
+        build_oracle.build_restatement()
+
+
+class Oracle:
+    """The C restatement.  ``fast=True`` loads the -O3/-march=native/OpenMP build that the
+    benchmark times; the default build keeps the arithmetic as written (-ffp-contract=off)."""
+
+    def __init__(self, fast: bool = False):
+        ensure_built()
+        self.lib = C.CDLL(os.path.join(HERE, "liboracle_fast.so" if fast else "liboracle.so"))
+        L = self.lib
+        L.orc_rmsnorm_batched.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int, C.c_float]
+        L.orc_rmsnorm_bwd_batched.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int,
+                                              C.c_float, C.c_int]
+        L.orc_residual.argtypes = [_f32p, _f32p, _f32p, C.c_float, C.c_size_t]
+        L.orc_scale.argtypes = [_f32p, _f32p, C.c_float, C.c_size_t]
+        L.orc_add.argtypes = [_f32p, _f32p, _f32p, C.c_size_t]
+        L.orc_swiglu.argtypes = [_f32p, _f32p, _f32p, C.c_size_t]
+        L.orc_swiglu_bwd.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, C.c_size_t]
+        L.orc_rope_batched.argtypes = [_f32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int]
+        L.orc_qknorm_rope_batched.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                              C.c_float, C.c_float, C.c_int]
+        L.orc_rope_qknorm_bwd_batched.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int,
+                                                  C.c_int, C.c_float, C.c_float, C.c_int, C.c_int]
+        L.orc_qknorm.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int, C.c_float]
+        L.orc_qknorm_bwd.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int, C.c_float,
+                                     C.c_int]
+        L.orc_embed_lookup.argtypes = [_f32p, _f32p, _i32p, C.c_int, C.c_int, C.c_int]
+        L.orc_embed_lookup.restype = C.c_int
+        L.orc_embed_backward.argtypes = [_f32p, _f32p, _i32p, C.c_int, C.c_int, C.c_int]
+        L.orc_embed_backward.restype = C.c_int
+        L.orc_cross_entropy.argtypes = [_f32p, _f32p, _i32p, C.c_int, C.c_int, C.c_float, C.POINTER(C.c_int)]
+        L.orc_cross_entropy.restype = C.c_float
+        L.orc_adam.argtypes = [_f32p, _f32p, _f32p, _f32p, C.c_size_t, C.c_int, C.c_float, C.c_float, C.c_float,
+                               C.c_float, C.c_float, C.c_int, C.c_float, C.c_float]
+        L.orc_grad_norm_sq.argtypes = [_f32p, C.c_size_t, C.c_float]
+        L.orc_grad_norm_sq.restype = C.c_double
+        L.orc_clip_factor.argtypes = [C.c_float, C.c_float]
+        L.orc_clip_factor.restype = C.c_float
+        L.orc_vocab_map_build.argtypes = [_i32p, C.c_size_t, C.c_int, _i32p, _i32p]
+        L.orc_vocab_map_build.restype = C.c_int
+        L.orc_num_threads.restype = C.c_int
+        L.orc_set_num_threads.argtypes = [C.c_int]
+
+    # --- norms -----------------------------------------------------------------------
+    def rmsnorm(self, x, w, eps=1e-5):
+        """x [B,C,S] or [C,S] fp32 -> y same shape."""
+        x3 = x.reshape((-1,) + x.shape[-2:])
+        out = np.empty_like(x3)
+        B, d, S = x3.shape
+        self.lib.orc_rmsnorm_batched(_fp(out), _fp(x3), _fp(w), B, d, S, eps)
+        return out.reshape(x.shape)
+
+    def rmsnorm_bwd(self, dy, x, w, dw=None, eps=1e-5, exact=False):
+        """Returns (dx, dw); dw is accumulated into a copy of the given array (zeros if None)."""
+        x3 = x.reshape((-1,) + x.shape[-2:])
+        dy3 = dy.reshape(x3.shape)
+        B, d, S = x3.shape
+        dx = np.zeros_like(x3)
+        dwo = np.zeros(d, np.float32) if dw is None else dw.copy()
+        self.lib.orc_rmsnorm_bwd_batched(_fp(dx), _fp(dwo), _fp(dy3), _fp(x3), _fp(w), B, d, S, eps, int(exact))
+        return dx.reshape(x.shape), dwo
+
+    # --- element-wise ------------------------------------------------------------------
+    def residual(self, x, f, alpha):
+        out = np.empty_like(x)
+        self.lib.orc_residual(_fp(out), _fp(x), _fp(f), alpha, x.size)
+        return out
+
+    def scale(self, x, alpha):
+        out = np.empty_like(x)
+        self.lib.orc_scale(_fp(out), _fp(x), alpha, x.size)
+        return out
+
+    def add(self, a, b):
+        out = np.empty_like(a)
+        self.lib.orc_add(_fp(out), _fp(a), _fp(b), a.size)
+        return out
+
+    def swiglu(self, h1, h3):
+        out = np.empty_like(h1)
+        self.lib.orc_swiglu(_fp(out), _fp(h1), _fp(h3), h1.size)
+        return out
+
+    def swiglu_bwd(self, h1, h3, d):
+        dh1 = np.empty_like(h1)
+        dh3 = np.empty_like(h1)
+        self.lib.orc_swiglu_bwd(_fp(dh1), _fp(dh3), _fp(h1), _fp(h3), _fp(d), h1.size)
+        return dh1, dh3
+
+    # --- rope / qk-norm ------------------------------------------------------------------
+    def rope(self, x, hd, base=10000.0, pos0=0, inverse=False):
+        x3 = np.ascontiguousarray(x.reshape((-1,) + x.shape[-2:])).copy()
+        B, dim, S = x3.shape
+        self.lib.orc_rope_batched(_fp(x3), B, S, dim, hd, base, pos0, int(inverse))
+        return x3.reshape(x.shape)
+
+    def qknorm(self, x, w, hd, eps=1e-6):
+        x3 = x.reshape((-1,) + x.shape[-2:])
+        B, dim, S = x3.shape
+        out = np.empty_like(x3)
+        for b in range(B):
+            self.lib.orc_qknorm(_fp(out[b]), _fp(x3[b]), _fp(w), dim // hd, hd, S, eps)
+        return out.reshape(x.shape)
+
+    def qknorm_bwd(self, dy, x, w, hd, dw=None, eps=1e-6, exact=False):
+        x3 = x.reshape((-1,) + x.shape[-2:])
+        dy3 = dy.reshape(x3.shape)
+        B, dim, S = x3.shape
+        dx = np.zeros_like(x3)
+        dwo = np.zeros(hd, np.float32) if dw is None else dw.copy()
+        for b in range(B):
+            self.lib.orc_qknorm_bwd(_fp(dx[b]), _fp(dwo), _fp(dy3[b]), _fp(x3[b]), _fp(w), dim // hd, hd, S, eps,
+                                    int(exact))
+        return dx.reshape(x.shape), dwo
+
+    def qknorm_rope(self, x, w, hd, eps=1e-6, base=1e6, pos0=0):
+        x3 = x.reshape((-1,) + x.shape[-2:])
+        B, dim, S = x3.shape
+        out = np.empty_like(x3)
+        self.lib.orc_qknorm_rope_batched(_fp(out), _fp(x3), _fp(w), B, dim // hd, hd, S, eps, base, pos0)
+        return out.reshape(x.shape)
+
+    def rope_qknorm_bwd(self, dy, x, w, hd, dw=None, eps=1e-6, base=1e6, pos0=0, exact=False):
+        x3 = x.reshape((-1,) + x.shape[-2:])
+        dy3 = dy.reshape(x3.shape)
+        B, dim, S = x3.shape
+        dx = np.zeros_like(x3)
+        dwo = np.zeros(hd, np.float32) if dw is None else dw.copy()
+        self.lib.orc_rope_qknorm_bwd_batched(_fp(dx), _fp(dwo), _fp(dy3), _fp(x3), _fp(w), B, dim // hd, hd, S,
+                                             eps, base, pos0, int(exact))
+        return dx.reshape(x.shape), dwo
+
+    # --- embedding -----------------------------------------------------------------------
+    def embed_lookup(self, table, tokens, x_init=None):
+        """table [V,D] fp32, tokens [B,S] int32 -> x [B,D,S]; returns (x, n_out_of_range)."""
+        tok = np.ascontiguousarray(tokens.reshape(-1, tokens.shape[-1]).astype(np.int32))
+        B, S = tok.shape
+        V, D = table.shape
+        x = np.zeros((B, D, S), np.float32) if x_init is None else x_init.reshape(B, D, S).copy()
+        oor = 0
+        for b in range(B):
+            oor += self.lib.orc_embed_lookup(_fp(x[b]), _fp(table), _ip(tok[b]), D, S, V)
+        return x, oor
+
+    def embed_backward(self, d_embed, dx, tokens):
+        """Accumulates into a copy of d_embed [V,D] in order b=0.., t=0..; returns (dE, n_oor)."""
+        tok = np.ascontiguousarray(tokens.reshape(-1, tokens.shape[-1]).astype(np.int32))
+        B, S = tok.shape
+        V, D = d_embed.shape
+        dx3 = dx.reshape(B, D, S)
+        out = d_embed.copy()
+        oor = 0
+        for b in range(B):
+            oor += self.lib.orc_embed_backward(_fp(out), _fp(dx3[b]), _ip(tok[b]), D, S, V)
+        return out, oor
+
+    # --- loss ------------------------------------------------------------------------------
+    def cross_entropy(self, logits, targets, grad_scale=1.0):
+        """logits [B,V,S] or [V,S]; returns (loss[B], dlogits, n_oor)."""
+        l3 = logits.reshape((-1,) + logits.shape[-2:])
+        B, V, S = l3.shape
+        tg = np.ascontiguousarray(targets.reshape(B, S).astype(np.int32))
+        dl = np.empty_like(l3)
+        loss = np.zeros(B, np.float32)
+        oor = 0
+        for b in range(B):
+            n = C.c_int(0)
+            loss[b] = self.lib.orc_cross_entropy(_fp(dl[b]), _fp(l3[b]), _ip(tg[b]), V, S, grad_scale, C.byref(n))
+            oor += n.value
+        return loss, dl.reshape(logits.shape), oor
+
+    # --- optimizer ---------------------------------------------------------------------------
+    def adam(self, w, g, m, v, t, lr, b1, b2, eps, wd=0.0, variant=1, gscale=1.0, clip=1.0):
+        """In place on w, m, v (flat fp32)."""
+        self.lib.orc_adam(_fp(w), _fp(g), _fp(m), _fp(v), w.size, t, lr, b1, b2, eps, wd, variant, gscale, clip)
+
+    def grad_norm_sq(self, g, gscale=1.0):
+        return float(self.lib.orc_grad_norm_sq(_fp(g), g.size, gscale))
+
+    def clip_factor(self, norm_sq, clip):
+        return float(self.lib.orc_clip_factor(norm_sq, clip))
+
+    def vocab_map_build(self, data, full_vocab):
+        d = np.ascontiguousarray(data.astype(np.int32).ravel())
+        f2c = np.empty(full_vocab, np.int32)
+        c2f = np.empty(full_vocab, np.int32)
+        cv = self.lib.orc_vocab_map_build(_ip(d), d.size, full_vocab, _ip(f2c), _ip(c2f))
+        return cv, f2c, c2f[:cv].copy()
+
+    def num_threads(self):
+        return int(self.lib.orc_num_threads())
+
+    def set_num_threads(self, n):
+        self.lib.orc_set_num_threads(int(n))
+
+
+def reference_available() -> bool:
+    return all(os.path.exists(os.path.join(HERE, "_ref", n)) for n in ("libref_stories.so", "libref_dynamic.so"))
+
+
+class Reference:
+    """The reference's own functions (single sequence, uint16 ids, reference signatures)."""
+
+    def __init__(self, fast: bool = False):
+        if not reference_available():
+            raise FileNotFoundError("oracle/_ref is not built (run oracle/build_oracle.py where the reference is)")
+        suf = "_fast" if fast else ""
+        self.st = C.CDLL(os.path.join(HERE, "_ref", f"libref_stories{suf}.so"))
+        self.dy = C.CDLL(os.path.join(HERE, "_ref", f"libref_dynamic{suf}.so"))
+        for lib, p in ((self.st, "ref_stories_"), (self.dy, "ref_dynamic_")):
+            getattr(lib, p + "rmsnorm").argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int]
+            getattr(lib, p + "rmsnorm_bwd").argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, C.c_int, C.c_int]
+            f = getattr(lib, p + "cross_entropy_loss")
+            f.argtypes = [_f32p, _f32p, _u16p, C.c_int, C.c_int]
+            f.restype = C.c_float
+            getattr(lib, p + "embed_lookup").argtypes = [_f32p, _f32p, _u16p, C.c_int, C.c_int]
+            getattr(lib, p + "embed_backward").argtypes = [_f32p, _f32p, _u16p, C.c_int, C.c_int]
+        self.st.ref_stories_adam_update.argtypes = [_f32p, _f32p, _f32p, _f32p, C.c_size_t, C.c_int, C.c_float,
+                                                    C.c_float, C.c_float, C.c_float]
+        self.dy.ref_dynamic_adam_update.argtypes = [_f32p, _f32p, _f32p, _f32p, C.c_size_t, C.c_int, C.c_float,
+                                                    C.c_float, C.c_float, C.c_float, C.c_float]
+        self.dy.ref_dynamic_rope_backward_inplace.argtypes = [_f32p, C.c_int, C.c_int, C.c_int]
+        self.dy.ref_dynamic_vocab_map_build.argtypes = [_u16p, C.c_size_t, C.c_int, _i32p, _i32p]
+        self.dy.ref_dynamic_vocab_map_build.restype = C.c_int
+        self.st.ref_stories_set_vocab.argtypes = [C.c_int]
+
+    def _lib(self, variant):
+        return (self.st, "ref_stories_") if variant == "stories" else (self.dy, "ref_dynamic_")
+
+    def rmsnorm(self, x, w, variant="stories"):
+        lib, p = self._lib(variant)
+        out = np.empty_like(x)
+        getattr(lib, p + "rmsnorm")(_fp(out), _fp(x), _fp(w), x.shape[0], x.shape[1])
+        return out
+
+    def rmsnorm_bwd(self, dy, x, w, dw=None, variant="stories"):
+        lib, p = self._lib(variant)
+        dx = np.zeros_like(x)
+        dwo = np.zeros(x.shape[0], np.float32) if dw is None else dw.copy()
+        getattr(lib, p + "rmsnorm_bwd")(_fp(dx), _fp(dwo), _fp(dy), _fp(x), _fp(w), x.shape[0], x.shape[1])
+        return dx, dwo
+
+    def cross_entropy_loss(self, logits, targets_u16, variant="stories"):
+        lib, p = self._lib(variant)
+        dl = np.empty_like(logits)
+        loss = getattr(lib, p + "cross_entropy_loss")(_fp(dl), _fp(logits), _up(targets_u16), logits.shape[0],
+                                                      logits.shape[1])
+        return float(loss), dl
+
+    def embed_lookup(self, table, tokens_u16, variant="stories", x_init=None):
+        lib, p = self._lib(variant)
+        V, D = table.shape
+        if variant == "stories":
+            self.st.ref_stories_set_vocab(V)
+        S = tokens_u16.size
+        x = np.zeros((D, S), np.float32) if x_init is None else x_init.copy()
+        getattr(lib, p + "embed_lookup")(_fp(x), _fp(table), _up(tokens_u16), D, S)
+        return x
+
+    def embed_backward(self, d_embed, dx, tokens_u16, variant="stories"):
+        lib, p = self._lib(variant)
+        V, D = d_embed.shape
+        if variant == "stories":
+            self.st.ref_stories_set_vocab(V)
+        out = d_embed.copy()
+        getattr(lib, p + "embed_backward")(_fp(out), _fp(dx), _up(tokens_u16), D, tokens_u16.size)
+        return out
+
+    def adam_update(self, w, g, m, v, t, lr, b1, b2, eps, wd=None):
+        if wd is None:
+            self.st.ref_stories_adam_update(_fp(w), _fp(g), _fp(m), _fp(v), w.size, t, lr, b1, b2, eps)
+        else:
+            self.dy.ref_dynamic_adam_update(_fp(w), _fp(g), _fp(m), _fp(v), w.size, t, lr, b1, b2, eps, wd)
+
+    def rope_backward_inplace(self, dx, hd):
+        out = dx.copy()
+        self.dy.ref_dynamic_rope_backward_inplace(_fp(out), dx.shape[1], dx.shape[0], hd)
+        return out
+
+    def vocab_map_build(self, data_u16, full_vocab):
+        f2c = np.empty(full_vocab, np.int32)
+        c2f = np.empty(full_vocab, np.int32)
+        cv = self.dy.ref_dynamic_vocab_map_build(_up(data_u16), data_u16.size, full_vocab, _ip(f2c), _ip(c2f))
+        return cv, f2c, c2f[:cv].copy()
