@@ -1,0 +1,384 @@
+// norm.cu -- RMSNorm forward / backward over channel-first [B][C][S] tensors, with the
+// DeepNet residual fused in front of the forward and the residual-gradient add fused behind
+// the backward.
+//
+// Data layout and work split.  S is the contiguous axis, the reduction runs over C with
+// stride S.  A block owns a token tile of LG*VEC tokens (one 128-byte line per channel row for
+// the vector paths) of one sequence: LG adjacent lanes cover the tile with 16-byte loads and
+// THREADS/LG "row groups" stride over the channels.  Per-token partial sums meet in shared
+// memory.  Each tensor is swept twice (reduce, then normalise); the tile of one block is at
+// most a few hundred KB, so the second sweep is served by the L2 cache and HBM sees every
+// input byte once.
+//
+// dw (a sum over all tokens) is made deterministic without float atomics: the backward kernel
+// is persistent, every block keeps dw partials for its tiles in shared memory in a fixed tile
+// order, writes them to a scratch matrix [blocks][C], and a second kernel adds the rows in
+// block order.
+#include "common.cuh"
+
+namespace ane {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_U = 4;  // channel rows in flight per thread and tensor
+
+template <typename T, int VEC, int LG, bool FUSE_RES>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_kernel(T *out, T *x2out, const T *x, const T *f,
+                   const float *__restrict__ w, int C, int S, int tiles_per_seq, float alpha, float eps) {
+    constexpr int R = NORM_THREADS / LG;
+    constexpr int TW = LG * VEC;
+    __shared__ float red[R][TW];
+    __shared__ float tot[TW];
+
+    const int b = blockIdx.x / tiles_per_seq;
+    const int t0 = (blockIdx.x % tiles_per_seq) * TW;
+    const int lg = threadIdx.x % LG, rg = threadIdx.x / LG;
+    const int t = t0 + lg * VEC;
+    const bool active = t < S;
+    const size_t base = (size_t)b * C * S + t;
+
+    float ss[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; j++) ss[j] = 0.0f;
+
+    // sweep 1: sum of squares (and, when fused, x2 = f*alpha + x written out)
+    for (int cb = 0; cb < C; cb += R * NORM_U) {
+        Raw<T, VEC> rx[NORM_U], rf[NORM_U];
+#pragma unroll
+        for (int u = 0; u < NORM_U; u++) {
+            const int c = cb + u * R + rg;
+            if (active && c < C) {
+                if (FUSE_RES) {
+                    rx[u].load_stream(x + base + (size_t)c * S);
+                    rf[u].load_stream(f + base + (size_t)c * S);
+                } else {
+                    rx[u].load(x + base + (size_t)c * S);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < NORM_U; u++) {
+            const int c = cb + u * R + rg;
+            if (active && c < C) {
+                float v[VEC];
+                rx[u].unpack(v);
+                if (FUSE_RES) {
+                    float fv[VEC];
+                    rf[u].unpack(fv);
+#pragma unroll
+                    for (int j = 0; j < VEC; j++) v[j] = round_through<T>(__fadd_rn(__fmul_rn(fv[j], alpha), v[j]));
+                    Raw<T, VEC> o;
+                    o.pack(v);
+                    o.store(x2out + base + (size_t)c * S);   // stays in L2 for sweep 2
+                }
+#pragma unroll
+                for (int j = 0; j < VEC; j++) ss[j] += v[j] * v[j];
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; j++) red[rg][lg * VEC + j] = ss[j];
+    __syncthreads();
+    if (threadIdx.x < TW) {
+        float s = 0.0f;
+#pragma unroll 8
+        for (int r = 0; r < R; r++) s += red[r][threadIdx.x];
+        tot[threadIdx.x] = s;
+    }
+    __syncthreads();
+    const float invd = 1.0f / (float)C;
+    float rr[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; j++) rr[j] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(tot[lg * VEC + j], invd), eps));
+
+    // sweep 2: out = (x * rrms) * w[c]          (stories_cpu_ops.h:16-19, in that order)
+    const T *src = FUSE_RES ? x2out : x;
+    for (int cb = 0; cb < C; cb += R * NORM_U) {
+        Raw<T, VEC> rx[NORM_U];
+#pragma unroll
+        for (int u = 0; u < NORM_U; u++) {
+            const int c = cb + u * R + rg;
+            if (active && c < C) {
+                if (FUSE_RES) rx[u].load(src + base + (size_t)c * S);
+                else rx[u].load_stream(src + base + (size_t)c * S);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < NORM_U; u++) {
+            const int c = cb + u * R + rg;
+            if (active && c < C) {
+                float v[VEC];
+                rx[u].unpack(v);
+                const float wc = __ldg(w + c);
+#pragma unroll
+                for (int j = 0; j < VEC; j++) v[j] = (v[j] * rr[j]) * wc;
+                Raw<T, VEC> o;
+                o.pack(v);
+                o.store_stream(out + base + (size_t)c * S);
+            }
+        }
+    }
+}
+
+template <typename T, int VEC, int LG, bool HAS_ADD>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *x,
+                   const float *__restrict__ w, const T *add, int C, int S, int tiles_per_seq,
+                   int ntiles, float eps, unsigned flags) {
+    constexpr int R = NORM_THREADS / LG;
+    constexpr int TW = LG * VEC;
+    __shared__ float red[2][R][TW];
+    __shared__ float tot[2][TW];
+    extern __shared__ float dwacc[];  // [C]
+
+    const int lg = threadIdx.x % LG, rg = threadIdx.x / LG;
+    const float invd = 1.0f / (float)C;
+    const bool exact = (flags & ANE_NORM_BWD_EXACT) != 0;
+
+    for (int c = threadIdx.x; c < C; c += NORM_THREADS) dwacc[c] = 0.0f;
+    __syncthreads();
+
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int b = tile / tiles_per_seq;
+        const int t = (tile % tiles_per_seq) * TW + lg * VEC;
+        const bool active = t < S;
+        const size_t base = (size_t)b * C * S + t;
+
+        float ss[VEC], dot[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; j++) { ss[j] = 0.0f; dot[j] = 0.0f; }
+
+        // sweep 1: ss = sum x^2 ; dot = sum (dy*x)*w       (stories_cpu_ops.h:26-38)
+        for (int cb = 0; cb < C; cb += R * NORM_U) {
+            Raw<T, VEC> rx[NORM_U], rd[NORM_U];
+#pragma unroll
+            for (int u = 0; u < NORM_U; u++) {
+                const int c = cb + u * R + rg;
+                if (active && c < C) {
+                    rx[u].load(x + base + (size_t)c * S);
+                    rd[u].load(dy + base + (size_t)c * S);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < NORM_U; u++) {
+                const int c = cb + u * R + rg;
+                if (active && c < C) {
+                    float xv[VEC], dv[VEC];
+                    rx[u].unpack(xv);
+                    rd[u].unpack(dv);
+                    const float wc = __ldg(w + c);
+#pragma unroll
+                    for (int j = 0; j < VEC; j++) {
+                        ss[j] += xv[j] * xv[j];
+                        dot[j] += (dv[j] * xv[j]) * wc;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < VEC; j++) { red[0][rg][lg * VEC + j] = ss[j]; red[1][rg][lg * VEC + j] = dot[j]; }
+        __syncthreads();
+        if (threadIdx.x < 2 * TW) {
+            const int which = threadIdx.x / TW, col = threadIdx.x % TW;
+            float s = 0.0f;
+#pragma unroll 8
+            for (int r = 0; r < R; r++) s += red[which][r][col];
+            tot[which][col] = s;
+        }
+        __syncthreads();
+        float rr[VEC], coef[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; j++) {
+            rr[j] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(tot[0][lg * VEC + j], invd), eps));
+            float r2 = rr[j] * rr[j];
+            r2 = r2 * invd;
+            coef[j] = tot[1][lg * VEC + j] * r2;          // stories_cpu_ops.h:39-41
+        }
+
+        // sweep 2: dx and the dw partials (inputs come back from L2)
+        for (int cb = 0; cb < C; cb += R * NORM_U) {
+            Raw<T, VEC> rx[NORM_U], rd[NORM_U], ra[NORM_U];
+#pragma unroll
+            for (int u = 0; u < NORM_U; u++) {
+                const int c = cb + u * R + rg;
+                if (active && c < C) {
+                    rx[u].load_stream(x + base + (size_t)c * S);
+                    rd[u].load_stream(dy + base + (size_t)c * S);
+                    if (HAS_ADD) ra[u].load_stream(add + base + (size_t)c * S);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < NORM_U; u++) {
+                const int c = cb + u * R + rg;
+                float dwp = 0.0f;
+                if (active && c < C) {
+                    float xv[VEC], dv[VEC], o[VEC];
+                    rx[u].unpack(xv);
+                    rd[u].unpack(dv);
+                    const float wc = __ldg(w + c);
+#pragma unroll
+                    for (int j = 0; j < VEC; j++) {
+                        if (exact) {
+                            o[j] = __fmul_rn(__fsub_rn(__fmul_rn(dv[j], wc), __fmul_rn(xv[j], coef[j])), rr[j]);
+                        } else {
+                            float tmp = __fmul_rn(xv[j], coef[j]);      // stories_cpu_ops.h:43-46
+                            tmp = __fsub_rn(dv[j], tmp);
+                            tmp = tmp * rr[j];
+                            o[j] = tmp * wc;
+                        }
+                        dwp += (dv[j] * xv[j]) * rr[j];                 // stories_cpu_ops.h:47-50
+                    }
+                    if (HAS_ADD) {
+                        float av[VEC];
+                        ra[u].unpack(av);
+#pragma unroll
+                        for (int j = 0; j < VEC; j++) o[j] = o[j] + av[j];   // train.m:590,721
+                    }
+                    Raw<T, VEC> ro;
+                    ro.pack(o);
+                    ro.store_stream(dx + base + (size_t)c * S);
+                }
+                // sum over the LG lanes that share channel c (the loop is uniform across the warp)
+#pragma unroll
+                for (int off = LG / 2; off > 0; off >>= 1) dwp += __shfl_xor_sync(0xffffffffu, dwp, off);
+                if (lg == 0 && c < C) dwacc[c] += dwp;   // row group rg is the only writer of channel c
+            }
+        }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < C; c += NORM_THREADS) partial[(size_t)blockIdx.x * C + c] = dwacc[c];
+}
+
+// dw[c] += sum over blocks, in block order.
+__global__ void dw_finalize_kernel(float *__restrict__ dw, const float *__restrict__ partial, int nblocks, int C) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float s = 0.0f;
+    for (int b = 0; b < nblocks; b++) s += partial[(size_t)b * C + c];
+    dw[c] += s;
+}
+
+template <typename T, bool FUSE_RES>
+static int launch_rmsnorm_fwd(cudaStream_t st, int B, int C, int S, void *out, void *x2, const void *x, const void *f,
+                              const float *w, float alpha, float eps) {
+    constexpr int VEC = Elt<T>::VEC;
+    const bool vec = (S % VEC == 0) && aligned16(out) && aligned16(x) && (!FUSE_RES || (aligned16(x2) && aligned16(f)));
+    if (vec) {
+        constexpr int LG = 8;
+        const int tps = (S + LG * VEC - 1) / (LG * VEC);
+        rmsnorm_fwd_kernel<T, VEC, LG, FUSE_RES><<<(unsigned)(B * tps), NORM_THREADS, 0, st>>>(
+            (T *)out, (T *)x2, (const T *)x, (const T *)f, w, C, S, tps, alpha, eps);
+    } else {
+        constexpr int LG = 32;
+        const int tps = (S + LG - 1) / LG;
+        rmsnorm_fwd_kernel<T, 1, LG, FUSE_RES><<<(unsigned)(B * tps), NORM_THREADS, 0, st>>>(
+            (T *)out, (T *)x2, (const T *)x, (const T *)f, w, C, S, tps, alpha, eps);
+    }
+    ANE_LAUNCH_OK(1);
+    return ANE_CUDA_OK;
+}
+
+template <typename KernelT>
+static int persistent_grid(KernelT kernel, size_t dyn_smem, int ntiles) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, NORM_THREADS, dyn_smem) != cudaSuccess || per_sm < 1)
+        per_sm = 1;
+    long g = (long)per_sm * ctx().sm_count;
+    if (g > ntiles) g = ntiles;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+template <typename T, bool HAS_ADD>
+static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, float *dw, const void *dy, const void *x,
+                              const float *w, const void *add, float eps, unsigned flags) {
+    constexpr int VEC = Elt<T>::VEC;
+    const bool vec = (S % VEC == 0) && aligned16(dx) && aligned16(dy) && aligned16(x) && (!HAS_ADD || aligned16(add));
+    const size_t smem = (size_t)C * sizeof(float);
+    int grid, ntiles;
+    float *partial;
+    if (vec) {
+        constexpr int LG = 8;
+        auto k = rmsnorm_bwd_kernel<T, VEC, LG, HAS_ADD>;
+        const int tps = (S + LG * VEC - 1) / (LG * VEC);
+        ntiles = B * tps;
+        grid = persistent_grid(k, smem, ntiles);
+        partial = static_cast<float *>(workspace((size_t)grid * C * sizeof(float)));
+        if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", grid, C);
+        k<<<grid, NORM_THREADS, smem, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps,
+                                            ntiles, eps, flags);
+    } else {
+        constexpr int LG = 32;
+        auto k = rmsnorm_bwd_kernel<T, 1, LG, HAS_ADD>;
+        const int tps = (S + LG - 1) / LG;
+        ntiles = B * tps;
+        grid = persistent_grid(k, smem, ntiles);
+        partial = static_cast<float *>(workspace((size_t)grid * C * sizeof(float)));
+        if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", grid, C);
+        k<<<grid, NORM_THREADS, smem, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps,
+                                            ntiles, eps, flags);
+    }
+    dw_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(dw, partial, grid, C);
+    ANE_LAUNCH_OK(2);
+    return ANE_CUDA_OK;
+}
+
+// Shared by the per-head operators, which treat [B][heads*hd][S] as [B*heads][hd][S].
+int rmsnorm_fwd_any(cudaStream_t st, ane_dtype dtype, int B, int C, int S, void *out, const void *x, const float *w, float eps) {
+    ANE_DISPATCH_DTYPE(dtype, T, return (launch_rmsnorm_fwd<T, false>(st, B, C, S, out, nullptr, x, nullptr, w, 0.0f, eps)));
+    return ANE_CUDA_OK;
+}
+int rmsnorm_bwd_any(cudaStream_t st, ane_dtype dtype, int B, int C, int S, void *dx, float *dw, const void *dy,
+                    const void *x, const float *w, const void *add, float eps, unsigned flags) {
+    if (add) {
+        ANE_DISPATCH_DTYPE(dtype, T, return (launch_rmsnorm_bwd<T, true>(st, B, C, S, dx, dw, dy, x, w, add, eps, flags)));
+    } else {
+        ANE_DISPATCH_DTYPE(dtype, T, return (launch_rmsnorm_bwd<T, false>(st, B, C, S, dx, dw, dy, x, w, nullptr, eps, flags)));
+    }
+    return ANE_CUDA_OK;
+}
+
+static int check_bcs(const char *fn, int B, int C, int S) {
+    if (B < 1 || C < 1 || S < 1) return fail(ANE_CUDA_ERR_INVALID, "%s: B, C, S must be positive (got %d, %d, %d)", fn, B, C, S);
+    if (C > 8192) return fail(ANE_CUDA_ERR_UNSUPPORTED, "%s: C = %d exceeds 8192", fn, C);
+    if ((long long)B * ((S + 7) / 8) > 0x7fffffffLL) return fail(ANE_CUDA_ERR_UNSUPPORTED, "%s: too many token tiles", fn);
+    return ANE_CUDA_OK;
+}
+
+}  // namespace ane
+
+using namespace ane;
+
+extern "C" {
+
+int ane_cuda_rmsnorm_dev(void *stream, ane_dtype dtype, int B, int C, int S, void *out, const void *x, const float *w,
+                         float eps) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(out && x && w, "%s: null pointer", __func__);
+    ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
+    if (int rc = check_bcs(__func__, B, C, S)) return rc;
+    return rmsnorm_fwd_any((cudaStream_t)stream, dtype, B, C, S, out, x, w, eps);
+}
+
+int ane_cuda_residual_rmsnorm_dev(void *stream, ane_dtype dtype, int B, int C, int S, void *x2, void *x2norm,
+                                  const void *x, const void *f, const float *w, float alpha, float eps) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(x2 && x2norm && x && f && w, "%s: null pointer", __func__);
+    ANE_REQUIRE(x2 != x2norm, "%s: x2 and x2norm must be different buffers", __func__);
+    ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
+    if (int rc = check_bcs(__func__, B, C, S)) return rc;
+    ANE_DISPATCH_DTYPE(dtype, T, return (launch_rmsnorm_fwd<T, true>((cudaStream_t)stream, B, C, S, x2norm, x2, x, f, w, alpha, eps)));
+    return ANE_CUDA_OK;
+}
+
+int ane_cuda_rmsnorm_bwd_dev(void *stream, ane_dtype dtype, int B, int C, int S, void *dx, float *dw, const void *dy,
+                             const void *x, const float *w, const void *add, float eps, unsigned flags) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(dx && dw && dy && x && w, "%s: null pointer", __func__);
+    ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
+    ANE_REQUIRE(flags == ANE_NORM_BWD_REFERENCE || flags == ANE_NORM_BWD_EXACT, "%s: bad flags %u", __func__, flags);
+    if (int rc = check_bcs(__func__, B, C, S)) return rc;
+    return rmsnorm_bwd_any((cudaStream_t)stream, dtype, B, C, S, dx, dw, dy, x, w, add, eps, flags);
+}
+
+}  // extern "C"

@@ -1,0 +1,474 @@
+// rope.cu -- rotary position embedding (interleaved channel pairs), per-head QK-RMSNorm, and
+// their fusions: qknorm -> rope (forward) and rope^-1 -> qknorm_bwd (backward).
+//
+// Tensors are [B][heads*hd][S].  A block owns a token tile of LG*VEC tokens of one sequence
+// and walks over the heads; inside a head the THREADS/LG row groups each hold RPT consecutive
+// channels (so both channels of a rotation pair sit in one thread) in registers between the
+// per-token reduction and the write: every byte crosses HBM once.  sin/cos for the thread's
+// pairs and tokens are computed once per tile and reused for every head.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace ane {
+
+int rmsnorm_fwd_any(cudaStream_t st, ane_dtype dtype, int B, int C, int S, void *out, const void *x, const float *w, float eps);
+int rmsnorm_bwd_any(cudaStream_t st, ane_dtype dtype, int B, int C, int S, void *dx, float *dw, const void *dy,
+                    const void *x, const float *w, const void *add, float eps, unsigned flags);
+
+constexpr int QK_THREADS = 256;
+
+// ------------------------------------------------------------------ stand-alone RoPE
+// One thread: one pair index i, VEC tokens, all heads.   cpu_ops.h:168-184 / forward.h:55-70
+template <typename T, int VEC, int LG>
+__global__ void __launch_bounds__(QK_THREADS)
+rope_kernel(T *out, const T *x, int heads, int hd, int S, int tiles_per_seq, int pos0, bool inverse,
+            const __grid_constant__ RopeFreq freq) {
+    constexpr int R = QK_THREADS / LG;
+    constexpr int TW = LG * VEC;
+    const int b = blockIdx.x / tiles_per_seq;
+    const int lg = threadIdx.x % LG, rg = threadIdx.x / LG;
+    const int t = (blockIdx.x % tiles_per_seq) * TW + lg * VEC;
+    if (t >= S) return;
+    const int C = heads * hd;
+    const size_t base = (size_t)b * C * S + t;
+    for (int i = blockIdx.y * R + rg; i < hd / 2; i += gridDim.y * R) {
+        float cs[VEC], sn[VEC];
+        const float fr = freq.f[i];
+#pragma unroll
+        for (int j = 0; j < VEC; j++) {
+            const float theta = (float)(pos0 + t + j) * fr;
+            cs[j] = cosf(theta);
+            sn[j] = inverse ? -sinf(theta) : sinf(theta);
+        }
+        for (int h = 0; h < heads; h++) {
+            const size_t o0 = base + (size_t)(h * hd + 2 * i) * S;
+            Raw<T, VEC> r0, r1;
+            r0.load_stream(x + o0);
+            r1.load_stream(x + o0 + S);
+            float a[VEC], bb[VEC], ya[VEC], yb[VEC];
+            r0.unpack(a);
+            r1.unpack(bb);
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                ya[j] = __fsub_rn(__fmul_rn(a[j], cs[j]), __fmul_rn(bb[j], sn[j]));
+                yb[j] = __fadd_rn(__fmul_rn(a[j], sn[j]), __fmul_rn(bb[j], cs[j]));
+            }
+            r0.pack(ya);
+            r1.pack(yb);
+            r0.store_stream(out + o0);
+            r1.store_stream(out + o0 + S);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ fused per-head kernels
+// hd == RPT * (QK_THREADS / LG); thread (rg, lg) holds channels rg*RPT .. rg*RPT+RPT-1.
+template <typename T, int VEC, int LG, int RPT, bool ROPE>
+__global__ void __launch_bounds__(QK_THREADS)
+qk_fwd_kernel(T *__restrict__ out, const T *__restrict__ x, const float *__restrict__ w, int heads, int S,
+              int tiles_per_seq, float eps, int pos0, const __grid_constant__ RopeFreq freq) {
+    constexpr int R = QK_THREADS / LG;
+    constexpr int TW = LG * VEC;
+    constexpr int HD = RPT * R;
+    __shared__ float red[2][R][TW];
+    __shared__ float tot[2][TW];
+
+    const int b = blockIdx.x / tiles_per_seq;
+    const int lg = threadIdx.x % LG, rg = threadIdx.x / LG;
+    const int t = (blockIdx.x % tiles_per_seq) * TW + lg * VEC;
+    const bool active = t < S;
+    const size_t base = (size_t)b * heads * HD * S + t;
+    const float invd = 1.0f / (float)HD;
+
+    float wc[RPT];
+#pragma unroll
+    for (int k = 0; k < RPT; k++) wc[k] = __ldg(w + rg * RPT + k);
+
+    float cs[RPT / 2][VEC], sn[RPT / 2][VEC];
+    if (ROPE) {
+#pragma unroll
+        for (int p = 0; p < RPT / 2; p++) {
+            const float fr = freq.f[rg * (RPT / 2) + p];
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                const float theta = (float)(pos0 + t + j) * fr;
+                cs[p][j] = cosf(theta);
+                sn[p][j] = sinf(theta);
+            }
+        }
+    }
+
+    for (int h = 0; h < heads; h++) {
+        const int buf = h & 1;
+        Raw<T, VEC> r[RPT];
+        float v[RPT][VEC];
+        const size_t hb = base + (size_t)(h * HD + rg * RPT) * S;
+        if (active) {
+#pragma unroll
+            for (int k = 0; k < RPT; k++) r[k].load_stream(x + hb + (size_t)k * S);
+        }
+        float ss[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; j++) ss[j] = 0.0f;
+        if (active) {
+#pragma unroll
+            for (int k = 0; k < RPT; k++) {
+                r[k].unpack(v[k]);
+#pragma unroll
+                for (int j = 0; j < VEC; j++) ss[j] += v[k][j] * v[k][j];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < VEC; j++) red[buf][rg][lg * VEC + j] = ss[j];
+        __syncthreads();
+        if (threadIdx.x < TW) {
+            float s = 0.0f;
+#pragma unroll 8
+            for (int q = 0; q < R; q++) s += red[buf][q][threadIdx.x];
+            tot[buf][threadIdx.x] = s;
+        }
+        __syncthreads();
+        if (active) {
+            float rr[VEC];
+#pragma unroll
+            for (int j = 0; j < VEC; j++) rr[j] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(tot[buf][lg * VEC + j], invd), eps));
+#pragma unroll
+            for (int k = 0; k < RPT; k++)
+#pragma unroll
+                for (int j = 0; j < VEC; j++) v[k][j] = (v[k][j] * rr[j]) * wc[k];
+            if (ROPE) {
+#pragma unroll
+                for (int p = 0; p < RPT / 2; p++)
+#pragma unroll
+                    for (int j = 0; j < VEC; j++) {
+                        const float a = v[2 * p][j], bb = v[2 * p + 1][j];
+                        v[2 * p][j] = __fsub_rn(__fmul_rn(a, cs[p][j]), __fmul_rn(bb, sn[p][j]));
+                        v[2 * p + 1][j] = __fadd_rn(__fmul_rn(a, sn[p][j]), __fmul_rn(bb, cs[p][j]));
+                    }
+            }
+#pragma unroll
+            for (int k = 0; k < RPT; k++) {
+                Raw<T, VEC> o;
+                o.pack(v[k]);
+                o.store_stream(out + hb + (size_t)k * S);
+            }
+        }
+    }
+}
+
+template <typename T, int VEC, int LG, int RPT, bool ROPE>
+__global__ void __launch_bounds__(QK_THREADS)
+qk_bwd_kernel(T *__restrict__ dx, float *__restrict__ partial, const T *__restrict__ dy, const T *__restrict__ x,
+              const float *__restrict__ w, int heads, int S, int tiles_per_seq, int ntiles, float eps, int pos0,
+              unsigned flags, const __grid_constant__ RopeFreq freq) {
+    constexpr int R = QK_THREADS / LG;
+    constexpr int TW = LG * VEC;
+    constexpr int HD = RPT * R;
+    __shared__ float red[2][2][R][TW];
+    __shared__ float tot[2][2][TW];
+
+    const int lg = threadIdx.x % LG, rg = threadIdx.x / LG;
+    const float invd = 1.0f / (float)HD;
+    const bool exact = (flags & ANE_NORM_BWD_EXACT) != 0;
+
+    float wc[RPT], dwacc[RPT];
+#pragma unroll
+    for (int k = 0; k < RPT; k++) { wc[k] = __ldg(w + rg * RPT + k); dwacc[k] = 0.0f; }
+
+    int it = 0;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int b = tile / tiles_per_seq;
+        const int t = (tile % tiles_per_seq) * TW + lg * VEC;
+        const bool active = t < S;
+        const size_t base = (size_t)b * heads * HD * S + t;
+
+        float cs[RPT / 2][VEC], sn[RPT / 2][VEC];
+        if (ROPE) {
+#pragma unroll
+            for (int p = 0; p < RPT / 2; p++) {
+                const float fr = freq.f[rg * (RPT / 2) + p];
+#pragma unroll
+                for (int j = 0; j < VEC; j++) {
+                    const float theta = (float)(pos0 + t + j) * fr;
+                    cs[p][j] = cosf(theta);
+                    sn[p][j] = sinf(theta);
+                }
+            }
+        }
+
+        for (int h = 0; h < heads; h++, it++) {
+            const int buf = it & 1;
+            Raw<T, VEC> rxr[RPT], rdr[RPT];
+            float xv[RPT][VEC], g[RPT][VEC];
+            const size_t hb = base + (size_t)(h * HD + rg * RPT) * S;
+            if (active) {
+#pragma unroll
+                for (int k = 0; k < RPT; k++) {
+                    rxr[k].load_stream(x + hb + (size_t)k * S);
+                    rdr[k].load_stream(dy + hb + (size_t)k * S);
+                }
+            }
+            float ss[VEC], dot[VEC];
+#pragma unroll
+            for (int j = 0; j < VEC; j++) { ss[j] = 0.0f; dot[j] = 0.0f; }
+            if (active) {
+#pragma unroll
+                for (int k = 0; k < RPT; k++) { rxr[k].unpack(xv[k]); rdr[k].unpack(g[k]); }
+                if (ROPE) {   // g = rope^-1(dy): (a cos + b sin, -a sin + b cos)   cpu_ops.h:178-181
+#pragma unroll
+                    for (int p = 0; p < RPT / 2; p++)
+#pragma unroll
+                        for (int j = 0; j < VEC; j++) {
+                            const float a = g[2 * p][j], bb = g[2 * p + 1][j];
+                            g[2 * p][j] = __fadd_rn(__fmul_rn(a, cs[p][j]), __fmul_rn(bb, sn[p][j]));
+                            g[2 * p + 1][j] = __fadd_rn(__fmul_rn(-a, sn[p][j]), __fmul_rn(bb, cs[p][j]));
+                        }
+                }
+#pragma unroll
+                for (int k = 0; k < RPT; k++)
+#pragma unroll
+                    for (int j = 0; j < VEC; j++) {
+                        ss[j] += xv[k][j] * xv[k][j];
+                        dot[j] += (g[k][j] * xv[k][j]) * wc[k];
+                    }
+            }
+#pragma unroll
+            for (int j = 0; j < VEC; j++) { red[buf][0][rg][lg * VEC + j] = ss[j]; red[buf][1][rg][lg * VEC + j] = dot[j]; }
+            __syncthreads();
+            if (threadIdx.x < 2 * TW) {
+                const int which = threadIdx.x / TW, col = threadIdx.x % TW;
+                float s = 0.0f;
+#pragma unroll 8
+                for (int q = 0; q < R; q++) s += red[buf][which][q][col];
+                tot[buf][which][col] = s;
+            }
+            __syncthreads();
+            if (active) {
+                float rr[VEC], coef[VEC];
+#pragma unroll
+                for (int j = 0; j < VEC; j++) {
+                    rr[j] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(tot[buf][0][lg * VEC + j], invd), eps));
+                    float r2 = rr[j] * rr[j];
+                    r2 = r2 * invd;
+                    coef[j] = tot[buf][1][lg * VEC + j] * r2;
+                }
+#pragma unroll
+                for (int k = 0; k < RPT; k++) {
+                    float o[VEC];
+                    float dwp = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < VEC; j++) {
+                        if (exact) {
+                            o[j] = __fmul_rn(__fsub_rn(__fmul_rn(g[k][j], wc[k]), __fmul_rn(xv[k][j], coef[j])), rr[j]);
+                        } else {
+                            float tmp = __fmul_rn(xv[k][j], coef[j]);
+                            tmp = __fsub_rn(g[k][j], tmp);
+                            tmp = tmp * rr[j];
+                            o[j] = tmp * wc[k];
+                        }
+                        dwp += (g[k][j] * xv[k][j]) * rr[j];
+                    }
+                    dwacc[k] += dwp;
+                    Raw<T, VEC> ro;
+                    ro.pack(o);
+                    ro.store_stream(dx + hb + (size_t)k * S);
+                }
+            }
+        }
+    }
+    // dw partial of this block: sum the LG lanes of each row group, fixed order
+#pragma unroll
+    for (int k = 0; k < RPT; k++) {
+        float s = dwacc[k];
+#pragma unroll
+        for (int off = LG / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (lg == 0) partial[(size_t)blockIdx.x * HD + rg * RPT + k] = s;
+    }
+}
+
+__global__ void qk_dw_finalize_kernel(float *__restrict__ dw, const float *__restrict__ partial, int nblocks, int hd) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= hd) return;
+    float s = 0.0f;
+    for (int b = 0; b < nblocks; b++) s += partial[(size_t)b * hd + c];
+    dw[c] += s;
+}
+
+static int fill_freq(RopeFreq &fq, int hd, float base) {
+    if (hd < 2 || (hd & 1) || hd > 256) return fail(ANE_CUDA_ERR_UNSUPPORTED, "rope: head dim %d must be even and <= 256", hd);
+    // freq = 1/powf(base, 2*i/hd) with the host libm                    cpu_ops.h:172
+    for (int i = 0; i < hd / 2; i++) fq.f[i] = 1.0f / powf(base, 2.0f * i / (float)hd);
+    for (int i = hd / 2; i < 128; i++) fq.f[i] = 0.0f;
+    return ANE_CUDA_OK;
+}
+
+template <typename T>
+static int launch_rope(cudaStream_t st, int B, int heads, int hd, int S, void *out, const void *x, int pos0, bool inverse,
+                       const RopeFreq &fq) {
+    constexpr int VEC = Elt<T>::VEC;
+    const bool vec = (S % VEC == 0) && aligned16(out) && aligned16(x);
+    if (vec) {
+        constexpr int LG = 8;
+        const int tps = (S + LG * VEC - 1) / (LG * VEC);
+        dim3 grid((unsigned)(B * tps), (unsigned)((hd / 2 + (QK_THREADS / LG) - 1) / (QK_THREADS / LG)));
+        rope_kernel<T, VEC, LG><<<grid, QK_THREADS, 0, st>>>((T *)out, (const T *)x, heads, hd, S, tps, pos0, inverse, fq);
+    } else {
+        constexpr int LG = 32;
+        const int tps = (S + LG - 1) / LG;
+        dim3 grid((unsigned)(B * tps), (unsigned)((hd / 2 + (QK_THREADS / LG) - 1) / (QK_THREADS / LG)));
+        rope_kernel<T, 1, LG><<<grid, QK_THREADS, 0, st>>>((T *)out, (const T *)x, heads, hd, S, tps, pos0, inverse, fq);
+    }
+    ANE_LAUNCH_OK(1);
+    return ANE_CUDA_OK;
+}
+
+template <typename KernelT>
+static int qk_persistent_grid(KernelT kernel, int ntiles) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, QK_THREADS, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+    long g = (long)per_sm * ctx().sm_count;
+    if (g > ntiles) g = ntiles;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+template <typename T, bool ROPE>
+static bool qk_fast_ok(int hd, int S, const void *a, const void *b, const void *c) {
+    constexpr int VEC = Elt<T>::VEC;
+    return (hd == 128 || hd == 64) && (S % VEC == 0) && aligned16(a) && aligned16(b) && (!c || aligned16(c));
+}
+
+template <typename T, bool ROPE>
+static int launch_qk_fwd(cudaStream_t st, int B, int heads, int hd, int S, void *out, const void *x, const float *w,
+                         float eps, int pos0, const RopeFreq &fq) {
+    constexpr int VEC = Elt<T>::VEC;
+    constexpr int LG = 8;
+    const int tps = (S + LG * VEC - 1) / (LG * VEC);
+    const unsigned grid = (unsigned)(B * tps);
+    if (hd == 128)
+        qk_fwd_kernel<T, VEC, LG, 4, ROPE><<<grid, QK_THREADS, 0, st>>>((T *)out, (const T *)x, w, heads, S, tps, eps, pos0, fq);
+    else
+        qk_fwd_kernel<T, VEC, LG, 2, ROPE><<<grid, QK_THREADS, 0, st>>>((T *)out, (const T *)x, w, heads, S, tps, eps, pos0, fq);
+    ANE_LAUNCH_OK(1);
+    return ANE_CUDA_OK;
+}
+
+template <typename T, bool ROPE>
+static int launch_qk_bwd(cudaStream_t st, int B, int heads, int hd, int S, void *dx, float *dw, const void *dy,
+                         const void *x, const float *w, float eps, int pos0, unsigned flags, const RopeFreq &fq) {
+    constexpr int VEC = Elt<T>::VEC;
+    constexpr int LG = 8;
+    const int tps = (S + LG * VEC - 1) / (LG * VEC);
+    const int ntiles = B * tps;
+    int grid;
+    float *partial;
+    if (hd == 128) {
+        auto k = qk_bwd_kernel<T, VEC, LG, 4, ROPE>;
+        grid = qk_persistent_grid(k, ntiles);
+        partial = static_cast<float *>(workspace((size_t)grid * hd * sizeof(float)));
+        if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "qknorm_bwd: no scratch");
+        k<<<grid, QK_THREADS, 0, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, heads, S, tps, ntiles, eps, pos0, flags, fq);
+    } else {
+        auto k = qk_bwd_kernel<T, VEC, LG, 2, ROPE>;
+        grid = qk_persistent_grid(k, ntiles);
+        partial = static_cast<float *>(workspace((size_t)grid * hd * sizeof(float)));
+        if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "qknorm_bwd: no scratch");
+        k<<<grid, QK_THREADS, 0, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, heads, S, tps, ntiles, eps, pos0, flags, fq);
+    }
+    qk_dw_finalize_kernel<<<(hd + 127) / 128, 128, 0, st>>>(dw, partial, grid, hd);
+    ANE_LAUNCH_OK(2);
+    return ANE_CUDA_OK;
+}
+
+static int check_qk(const char *fn, int B, int heads, int hd, int S) {
+    if (B < 1 || heads < 1 || hd < 1 || S < 1)
+        return fail(ANE_CUDA_ERR_INVALID, "%s: B, heads, hd, S must be positive (got %d, %d, %d, %d)", fn, B, heads, hd, S);
+    if ((long long)B * heads > 0x7fffffLL || (long long)B * ((S + 7) / 8) > 0x7fffffffLL)
+        return fail(ANE_CUDA_ERR_UNSUPPORTED, "%s: shape too large", fn);
+    return ANE_CUDA_OK;
+}
+
+}  // namespace ane
+
+using namespace ane;
+
+extern "C" {
+
+int ane_cuda_rope_dev(void *stream, ane_dtype dtype, int B, int C, int S, int hd, void *out, const void *x, float base,
+                      int pos0, unsigned flags) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(out && x, "%s: null pointer", __func__);
+    ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
+    ANE_REQUIRE(B >= 1 && C >= 1 && S >= 1 && hd >= 2 && C % hd == 0, "%s: bad shape B=%d C=%d S=%d hd=%d", __func__, B, C, S, hd);
+    ANE_REQUIRE(flags == ANE_ROPE_FORWARD || flags == ANE_ROPE_INVERSE, "%s: bad flags %u", __func__, flags);
+    RopeFreq fq;
+    if (int rc = fill_freq(fq, hd, base)) return rc;
+    ANE_DISPATCH_DTYPE(dtype, T, return (launch_rope<T>((cudaStream_t)stream, B, C / hd, hd, S, out, x, pos0, flags == ANE_ROPE_INVERSE, fq)));
+    return ANE_CUDA_OK;
+}
+
+int ane_cuda_qknorm_dev(void *stream, ane_dtype dtype, int B, int heads, int hd, int S, void *out, const void *x,
+                        const float *w, float eps) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(out && x && w, "%s: null pointer", __func__);
+    ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
+    if (int rc = check_qk(__func__, B, heads, hd, S)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    RopeFreq fq = {};
+    ANE_DISPATCH_DTYPE(dtype, T,
+        if (qk_fast_ok<T, false>(hd, S, out, x, nullptr)) return (launch_qk_fwd<T, false>(st, B, heads, hd, S, out, x, w, eps, 0, fq)));
+    return rmsnorm_fwd_any(st, dtype, B * heads, hd, S, out, x, w, eps);
+}
+
+int ane_cuda_qknorm_bwd_dev(void *stream, ane_dtype dtype, int B, int heads, int hd, int S, void *dx, float *dw,
+                            const void *dy, const void *x, const float *w, float eps, unsigned flags) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(dx && dw && dy && x && w, "%s: null pointer", __func__);
+    ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
+    ANE_REQUIRE(flags == ANE_NORM_BWD_REFERENCE || flags == ANE_NORM_BWD_EXACT, "%s: bad flags %u", __func__, flags);
+    if (int rc = check_qk(__func__, B, heads, hd, S)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    RopeFreq fq = {};
+    ANE_DISPATCH_DTYPE(dtype, T,
+        if (qk_fast_ok<T, false>(hd, S, dx, dy, x)) return (launch_qk_bwd<T, false>(st, B, heads, hd, S, dx, dw, dy, x, w, eps, 0, flags, fq)));
+    return rmsnorm_bwd_any(st, dtype, B * heads, hd, S, dx, dw, dy, x, w, nullptr, eps, flags);
+}
+
+int ane_cuda_qknorm_rope_dev(void *stream, ane_dtype dtype, int B, int heads, int hd, int S, void *out, const void *x,
+                             const float *w, float eps, float base, int pos0) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(out && x && w, "%s: null pointer", __func__);
+    ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
+    if (int rc = check_qk(__func__, B, heads, hd, S)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    RopeFreq fq;
+    if (int rc = fill_freq(fq, hd, base)) return rc;
+    ANE_DISPATCH_DTYPE(dtype, T,
+        if (qk_fast_ok<T, true>(hd, S, out, x, nullptr)) return (launch_qk_fwd<T, true>(st, B, heads, hd, S, out, x, w, eps, pos0, fq)));
+    // other head widths and unaligned shapes: the two operators back to back (rope in place on out)
+    if (int rc = rmsnorm_fwd_any(st, dtype, B * heads, hd, S, out, x, w, eps)) return rc;
+    ANE_DISPATCH_DTYPE(dtype, T, return (launch_rope<T>(st, B, heads, hd, S, out, out, pos0, false, fq)));
+    return ANE_CUDA_OK;
+}
+
+int ane_cuda_rope_qknorm_bwd_dev(void *stream, ane_dtype dtype, int B, int heads, int hd, int S, void *dx, float *dw,
+                                 const void *dy, const void *x, const float *w, float eps, float base, int pos0,
+                                 unsigned flags) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(dx && dw && dy && x && w, "%s: null pointer", __func__);
+    ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
+    ANE_REQUIRE(flags == ANE_NORM_BWD_REFERENCE || flags == ANE_NORM_BWD_EXACT, "%s: bad flags %u", __func__, flags);
+    if (int rc = check_qk(__func__, B, heads, hd, S)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    RopeFreq fq;
+    if (int rc = fill_freq(fq, hd, base)) return rc;
+    ANE_DISPATCH_DTYPE(dtype, T,
+        if (qk_fast_ok<T, true>(hd, S, dx, dy, x)) return (launch_qk_bwd<T, true>(st, B, heads, hd, S, dx, dw, dy, x, w, eps, pos0, flags, fq)));
+    // fallback: g = rope^-1(dy) into dx, then the norm backward reads g from dx and overwrites it
+    // element by element (each thread re-reads exactly the elements it later writes).
+    ANE_DISPATCH_DTYPE(dtype, T, if (int rc = launch_rope<T>(st, B, heads, hd, S, dx, dy, pos0, true, fq)) return rc);
+    return rmsnorm_bwd_any(st, dtype, B * heads, hd, S, dx, dw, dx, x, w, nullptr, eps, flags);
+}
+
+}  // extern "C"

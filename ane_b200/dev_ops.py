@@ -1,0 +1,175 @@
+"""Device-resident operators on torch CUDA tensors.
+
+PyTorch is used for device memory and streams only: each function passes ``data_ptr()`` and the
+current stream handle to the ``_dev`` entry points of libane_cuda.  Tensors are channel-first
+``[B, C, S]`` (or flat), contiguous, on the device the library was initialised on.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import lib as _l
+
+_DT = {torch.float32: _l.F32, torch.bfloat16: _l.BF16, torch.float16: _l.F16}
+_ID = {torch.int32: _l.ID_I32, torch.uint16: _l.ID_U16, torch.int16: _l.ID_U16}
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t):
+    if t is None:
+        return None
+    if not t.is_cuda or not t.is_contiguous():
+        raise ValueError("expected a contiguous CUDA tensor")
+    return t.data_ptr()
+
+
+def _dt(t):
+    return _DT[t.dtype]
+
+
+def _bcs(t):
+    if t.dim() == 2:
+        return 1, t.shape[0], t.shape[1]
+    if t.dim() == 3:
+        return t.shape
+    raise ValueError("expected [B, C, S] or [C, S]")
+
+
+def rmsnorm(x, w, eps=1e-5, out=None):
+    out = torch.empty_like(x) if out is None else out
+    B, Cn, S = _bcs(x)
+    _l.check(_l.load().ane_cuda_rmsnorm_dev(_stream(), _dt(x), B, Cn, S, _p(out), _p(x), _p(w), eps))
+    return out
+
+
+def rmsnorm_bwd(dy, x, w, dw, add=None, eps=1e-5, exact=False, out=None):
+    """dx = rmsnorm_bwd(dy, x, w) (+ add); dw (fp32 [C]) is accumulated into."""
+    out = torch.empty_like(x) if out is None else out
+    B, Cn, S = _bcs(x)
+    _l.check(_l.load().ane_cuda_rmsnorm_bwd_dev(_stream(), _dt(x), B, Cn, S, _p(out), _p(dw), _p(dy), _p(x), _p(w),
+                                               _p(add), eps, _l.NORM_BWD_EXACT if exact else _l.NORM_BWD_REFERENCE))
+    return out
+
+
+def residual(x, f, alpha, out=None):
+    out = torch.empty_like(x) if out is None else out
+    _l.check(_l.load().ane_cuda_residual_dev(_stream(), _dt(x), x.numel(), _p(out), _p(x), _p(f), alpha))
+    return out
+
+
+def scale(x, alpha, out=None):
+    out = torch.empty_like(x) if out is None else out
+    _l.check(_l.load().ane_cuda_scale_dev(_stream(), _dt(x), x.numel(), _p(out), _p(x), alpha))
+    return out
+
+
+def residual_rmsnorm(x, f, w, alpha, eps=1e-5, x2=None, x2norm=None):
+    x2 = torch.empty_like(x) if x2 is None else x2
+    x2norm = torch.empty_like(x) if x2norm is None else x2norm
+    B, Cn, S = _bcs(x)
+    _l.check(_l.load().ane_cuda_residual_rmsnorm_dev(_stream(), _dt(x), B, Cn, S, _p(x2), _p(x2norm), _p(x), _p(f),
+                                                    _p(w), alpha, eps))
+    return x2, x2norm
+
+
+def swiglu(h1, h3, out=None):
+    out = torch.empty_like(h1) if out is None else out
+    _l.check(_l.load().ane_cuda_swiglu_dev(_stream(), _dt(h1), h1.numel(), _p(out), _p(h1), _p(h3)))
+    return out
+
+
+def swiglu_bwd(h1, h3, d, dh1=None, dh3=None):
+    dh1 = torch.empty_like(h1) if dh1 is None else dh1
+    dh3 = torch.empty_like(h1) if dh3 is None else dh3
+    _l.check(_l.load().ane_cuda_swiglu_bwd_dev(_stream(), _dt(h1), h1.numel(), _p(dh1), _p(dh3), _p(h1), _p(h3),
+                                              _p(d)))
+    return dh1, dh3
+
+
+def rope(x, hd, base=10000.0, pos0=0, inverse=False, out=None):
+    out = torch.empty_like(x) if out is None else out
+    B, Cn, S = _bcs(x)
+    _l.check(_l.load().ane_cuda_rope_dev(_stream(), _dt(x), B, Cn, S, hd, _p(out), _p(x), base, pos0,
+                                        _l.ROPE_INVERSE if inverse else _l.ROPE_FORWARD))
+    return out
+
+
+def qknorm(x, w, hd, eps=1e-6, out=None):
+    out = torch.empty_like(x) if out is None else out
+    B, Cn, S = _bcs(x)
+    _l.check(_l.load().ane_cuda_qknorm_dev(_stream(), _dt(x), B, Cn // hd, hd, S, _p(out), _p(x), _p(w), eps))
+    return out
+
+
+def qknorm_bwd(dy, x, w, dw, hd, eps=1e-6, exact=False, out=None):
+    out = torch.empty_like(x) if out is None else out
+    B, Cn, S = _bcs(x)
+    _l.check(_l.load().ane_cuda_qknorm_bwd_dev(_stream(), _dt(x), B, Cn // hd, hd, S, _p(out), _p(dw), _p(dy), _p(x),
+                                              _p(w), eps, _l.NORM_BWD_EXACT if exact else _l.NORM_BWD_REFERENCE))
+    return out
+
+
+def qknorm_rope(x, w, hd, eps=1e-6, base=1e6, pos0=0, out=None):
+    out = torch.empty_like(x) if out is None else out
+    B, Cn, S = _bcs(x)
+    _l.check(_l.load().ane_cuda_qknorm_rope_dev(_stream(), _dt(x), B, Cn // hd, hd, S, _p(out), _p(x), _p(w), eps,
+                                               base, pos0))
+    return out
+
+
+def rope_qknorm_bwd(dy, x, w, dw, hd, eps=1e-6, base=1e6, pos0=0, exact=False, out=None):
+    out = torch.empty_like(x) if out is None else out
+    B, Cn, S = _bcs(x)
+    _l.check(_l.load().ane_cuda_rope_qknorm_bwd_dev(_stream(), _dt(x), B, Cn // hd, hd, S, _p(out), _p(dw), _p(dy),
+                                                   _p(x), _p(w), eps, base, pos0,
+                                                   _l.NORM_BWD_EXACT if exact else _l.NORM_BWD_REFERENCE))
+    return out
+
+
+def embed_lookup(table, tokens, out=None, zero_oor=False):
+    """table [V, D], tokens [B, S] (int32 or uint16 bits) -> x [B, D, S] of table's dtype."""
+    B, S = tokens.shape
+    V, D = table.shape
+    out = torch.empty((B, D, S), dtype=table.dtype, device=table.device) if out is None else out
+    _l.check(_l.load().ane_cuda_embed_lookup_dev(_stream(), _dt(table), _ID[tokens.dtype], B, D, S, _p(out), _p(table),
+                                                _p(tokens), V, _l.OOR_ZERO if zero_oor else _l.OOR_SKIP))
+    return out
+
+
+def embed_backward(d_embed, dx, tokens):
+    """d_embed [V, D] fp32 accumulated into; dx [B, D, S]; tokens [B, S]."""
+    B, D, S = dx.shape
+    V = d_embed.shape[0]
+    _l.check(_l.load().ane_cuda_embed_backward_dev(_stream(), _dt(dx), _ID[tokens.dtype], B, D, S, _p(d_embed), _p(dx),
+                                                  _p(tokens), V))
+    return d_embed
+
+
+def cross_entropy(logits, targets, grad_scale=1.0, dlogits=None):
+    """logits [B, V, S] fp32; returns (loss_seq [B], dlogits).  dlogits may be logits (in place)."""
+    B, V, S = _bcs(logits)
+    dlogits = torch.empty_like(logits) if dlogits is None else dlogits
+    loss = torch.empty(B, dtype=torch.float32, device=logits.device)
+    _l.check(_l.load().ane_cuda_cross_entropy_dev(_stream(), _ID[targets.dtype], B, V, S, _p(dlogits), _p(logits),
+                                                 _p(targets), _p(loss), grad_scale))
+    return loss, dlogits
+
+
+def adam(w, g, m, v, t, lr, b1, b2, eps, wd=0.0, gscale=1.0, clip=None, dynamic=True):
+    _l.check(_l.load().ane_cuda_adam_dev(_stream(), w.numel(), _p(w), _p(g), _p(m), _p(v), t, lr, b1, b2, eps, wd,
+                                        gscale, _p(clip), _l.ADAM_DYNAMIC if dynamic else _l.ADAM_STORIES))
+
+
+def grad_norm_sq(g, gscale=1.0, out=None):
+    out = torch.empty(1, dtype=torch.float32, device=g.device) if out is None else out
+    _l.check(_l.load().ane_cuda_grad_norm_sq_dev(_stream(), g.numel(), _p(g), gscale, _p(out)))
+    return out
+
+
+def clip_factor(normsq, clip, out=None):
+    out = torch.empty(1, dtype=torch.float32, device=normsq.device) if out is None else out
+    _l.check(_l.load().ane_cuda_clip_factor_dev(_stream(), _p(normsq), normsq.numel(), clip, _p(out)))
+    return out

@@ -1,0 +1,141 @@
+"""ctypes binding of libane_cuda.so (the C ABI declared in include/ane_cuda.h).
+
+The library is the product; this module only loads it and declares the prototypes.  There is
+no fallback: if the shared object is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libane_cuda.so")
+
+# enums of include/ane_cuda.h
+F32, BF16, F16 = 0, 1, 2
+ID_U16, ID_I32 = 0, 1
+NORM_BWD_REFERENCE, NORM_BWD_EXACT = 0, 1
+ROPE_FORWARD, ROPE_INVERSE = 0, 1
+ADAM_STORIES, ADAM_DYNAMIC = 0, 1
+OOR_SKIP, OOR_ZERO = 0, 2
+
+OK = 0
+ERR_INVALID, ERR_CUDA, ERR_NOT_INIT, ERR_NOMEM, ERR_UNSUPPORTED, ERR_TIMEOUT = -1, -2, -3, -4, -5, -6
+
+
+class AneCudaError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"libane_cuda error {code}: {msg}")
+        self.code = code
+
+
+class AdamState(C.Structure):
+    """training/stories_config.h:56-59"""
+    _fields_ = [("m", C.POINTER(C.c_float)), ("v", C.POINTER(C.c_float)), ("n", C.c_size_t)]
+
+
+class Status(C.Structure):
+    _fields_ = [("oor_ids", C.c_int32), ("nonfinite", C.c_int32), ("wait_giveups", C.c_int32),
+                ("reserved", C.c_int32)]
+
+
+_vp, _i, _u, _f, _sz = C.c_void_p, C.c_int, C.c_uint, C.c_float, C.c_size_t
+_fp = C.POINTER(C.c_float)
+_u16p = C.POINTER(C.c_uint16)
+
+# name -> (restype, argtypes).  Every symbol include/ane_cuda.h declares is listed here; the CPU
+# test-suite checks that the shared object exports each of them.
+PROTOTYPES = {
+    "ane_cuda_init": (_i, [_i]),
+    "ane_cuda_shutdown": (None, []),
+    "ane_cuda_version": (_i, []),
+    "ane_cuda_device_count": (_i, []),
+    "ane_cuda_last_error": (C.c_char_p, []),
+    "ane_cuda_launch_count": (C.c_longlong, []),
+    "ane_cuda_reset_launch_count": (None, []),
+    "ane_cuda_alloc": (_vp, [_sz]),
+    "ane_cuda_write": (_i, [_vp, _sz, _vp, _sz]),
+    "ane_cuda_read": (_i, [_vp, _sz, _vp, _sz]),
+    "ane_cuda_devptr": (_vp, [_vp]),
+    "ane_cuda_bufsize": (_sz, [_vp]),
+    "ane_cuda_free": (None, [_vp]),
+    "ane_cuda_host_alloc": (_vp, [_sz]),
+    "ane_cuda_host_free": (None, [_vp]),
+    "ane_cuda_sync": (_i, [_vp]),
+    "ane_cuda_poll_status": (_i, [C.POINTER(Status), _i]),
+    "ane_cuda_workspace_bytes": (_sz, []),
+    # host-pointer drop-ins
+    "ane_cuda_rmsnorm": (_i, [_fp, _fp, _fp, _i, _i]),
+    "ane_cuda_rmsnorm_bwd": (_i, [_fp, _fp, _fp, _fp, _fp, _i, _i]),
+    "ane_cuda_adam_update": (_i, [_fp, _fp, C.POINTER(AdamState), _i, _f, _f, _f, _f]),
+    "ane_cuda_adam_update_wd": (_i, [_fp, _fp, C.POINTER(AdamState), _i, _f, _f, _f, _f, _f]),
+    "ane_cuda_cross_entropy_loss": (_i, [_fp, _fp, _fp, _u16p, _i, _i]),
+    "ane_cuda_embed_lookup": (_i, [_fp, _fp, _u16p, _i, _i, _i]),
+    "ane_cuda_embed_backward": (_i, [_fp, _fp, _u16p, _i, _i, _i]),
+    "ane_cuda_rope_backward_inplace": (_i, [_fp, _i, _i, _i]),
+    "ane_cuda_residual": (_i, [_fp, _fp, _fp, _f, _sz]),
+    "ane_cuda_swiglu": (_i, [_fp, _fp, _fp, _sz]),
+    "ane_cuda_swiglu_bwd": (_i, [_fp, _fp, _fp, _fp, _fp, _sz]),
+    # device-resident operators
+    "ane_cuda_rmsnorm_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _f]),
+    "ane_cuda_rmsnorm_bwd_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _u]),
+    "ane_cuda_residual_dev": (_i, [_vp, _i, _sz, _vp, _vp, _vp, _f]),
+    "ane_cuda_scale_dev": (_i, [_vp, _i, _sz, _vp, _vp, _f]),
+    "ane_cuda_residual_rmsnorm_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _f]),
+    "ane_cuda_swiglu_dev": (_i, [_vp, _i, _sz, _vp, _vp, _vp]),
+    "ane_cuda_swiglu_bwd_dev": (_i, [_vp, _i, _sz, _vp, _vp, _vp, _vp, _vp]),
+    "ane_cuda_rope_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _f, _i, _u]),
+    "ane_cuda_qknorm_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _f]),
+    "ane_cuda_qknorm_bwd_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _u]),
+    "ane_cuda_qknorm_rope_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _f, _f, _i]),
+    "ane_cuda_rope_qknorm_bwd_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _u]),
+    "ane_cuda_embed_lookup_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _u]),
+    "ane_cuda_embed_backward_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i]),
+    "ane_cuda_cross_entropy_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _f]),
+    "ane_cuda_adam_dev": (_i, [_vp, _sz, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _f, _f, _f, _vp, _u]),
+    "ane_cuda_grad_norm_sq_dev": (_i, [_vp, _sz, _vp, _f, _vp]),
+    "ane_cuda_clip_factor_dev": (_i, [_vp, _vp, _i, _f, _vp]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the shared object and declare the prototypes.  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise FileNotFoundError(
+            f"{LIB_PATH} is missing: build it with `python -m ane_b200.build` (needs nvcc). "
+            "libane_cuda has no CPU or PyTorch fallback.")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in PROTOTYPES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(rc: int) -> None:
+    if rc != OK:
+        raise AneCudaError(rc, load().ane_cuda_last_error().decode("utf-8", "replace"))
+
+
+def init(device: int = 0) -> None:
+    check(load().ane_cuda_init(int(device)))
+
+
+def launch_count() -> int:
+    return int(load().ane_cuda_launch_count())
+
+
+def reset_launch_count() -> None:
+    load().ane_cuda_reset_launch_count()
+
+
+def poll_status(reset: bool = True) -> Status:
+    s = Status()
+    check(load().ane_cuda_poll_status(C.byref(s), int(reset)))
+    return s

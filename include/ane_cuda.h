@@ -1,0 +1,209 @@
+/* ane_cuda.h -- C ABI of libane_cuda: the maderix/ANE per-layer non-matmul operator set as
+ * hand-written CUDA kernels for NVIDIA B200 (sm_100a).
+ *
+ * The boundary follows the one C ABI the reference has, bridge/ane_bridge.h:16-94: opaque
+ * handles, int status returns, byte-count reads and writes of device-visible buffers, explicit
+ * free, no C++ types.  Three groups of entry points:
+ *
+ *   1. lifecycle and device buffers        (the ane_bridge_init / write_input / read_output
+ *                                           / free analogue)
+ *   2. host-pointer drop-ins               same argument order and overwrite / accumulate
+ *                                           behaviour as the `static` functions of
+ *                                           training/stories_cpu_ops.h and
+ *                                           training/training_dynamic/cpu_ops.h; they stage
+ *                                           host <-> device and are PCIe-bound
+ *   3. device-resident operators (`_dev`)  asynchronous on a caller-given CUDA stream; these
+ *                                           are what a GPU training loop calls and what the
+ *                                           benchmark times
+ *
+ * Tensor layout everywhere: channel-first, batched as [B][C][S]; element (b, c, t) lives at
+ * (b*C + c)*S + t (training/stories_cpu_ops.h:10,117).  S is the contiguous axis.
+ *
+ * There is no CPU fallback: every operator runs on the GPU or returns an error.
+ * Threading: one host thread per device at a time (the reference's operators are likewise
+ * never re-entered concurrently, training/training_dynamic/train.m:727-749).
+ */
+#ifndef ANE_CUDA_H
+#define ANE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ANE_CUDA_VERSION 100
+
+/* ---- status codes (0 = success, negative = failure; ane_cuda_last_error() has the text) */
+#define ANE_CUDA_OK              0
+#define ANE_CUDA_ERR_INVALID    (-1)  /* bad argument: null pointer, non-positive size, misaligned ... */
+#define ANE_CUDA_ERR_CUDA       (-2)  /* a CUDA runtime call failed */
+#define ANE_CUDA_ERR_NOT_INIT   (-3)  /* ane_cuda_init() has not succeeded on this process */
+#define ANE_CUDA_ERR_NOMEM      (-4)  /* device or pinned-host allocation failed */
+#define ANE_CUDA_ERR_UNSUPPORTED (-5) /* shape outside what the kernels cover (documented per op) */
+#define ANE_CUDA_ERR_TIMEOUT    (-6)  /* a bounded device-side wait gave up (status word has details) */
+
+/* ---- element types of activation tensors (math is always fp32 inside the kernels) */
+typedef enum { ANE_F32 = 0, ANE_BF16 = 1, ANE_F16 = 2 } ane_dtype;
+/* ---- token id types: the reference uses uint16_t (stories_cpu_ops.h:112), Qwen3's vocabulary
+ *      of 151936 needs int32 */
+typedef enum { ANE_ID_U16 = 0, ANE_ID_I32 = 1 } ane_idtype;
+
+/* ---- flags */
+#define ANE_NORM_BWD_REFERENCE 0u /* dx = w*rrms*(dy - x*coef): what stories_cpu_ops.h:42-46 computes */
+#define ANE_NORM_BWD_EXACT     1u /* dx = rrms*(w*dy - x*coef): analytic form, ane_rmsnorm_bwd.h:56,70-74 */
+#define ANE_ROPE_FORWARD       0u
+#define ANE_ROPE_INVERSE       1u /* the backward rotation of training_dynamic/cpu_ops.h:168-184 */
+#define ANE_ADAM_STORIES       0u /* w -= lr*mh/(sqrt(vh)+eps)                 stories_cpu_ops.h:55-63 */
+#define ANE_ADAM_DYNAMIC       1u /* w -= lr*(mh/(sqrt(vh)+eps) + wd*w)        training_dynamic/cpu_ops.h:56-64 */
+#define ANE_OOR_SKIP           0u /* out-of-range id: leave the column / row untouched (stories_cpu_ops.h:115,126) */
+#define ANE_OOR_ZERO           2u /* out-of-range id: write zeros instead */
+
+/* AdamState, laid out as in training/stories_config.h:56-59 and training_dynamic/config.h:46. */
+typedef struct { float *m, *v; size_t n; } AdamState;
+
+/* Device-side status words written by the kernels (ane_cuda_poll_status copies them out). */
+typedef struct {
+    int32_t oor_ids;      /* token / target ids outside [0, vocab) seen since the last reset */
+    int32_t nonfinite;    /* per-token losses that were not finite */
+    int32_t wait_giveups; /* bounded device-side waits that ran out */
+    int32_t reserved;
+} ane_cuda_status;
+
+typedef struct ANECudaBuf ANECudaBuf; /* opaque device buffer, the IOSurface analogue (ane_bridge.h:16) */
+
+/* =====================================================================================
+ * 1. Lifecycle and buffers                      replaces bridge/ane_bridge.h:20,54-68
+ * ===================================================================================== */
+/* Select `device`, create the library's context on it.  Idempotent per device, like
+ * ane_bridge_init (bridge/ane_bridge.m:34).  Returns ANE_CUDA_OK or a negative code. */
+int ane_cuda_init(int device);
+void ane_cuda_shutdown(void);
+int ane_cuda_version(void);
+int ane_cuda_device_count(void);
+const char *ane_cuda_last_error(void);
+/* Number of this library's kernels launched since the last reset (cf. the compile counter of
+ * ane_bridge.h:65-68). */
+long long ane_cuda_launch_count(void);
+void ane_cuda_reset_launch_count(void);
+
+ANECudaBuf *ane_cuda_alloc(size_t bytes);                       /* NULL on failure */
+int ane_cuda_write(ANECudaBuf *buf, size_t offset, const void *host, size_t bytes);  /* ane_bridge_write_input */
+int ane_cuda_read(ANECudaBuf *buf, size_t offset, void *host, size_t bytes);         /* ane_bridge_read_output */
+void *ane_cuda_devptr(ANECudaBuf *buf);
+size_t ane_cuda_bufsize(ANECudaBuf *buf);
+void ane_cuda_free(ANECudaBuf *buf);                            /* ane_bridge_free */
+/* Page-locked host memory; the drop-ins of group 2 copy asynchronously from / to it. */
+void *ane_cuda_host_alloc(size_t bytes);
+void ane_cuda_host_free(void *p);
+int ane_cuda_sync(void *stream);
+/* Copy the device status words to *out and optionally clear them. */
+int ane_cuda_poll_status(ane_cuda_status *out, int reset);
+/* Bytes of library-owned scratch currently held on the device (grow-only cache). */
+size_t ane_cuda_workspace_bytes(void);
+
+/* =====================================================================================
+ * 2. Host-pointer drop-ins (fp32, one sequence, reference signatures)
+ * ===================================================================================== */
+/* training/stories_cpu_ops.h:6 and training_dynamic/cpu_ops.h:7 -- rmsnorm(out,x,w,d,S), eps 1e-5 */
+int ane_cuda_rmsnorm(float *out, const float *x, const float *w, int d, int S);
+/* stories_cpu_ops.h:23 / cpu_ops.h:24 -- dx is overwritten, dw is accumulated into */
+int ane_cuda_rmsnorm_bwd(float *dx, float *dw, const float *dy, const float *x, const float *w, int d, int S);
+/* stories_cpu_ops.h:55 */
+int ane_cuda_adam_update(float *w, const float *g, AdamState *s, int t, float lr, float b1, float b2, float eps);
+/* training_dynamic/cpu_ops.h:56 (decoupled weight decay inside the lr bracket) */
+int ane_cuda_adam_update_wd(float *w, const float *g, AdamState *s, int t, float lr, float b1, float b2,
+                            float eps, float wd);
+/* stories_cpu_ops.h:71 / cpu_ops.h:68 -- returns the mean loss through *loss; an out-of-range
+ * target behaves as stories_cpu_ops.h:94-103 (column keeps the plain softmax, no loss term) */
+int ane_cuda_cross_entropy_loss(float *loss, float *dlogits, const float *logits, const uint16_t *targets,
+                                int V, int S);
+/* stories_cpu_ops.h:112 / cpu_ops.h:150 -- `vocab` is the reference's compile-time VOCAB */
+int ane_cuda_embed_lookup(float *x, const float *embed, const uint16_t *tokens, int dim, int seq, int vocab);
+/* stories_cpu_ops.h:123 / cpu_ops.h:158 -- d_embed [vocab, dim] is accumulated into */
+int ane_cuda_embed_backward(float *d_embed, const float *dx, const uint16_t *tokens, int dim, int seq, int vocab);
+/* training_dynamic/cpu_ops.h:168 -- in place, base 10000 */
+int ane_cuda_rope_backward_inplace(float *dx, int seq, int dim, int hd);
+/* the inline blocks of training_dynamic/train.m: :460 residual, :537-554 SwiGLU backward */
+int ane_cuda_residual(float *out, const float *x, const float *f, float alpha, size_t n);
+int ane_cuda_swiglu(float *out, const float *h1, const float *h3, size_t n);
+int ane_cuda_swiglu_bwd(float *dh1, float *dh3, const float *h1, const float *h3, const float *dsilu, size_t n);
+
+/* =====================================================================================
+ * 3. Device-resident operators.  `stream` is a cudaStream_t (NULL = default stream).
+ *    All pointers are device pointers.  Weights (w, dw) and optimizer state are fp32;
+ *    activations have `dtype`.  Vectorised paths need 16-byte aligned pointers and S a
+ *    multiple of 16/sizeof(element); other shapes take a slower scalar path.
+ * ===================================================================================== */
+/* a1: out = (x * rrms) * w[c], rrms = 1/sqrt(mean_c x^2 + eps)         stories_cpu_ops.h:6-21 */
+int ane_cuda_rmsnorm_dev(void *stream, ane_dtype dtype, int B, int C, int S,
+                         void *out, const void *x, const float *w, float eps);
+/* a2 (+a3 backward add): dx = rmsnorm_bwd(dy, x, w) [+ add] ; dw[c] += sum_tokens dy*x*rrms
+ * (deterministic: per-block partials summed in a fixed order).  add may be NULL.
+ * stories_cpu_ops.h:23-53 ; the add is training_dynamic/train.m:590,721 */
+int ane_cuda_rmsnorm_bwd_dev(void *stream, ane_dtype dtype, int B, int C, int S,
+                             void *dx, float *dw, const void *dy, const void *x, const float *w,
+                             const void *add, float eps, unsigned flags);
+/* a3: out = f*alpha + x (flat, n elements)                            train.m:460, mil_dynamic.h:279-283 */
+int ane_cuda_residual_dev(void *stream, ane_dtype dtype, size_t n, void *out, const void *x, const void *f,
+                          float alpha);
+/* out = alpha * x                                                      train.m:497,523,595 */
+int ane_cuda_scale_dev(void *stream, ane_dtype dtype, size_t n, void *out, const void *x, float alpha);
+/* a3+a1 fused: x2 = f*alpha + x ; x2norm = rmsnorm(x2)                 train.m:460-461 */
+int ane_cuda_residual_rmsnorm_dev(void *stream, ane_dtype dtype, int B, int C, int S,
+                                  void *x2, void *x2norm, const void *x, const void *f, const float *w,
+                                  float alpha, float eps);
+/* a4: out = h1*sigmoid(h1)*h3                                          forward.h:101,149-151 */
+int ane_cuda_swiglu_dev(void *stream, ane_dtype dtype, size_t n, void *out, const void *h1, const void *h3);
+/* a5: dh1, dh3 from h1, h3, dsilu (one pass; dscale multiplies dsilu first, for train.m:523) */
+int ane_cuda_swiglu_bwd_dev(void *stream, ane_dtype dtype, size_t n, void *dh1, void *dh3,
+                            const void *h1, const void *h3, const void *dsilu);
+/* a6/a7: rotate interleaved channel pairs (2i, 2i+1) of every head by theta = (pos0+t)*base^(-2i/hd);
+ * flags = ANE_ROPE_FORWARD or ANE_ROPE_INVERSE; out may equal x (in place).
+ * cpu_ops.h:168-184, forward.h:55-70 */
+int ane_cuda_rope_dev(void *stream, ane_dtype dtype, int B, int C, int S, int hd,
+                      void *out, const void *x, float base, int pos0, unsigned flags);
+/* a8: per-head RMSNorm over the hd channels of each head, weight w[hd] shared by the heads. */
+int ane_cuda_qknorm_dev(void *stream, ane_dtype dtype, int B, int heads, int hd, int S,
+                        void *out, const void *x, const float *w, float eps);
+int ane_cuda_qknorm_bwd_dev(void *stream, ane_dtype dtype, int B, int heads, int hd, int S,
+                            void *dx, float *dw, const void *dy, const void *x, const float *w,
+                            float eps, unsigned flags);
+/* a8+a6 fused: out = rope(qknorm(x)) */
+int ane_cuda_qknorm_rope_dev(void *stream, ane_dtype dtype, int B, int heads, int hd, int S,
+                             void *out, const void *x, const float *w, float eps, float base, int pos0);
+/* a7+a8 fused: dx = qknorm_bwd(rope^-1(dy), x, w) ; dw[hd] += ... */
+int ane_cuda_rope_qknorm_bwd_dev(void *stream, ane_dtype dtype, int B, int heads, int hd, int S,
+                                 void *dx, float *dw, const void *dy, const void *x, const float *w,
+                                 float eps, float base, int pos0, unsigned flags);
+/* a9: x[b][d][t] = table[tok[b][t]][d] (bit-exact copy; table has the same dtype as x).
+ * flags: ANE_OOR_SKIP (default) or ANE_OOR_ZERO.  stories_cpu_ops.h:112-120 */
+int ane_cuda_embed_lookup_dev(void *stream, ane_dtype dtype, ane_idtype idtype, int B, int D, int S,
+                              void *x, const void *table, const void *tokens, int vocab, unsigned flags);
+/* a10: d_embed[tok[b][t]][d] += dx[b][d][t], fp32 accumulate in increasing (b, t) order per row;
+ * run-to-run bit-identical (sort by id, then one writer per row).  stories_cpu_ops.h:123-131 */
+int ane_cuda_embed_backward_dev(void *stream, ane_dtype dtype, ane_idtype idtype, int B, int D, int S,
+                                float *d_embed, const void *dx, const void *tokens, int vocab);
+/* a11: per token softmax over V, loss_seq[b] = -mean_t log(p[tgt]+1e-10),
+ * dlogits = (p - onehot)/S * grad_scale ; fp32 logits [B][V][S]; dlogits may equal logits.
+ * stories_cpu_ops.h:71-108 ; grad_scale is train.m:497 */
+int ane_cuda_cross_entropy_dev(void *stream, ane_idtype idtype, int B, int V, int S,
+                               float *dlogits, const float *logits, const void *targets,
+                               float *loss_seq, float grad_scale);
+/* a12 (+a13 folded): Adam over a flat fp32 range.  g is first multiplied by gscale and then by
+ * *clip_dev (a device scalar, NULL = 1), as train.m:750-767 and :809-825 do in two passes.
+ * flags = ANE_ADAM_STORIES or ANE_ADAM_DYNAMIC. */
+int ane_cuda_adam_dev(void *stream, size_t n, float *w, const float *g, float *m, float *v, int t,
+                      float lr, float b1, float b2, float eps, float wd, float gscale,
+                      const float *clip_dev, unsigned flags);
+/* a13: *out_dev = sum_i (g[i]*gscale)^2, fixed summation order.        train.m:770-788 */
+int ane_cuda_grad_norm_sq_dev(void *stream, size_t n, const float *g, float gscale, float *out_dev);
+/* a13: *factor_dev = clip/norm if clip > 0 and norm > clip else 1, norm = sqrt(sum of the
+ * n_terms partial squares at normsq_dev).                               train.m:788,809-810 */
+int ane_cuda_clip_factor_dev(void *stream, const float *normsq_dev, int n_terms, float clip, float *factor_dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ANE_CUDA_H */

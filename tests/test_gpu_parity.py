@@ -1,0 +1,513 @@
+"""GPU parity tests: every operator of libane_cuda, called through its C ABI, against the CPU
+oracle (oracle/oracle_ops.c) on the same seeded inputs.
+
+Tolerances (max |got - ref| / max |ref| per tensor):
+  * fp32 operators               <= 1e-5
+  * bf16 / fp16 variants         <= 2e-3 against the fp32 oracle run on the rounded inputs
+  * gathers, token indexing and the scatter-add (same addition order as the reference loop)
+                                 bit-exact
+Shapes cover the reference's own (DIM 768, SEQ 256, VOCAB 32000), the benchmark configurations
+at sizes the oracle finishes in seconds, and ragged / tiny cases that break every alignment the
+vector paths rely on.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from tests.conftest import rel_err
+from tests.golden import gen_inputs as gi
+
+pytestmark = pytest.mark.gpu
+
+TOL32 = 1e-5
+TOL16 = 2e-3
+
+
+@pytest.fixture(scope="module")
+def dev():
+    import torch
+    from ane_b200 import dev_ops, lib
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    lib.init(0)
+    return dev_ops
+
+
+def _torch():
+    import torch
+    return torch
+
+
+DT = {"f32": "float32", "bf16": "bfloat16", "f16": "float16"}
+
+
+def up(a, dt="f32"):
+    """numpy fp32 -> device tensor of dtype dt; also returns the rounded values as fp32 numpy."""
+    torch = _torch()
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda().to(getattr(torch, DT[dt])).contiguous()
+    return t, t.float().cpu().numpy()
+
+
+def down(t):
+    return t.float().cpu().numpy()
+
+
+def tol(dt):
+    return TOL32 if dt == "f32" else TOL16
+
+
+NORM_SHAPES = [(1, 768, 256), (3, 7, 5), (2, 128, 257), (1, 1, 1), (2, 1024, 64), (1, 2, 3), (5, 33, 48), (1, 300, 8)]
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("shape", NORM_SHAPES)
+def test_rmsnorm_fwd(dev, oracle, shape, dt):
+    B, Cn, S = shape
+    x, w, _ = gi.cfg1(seed=11, B=B, dim=Cn, seq=S)
+    xd, xr = up(x, dt)
+    wd, _ = up(w)
+    got = down(dev.rmsnorm(xd, wd, 1e-5))
+    assert rel_err(got, oracle.rmsnorm(xr, w, 1e-5)) <= tol(dt)
+
+
+@pytest.mark.parametrize("exact", [False, True])
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("shape", NORM_SHAPES)
+def test_rmsnorm_bwd(dev, oracle, shape, dt, exact):
+    torch = _torch()
+    B, Cn, S = shape
+    x, w, dy = gi.cfg1(seed=12, B=B, dim=Cn, seq=S)
+    xd, xr = up(x, dt)
+    dyd, dyr = up(dy, dt)
+    wd, _ = up(w)
+    dw0 = gi.normal(gi.rng(5), (Cn,), 0.1)
+    dwd, _ = up(dw0)
+    dx = down(dev.rmsnorm_bwd(dyd, xd, wd, dwd, eps=1e-5, exact=exact))
+    rdx, rdw = oracle.rmsnorm_bwd(dyr, xr, w, dw=dw0, eps=1e-5, exact=exact)
+    assert rel_err(dx, rdx) <= tol(dt)
+    assert rel_err(down(dwd), rdw) <= (TOL32 if dt == "f32" else 1e-4)
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_rmsnorm_bwd_fused_add_and_determinism(dev, oracle, dt):
+    torch = _torch()
+    B, Cn, S = 4, 768, 256
+    x, w, dy = gi.cfg1(seed=13, B=B, dim=Cn, seq=S)
+    add = gi.normal(gi.rng(6), (B, Cn, S))
+    xd, xr = up(x, dt)
+    dyd, dyr = up(dy, dt)
+    ad, ar = up(add, dt)
+    wd, _ = up(w)
+    dw1 = torch.zeros(Cn, device="cuda")
+    dx1 = dev.rmsnorm_bwd(dyd, xd, wd, dw1, add=ad)
+    rdx, rdw = oracle.rmsnorm_bwd(dyr, xr, w)
+    assert rel_err(down(dx1), oracle.add(rdx, ar)) <= tol(dt)          # train.m:590,721
+    assert rel_err(down(dw1), rdw) <= (TOL32 if dt == "f32" else 1e-4)
+    dw2 = torch.zeros(Cn, device="cuda")
+    dx2 = dev.rmsnorm_bwd(dyd, xd, wd, dw2, add=ad)
+    assert torch.equal(dx1, dx2) and torch.equal(dw1, dw2)              # bit-stable run to run
+
+
+def test_rmsnorm_reference_fixtures_on_gpu(dev, golden):
+    """The reference tests' own inputs (test_rmsnorm_bwd.m:26-33, test_classifier.m:25-27)
+    against the committed outputs of the reference functions."""
+    torch = _torch()
+    x, dy, w = gi.fixture_rmsnorm_bwd()
+    dw = torch.zeros(768, device="cuda")
+    dx = down(dev.rmsnorm_bwd(up(dy)[0], up(x)[0], up(w)[0], dw))
+    s = int(golden["rmsbwd_fixture_stories_dx_stride"])
+    assert rel_err(dx.reshape(-1)[::s], golden["rmsbwd_fixture_stories_dx"]) <= TOL32
+    assert rel_err(down(dw), golden["rmsbwd_fixture_stories_dw"]) <= TOL32
+    x, w = gi.fixture_rmsnorm_fwd()
+    out = down(dev.rmsnorm(up(x)[0], up(w)[0]))
+    s = int(golden["rms_fixture_stories_out_stride"])
+    assert rel_err(out.reshape(-1)[::s], golden["rms_fixture_stories_out"]) <= TOL32
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("n,off", [(2048 * 256, 0), (1, 0), (1023, 0), (4099, 1), (768 * 256, 3)])
+def test_elementwise(dev, oracle, n, off, dt):
+    """residual (train.m:460), scale (train.m:523), SwiGLU fwd (forward.h:101) and bwd
+    (train.m:537-554); off > 0 shifts the pointers off 16-byte alignment."""
+    torch = _torch()
+    r = gi.rng(21)
+    arrs = [gi.normal(r, (n + off,)) for _ in range(3)]
+    (h1d, h1), (h3d, h3), (dd, d) = [up(a, dt) for a in arrs]
+    h1d, h3d, dd = h1d[off:], h3d[off:], dd[off:]
+    h1, h3, d = (np.ascontiguousarray(a[off:]) for a in (h1, h3, d))
+    alpha = float(np.float32((2.0 * 12) ** -0.25))
+    assert rel_err(down(dev.residual(h1d, h3d, alpha, out=torch.empty_like(h1d))), oracle.residual(h1, h3, alpha)) <= tol(dt)
+    assert rel_err(down(dev.scale(h1d, alpha, out=torch.empty_like(h1d))), oracle.scale(h1, alpha)) <= tol(dt)
+    assert rel_err(down(dev.swiglu(h1d, h3d, out=torch.empty_like(h1d))), oracle.swiglu(h1, h3)) <= tol(dt)
+    g1, g3 = dev.swiglu_bwd(h1d, h3d, dd, dh1=torch.empty_like(h1d), dh3=torch.empty_like(h1d))
+    r1, r3 = oracle.swiglu_bwd(h1, h3, d)
+    assert rel_err(down(g1), r1) <= tol(dt) and rel_err(down(g3), r3) <= tol(dt)
+
+
+def test_residual_alpha_of_the_reference(dev, oracle):
+    """alpha = 1/sqrt(2*NLAYERS) (train.m:188) and alpha = 1 (train_large.m:427): bit-exact."""
+    _, _, _, x, f = gi.cfg2()
+    for alpha in (float(np.float32(1.0) / np.sqrt(np.float32(24.0))), 1.0):
+        got = down(dev.residual(up(x)[0], up(f)[0], alpha))
+        assert np.array_equal(got, oracle.residual(x, f, alpha))
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("shape", [(1, 768, 256), (2, 1024, 128), (3, 7, 5), (2, 100, 37)])
+def test_residual_rmsnorm_fused(dev, oracle, shape, dt):
+    B, Cn, S = shape
+    r = gi.rng(31)
+    x, f = gi.normal(r, shape), gi.normal(r, shape)
+    w = gi.normal(r, (Cn,), 0.02, 1.0)
+    alpha = float(np.float32((2.0 * 28) ** -0.5))
+    (xd, xr), (fd, fr) = up(x, dt), up(f, dt)
+    x2, x2n = dev.residual_rmsnorm(xd, fd, up(w)[0], alpha, 1e-5)
+    assert rel_err(down(x2), oracle.residual(xr, fr, alpha)) <= tol(dt)
+    # the norm is taken over the stored (rounded) x2, which is what the backward pass will read
+    assert rel_err(down(x2n), oracle.rmsnorm(down(x2), w, 1e-5)) <= tol(dt)
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("B,heads,hd,S,base,pos0", [(1, 16, 128, 256, 1e4, 0), (2, 8, 128, 64, 1e6, 0), (1, 12, 64, 256, 1e4, 0),
+                                                     (2, 3, 8, 37, 1e6, 11), (1, 2, 2, 1, 1e4, 0), (1, 4, 128, 2048, 1e6, 0)])
+def test_rope_fwd_and_inverse(dev, oracle, B, heads, hd, S, base, pos0, dt):
+    x = gi.normal(gi.rng(41), (B, heads * hd, S))
+    xd, xr = up(x, dt)
+    for inverse in (False, True):
+        got = down(dev.rope(xd, hd, base=base, pos0=pos0, inverse=inverse))
+        assert rel_err(got, oracle.rope(xr, hd, base=base, pos0=pos0, inverse=inverse)) <= tol(dt)
+    # in place
+    y = xd.clone()
+    dev.rope(y, hd, base=base, pos0=pos0, out=y)
+    assert rel_err(down(y), oracle.rope(xr, hd, base=base, pos0=pos0)) <= tol(dt)
+
+
+def test_rope_bwd_golden_on_gpu(dev, golden):
+    """training_dynamic/cpu_ops.h:168 on the committed reference outputs."""
+    for name, (dim, hd) in (("hd64", (768, 64)), ("hd128", (2048, 128))):
+        d = gi.normal(gi.rng(88), (dim, 256))
+        got = down(dev.rope(up(d)[0], hd, base=10000.0, inverse=True))
+        s = int(golden[f"ropebwd_{name}_stride"])
+        assert rel_err(got.reshape(-1)[::s], golden[f"ropebwd_{name}"]) <= TOL32
+
+
+QK_CASES = [(1, 16, 128, 256), (2, 8, 128, 64), (1, 12, 64, 128), (2, 3, 8, 37), (1, 2, 32, 5), (3, 16, 128, 40)]
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("B,heads,hd,S", QK_CASES)
+def test_qknorm_and_fusions_fwd(dev, oracle, B, heads, hd, S, dt):
+    r = gi.rng(51)
+    x = gi.normal(r, (B, heads * hd, S))
+    w = gi.normal(r, (hd,), 0.02, 1.0)
+    xd, xr = up(x, dt)
+    wd, _ = up(w)
+    assert rel_err(down(dev.qknorm(xd, wd, hd, 1e-6)), oracle.qknorm(xr, w, hd, 1e-6)) <= tol(dt)
+    got = down(dev.qknorm_rope(xd, wd, hd, 1e-6, 1e6, 3))
+    assert rel_err(got, oracle.qknorm_rope(xr, w, hd, 1e-6, 1e6, 3)) <= tol(dt)
+
+
+@pytest.mark.parametrize("exact", [False, True])
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("B,heads,hd,S", QK_CASES)
+def test_qknorm_and_fusions_bwd(dev, oracle, B, heads, hd, S, dt, exact):
+    torch = _torch()
+    r = gi.rng(52)
+    x = gi.normal(r, (B, heads * hd, S))
+    dy = gi.normal(r, (B, heads * hd, S))
+    w = gi.normal(r, (hd,), 0.02, 1.0)
+    (xd, xr), (dyd, dyr) = up(x, dt), up(dy, dt)
+    wd, _ = up(w)
+    dwtol = TOL32 if dt == "f32" else 1e-4
+    dw = torch.zeros(hd, device="cuda")
+    dx = down(dev.qknorm_bwd(dyd, xd, wd, dw, hd, 1e-6, exact=exact))
+    rdx, rdw = oracle.qknorm_bwd(dyr, xr, w, hd, eps=1e-6, exact=exact)
+    assert rel_err(dx, rdx) <= tol(dt) and rel_err(down(dw), rdw) <= dwtol
+    dw = torch.zeros(hd, device="cuda")
+    dx = down(dev.rope_qknorm_bwd(dyd, xd, wd, dw, hd, 1e-6, 1e6, 3, exact=exact))
+    rdx, rdw = oracle.rope_qknorm_bwd(dyr, xr, w, hd, eps=1e-6, base=1e6, pos0=3, exact=exact)
+    assert rel_err(dx, rdx) <= tol(dt) and rel_err(down(dw), rdw) <= dwtol
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("idt", ["int32", "uint16"])
+@pytest.mark.parametrize("B,D,S,V", [(1, 768, 256, 32000), (2, 1024, 64, 151936), (3, 5, 7, 11), (1, 100, 33, 70000)])
+def test_embed_lookup_bit_exact(dev, oracle, B, D, S, V, idt, dt):
+    torch = _torch()
+    from ane_b200 import lib
+    if idt == "uint16" and V > 65536:
+        pytest.skip("uint16 ids cannot address this vocabulary")
+    r = gi.rng(61)
+    table = gi.normal(r, (V, D), 0.02)
+    tok = r.integers(0, V, size=(B, S)).astype(np.int32)
+    tabd, tabr = up(table, dt)
+    tokd = torch.from_numpy(tok.astype(np.uint16 if idt == "uint16" else np.int32)).cuda()
+    lib.poll_status(reset=True)
+    got = down(dev.embed_lookup(tabd, tokd))
+    want, _ = oracle.embed_lookup(tabr, tok)
+    assert np.array_equal(got, want)
+    assert lib.poll_status().oor_ids == 0
+
+
+def test_embed_lookup_out_of_range(dev, oracle):
+    torch = _torch()
+    from ane_b200 import lib
+    table = gi.normal(gi.rng(62), (100, 40))
+    tok = np.array([[3, 100, -1, 99, 5]], np.int32)
+    tabd, _ = up(table)
+    lib.poll_status(reset=True)
+    init = torch.full((1, 40, 5), 7.0, device="cuda")
+    got = down(dev.embed_lookup(tabd, torch.from_numpy(tok).cuda(), out=init.clone()))
+    want, oor = oracle.embed_lookup(table, tok, x_init=np.full((1, 40, 5), 7.0, np.float32))
+    assert np.array_equal(got, want)                       # stale columns kept (stories_cpu_ops.h:115)
+    assert lib.poll_status().oor_ids == oor == 2
+    got = down(dev.embed_lookup(tabd, torch.from_numpy(tok).cuda(), out=init.clone(), zero_oor=True))
+    assert np.all(got[0, :, 1] == 0) and np.all(got[0, :, 2] == 0)
+    lib.poll_status(reset=True)
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("B,D,S,V,dup", [(1, 768, 256, 32000, 10), (2, 1024, 64, 151936, 0), (3, 5, 7, 11, 0),
+                                         (2, 96, 130, 50, 0), (1, 64, 300, 1000, 300)])
+def test_embed_backward_bit_exact_and_deterministic(dev, oracle, B, D, S, V, dup, dt):
+    """fp32 additions happen in the reference's order (increasing (b, t) per row), so the result
+    equals the sequential CPU sum bit for bit."""
+    torch = _torch()
+    r = gi.rng(63)
+    tok = r.integers(0, V, size=(B, S)).astype(np.int32)
+    if dup:
+        tok[0, :dup] = tok[0, 0]
+    dx = gi.normal(r, (B, D, S))
+    dE0 = gi.normal(r, (V, D), 0.01)
+    dxd, dxr = up(dx, dt)
+    tokd = torch.from_numpy(tok).cuda()
+    want, _ = oracle.embed_backward(dE0, dxr, tok)
+    outs = []
+    for _ in range(2):
+        dE = torch.from_numpy(dE0).cuda()
+        dev.embed_backward(dE, dxd, tokd)
+        outs.append(dE)
+    assert torch.equal(outs[0], outs[1])
+    assert np.array_equal(down(outs[0]), want)
+
+
+def test_embed_backward_skips_out_of_range(dev, oracle):
+    torch = _torch()
+    from ane_b200 import lib
+    tok = np.array([[1, 50, 2, -3, 1]], np.int32)
+    dx = gi.normal(gi.rng(64), (1, 16, 5))
+    dE = torch.zeros(50, 16, device="cuda")
+    lib.poll_status(reset=True)
+    dev.embed_backward(dE, up(dx)[0], torch.from_numpy(tok).cuda())
+    want, oor = oracle.embed_backward(np.zeros((50, 16), np.float32), dx, tok)
+    assert np.array_equal(down(dE), want)
+    assert lib.poll_status().oor_ids == oor == 2
+    lib.poll_status(reset=True)
+
+
+@pytest.mark.parametrize("idt", ["int32", "uint16"])
+@pytest.mark.parametrize("B,V,S,gs", [(1, 32000, 256, 1.0), (2, 1000, 37, 256.0), (1, 151936, 64, 1.0), (3, 17, 4, 1.0), (1, 9200, 256, 1.0)])
+def test_cross_entropy(dev, oracle, B, V, S, gs, idt):
+    torch = _torch()
+    if idt == "uint16" and V > 65536:
+        pytest.skip("uint16 ids cannot address this vocabulary")
+    r = gi.rng(71)
+    logits = gi.normal(r, (B, V, S))
+    tg = r.integers(0, V, size=(B, S)).astype(np.int32)
+    ld, _ = up(logits)
+    tgd = torch.from_numpy(tg.astype(np.uint16 if idt == "uint16" else np.int32)).cuda()
+    loss, dl = dev.cross_entropy(ld, tgd, grad_scale=gs)
+    rloss, rdl, _ = oracle.cross_entropy(logits, tg, grad_scale=gs)
+    assert rel_err(down(loss), rloss) <= TOL32
+    assert rel_err(down(dl), rdl) <= TOL32
+    # in place
+    loss2, dl2 = dev.cross_entropy(ld, tgd, grad_scale=gs, dlogits=ld)
+    assert torch.equal(dl2, dl) and torch.equal(loss2, loss)
+
+
+def test_cross_entropy_reference_fixture_and_oor(dev, oracle, golden):
+    torch = _torch()
+    from ane_b200 import lib
+    logits = gi.fixture_softmax_logits()                 # test_classifier.m:132-134
+    tg = golden["ce_fixture_targets"].astype(np.int32)
+    loss, dl = dev.cross_entropy(up(logits[None])[0], torch.from_numpy(tg[None]).cuda())
+    assert abs(float(loss[0]) - float(golden["ce_fixture_stories_loss"])) <= TOL32 * float(golden["ce_fixture_stories_loss"])
+    s = int(golden["ce_fixture_stories_dlogits_stride"])
+    assert rel_err(down(dl).reshape(-1)[::s], golden["ce_fixture_stories_dlogits"]) <= TOL32
+    # out-of-range target: plain softmax stays in the column (stories_cpu_ops.h:94-103)
+    lg = gi.cfg4_logits(B=1, vocab=500, seq=8)
+    tg = np.array([[1, 2, 600, 3, 4, 5, -6, 7]], np.int32)
+    lib.poll_status(reset=True)
+    loss, dl = dev.cross_entropy(up(lg)[0], torch.from_numpy(tg).cuda())
+    rloss, rdl, oor = oracle.cross_entropy(lg, tg)
+    assert rel_err(down(loss), rloss) <= TOL32 and rel_err(down(dl), rdl) <= TOL32
+    assert lib.poll_status().oor_ids == oor == 2
+    lib.poll_status(reset=True)
+
+
+@pytest.mark.parametrize("dynamic,wd,b2", [(False, 0.0, 0.999), (True, 0.1, 0.95), (True, 0.0, 0.95)])
+@pytest.mark.parametrize("n", [1 << 16, 1000003, 5])
+def test_adam(dev, oracle, n, dynamic, wd, b2):
+    torch = _torch()
+    w, g, m, v = gi.adam_inputs(n=n)
+    wd_, gd, md, vd = (torch.from_numpy(a.copy()).cuda() for a in (w, g, m, v))
+    for t in (1, 2, 3):
+        dev.adam(wd_, gd, md, vd, t, 3e-4, 0.9, b2, 1e-8, wd=wd, dynamic=dynamic)
+        oracle.adam(w, g, m, v, t, 3e-4, 0.9, b2, 1e-8, wd=wd, variant=int(dynamic))
+    for got, want in ((wd_, w), (md, m), (vd, v)):
+        assert rel_err(down(got), want) <= TOL32
+
+
+def test_adam_golden_and_grad_postprocessing(dev, oracle, golden):
+    """Reference outputs (both Adam variants) and the scale / norm / clip chain of train.m:750-825."""
+    torch = _torch()
+    for name, wd, b2, dyn in (("stories", 0.0, 0.999, False), ("dynamic", 0.1, 0.95, True)):
+        w, g, m, v = (torch.from_numpy(a).cuda() for a in gi.adam_inputs())
+        for t in (1, 2, 3):
+            dev.adam(w, g, m, v, t, 3e-4, 0.9, b2, 1e-8, wd=wd, dynamic=dyn)
+        for arr, key in ((w, "w"), (m, "m"), (v, "v")):
+            s = int(golden[f"adam_{name}_{key}_stride"])
+            assert rel_err(down(arr).reshape(-1)[::s], golden[f"adam_{name}_{key}"]) <= TOL32
+    n = 3000001
+    w, g, m, v = gi.adam_inputs(n=n)
+    g *= 300.0
+    gsc = 1.0 / (10 * 256.0)
+    gd = torch.from_numpy(g).cuda()
+    nsq = dev.grad_norm_sq(gd, gsc)
+    want = oracle.grad_norm_sq(g, gsc)
+    assert abs(float(nsq[0]) - want) <= 1e-5 * want
+    nsq2 = dev.grad_norm_sq(gd, gsc)
+    assert torch.equal(nsq, nsq2)                              # fixed summation order
+    clip = dev.clip_factor(nsq, 1.0)
+    cf = oracle.clip_factor(np.float32(float(nsq[0])), 1.0)
+    assert abs(float(clip[0]) - cf) <= 1e-6 * cf and cf < 1.0
+    wd_, md, vd = (torch.from_numpy(a.copy()).cuda() for a in (w, m, v))
+    dev.adam(wd_, gd, md, vd, 1, 3e-4, 0.9, 0.95, 1e-8, wd=0.1, gscale=gsc, clip=clip)
+    oracle.adam(w, g, m, v, 1, 3e-4, 0.9, 0.95, 1e-8, wd=0.1, variant=1, gscale=gsc, clip=float(clip[0]))
+    assert rel_err(down(wd_), w) <= TOL32 and rel_err(down(md), m) <= TOL32 and rel_err(down(vd), v) <= TOL32
+
+
+# ------------------------------------------------------------------ host-pointer drop-ins
+def test_host_dropins_match_oracle(dev, oracle):
+    from ane_b200 import cpu_ops as ops
+    x, w, dy = gi.cfg1()
+    d, S = 768, 256
+    out = np.empty((d, S), np.float32)
+    ops.rmsnorm(out, x[0], w, d, S)
+    assert rel_err(out, oracle.rmsnorm(x[0], w)) <= TOL32
+    dx = np.zeros((d, S), np.float32)
+    dw = np.full(d, 0.5, np.float32)
+    ops.rmsnorm_bwd(dx, dw, dy[0], x[0], w, d, S)
+    rdx, rdw = oracle.rmsnorm_bwd(dy[0], x[0], w, dw=np.full(d, 0.5, np.float32))
+    assert rel_err(dx, rdx) <= TOL32 and rel_err(dw, rdw) <= TOL32
+
+    wv, g, m, v = gi.adam_inputs(n=24 * 1024)
+    st = ops.AdamState(wv.size)
+    st.m[:], st.v[:] = m, v
+    w2 = wv.copy()
+    ops.adam_update(w2, g, st, 2, 3e-4, 0.9, 0.999, 1e-8)
+    oracle.adam(wv, g, m, v, 2, 3e-4, 0.9, 0.999, 1e-8, variant=0)
+    assert rel_err(w2, wv) <= TOL32 and rel_err(st.m, m) <= TOL32 and rel_err(st.v, v) <= TOL32
+    ops.adam_update(w2, g, st, 3, 3e-4, 0.9, 0.95, 1e-8, wd=0.1)
+    oracle.adam(wv, g, m, v, 3, 3e-4, 0.9, 0.95, 1e-8, wd=0.1, variant=1)
+    assert rel_err(w2, wv) <= TOL32
+
+    V = 9200
+    logits = gi.cfg4_logits(B=1, vocab=V, seq=S)[0]
+    tg = gi.rng(2).integers(0, V, size=S).astype(np.uint16)
+    dl = np.empty_like(logits)
+    loss = ops.cross_entropy_loss(dl, logits, tg, V, S)
+    rl, rdl, _ = oracle.cross_entropy(logits, tg.astype(np.int32))
+    assert abs(loss - rl[0]) <= TOL32 * rl[0] and rel_err(dl, rdl) <= TOL32
+
+    r = gi.rng(3)
+    table = gi.normal(r, (32000, d), 0.02)
+    tok = r.integers(0, 32000, size=S).astype(np.uint16)
+    tok[5:9] = tok[4]
+    xg = np.zeros((d, S), np.float32)
+    ops.embed_lookup(xg, table, tok, d, S)
+    assert np.array_equal(xg, oracle.embed_lookup(table, tok.astype(np.int32)[None])[0][0])
+    dE = np.zeros((32000, d), np.float32)
+    ops.embed_backward(dE, dy[0], tok, d, S)
+    assert np.array_equal(dE, oracle.embed_backward(np.zeros((32000, d), np.float32), dy, tok.astype(np.int32)[None])[0])
+
+    dq = gi.normal(r, (2048, S))
+    want = oracle.rope(dq, 128, base=10000.0, inverse=True)
+    ops.rope_backward_inplace(dq, S, 2048, 128)
+    assert rel_err(dq, want) <= TOL32
+
+    h1, h3, dd, xx, ff = (a[0] for a in gi.cfg2())
+    o = np.empty_like(h1)
+    ops.swiglu(o, h1, h3)
+    assert rel_err(o, oracle.swiglu(h1, h3)) <= TOL32
+    g1, g3 = np.empty_like(h1), np.empty_like(h1)
+    ops.swiglu_bwd(g1, g3, h1, h3, dd)
+    r1, r3 = oracle.swiglu_bwd(h1, h3, dd)
+    assert rel_err(g1, r1) <= TOL32 and rel_err(g3, r3) <= TOL32
+    o = np.empty_like(xx)
+    ops.residual(o, xx, ff, 0.2041241452)
+    assert np.array_equal(o, oracle.residual(xx, ff, np.float32(0.2041241452)))
+
+
+def test_buffers_and_errors(dev):
+    from ane_b200 import lib
+    L = lib.load()
+    assert L.ane_cuda_version() == 100 and L.ane_cuda_device_count() >= 1
+    buf = L.ane_cuda_alloc(1024)
+    assert buf and L.ane_cuda_bufsize(buf) == 1024 and L.ane_cuda_devptr(buf)
+    src = np.arange(256, dtype=np.float32)
+    dst = np.zeros_like(src)
+    assert L.ane_cuda_write(buf, 0, src.ctypes.data, 1024) == 0
+    assert L.ane_cuda_read(buf, 0, dst.ctypes.data, 1024) == 0 and np.array_equal(src, dst)
+    assert L.ane_cuda_write(buf, 512, src.ctypes.data, 1024) == lib.ERR_INVALID      # past the end
+    assert b"outside buffer" in L.ane_cuda_last_error()
+    L.ane_cuda_free(buf)
+    p = L.ane_cuda_host_alloc(4096)
+    assert p
+    L.ane_cuda_host_free(p)
+    # argument errors come back as codes, nothing is launched
+    assert L.ane_cuda_rmsnorm_dev(None, lib.F32, 1, 0, 8, 1, 1, 1, C.c_float(1e-5)) == lib.ERR_INVALID
+    assert L.ane_cuda_rmsnorm_dev(None, 7, 1, 8, 8, 1, 1, 1, C.c_float(1e-5)) == lib.ERR_INVALID
+    assert L.ane_cuda_rmsnorm_dev(None, lib.F32, 1, 8, 8, None, None, None, C.c_float(1e-5)) == lib.ERR_INVALID
+    assert L.ane_cuda_rope_dev(None, lib.F32, 1, 12, 8, 5, 1, 1, C.c_float(1e4), 0, 0) == lib.ERR_INVALID   # C % hd != 0
+    assert L.ane_cuda_adam_dev(None, 8, 1, 1, 1, 1, 0, 0, 0, 0, 0, 0, 1, None, 0) == lib.ERR_INVALID          # t = 0
+    before = lib.launch_count()
+    assert L.ane_cuda_init(0) == 0                                                      # idempotent
+    assert lib.launch_count() == before
+
+
+# ------------------------------------------------------------------ benchmark sizes: size-independent properties
+def test_full_size_properties(dev):
+    """Qwen3 shapes at S = 2048 in bf16: RoPE forward then inverse returns the input (to bf16
+    rounding), the gather is a permutation of table rows (checksum), dlogits columns sum to zero,
+    and the fused kernels agree with the unfused sequence of operators."""
+    torch = _torch()
+    torch.manual_seed(0)
+    B, S, hd = 4, 2048, 128
+    q = torch.randn(B, 16 * hd, S, device="cuda", dtype=torch.bfloat16)
+    w = (1 + 0.02 * torch.randn(hd, device="cuda")).float()
+    y = dev.rope(q, hd, base=1e6)
+    z = dev.rope(y, hd, base=1e6, inverse=True)
+    assert float((z.float() - q.float()).abs().max()) <= 2 * 2 ** -8 * float(q.float().abs().max())
+    fused = dev.qknorm_rope(q, w, hd)
+    unfused = dev.rope(dev.qknorm(q, w, hd), hd, base=1e6)
+    assert float((fused.float() - unfused.float()).abs().max()) <= 2 ** -7 * float(unfused.float().abs().max())
+
+    V, D = 151936, 1024
+    table = (0.02 * torch.randn(V, D, device="cuda")).to(torch.bfloat16)
+    tok = torch.randint(0, V, (B, S), device="cuda", dtype=torch.int32)
+    x = dev.embed_lookup(table, tok)
+    assert torch.equal(x, table[tok.long()].permute(0, 2, 1).contiguous())
+
+    dE = torch.zeros(V, D, device="cuda")
+    dev.embed_backward(dE, x, tok)
+    ref = torch.zeros(V, D, device="cuda", dtype=torch.float64)
+    ref.index_add_(0, tok.long().reshape(-1), x.permute(0, 2, 1).reshape(-1, D).double())
+    assert float((dE.double() - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
+
+    Vs = 151936
+    logits = torch.randn(1, Vs, 256, device="cuda")
+    tg = torch.randint(0, Vs, (1, 256), device="cuda", dtype=torch.int32)
+    loss, dl = dev.cross_entropy(logits, tg)
+    assert float(dl.double().sum(dim=1).abs().max()) <= 1e-6          # sum_v (p - onehot) = 0 per token
+    assert abs(float(loss[0]) - (np.log(Vs) + 0.5)) < 0.2              # E[loss] = log V + sigma^2/2 for N(0,1) logits
