@@ -79,6 +79,7 @@ static int stage_reserve(Stage &s, size_t total) {
 }
 
 static inline size_t pad(size_t b) { return round_up(b, 256); }
+static void pipe_destroy();
 
 }  // namespace ane
 
@@ -133,6 +134,7 @@ void ane_cuda_shutdown(void) {
     Context &c = g_ctx;
     if (!c.inited) return;
     cudaDeviceSynchronize();
+    pipe_destroy();
     if (c.ws) cudaFree(c.ws);
     if (c.stage) cudaFree(c.stage);
     if (c.status) cudaFree(c.status);
@@ -200,58 +202,349 @@ int ane_cuda_poll_status(ane_cuda_status *out, int reset) {
 
 size_t ane_cuda_workspace_bytes(void) { return g_ctx.ws_bytes; }
 
-// ===================================================================== host-pointer drop-ins
-int ane_cuda_rmsnorm(float *out, const float *x, const float *w, int d, int S) {
-    ANE_REQUIRE_INIT();
-    ANE_REQUIRE(out && x && w && d > 0 && S > 0, "%s: bad argument", __func__);
-    const size_t nb = (size_t)d * S * 4;
-    Stage s;
-    TRY(stage_reserve(s, 2 * pad(nb) + pad((size_t)d * 4)));
-    float *dx_ = s.take<float>(nb), *dout = s.take<float>(nb), *dw_ = s.take<float>((size_t)d * 4);
-    H2D(dx_, x, nb);
-    H2D(dw_, w, (size_t)d * 4);
-    TRY(ane_cuda_rmsnorm_dev(0, ANE_F32, 1, d, S, dout, dx_, dw_, 1e-5f));   // eps literal of stories_cpu_ops.h:13
-    D2H(out, dout, nb);
-    SYNC0();
+}  // extern "C"
+
+// ===================================================================== host-buffer entry points
+// Generic form: activations of any supported dtype in HOST memory, batched [B][C][S].  The batch
+// is cut into chunks that flow through a three-stream pipeline (host->device copy, kernel,
+// device->host copy) over two staging slots, so PCIe traffic in both directions overlaps the
+// kernels.  Page-locked host memory (ane_cuda_host_alloc) makes the copies truly asynchronous;
+// pageable memory works but serialises them.
+namespace ane {
+
+struct Pipe {
+    bool ready = false;
+    cudaStream_t s_in = nullptr, s_k = nullptr, s_out = nullptr;
+    cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_k[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
+};
+static Pipe g_pipe;
+
+static int pipe_init() {
+    Pipe &p = g_pipe;
+    if (p.ready) return ANE_CUDA_OK;
+    ANE_CUDA_TRY(cudaStreamCreateWithFlags(&p.s_in, cudaStreamNonBlocking));
+    ANE_CUDA_TRY(cudaStreamCreateWithFlags(&p.s_k, cudaStreamNonBlocking));
+    ANE_CUDA_TRY(cudaStreamCreateWithFlags(&p.s_out, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; i++) {
+        ANE_CUDA_TRY(cudaEventCreateWithFlags(&p.ev_in[i], cudaEventDisableTiming));
+        ANE_CUDA_TRY(cudaEventCreateWithFlags(&p.ev_k[i], cudaEventDisableTiming));
+        ANE_CUDA_TRY(cudaEventCreateWithFlags(&p.ev_out[i], cudaEventDisableTiming));
+    }
+    p.ready = true;
     return ANE_CUDA_OK;
 }
 
-int ane_cuda_rmsnorm_bwd(float *dx, float *dw, const float *dy, const float *x, const float *w, int d, int S) {
-    ANE_REQUIRE_INIT();
-    ANE_REQUIRE(dx && dw && dy && x && w && d > 0 && S > 0, "%s: bad argument", __func__);
-    const size_t nb = (size_t)d * S * 4, wb = (size_t)d * 4;
-    Stage s;
-    TRY(stage_reserve(s, 3 * pad(nb) + 2 * pad(wb)));
-    float *ddx = s.take<float>(nb), *ddy = s.take<float>(nb), *dx_ = s.take<float>(nb);
-    float *dw_ = s.take<float>(wb), *ddw = s.take<float>(wb);
-    H2D(ddy, dy, nb);
-    H2D(dx_, x, nb);
-    H2D(dw_, w, wb);
-    H2D(ddw, dw, wb);                                                           // dw is accumulated into (:50)
-    TRY(ane_cuda_rmsnorm_bwd_dev(0, ANE_F32, 1, d, S, ddx, ddw, ddy, dx_, dw_, nullptr, 1e-5f, ANE_NORM_BWD_REFERENCE));
-    D2H(dx, ddx, nb);
-    D2H(dw, ddw, wb);
-    SYNC0();
+static void pipe_destroy() {
+    Pipe &p = g_pipe;
+    if (!p.ready) return;
+    cudaStreamDestroy(p.s_in); cudaStreamDestroy(p.s_k); cudaStreamDestroy(p.s_out);
+    for (int i = 0; i < 2; i++) { cudaEventDestroy(p.ev_in[i]); cudaEventDestroy(p.ev_k[i]); cudaEventDestroy(p.ev_out[i]); }
+    p = Pipe();
+}
+
+constexpr int MAX_T = 4;
+struct HostTensors {
+    int n_in = 0, n_out = 0;
+    const void *in[MAX_T] = {};
+    size_t in_item[MAX_T] = {};     // bytes per item
+    void *out[MAX_T] = {};
+    size_t out_item[MAX_T] = {};
+};
+
+// launch(stream, n_items, dev_in[], dev_out[]) enqueues the kernel(s) for one chunk.
+template <class Launch>
+static int run_pipelined(size_t items, const HostTensors &ht, size_t extra_stage_bytes, char **extra_stage, Launch launch) {
+    TRY(pipe_init());
+    Pipe &p = g_pipe;
+    size_t per_item = 0;
+    for (int i = 0; i < ht.n_in; i++) per_item += ht.in_item[i];
+    for (int i = 0; i < ht.n_out; i++) per_item += ht.out_item[i];
+    // chunks of about 16 MiB of traffic, at least one item
+    size_t chunk = per_item ? ((size_t)16 << 20) / per_item : items;
+    if (chunk < 1) chunk = 1;
+    if (chunk > items) chunk = items;
+    size_t slot_bytes = 0;
+    for (int i = 0; i < ht.n_in; i++) slot_bytes += pad(ht.in_item[i] * chunk);
+    for (int i = 0; i < ht.n_out; i++) slot_bytes += pad(ht.out_item[i] * chunk);
+    Stage st;
+    TRY(stage_reserve(st, 2 * slot_bytes + pad(extra_stage_bytes)));
+    char *din[2][MAX_T], *dout[2][MAX_T];
+    for (int s = 0; s < 2; s++) {
+        for (int i = 0; i < ht.n_in; i++) din[s][i] = st.take<char>(ht.in_item[i] * chunk);
+        for (int i = 0; i < ht.n_out; i++) dout[s][i] = st.take<char>(ht.out_item[i] * chunk);
+    }
+    if (extra_stage) *extra_stage = st.take<char>(extra_stage_bytes);
+    // work queued earlier on the default stream (e.g. weight uploads by the caller of this helper) is ordered first
+    ANE_CUDA_TRY(cudaStreamSynchronize(0));
+    size_t done = 0;
+    for (size_t c = 0; done < items; c++) {
+        const int s = (int)(c & 1);
+        const size_t n = items - done < chunk ? items - done : chunk;
+        if (c >= 2) ANE_CUDA_TRY(cudaStreamWaitEvent(p.s_in, p.ev_k[s], 0));       // slot inputs consumed
+        for (int i = 0; i < ht.n_in; i++)
+            ANE_CUDA_TRY(cudaMemcpyAsync(din[s][i], static_cast<const char *>(ht.in[i]) + done * ht.in_item[i], n * ht.in_item[i],
+                                         cudaMemcpyHostToDevice, p.s_in));
+        ANE_CUDA_TRY(cudaEventRecord(p.ev_in[s], p.s_in));
+        ANE_CUDA_TRY(cudaStreamWaitEvent(p.s_k, p.ev_in[s], 0));
+        if (c >= 2) ANE_CUDA_TRY(cudaStreamWaitEvent(p.s_k, p.ev_out[s], 0));      // slot outputs drained
+        void *vin[MAX_T], *vout[MAX_T];
+        for (int i = 0; i < ht.n_in; i++) vin[i] = din[s][i];
+        for (int i = 0; i < ht.n_out; i++) vout[i] = dout[s][i];
+        TRY(launch(p.s_k, n, vin, vout));
+        ANE_CUDA_TRY(cudaEventRecord(p.ev_k[s], p.s_k));
+        ANE_CUDA_TRY(cudaStreamWaitEvent(p.s_out, p.ev_k[s], 0));
+        for (int i = 0; i < ht.n_out; i++)
+            ANE_CUDA_TRY(cudaMemcpyAsync(static_cast<char *>(ht.out[i]) + done * ht.out_item[i], dout[s][i], n * ht.out_item[i],
+                                         cudaMemcpyDeviceToHost, p.s_out));
+        ANE_CUDA_TRY(cudaEventRecord(p.ev_out[s], p.s_out));
+        done += n;
+    }
+    ANE_CUDA_TRY(cudaStreamSynchronize(p.s_k));
+    ANE_CUDA_TRY(cudaStreamSynchronize(p.s_out));
     return ANE_CUDA_OK;
+}
+
+static int check_host_shape(const char *fn, ane_dtype dtype, long long B, long long C, long long S) {
+    if (!dtype_ok(dtype)) return fail(ANE_CUDA_ERR_INVALID, "%s: bad dtype %d", fn, (int)dtype);
+    if (B < 1 || C < 1 || S < 1) return fail(ANE_CUDA_ERR_INVALID, "%s: B, C, S must be positive", fn);
+    return ANE_CUDA_OK;
+}
+
+}  // namespace ane
+
+extern "C" {
+
+int ane_cuda_rmsnorm_host(ane_dtype dtype, int B, int C, int S, void *out, const void *x, const float *w, float eps) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(out && x && w, "%s: null pointer", __func__);
+    TRY(check_host_shape(__func__, dtype, B, C, S));
+    const size_t item = (size_t)C * S * dtype_size(dtype);
+    HostTensors ht;
+    ht.n_in = 1; ht.in[0] = x; ht.in_item[0] = item;
+    ht.n_out = 1; ht.out[0] = out; ht.out_item[0] = item;
+    char *ex = nullptr;
+    // the weight upload happens inside the first launch closure's stream order
+    bool first = true;
+    return run_pipelined((size_t)B, ht, (size_t)C * 4, &ex, [&](cudaStream_t st, size_t n, void **di, void **dout_) -> int {
+        if (first) { ANE_CUDA_TRY(cudaMemcpyAsync(ex, w, (size_t)C * 4, cudaMemcpyHostToDevice, st)); first = false; }
+        return ane_cuda_rmsnorm_dev(st, dtype, (int)n, C, S, dout_[0], di[0], reinterpret_cast<float *>(ex), eps);
+    });
+}
+
+int ane_cuda_rmsnorm_bwd_host(ane_dtype dtype, int B, int C, int S, void *dx, float *dw, const void *dy, const void *x,
+                              const float *w, const void *add, float eps, unsigned flags) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(dx && dw && dy && x && w, "%s: null pointer", __func__);
+    TRY(check_host_shape(__func__, dtype, B, C, S));
+    const size_t item = (size_t)C * S * dtype_size(dtype);
+    HostTensors ht;
+    ht.n_in = add ? 3 : 2;
+    ht.in[0] = dy; ht.in[1] = x; ht.in[2] = add;
+    ht.in_item[0] = ht.in_item[1] = ht.in_item[2] = item;
+    ht.n_out = 1; ht.out[0] = dx; ht.out_item[0] = item;
+    char *ex = nullptr;
+    bool first = true;
+    const size_t wb = pad((size_t)C * 4);
+    cudaStream_t kst = nullptr;
+    int rc = run_pipelined((size_t)B, ht, 2 * wb, &ex, [&](cudaStream_t st, size_t n, void **di, void **dout_) -> int {
+        float *dw_w = reinterpret_cast<float *>(ex), *dw_dw = reinterpret_cast<float *>(ex + wb);
+        if (first) {
+            ANE_CUDA_TRY(cudaMemcpyAsync(dw_w, w, (size_t)C * 4, cudaMemcpyHostToDevice, st));
+            ANE_CUDA_TRY(cudaMemcpyAsync(dw_dw, dw, (size_t)C * 4, cudaMemcpyHostToDevice, st));   // accumulated into
+            first = false;
+            kst = st;
+        }
+        return ane_cuda_rmsnorm_bwd_dev(st, dtype, (int)n, C, S, dout_[0], dw_dw, di[0], di[1], dw_w, add ? di[2] : nullptr, eps, flags);
+    });
+    if (rc != ANE_CUDA_OK) return rc;
+    ANE_CUDA_TRY(cudaMemcpyAsync(dw, ex + wb, (size_t)C * 4, cudaMemcpyDeviceToHost, kst));
+    ANE_CUDA_TRY(cudaStreamSynchronize(kst));
+    return ANE_CUDA_OK;
+}
+
+int ane_cuda_residual_rmsnorm_host(ane_dtype dtype, int B, int C, int S, void *x2, void *x2norm, const void *x,
+                                   const void *f, const float *w, float alpha, float eps) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(x2 && x2norm && x && f && w, "%s: null pointer", __func__);
+    TRY(check_host_shape(__func__, dtype, B, C, S));
+    const size_t item = (size_t)C * S * dtype_size(dtype);
+    HostTensors ht;
+    ht.n_in = 2; ht.in[0] = x; ht.in[1] = f; ht.in_item[0] = ht.in_item[1] = item;
+    ht.n_out = 2; ht.out[0] = x2; ht.out[1] = x2norm; ht.out_item[0] = ht.out_item[1] = item;
+    char *ex = nullptr;
+    bool first = true;
+    return run_pipelined((size_t)B, ht, (size_t)C * 4, &ex, [&](cudaStream_t st, size_t n, void **di, void **dout_) -> int {
+        if (first) { ANE_CUDA_TRY(cudaMemcpyAsync(ex, w, (size_t)C * 4, cudaMemcpyHostToDevice, st)); first = false; }
+        return ane_cuda_residual_rmsnorm_dev(st, dtype, (int)n, C, S, dout_[0], dout_[1], di[0], di[1], reinterpret_cast<float *>(ex), alpha, eps);
+    });
+}
+
+// Flat operators: an item is a block of 64 Ki elements (the last block may be short).
+static int flat_host(ane_dtype dtype, size_t n, int n_in, const void *const *in, int n_out, void *const *out, int op, float alpha) {
+    const size_t esz = dtype_size(dtype);
+    const size_t blk = (size_t)64 << 10;
+    const size_t full = n / blk, tail = n % blk;
+    for (int pass = 0; pass < 2; pass++) {
+        const size_t items = pass == 0 ? full : (tail ? 1 : 0);
+        if (!items) continue;
+        const size_t item_elems = pass == 0 ? blk : tail;
+        const size_t off = pass == 0 ? 0 : full * blk * esz;
+        HostTensors ht;
+        ht.n_in = n_in; ht.n_out = n_out;
+        for (int i = 0; i < n_in; i++) { ht.in[i] = static_cast<const char *>(in[i]) + off; ht.in_item[i] = item_elems * esz; }
+        for (int i = 0; i < n_out; i++) { ht.out[i] = static_cast<char *>(out[i]) + off; ht.out_item[i] = item_elems * esz; }
+        TRY(run_pipelined(items, ht, 0, nullptr, [&](cudaStream_t st, size_t k, void **di, void **dout_) -> int {
+            const size_t ne = k * item_elems;
+            switch (op) {
+                case 0: return ane_cuda_residual_dev(st, dtype, ne, dout_[0], di[0], di[1], alpha);
+                case 1: return ane_cuda_swiglu_dev(st, dtype, ne, dout_[0], di[0], di[1]);
+                default: return ane_cuda_swiglu_bwd_dev(st, dtype, ne, dout_[0], dout_[1], di[0], di[1], di[2]);
+            }
+        }));
+    }
+    return ANE_CUDA_OK;
+}
+
+int ane_cuda_residual_host(ane_dtype dtype, size_t n, void *out, const void *x, const void *f, float alpha) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(out && x && f && dtype_ok(dtype), "%s: bad argument", __func__);
+    if (n == 0) return ANE_CUDA_OK;
+    const void *in[2] = {x, f};
+    void *o[1] = {out};
+    return flat_host(dtype, n, 2, in, 1, o, 0, alpha);
+}
+
+int ane_cuda_swiglu_host(ane_dtype dtype, size_t n, void *out, const void *h1, const void *h3) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(out && h1 && h3 && dtype_ok(dtype), "%s: bad argument", __func__);
+    if (n == 0) return ANE_CUDA_OK;
+    const void *in[2] = {h1, h3};
+    void *o[1] = {out};
+    return flat_host(dtype, n, 2, in, 1, o, 1, 0.0f);
+}
+
+int ane_cuda_swiglu_bwd_host(ane_dtype dtype, size_t n, void *dh1, void *dh3, const void *h1, const void *h3, const void *dsilu) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(dh1 && dh3 && h1 && h3 && dsilu && dtype_ok(dtype), "%s: bad argument", __func__);
+    if (n == 0) return ANE_CUDA_OK;
+    const void *in[3] = {h1, h3, dsilu};
+    void *o[2] = {dh1, dh3};
+    return flat_host(dtype, n, 3, in, 2, o, 2, 0.0f);
+}
+
+int ane_cuda_rope_host(ane_dtype dtype, int B, int C, int S, int hd, void *out, const void *x, float base, int pos0, unsigned flags) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(out && x, "%s: null pointer", __func__);
+    TRY(check_host_shape(__func__, dtype, B, C, S));
+    const size_t item = (size_t)C * S * dtype_size(dtype);
+    HostTensors ht;
+    ht.n_in = 1; ht.in[0] = x; ht.in_item[0] = item;
+    ht.n_out = 1; ht.out[0] = out; ht.out_item[0] = item;
+    return run_pipelined((size_t)B, ht, 0, nullptr, [&](cudaStream_t st, size_t n, void **di, void **dout_) -> int {
+        return ane_cuda_rope_dev(st, dtype, (int)n, C, S, hd, dout_[0], di[0], base, pos0, flags);
+    });
+}
+
+int ane_cuda_qknorm_rope_host(ane_dtype dtype, int B, int heads, int hd, int S, void *out, const void *x, const float *w,
+                              float eps, float base, int pos0) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(out && x && w, "%s: null pointer", __func__);
+    TRY(check_host_shape(__func__, dtype, B, (long long)heads * hd, S));
+    const size_t item = (size_t)heads * hd * S * dtype_size(dtype);
+    HostTensors ht;
+    ht.n_in = 1; ht.in[0] = x; ht.in_item[0] = item;
+    ht.n_out = 1; ht.out[0] = out; ht.out_item[0] = item;
+    char *ex = nullptr;
+    bool first = true;
+    return run_pipelined((size_t)B, ht, (size_t)hd * 4, &ex, [&](cudaStream_t st, size_t n, void **di, void **dout_) -> int {
+        if (first) { ANE_CUDA_TRY(cudaMemcpyAsync(ex, w, (size_t)hd * 4, cudaMemcpyHostToDevice, st)); first = false; }
+        return ane_cuda_qknorm_rope_dev(st, dtype, (int)n, heads, hd, S, dout_[0], di[0], reinterpret_cast<float *>(ex), eps, base, pos0);
+    });
+}
+
+int ane_cuda_rope_qknorm_bwd_host(ane_dtype dtype, int B, int heads, int hd, int S, void *dx, float *dw, const void *dy,
+                                  const void *x, const float *w, float eps, float base, int pos0, unsigned flags) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(dx && dw && dy && x && w, "%s: null pointer", __func__);
+    TRY(check_host_shape(__func__, dtype, B, (long long)heads * hd, S));
+    const size_t item = (size_t)heads * hd * S * dtype_size(dtype);
+    HostTensors ht;
+    ht.n_in = 2; ht.in[0] = dy; ht.in[1] = x; ht.in_item[0] = ht.in_item[1] = item;
+    ht.n_out = 1; ht.out[0] = dx; ht.out_item[0] = item;
+    char *ex = nullptr;
+    bool first = true;
+    const size_t wb = pad((size_t)hd * 4);
+    cudaStream_t kst = nullptr;
+    int rc = run_pipelined((size_t)B, ht, 2 * wb, &ex, [&](cudaStream_t st, size_t n, void **di, void **dout_) -> int {
+        float *dw_w = reinterpret_cast<float *>(ex), *dw_dw = reinterpret_cast<float *>(ex + wb);
+        if (first) {
+            ANE_CUDA_TRY(cudaMemcpyAsync(dw_w, w, (size_t)hd * 4, cudaMemcpyHostToDevice, st));
+            ANE_CUDA_TRY(cudaMemcpyAsync(dw_dw, dw, (size_t)hd * 4, cudaMemcpyHostToDevice, st));
+            first = false;
+            kst = st;
+        }
+        return ane_cuda_rope_qknorm_bwd_dev(st, dtype, (int)n, heads, hd, S, dout_[0], dw_dw, di[0], di[1], dw_w, eps, base, pos0, flags);
+    });
+    if (rc != ANE_CUDA_OK) return rc;
+    ANE_CUDA_TRY(cudaMemcpyAsync(dw, ex + wb, (size_t)hd * 4, cudaMemcpyDeviceToHost, kst));
+    ANE_CUDA_TRY(cudaStreamSynchronize(kst));
+    return ANE_CUDA_OK;
+}
+
+// ===================================================================== reference-signature drop-ins
+// fp32, one sequence, the literals of the reference (eps 1e-5, base 10000).
+int ane_cuda_rmsnorm(float *out, const float *x, const float *w, int d, int S) {
+    return ane_cuda_rmsnorm_host(ANE_F32, 1, d, S, out, x, w, 1e-5f);                 // eps literal of stories_cpu_ops.h:13
+}
+
+int ane_cuda_rmsnorm_bwd(float *dx, float *dw, const float *dy, const float *x, const float *w, int d, int S) {
+    return ane_cuda_rmsnorm_bwd_host(ANE_F32, 1, d, S, dx, dw, dy, x, w, nullptr, 1e-5f, ANE_NORM_BWD_REFERENCE);
+}
+
+int ane_cuda_rope_backward_inplace(float *dx, int seq, int dim, int hd) {
+    return ane_cuda_rope_host(ANE_F32, 1, dim, seq, hd, dx, dx, 10000.0f, 0, ANE_ROPE_INVERSE);   // base literal of cpu_ops.h:172
+}
+
+int ane_cuda_residual(float *out, const float *x, const float *f, float alpha, size_t n) {
+    return ane_cuda_residual_host(ANE_F32, n, out, x, f, alpha);
+}
+
+int ane_cuda_swiglu(float *out, const float *h1, const float *h3, size_t n) {
+    return ane_cuda_swiglu_host(ANE_F32, n, out, h1, h3);
+}
+
+int ane_cuda_swiglu_bwd(float *dh1, float *dh3, const float *h1, const float *h3, const float *dsilu, size_t n) {
+    return ane_cuda_swiglu_bwd_host(ANE_F32, n, dh1, dh3, h1, h3, dsilu);
 }
 
 static int adam_host(float *w, const float *g, AdamState *st, int t, float lr, float b1, float b2, float eps, float wd, unsigned variant) {
     ANE_REQUIRE_INIT();
     ANE_REQUIRE(w && g && st && st->m && st->v, "adam_update: null pointer");
-    const size_t n = st->n, nb = n * 4;
+    const size_t n = st->n;
     if (n == 0) return ANE_CUDA_OK;
-    Stage s;
-    TRY(stage_reserve(s, 4 * pad(nb)));
-    float *dw_ = s.take<float>(nb), *dg = s.take<float>(nb), *dm = s.take<float>(nb), *dv = s.take<float>(nb);
-    H2D(dw_, w, nb);
-    H2D(dg, g, nb);
-    H2D(dm, st->m, nb);
-    H2D(dv, st->v, nb);
-    TRY(ane_cuda_adam_dev(0, n, dw_, dg, dm, dv, t, lr, b1, b2, eps, wd, 1.0f, nullptr, variant));
-    D2H(w, dw_, nb);
-    D2H(st->m, dm, nb);
-    D2H(st->v, dv, nb);
-    SYNC0();
+    const size_t blk = (size_t)64 << 10;
+    const size_t full = n / blk, tail = n % blk;
+    for (int pass = 0; pass < 2; pass++) {
+        const size_t items = pass == 0 ? full : (tail ? 1 : 0);
+        if (!items) continue;
+        const size_t ie = pass == 0 ? blk : tail;
+        const size_t off = pass == 0 ? 0 : full * blk;
+        HostTensors ht;
+        ht.n_in = 4; ht.n_out = 3;
+        ht.in[0] = w + off; ht.in[1] = g + off; ht.in[2] = st->m + off; ht.in[3] = st->v + off;
+        ht.out[0] = w + off; ht.out[1] = st->m + off; ht.out[2] = st->v + off;
+        for (int i = 0; i < 4; i++) ht.in_item[i] = ie * 4;
+        for (int i = 0; i < 3; i++) ht.out_item[i] = ie * 4;
+        TRY(run_pipelined(items, ht, 0, nullptr, [&](cudaStream_t s, size_t k, void **di, void **dout_) -> int {
+            const size_t ne = k * ie;
+            // update in place in the input slot, then copy the three results to the output slot
+            TRY(ane_cuda_adam_dev(s, ne, (float *)di[0], (const float *)di[1], (float *)di[2], (float *)di[3], t, lr, b1, b2, eps, wd, 1.0f, nullptr, variant));
+            ANE_CUDA_TRY(cudaMemcpyAsync(dout_[0], di[0], ne * 4, cudaMemcpyDeviceToDevice, s));
+            ANE_CUDA_TRY(cudaMemcpyAsync(dout_[1], di[2], ne * 4, cudaMemcpyDeviceToDevice, s));
+            ANE_CUDA_TRY(cudaMemcpyAsync(dout_[2], di[3], ne * 4, cudaMemcpyDeviceToDevice, s));
+            return ANE_CUDA_OK;
+        }));
+    }
     return ANE_CUDA_OK;
 }
 
@@ -311,67 +604,6 @@ int ane_cuda_embed_backward(float *d_embed, const float *dx, const uint16_t *tok
     H2D(dt, tokens, (size_t)seq * 2);
     TRY(ane_cuda_embed_backward_dev(0, ANE_F32, ANE_ID_U16, 1, dim, seq, de, dx_, dt, vocab));
     D2H(d_embed, de, eb);
-    SYNC0();
-    return ANE_CUDA_OK;
-}
-
-int ane_cuda_rope_backward_inplace(float *dx, int seq, int dim, int hd) {
-    ANE_REQUIRE_INIT();
-    ANE_REQUIRE(dx && seq > 0 && dim > 0 && hd > 0, "%s: bad argument", __func__);
-    const size_t nb = (size_t)dim * seq * 4;
-    Stage s;
-    TRY(stage_reserve(s, pad(nb)));
-    float *d = s.take<float>(nb);
-    H2D(d, dx, nb);
-    TRY(ane_cuda_rope_dev(0, ANE_F32, 1, dim, seq, hd, d, d, 10000.0f, 0, ANE_ROPE_INVERSE));   // base literal of cpu_ops.h:172
-    D2H(dx, d, nb);
-    SYNC0();
-    return ANE_CUDA_OK;
-}
-
-int ane_cuda_residual(float *out, const float *x, const float *f, float alpha, size_t n) {
-    ANE_REQUIRE_INIT();
-    ANE_REQUIRE(out && x && f, "%s: null pointer", __func__);
-    if (n == 0) return ANE_CUDA_OK;
-    Stage s;
-    TRY(stage_reserve(s, 2 * pad(n * 4)));
-    float *a = s.take<float>(n * 4), *b = s.take<float>(n * 4);
-    H2D(a, x, n * 4);
-    H2D(b, f, n * 4);
-    TRY(ane_cuda_residual_dev(0, ANE_F32, n, a, a, b, alpha));
-    D2H(out, a, n * 4);
-    SYNC0();
-    return ANE_CUDA_OK;
-}
-
-int ane_cuda_swiglu(float *out, const float *h1, const float *h3, size_t n) {
-    ANE_REQUIRE_INIT();
-    ANE_REQUIRE(out && h1 && h3, "%s: null pointer", __func__);
-    if (n == 0) return ANE_CUDA_OK;
-    Stage s;
-    TRY(stage_reserve(s, 2 * pad(n * 4)));
-    float *a = s.take<float>(n * 4), *b = s.take<float>(n * 4);
-    H2D(a, h1, n * 4);
-    H2D(b, h3, n * 4);
-    TRY(ane_cuda_swiglu_dev(0, ANE_F32, n, a, a, b));
-    D2H(out, a, n * 4);
-    SYNC0();
-    return ANE_CUDA_OK;
-}
-
-int ane_cuda_swiglu_bwd(float *dh1, float *dh3, const float *h1, const float *h3, const float *dsilu, size_t n) {
-    ANE_REQUIRE_INIT();
-    ANE_REQUIRE(dh1 && dh3 && h1 && h3 && dsilu, "%s: null pointer", __func__);
-    if (n == 0) return ANE_CUDA_OK;
-    Stage s;
-    TRY(stage_reserve(s, 3 * pad(n * 4)));
-    float *a = s.take<float>(n * 4), *b = s.take<float>(n * 4), *c = s.take<float>(n * 4);
-    H2D(a, h1, n * 4);
-    H2D(b, h3, n * 4);
-    H2D(c, dsilu, n * 4);
-    TRY(ane_cuda_swiglu_bwd_dev(0, ANE_F32, n, a, b, a, b, c));   // dh1 over h1, dh3 over h3
-    D2H(dh1, a, n * 4);
-    D2H(dh3, b, n * 4);
     SYNC0();
     return ANE_CUDA_OK;
 }

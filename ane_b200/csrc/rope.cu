@@ -295,6 +295,137 @@ __global__ void qk_dw_finalize_kernel(float *__restrict__ dw, const float *__res
     dw[c] += s;
 }
 
+// ------------------------------------------------------------------ fused kernels, any head width
+// One thread per (sequence, head, token), scalar loads that coalesce along S.  Used for head
+// widths and alignments the register-resident kernels above do not cover; same arithmetic, so a
+// result does not depend on which path ran (a single rounding to the storage type at the end).
+constexpr int QKG_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(QKG_THREADS)
+qk_rope_fwd_generic_kernel(T *__restrict__ out, const T *__restrict__ x, const float *__restrict__ w, int hd, int S,
+                           long long total, float eps, int pos0, const __grid_constant__ RopeFreq freq) {
+    const long long idx = (long long)blockIdx.x * QKG_THREADS + threadIdx.x;
+    if (idx >= total) return;
+    const int t = (int)(idx % S);
+    const size_t base = (size_t)(idx / S) * hd * S + t;
+    float ss = 0.0f;
+    for (int c = 0; c < hd; c++) { const float v = Elt<T>::to_f(x[base + (size_t)c * S]); ss += v * v; }
+    const float rr = 1.0f / sqrtf(__fadd_rn(__fmul_rn(ss, 1.0f / (float)hd), eps));
+    for (int i = 0; i < hd / 2; i++) {
+        const float theta = (float)(pos0 + t) * freq.f[i];
+        const float cs = cosf(theta), sn = sinf(theta);
+        const float a = (Elt<T>::to_f(x[base + (size_t)(2 * i) * S]) * rr) * __ldg(w + 2 * i);
+        const float b = (Elt<T>::to_f(x[base + (size_t)(2 * i + 1) * S]) * rr) * __ldg(w + 2 * i + 1);
+        out[base + (size_t)(2 * i) * S] = Elt<T>::from_f(__fsub_rn(__fmul_rn(a, cs), __fmul_rn(b, sn)));
+        out[base + (size_t)(2 * i + 1) * S] = Elt<T>::from_f(__fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, cs)));
+    }
+}
+
+__device__ __forceinline__ float block_sum_128(float v, float *sh) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    return (sh[0] + sh[1]) + (sh[2] + sh[3]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(QKG_THREADS)
+qk_rope_bwd_generic_kernel(T *__restrict__ dx, float *__restrict__ partial, const T *__restrict__ dy,
+                           const T *__restrict__ x, const float *__restrict__ w, int hd, int S, long long total,
+                           float eps, int pos0, unsigned flags, const __grid_constant__ RopeFreq freq) {
+    __shared__ float dwacc[256];
+    __shared__ float sh[4];
+    const bool exact = (flags & ANE_NORM_BWD_EXACT) != 0;
+    const float invd = 1.0f / (float)hd;
+    for (int c = threadIdx.x; c < hd; c += QKG_THREADS) dwacc[c] = 0.0f;
+    __syncthreads();
+    for (long long blk = (long long)blockIdx.x * QKG_THREADS; blk < total; blk += (long long)gridDim.x * QKG_THREADS) {
+        const long long idx = blk + threadIdx.x;
+        const bool valid = idx < total;
+        const int t = valid ? (int)(idx % S) : 0;
+        const size_t base = valid ? (size_t)(idx / S) * hd * S + t : 0;
+        float ss = 0.0f, dot = 0.0f;
+        if (valid) {
+            for (int i = 0; i < hd / 2; i++) {
+                const float theta = (float)(pos0 + t) * freq.f[i];
+                const float cs = cosf(theta), sn = sinf(theta);
+                const float a = Elt<T>::to_f(dy[base + (size_t)(2 * i) * S]), b = Elt<T>::to_f(dy[base + (size_t)(2 * i + 1) * S]);
+                const float g0 = __fadd_rn(__fmul_rn(a, cs), __fmul_rn(b, sn));
+                const float g1 = __fadd_rn(__fmul_rn(-a, sn), __fmul_rn(b, cs));
+                const float x0 = Elt<T>::to_f(x[base + (size_t)(2 * i) * S]), x1 = Elt<T>::to_f(x[base + (size_t)(2 * i + 1) * S]);
+                ss += x0 * x0; ss += x1 * x1;
+                dot += (g0 * x0) * __ldg(w + 2 * i);
+                dot += (g1 * x1) * __ldg(w + 2 * i + 1);
+            }
+        }
+        const float rr = 1.0f / sqrtf(__fadd_rn(__fmul_rn(ss, invd), eps));
+        float r2 = rr * rr;
+        r2 = r2 * invd;
+        const float coef = dot * r2;
+        for (int i = 0; i < hd / 2; i++) {
+            float dwp[2] = {0.0f, 0.0f};
+            if (valid) {
+                const float theta = (float)(pos0 + t) * freq.f[i];
+                const float cs = cosf(theta), sn = sinf(theta);
+                const float a = Elt<T>::to_f(dy[base + (size_t)(2 * i) * S]), b = Elt<T>::to_f(dy[base + (size_t)(2 * i + 1) * S]);
+                float g[2];
+                g[0] = __fadd_rn(__fmul_rn(a, cs), __fmul_rn(b, sn));
+                g[1] = __fadd_rn(__fmul_rn(-a, sn), __fmul_rn(b, cs));
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    const int c = 2 * i + k;
+                    const float xv = Elt<T>::to_f(x[base + (size_t)c * S]);
+                    const float wc = __ldg(w + c);
+                    float o;
+                    if (exact) {
+                        o = __fmul_rn(__fsub_rn(__fmul_rn(g[k], wc), __fmul_rn(xv, coef)), rr);
+                    } else {
+                        float tmp = __fmul_rn(xv, coef);
+                        tmp = __fsub_rn(g[k], tmp);
+                        tmp = tmp * rr;
+                        o = tmp * wc;
+                    }
+                    dx[base + (size_t)c * S] = Elt<T>::from_f(o);
+                    dwp[k] = (g[k] * xv) * rr;
+                }
+            }
+            const float s0 = block_sum_128(dwp[0], sh);
+            const float s1 = block_sum_128(dwp[1], sh);
+            if (threadIdx.x == 0) { dwacc[2 * i] += s0; dwacc[2 * i + 1] += s1; }
+        }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < hd; c += QKG_THREADS) partial[(size_t)blockIdx.x * hd + c] = dwacc[c];
+}
+
+template <typename T>
+static int launch_qk_rope_fwd_generic(cudaStream_t st, int B, int heads, int hd, int S, void *out, const void *x,
+                                      const float *w, float eps, int pos0, const RopeFreq &fq) {
+    const long long total = (long long)B * heads * S;
+    const long long blocks = (total + QKG_THREADS - 1) / QKG_THREADS;
+    qk_rope_fwd_generic_kernel<T><<<(unsigned)blocks, QKG_THREADS, 0, st>>>((T *)out, (const T *)x, w, hd, S, total, eps, pos0, fq);
+    ANE_LAUNCH_OK(1);
+    return ANE_CUDA_OK;
+}
+
+template <typename T>
+static int launch_qk_rope_bwd_generic(cudaStream_t st, int B, int heads, int hd, int S, void *dx, float *dw, const void *dy,
+                                      const void *x, const float *w, float eps, int pos0, unsigned flags, const RopeFreq &fq) {
+    const long long total = (long long)B * heads * S;
+    long long blocks = (total + QKG_THREADS - 1) / QKG_THREADS;
+    const long long cap = (long long)ctx().sm_count * 8;
+    if (blocks > cap) blocks = cap;
+    float *partial = static_cast<float *>(workspace((size_t)blocks * hd * sizeof(float)));
+    if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rope_qknorm_bwd: no scratch");
+    qk_rope_bwd_generic_kernel<T><<<(unsigned)blocks, QKG_THREADS, 0, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, hd, S,
+                                                                           total, eps, pos0, flags, fq);
+    qk_dw_finalize_kernel<<<(hd + 127) / 128, 128, 0, st>>>(dw, partial, (int)blocks, hd);
+    ANE_LAUNCH_OK(2);
+    return ANE_CUDA_OK;
+}
+
 static int fill_freq(RopeFreq &fq, int hd, float base) {
     if (hd < 2 || (hd & 1) || hd > 256) return fail(ANE_CUDA_ERR_UNSUPPORTED, "rope: head dim %d must be even and <= 256", hd);
     // freq = 1/powf(base, 2*i/hd) with the host libm                    cpu_ops.h:172
@@ -446,9 +577,8 @@ int ane_cuda_qknorm_rope_dev(void *stream, ane_dtype dtype, int B, int heads, in
     if (int rc = fill_freq(fq, hd, base)) return rc;
     ANE_DISPATCH_DTYPE(dtype, T,
         if (qk_fast_ok<T, true>(hd, S, out, x, nullptr)) return (launch_qk_fwd<T, true>(st, B, heads, hd, S, out, x, w, eps, pos0, fq)));
-    // other head widths and unaligned shapes: the two operators back to back (rope in place on out)
-    if (int rc = rmsnorm_fwd_any(st, dtype, B * heads, hd, S, out, x, w, eps)) return rc;
-    ANE_DISPATCH_DTYPE(dtype, T, return (launch_rope<T>(st, B, heads, hd, S, out, out, pos0, false, fq)));
+    // other head widths and unaligned shapes
+    ANE_DISPATCH_DTYPE(dtype, T, return (launch_qk_rope_fwd_generic<T>(st, B, heads, hd, S, out, x, w, eps, pos0, fq)));
     return ANE_CUDA_OK;
 }
 
@@ -465,10 +595,9 @@ int ane_cuda_rope_qknorm_bwd_dev(void *stream, ane_dtype dtype, int B, int heads
     if (int rc = fill_freq(fq, hd, base)) return rc;
     ANE_DISPATCH_DTYPE(dtype, T,
         if (qk_fast_ok<T, true>(hd, S, dx, dy, x)) return (launch_qk_bwd<T, true>(st, B, heads, hd, S, dx, dw, dy, x, w, eps, pos0, flags, fq)));
-    // fallback: g = rope^-1(dy) into dx, then the norm backward reads g from dx and overwrites it
-    // element by element (each thread re-reads exactly the elements it later writes).
-    ANE_DISPATCH_DTYPE(dtype, T, if (int rc = launch_rope<T>(st, B, heads, hd, S, dx, dy, pos0, true, fq)) return rc);
-    return rmsnorm_bwd_any(st, dtype, B * heads, hd, S, dx, dw, dx, x, w, nullptr, eps, flags);
+    // other head widths and unaligned shapes
+    ANE_DISPATCH_DTYPE(dtype, T, return (launch_qk_rope_bwd_generic<T>(st, B, heads, hd, S, dx, dw, dy, x, w, eps, pos0, flags, fq)));
+    return ANE_CUDA_OK;
 }
 
 }  // extern "C"

@@ -76,6 +76,16 @@ PROTOTYPES = {
     "ane_cuda_residual": (_i, [_fp, _fp, _fp, _f, _sz]),
     "ane_cuda_swiglu": (_i, [_fp, _fp, _fp, _sz]),
     "ane_cuda_swiglu_bwd": (_i, [_fp, _fp, _fp, _fp, _fp, _sz]),
+    # batched host-buffer forms
+    "ane_cuda_rmsnorm_host": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _f]),
+    "ane_cuda_rmsnorm_bwd_host": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _u]),
+    "ane_cuda_residual_host": (_i, [_i, _sz, _vp, _vp, _vp, _f]),
+    "ane_cuda_residual_rmsnorm_host": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _f]),
+    "ane_cuda_swiglu_host": (_i, [_i, _sz, _vp, _vp, _vp]),
+    "ane_cuda_swiglu_bwd_host": (_i, [_i, _sz, _vp, _vp, _vp, _vp, _vp]),
+    "ane_cuda_rope_host": (_i, [_i, _i, _i, _i, _i, _vp, _vp, _f, _i, _u]),
+    "ane_cuda_qknorm_rope_host": (_i, [_i, _i, _i, _i, _i, _vp, _vp, _vp, _f, _f, _i]),
+    "ane_cuda_rope_qknorm_bwd_host": (_i, [_i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _u]),
     # device-resident operators
     "ane_cuda_rmsnorm_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _f]),
     "ane_cuda_rmsnorm_bwd_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _u]),

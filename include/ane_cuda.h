@@ -7,11 +7,12 @@
  *
  *   1. lifecycle and device buffers        (the ane_bridge_init / write_input / read_output
  *                                           / free analogue)
- *   2. host-pointer drop-ins               same argument order and overwrite / accumulate
- *                                           behaviour as the `static` functions of
+ *   2. host-buffer entry points            (a) drop-ins with the argument order and overwrite /
+ *                                           accumulate behaviour of the `static` functions of
  *                                           training/stories_cpu_ops.h and
- *                                           training/training_dynamic/cpu_ops.h; they stage
- *                                           host <-> device and are PCIe-bound
+ *                                           training/training_dynamic/cpu_ops.h; (b) batched,
+ *                                           any-dtype, fused forms.  Both stage host <-> device
+ *                                           and are PCIe-bound
  *   3. device-resident operators (`_dev`)  asynchronous on a caller-given CUDA stream; these
  *                                           are what a GPU training loop calls and what the
  *                                           benchmark times
@@ -104,9 +105,10 @@ int ane_cuda_poll_status(ane_cuda_status *out, int reset);
 size_t ane_cuda_workspace_bytes(void);
 
 /* =====================================================================================
- * 2. Host-pointer drop-ins (fp32, one sequence, reference signatures)
+ * 2. Host-buffer entry points
  * ===================================================================================== */
-/* training/stories_cpu_ops.h:6 and training_dynamic/cpu_ops.h:7 -- rmsnorm(out,x,w,d,S), eps 1e-5 */
+/* 2a. Reference signatures: fp32, one sequence, the reference's literals (eps 1e-5, base 1e4). */
+/* training/stories_cpu_ops.h:6 and training_dynamic/cpu_ops.h:7 -- rmsnorm(out,x,w,d,S) */
 int ane_cuda_rmsnorm(float *out, const float *x, const float *w, int d, int S);
 /* stories_cpu_ops.h:23 / cpu_ops.h:24 -- dx is overwritten, dw is accumulated into */
 int ane_cuda_rmsnorm_bwd(float *dx, float *dw, const float *dy, const float *x, const float *w, int d, int S);
@@ -129,6 +131,28 @@ int ane_cuda_rope_backward_inplace(float *dx, int seq, int dim, int hd);
 int ane_cuda_residual(float *out, const float *x, const float *f, float alpha, size_t n);
 int ane_cuda_swiglu(float *out, const float *h1, const float *h3, size_t n);
 int ane_cuda_swiglu_bwd(float *dh1, float *dh3, const float *h1, const float *h3, const float *dsilu, size_t n);
+
+/* 2b. Batched, any dtype, fused forms: the same operators as group 3 with activations in HOST
+ * memory ([B][C][S], dtype elements; w / dw fp32).  The batch is cut into chunks that flow
+ * through a three-stream pipeline (upload, kernel, download), so both PCIe directions overlap
+ * the kernels when the buffers are page-locked (ane_cuda_host_alloc).  They block until the
+ * results are in host memory.  Reference call sites as for the `_dev` forms below. */
+int ane_cuda_rmsnorm_host(ane_dtype dtype, int B, int C, int S, void *out, const void *x, const float *w, float eps);
+int ane_cuda_rmsnorm_bwd_host(ane_dtype dtype, int B, int C, int S, void *dx, float *dw, const void *dy,
+                              const void *x, const float *w, const void *add, float eps, unsigned flags);
+int ane_cuda_residual_host(ane_dtype dtype, size_t n, void *out, const void *x, const void *f, float alpha);
+int ane_cuda_residual_rmsnorm_host(ane_dtype dtype, int B, int C, int S, void *x2, void *x2norm, const void *x,
+                                   const void *f, const float *w, float alpha, float eps);
+int ane_cuda_swiglu_host(ane_dtype dtype, size_t n, void *out, const void *h1, const void *h3);
+int ane_cuda_swiglu_bwd_host(ane_dtype dtype, size_t n, void *dh1, void *dh3, const void *h1, const void *h3,
+                             const void *dsilu);
+int ane_cuda_rope_host(ane_dtype dtype, int B, int C, int S, int hd, void *out, const void *x, float base, int pos0,
+                       unsigned flags);
+int ane_cuda_qknorm_rope_host(ane_dtype dtype, int B, int heads, int hd, int S, void *out, const void *x,
+                              const float *w, float eps, float base, int pos0);
+int ane_cuda_rope_qknorm_bwd_host(ane_dtype dtype, int B, int heads, int hd, int S, void *dx, float *dw,
+                                  const void *dy, const void *x, const float *w, float eps, float base, int pos0,
+                                  unsigned flags);
 
 /* =====================================================================================
  * 3. Device-resident operators.  `stream` is a cudaStream_t (NULL = default stream).
@@ -156,7 +180,7 @@ int ane_cuda_residual_rmsnorm_dev(void *stream, ane_dtype dtype, int B, int C, i
                                   float alpha, float eps);
 /* a4: out = h1*sigmoid(h1)*h3                                          forward.h:101,149-151 */
 int ane_cuda_swiglu_dev(void *stream, ane_dtype dtype, size_t n, void *out, const void *h1, const void *h3);
-/* a5: dh1, dh3 from h1, h3, dsilu (one pass; dscale multiplies dsilu first, for train.m:523) */
+/* a5: dh1, dh3 from h1, h3, dsilu in one pass                          train.m:537-554 */
 int ane_cuda_swiglu_bwd_dev(void *stream, ane_dtype dtype, size_t n, void *dh1, void *dh3,
                             const void *h1, const void *h3, const void *dsilu);
 /* a6/a7: rotate interleaved channel pairs (2i, 2i+1) of every head by theta = (pos0+t)*base^(-2i/hd);

@@ -1,9 +1,14 @@
 """GPU parity tests: every operator of libane_cuda, called through its C ABI, against the CPU
 oracle (oracle/oracle_ops.c) on the same seeded inputs.
 
-Tolerances (max |got - ref| / max |ref| per tensor):
-  * fp32 operators               <= 1e-5
-  * bf16 / fp16 variants         <= 2e-3 against the fp32 oracle run on the rounded inputs
+Tolerances:
+  * fp32 operators               max |got - ref| / max |ref| <= 1e-5 per tensor
+  * bf16 / fp16 variants         against the fp32 oracle run on the rounded inputs:
+                                 relative L2 error <= 2e-3, max-norm error within the unit
+                                 roundoff of the storage type (2^-8 bf16, 2^-11 fp16: one
+                                 correctly rounded store of a value that is itself within
+                                 1e-5), and all but a handful of elements bit-identical to
+                                 the oracle's result rounded to the storage type
   * gathers, token indexing and the scatter-add (same addition order as the reference loop)
                                  bit-exact
 Shapes cover the reference's own (DIM 768, SEQ 256, VOCAB 32000), the benchmark configurations
@@ -56,6 +61,28 @@ def tol(dt):
     return TOL32 if dt == "f32" else TOL16
 
 
+UNIT_ROUNDOFF = {"bf16": 2.0 ** -8, "f16": 2.0 ** -11}
+
+
+def close(got, ref, dt):
+    """True when `got` (fp32 view of the device result) matches the fp32 oracle result `ref`
+    within the tolerance of storage type dt (see the module docstring)."""
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    if dt == "f32":
+        return rel_err(got, ref) <= TOL32
+    den = float(np.sqrt((ref * ref).sum())) or 1.0
+    l2 = float(np.sqrt(((got - ref) ** 2).sum())) / den
+    mx = rel_err(got, ref)
+    rounded = gi.round_bf16(ref.astype(np.float32)) if dt == "bf16" else gi.round_f16(ref.astype(np.float32))
+    mismatch = float(np.mean(rounded.astype(np.float64) != got)) if ref.size else 0.0
+    l2_tol = TOL16 if ref.size >= 256 else UNIT_ROUNDOFF[dt] * 1.01     # the L2 figure is statistical
+    ok = l2 <= l2_tol and mx <= UNIT_ROUNDOFF[dt] * 1.01 and mismatch <= max(2e-3, 2.0 / max(ref.size, 1))
+    if not ok:
+        print(f"close({dt}): rel L2 {l2:.3e}, max-norm {mx:.3e}, non-identical fraction {mismatch:.3e}")
+    return ok
+
+
 NORM_SHAPES = [(1, 768, 256), (3, 7, 5), (2, 128, 257), (1, 1, 1), (2, 1024, 64), (1, 2, 3), (5, 33, 48), (1, 300, 8)]
 
 
@@ -67,7 +94,7 @@ def test_rmsnorm_fwd(dev, oracle, shape, dt):
     xd, xr = up(x, dt)
     wd, _ = up(w)
     got = down(dev.rmsnorm(xd, wd, 1e-5))
-    assert rel_err(got, oracle.rmsnorm(xr, w, 1e-5)) <= tol(dt)
+    assert close(got, oracle.rmsnorm(xr, w, 1e-5), dt)
 
 
 @pytest.mark.parametrize("exact", [False, True])
@@ -84,7 +111,7 @@ def test_rmsnorm_bwd(dev, oracle, shape, dt, exact):
     dwd, _ = up(dw0)
     dx = down(dev.rmsnorm_bwd(dyd, xd, wd, dwd, eps=1e-5, exact=exact))
     rdx, rdw = oracle.rmsnorm_bwd(dyr, xr, w, dw=dw0, eps=1e-5, exact=exact)
-    assert rel_err(dx, rdx) <= tol(dt)
+    assert close(dx, rdx, dt)
     assert rel_err(down(dwd), rdw) <= (TOL32 if dt == "f32" else 1e-4)
 
 
@@ -101,7 +128,7 @@ def test_rmsnorm_bwd_fused_add_and_determinism(dev, oracle, dt):
     dw1 = torch.zeros(Cn, device="cuda")
     dx1 = dev.rmsnorm_bwd(dyd, xd, wd, dw1, add=ad)
     rdx, rdw = oracle.rmsnorm_bwd(dyr, xr, w)
-    assert rel_err(down(dx1), oracle.add(rdx, ar)) <= tol(dt)          # train.m:590,721
+    assert close(down(dx1), oracle.add(rdx, ar), dt)          # train.m:590,721
     assert rel_err(down(dw1), rdw) <= (TOL32 if dt == "f32" else 1e-4)
     dw2 = torch.zeros(Cn, device="cuda")
     dx2 = dev.rmsnorm_bwd(dyd, xd, wd, dw2, add=ad)
@@ -136,12 +163,12 @@ def test_elementwise(dev, oracle, n, off, dt):
     h1d, h3d, dd = h1d[off:], h3d[off:], dd[off:]
     h1, h3, d = (np.ascontiguousarray(a[off:]) for a in (h1, h3, d))
     alpha = float(np.float32((2.0 * 12) ** -0.25))
-    assert rel_err(down(dev.residual(h1d, h3d, alpha, out=torch.empty_like(h1d))), oracle.residual(h1, h3, alpha)) <= tol(dt)
-    assert rel_err(down(dev.scale(h1d, alpha, out=torch.empty_like(h1d))), oracle.scale(h1, alpha)) <= tol(dt)
-    assert rel_err(down(dev.swiglu(h1d, h3d, out=torch.empty_like(h1d))), oracle.swiglu(h1, h3)) <= tol(dt)
+    assert close(down(dev.residual(h1d, h3d, alpha, out=torch.empty_like(h1d))), oracle.residual(h1, h3, alpha), dt)
+    assert close(down(dev.scale(h1d, alpha, out=torch.empty_like(h1d))), oracle.scale(h1, alpha), dt)
+    assert close(down(dev.swiglu(h1d, h3d, out=torch.empty_like(h1d))), oracle.swiglu(h1, h3), dt)
     g1, g3 = dev.swiglu_bwd(h1d, h3d, dd, dh1=torch.empty_like(h1d), dh3=torch.empty_like(h1d))
     r1, r3 = oracle.swiglu_bwd(h1, h3, d)
-    assert rel_err(down(g1), r1) <= tol(dt) and rel_err(down(g3), r3) <= tol(dt)
+    assert close(down(g1), r1, dt) and close(down(g3), r3, dt)
 
 
 def test_residual_alpha_of_the_reference(dev, oracle):
@@ -162,9 +189,9 @@ def test_residual_rmsnorm_fused(dev, oracle, shape, dt):
     alpha = float(np.float32((2.0 * 28) ** -0.5))
     (xd, xr), (fd, fr) = up(x, dt), up(f, dt)
     x2, x2n = dev.residual_rmsnorm(xd, fd, up(w)[0], alpha, 1e-5)
-    assert rel_err(down(x2), oracle.residual(xr, fr, alpha)) <= tol(dt)
+    assert close(down(x2), oracle.residual(xr, fr, alpha), dt)
     # the norm is taken over the stored (rounded) x2, which is what the backward pass will read
-    assert rel_err(down(x2n), oracle.rmsnorm(down(x2), w, 1e-5)) <= tol(dt)
+    assert close(down(x2n), oracle.rmsnorm(down(x2), w, 1e-5), dt)
 
 
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
@@ -175,11 +202,11 @@ def test_rope_fwd_and_inverse(dev, oracle, B, heads, hd, S, base, pos0, dt):
     xd, xr = up(x, dt)
     for inverse in (False, True):
         got = down(dev.rope(xd, hd, base=base, pos0=pos0, inverse=inverse))
-        assert rel_err(got, oracle.rope(xr, hd, base=base, pos0=pos0, inverse=inverse)) <= tol(dt)
+        assert close(got, oracle.rope(xr, hd, base=base, pos0=pos0, inverse=inverse), dt)
     # in place
     y = xd.clone()
     dev.rope(y, hd, base=base, pos0=pos0, out=y)
-    assert rel_err(down(y), oracle.rope(xr, hd, base=base, pos0=pos0)) <= tol(dt)
+    assert close(down(y), oracle.rope(xr, hd, base=base, pos0=pos0), dt)
 
 
 def test_rope_bwd_golden_on_gpu(dev, golden):
@@ -202,9 +229,9 @@ def test_qknorm_and_fusions_fwd(dev, oracle, B, heads, hd, S, dt):
     w = gi.normal(r, (hd,), 0.02, 1.0)
     xd, xr = up(x, dt)
     wd, _ = up(w)
-    assert rel_err(down(dev.qknorm(xd, wd, hd, 1e-6)), oracle.qknorm(xr, w, hd, 1e-6)) <= tol(dt)
+    assert close(down(dev.qknorm(xd, wd, hd, 1e-6)), oracle.qknorm(xr, w, hd, 1e-6), dt)
     got = down(dev.qknorm_rope(xd, wd, hd, 1e-6, 1e6, 3))
-    assert rel_err(got, oracle.qknorm_rope(xr, w, hd, 1e-6, 1e6, 3)) <= tol(dt)
+    assert close(got, oracle.qknorm_rope(xr, w, hd, 1e-6, 1e6, 3), dt)
 
 
 @pytest.mark.parametrize("exact", [False, True])
@@ -222,11 +249,11 @@ def test_qknorm_and_fusions_bwd(dev, oracle, B, heads, hd, S, dt, exact):
     dw = torch.zeros(hd, device="cuda")
     dx = down(dev.qknorm_bwd(dyd, xd, wd, dw, hd, 1e-6, exact=exact))
     rdx, rdw = oracle.qknorm_bwd(dyr, xr, w, hd, eps=1e-6, exact=exact)
-    assert rel_err(dx, rdx) <= tol(dt) and rel_err(down(dw), rdw) <= dwtol
+    assert close(dx, rdx, dt) and rel_err(down(dw), rdw) <= dwtol
     dw = torch.zeros(hd, device="cuda")
     dx = down(dev.rope_qknorm_bwd(dyd, xd, wd, dw, hd, 1e-6, 1e6, 3, exact=exact))
     rdx, rdw = oracle.rope_qknorm_bwd(dyr, xr, w, hd, eps=1e-6, base=1e6, pos0=3, exact=exact)
-    assert rel_err(dx, rdx) <= tol(dt) and rel_err(down(dw), rdw) <= dwtol
+    assert close(dx, rdx, dt) and rel_err(down(dw), rdw) <= dwtol
 
 
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
@@ -447,6 +474,67 @@ def test_host_dropins_match_oracle(dev, oracle):
     o = np.empty_like(xx)
     ops.residual(o, xx, ff, 0.2041241452)
     assert np.array_equal(o, oracle.residual(xx, ff, np.float32(0.2041241452)))
+
+
+@pytest.mark.parametrize("pinned", [False, True])
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_host_batched_forms(dev, oracle, dt, pinned):
+    """The batched host-buffer entry points (several pipeline chunks, odd batch) give the same
+    results as the device-resident operators they wrap."""
+    torch = _torch()
+    from ane_b200 import host_ops as hop
+    tdt = getattr(torch, DT[dt])
+    B, Cn, S, H, hd = 5, 1024, 2048, 3072, 128          # 4 or 8 MiB per sequence and tensor -> multi-chunk
+    g = torch.Generator().manual_seed(3)
+
+    def mk(*shape, dtype=tdt):
+        t = torch.randn(*shape, generator=g).to(dtype)
+        return t.pin_memory() if pinned else t
+
+    def out_like(t):
+        o = torch.empty_like(t)
+        return o.pin_memory() if pinned else o
+
+    x, f, dy, add = mk(B, Cn, S), mk(B, Cn, S), mk(B, Cn, S), mk(B, Cn, S)
+    w = (1 + 0.02 * torch.randn(Cn, generator=g)).float()
+    wd = w.cuda()
+    o = out_like(x)
+    hop.rmsnorm(o, x, w)
+    assert torch.equal(o, dev.rmsnorm(x.cuda(), wd).cpu())
+    x2, x2n = out_like(x), out_like(x)
+    hop.residual_rmsnorm(x2, x2n, x, f, w, 0.25)
+    d2, d2n = dev.residual_rmsnorm(x.cuda(), f.cuda(), wd, 0.25)
+    assert torch.equal(x2, d2.cpu()) and torch.equal(x2n, d2n.cpu())
+    dx, dw = out_like(x), torch.full((Cn,), 0.5)
+    hop.rmsnorm_bwd(dx, dw, dy, x, w, add=add)
+    ddw = torch.full((Cn,), 0.5, device="cuda")
+    ddx = dev.rmsnorm_bwd(dy.cuda(), x.cuda(), wd, ddw, add=add.cuda())
+    assert torch.equal(dx, ddx.cpu())
+    assert rel_err(dw.numpy(), ddw.cpu().numpy()) <= 1e-5     # chunked accumulation order differs
+    h1, h3, ds = mk(B, H, S), mk(B, H, S), mk(B, H, S)
+    o = out_like(h1)
+    hop.swiglu(o, h1, h3)
+    assert torch.equal(o, dev.swiglu(h1.cuda(), h3.cuda()).cpu())
+    g1, g3 = out_like(h1), out_like(h1)
+    hop.swiglu_bwd(g1, g3, h1, h3, ds)
+    e1, e3 = dev.swiglu_bwd(h1.cuda(), h3.cuda(), ds.cuda())
+    assert torch.equal(g1, e1.cpu()) and torch.equal(g3, e3.cpu())
+    o = out_like(x)
+    hop.residual(o, x, f, 0.25)
+    assert torch.equal(o, dev.residual(x.cuda(), f.cuda(), 0.25).cpu())
+    q, dq = mk(B, 16 * hd, S), mk(B, 16 * hd, S)
+    wq = (1 + 0.02 * torch.randn(hd, generator=g)).float()
+    o = out_like(q)
+    hop.qknorm_rope(o, q, wq, hd)
+    assert torch.equal(o, dev.qknorm_rope(q.cuda(), wq.cuda(), hd).cpu())
+    dxq, dwq = out_like(q), torch.zeros(hd)
+    hop.rope_qknorm_bwd(dxq, dwq, dq, q, wq, hd)
+    ddwq = torch.zeros(hd, device="cuda")
+    ddxq = dev.rope_qknorm_bwd(dq.cuda(), q.cuda(), wq.cuda(), ddwq, hd)
+    assert torch.equal(dxq, ddxq.cpu()) and rel_err(dwq.numpy(), ddwq.cpu().numpy()) <= 1e-5
+    o = out_like(q)
+    hop.rope(o, q, hd, base=1e6, inverse=True)
+    assert torch.equal(o, dev.rope(q.cuda(), hd, base=1e6, inverse=True).cpu())
 
 
 def test_buffers_and_errors(dev):
