@@ -1,0 +1,103 @@
+"""Token sharding and the collectives around the operator chain (one process per GPU).
+
+Every operator of the chain is independent per token (per sequence for RoPE positions), so the
+sequences of a step are split contiguously over the ranks and no collective runs inside the
+layer loop.  The exchanges are the ones a data-parallel step needs:
+
+* gradients: one reduce-scatter (sum) over the flat fp32 gradient buffer -- it carries the
+  embedding gradient and the norm-weight gradients produced by this library together with the
+  matmul gradients the caller produced;
+* the squared gradient norm: one scalar all-reduce, so that every rank clips with the same factor
+  (train.m:770-825);
+* parameters: Adam runs on the rank's 1/N slice of (w, m, v) and the updated slices are
+  all-gathered.
+
+``torch.distributed`` (NCCL on GPUs, gloo in the CPU tests) is the transport.  The reduction
+order inside NCCL is fixed for a given world size, so results are reproducible run to run; they
+agree with the single-GPU result to fp32 rounding, not bit for bit.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n_items: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous balanced split of range(n_items): the first n_items % world ranks get one more."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} / world {world}")
+    base, extra = divmod(n_items, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def padded_length(n: int, world: int, align: int = 256) -> int:
+    """Length of a flat buffer that splits into `world` equal slices of a multiple of `align`."""
+    q = world * align
+    return (n + q - 1) // q * q
+
+
+class ShardedAdam:
+    """ZeRO-1 style optimizer step over FlatParams-like flat buffers.
+
+    ``kernels`` supplies grad_norm_sq(g, gscale) -> 1-element tensor, clip_factor(normsq, clip)
+    -> 1-element tensor and adam(w, g, m, v, t, lr, b1, b2, eps, wd=, gscale=, clip=); the default
+    is this library's device operators.  The CPU tests pass stand-ins to exercise the collective
+    choreography without a GPU."""
+
+    def __init__(self, w, g, m, v, n_decay: int, n_params: int, world: int = 1, rank: int = 0, group=None,
+                 lr: float = 3e-4, b1: float = 0.9, b2: float = 0.95, eps: float = 1e-8, wd: float = 0.1,
+                 clip: float = 1.0, kernels=None):
+        if w.numel() % world:
+            raise ValueError("flat buffers must be padded to a multiple of the world size (see padded_length)")
+        self.w, self.g, self.m, self.v = w, g, m, v
+        self.n_decay, self.n_params = n_decay, n_params
+        self.world, self.rank, self.group = world, rank, group
+        self.lr, self.b1, self.b2, self.eps, self.wd, self.clip = lr, b1, b2, eps, wd, clip
+        self.slice_len = w.numel() // world
+        self.lo = rank * self.slice_len
+        self.hi = self.lo + self.slice_len
+        if kernels is None:
+            from . import dev_ops as kernels  # noqa: WPS433
+        self.k = kernels
+        self.g_slice = torch.empty(self.slice_len, dtype=g.dtype, device=g.device) if world > 1 else None
+        self.normsq = None
+
+    def _reduce_scatter(self):
+        if self.world == 1:
+            return self.g[self.lo:self.hi]
+        if dist.get_backend(self.group) == "gloo":      # gloo has no reduce-scatter
+            dist.all_reduce(self.g, op=dist.ReduceOp.SUM, group=self.group)
+            self.g_slice.copy_(self.g[self.lo:self.hi])
+        else:
+            dist.reduce_scatter_tensor(self.g_slice, self.g, op=dist.ReduceOp.SUM, group=self.group)
+        return self.g_slice
+
+    def step(self, t: int, gscale: float = 1.0):
+        gs = self._reduce_scatter()
+        normsq = self.k.grad_norm_sq(gs, gscale)
+        if self.world > 1:
+            dist.all_reduce(normsq, op=dist.ReduceOp.SUM, group=self.group)
+        self.normsq = normsq
+        factor = self.k.clip_factor(normsq, self.clip)
+        # slice ∩ [0, n_decay): weight decay; slice ∩ [n_decay, n_params): none (train.m:837-869)
+        for lo, hi, wd in ((0, self.n_decay, self.wd), (self.n_decay, self.n_params, 0.0)):
+            a, b = max(lo, self.lo), min(hi, self.hi)
+            if a < b:
+                sl = slice(a, b)
+                gl = slice(a - self.lo, b - self.lo)
+                self.k.adam(self.w[sl], gs[gl], self.m[sl], self.v[sl], t, self.lr, self.b1, self.b2, self.eps,
+                            wd=wd, gscale=gscale, clip=factor)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.w, self.w[self.lo:self.hi].clone() if dist.get_backend(self.group) == "gloo"
+                                        else self.w[self.lo:self.hi], group=self.group)
+        return factor
+
+
+def allreduce_scalar_sum(x: torch.Tensor, world: int, group=None) -> torch.Tensor:
+    """Sum of a small tensor over the ranks (the loss all-reduce of a data-parallel step)."""
+    if world > 1:
+        dist.all_reduce(x, op=dist.ReduceOp.SUM, group=group)
+    return x

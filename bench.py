@@ -1,0 +1,529 @@
+"""Benchmark of the hot path: the Qwen3-0.6B non-matmul layer chain plus the Adam step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step = one pass of the operator chain (ane_b200.layer_chain: embedding gather, 28 layers of
+forward and backward operators, final norm, embedding scatter-add) over 256 sequences x 2048
+tokens in bf16, followed by gradient-norm / clip / Adam over 596 M fp32 parameters.  The 256
+sequences are split over the N ranks (total work fixed: strong scaling) and run in micro-batches;
+matmul and attention outputs are pre-filled synthetic buffers (not executed, not timed).
+
+Rank 0 prints ONE JSON line:
+  value      tokens/s, inputs resident in HBM, device-timed (CUDA events, max over ranks)
+  roofline   the dominant kernel (SwiGLU backward): algorithmic bytes / measured launch time
+             against the measured HBM copy bandwidth of MEASURED_PEAKS.json
+  ops        per-operator achieved GB/s on benchmark-sized tensors (each launch rotates over
+             buffer sets larger than L2)
+  e2e        the same chain through the host-buffer entry points (ane_cuda_*_host) with
+             page-locked host tensors: every operator's inputs are uploaded and its outputs
+             downloaded inside the timed region
+  cpu_baseline  the CPU oracle (a port of the reference's operators) on the host cores, bounded sample
+`--impl reference` times that CPU path alone, on the same configuration and metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+TOTAL_SEQS = 256
+FALLBACK_HBM_GBS = 6650.0
+NOMINAL_HBM_GBS = 8000.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--micro-batch", type=int, default=16, help="sequences per micro-batch and GPU")
+    ap.add_argument("--seqs", type=int, default=TOTAL_SEQS, help="sequences per step over all GPUs")
+    ap.add_argument("--layers", type=int, default=28)
+    ap.add_argument("--no-ops", action="store_true", help="skip the per-operator table")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-seqs", type=int, default=2, help="sequences in the CPU sample")
+    return ap.parse_args()
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ------------------------------------------------------------------------------------- clocks
+class ClockSampler(threading.Thread):
+    """Samples SM clock, power and throttle reasons through NVML while the timed region runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index: int, period: float = 0.1):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons, self.power = [], set(), []
+        self.max_mhz = None
+        self._halt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self._halt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._halt.wait(self.period)
+
+    def stop(self):
+        self._halt.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["nvml unavailable"]}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "power_w_max": max(self.power) if self.power else None, "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------- CPU path
+def cpu_chain(cfg_kw, n_seqs: int, steps: int, warmup: int, threads=None):
+    """The same operator chain on the host cores with the CPU oracle (fp32, as the reference's CPU
+    operators are), on `n_seqs` sequences, all host threads; Adam on 1/32 of the parameters.
+    Returns tokens/s extrapolated to the full step: t_step = t_chain * (seqs / n_seqs) + t_adam * 32.
+    Output buffers are allocated once, outside the timed region."""
+    import numpy as np
+
+    from oracle.oracle import Oracle, _fp, _ip
+
+    orc = Oracle(fast=True)
+    if threads:
+        orc.set_num_threads(threads)
+    nthreads = orc.num_threads()
+    orc.set_chunk(128)      # spread (sequence, 128-token block) pairs over the threads
+    C = orc.lib
+    L, D, H = cfg_kw["layers"], 1024, 3072
+    Qd, KVd, hd, S, V = 2048, 1024, 128, 2048, 151936
+    alpha = float(np.float32((2.0 * L) ** -0.5))
+    rng = np.random.Generator(np.random.PCG64(1234))
+
+    def rnd(*shape, std=1.0):
+        return (rng.standard_normal(shape, dtype=np.float32) * np.float32(std)).astype(np.float32)
+
+    def emp(ch):
+        return np.zeros((n_seqs, ch, S), np.float32)
+
+    B = n_seqs
+    sets = 2
+    bufs = [dict(q=rnd(B, Qd, S), k=rnd(B, KVd, S), o=rnd(B, D, S), h1=rnd(B, H, S), h3=rnd(B, H, S), f=rnd(B, D, S),
+                 dsilu=rnd(B, H, S), dxf=rnd(B, D, S), dq=rnd(B, Qd, S), dk=rnd(B, KVd, S), dxa=rnd(B, D, S)) for _ in range(sets)]
+    table = rnd(V, D, std=0.02)
+    tok = rng.integers(0, V, size=(B, S)).astype(np.int32)
+    w = (1 + rnd(D, std=0.02)).astype(np.float32)
+    wq = (1 + rnd(hd, std=0.02)).astype(np.float32)
+    dw, dwq = np.zeros(D, np.float32), np.zeros(hd, np.float32)
+    dE = np.zeros((V, D), np.float32)
+    xs = [emp(D) for _ in range(L + 1)]
+    x2s = [emp(D) for _ in range(L)]
+    xn, qr, kr, gate, dh1, dh3, dqo, dko = emp(D), emp(Qd), emp(KVd), emp(H), emp(H), emp(H), emp(Qd), emp(KVd)
+    dy, dy2, dx2, tmp = emp(D), emp(D), emp(D), emp(D)
+    dy_cls = rnd(B, D, S)
+    n_adam = 596_042_752 // 32
+    aw, ag, am, av = rnd(n_adam, std=0.02), rnd(n_adam, std=1e-2), np.zeros(n_adam, np.float32), np.zeros(n_adam, np.float32)
+    nD, nH = B * D * S, B * H * S
+
+    def chain():
+        for b in range(B):
+            C.orc_embed_lookup(_fp(xs[0][b]), _fp(table), _ip(tok[b]), D, S, V)
+        for l in range(L):
+            u = bufs[l % sets]
+            C.orc_rmsnorm_batched(_fp(xn), _fp(xs[l]), _fp(w), B, D, S, 1e-5)
+            C.orc_qknorm_rope_batched(_fp(qr), _fp(u["q"]), _fp(wq), B, Qd // hd, hd, S, 1e-6, 1e6, 0)
+            C.orc_qknorm_rope_batched(_fp(kr), _fp(u["k"]), _fp(wq), B, KVd // hd, hd, S, 1e-6, 1e6, 0)
+            C.orc_residual(_fp(x2s[l]), _fp(xs[l]), _fp(u["o"]), alpha, nD)          # train.m:460
+            C.orc_rmsnorm_batched(_fp(xn), _fp(x2s[l]), _fp(w), B, D, S, 1e-5)        # train.m:461
+            C.orc_swiglu(_fp(gate), _fp(u["h1"]), _fp(u["h3"]), nH)
+            C.orc_residual(_fp(xs[l + 1]), _fp(x2s[l]), _fp(u["f"]), alpha, nD)
+        C.orc_rmsnorm_batched(_fp(xn), _fp(xs[L]), _fp(w), B, D, S, 1e-5)
+        C.orc_rmsnorm_bwd_batched(_fp(dy), _fp(dw), _fp(dy_cls), _fp(xs[L]), _fp(w), B, D, S, 1e-5, 0)
+        cur, nxt = dy, dy2
+        for l in range(L - 1, -1, -1):
+            u = bufs[l % sets]
+            C.orc_swiglu_bwd(_fp(dh1), _fp(dh3), _fp(u["h1"]), _fp(u["h3"]), _fp(u["dsilu"]), nH)
+            C.orc_rmsnorm_bwd_batched(_fp(tmp), _fp(dw), _fp(u["dxf"]), _fp(x2s[l]), _fp(w), B, D, S, 1e-5, 0)
+            C.orc_add(_fp(dx2), _fp(tmp), _fp(cur), nD)                                # train.m:590
+            C.orc_rope_qknorm_bwd_batched(_fp(dqo), _fp(dwq), _fp(u["dq"]), _fp(u["q"]), _fp(wq), B, Qd // hd, hd, S, 1e-6, 1e6, 0, 0)
+            C.orc_rope_qknorm_bwd_batched(_fp(dko), _fp(dwq), _fp(u["dk"]), _fp(u["k"]), _fp(wq), B, KVd // hd, hd, S, 1e-6, 1e6, 0, 0)
+            C.orc_rmsnorm_bwd_batched(_fp(tmp), _fp(dw), _fp(u["dxa"]), _fp(xs[l]), _fp(w), B, D, S, 1e-5, 0)
+            C.orc_add(_fp(nxt), _fp(tmp), _fp(dx2), nD)                                # train.m:721
+            cur, nxt = nxt, cur
+        for b in range(B):
+            C.orc_embed_backward(_fp(dE), _fp(cur[b]), _ip(tok[b]), D, S, V)
+
+    def adam_part():
+        nsq = orc.grad_norm_sq(ag, 1.0 / 2560.0)
+        cf = orc.clip_factor(np.float32(nsq), 1.0)
+        orc.adam(aw, ag, am, av, 1, 3e-4, 0.9, 0.95, 1e-8, wd=0.1, variant=1, gscale=1.0 / 2560.0, clip=cf)
+
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        chain()
+        t1 = time.perf_counter()
+        adam_part()
+        t2 = time.perf_counter()
+        if i >= warmup:
+            times.append((t1 - t0, t2 - t1))
+    t_chain = statistics.mean(t[0] for t in times)
+    t_adam = statistics.mean(t[1] for t in times)
+    full = t_chain * (cfg_kw["seqs"] / n_seqs) + t_adam * 32
+    return {
+        "tokens_per_s": cfg_kw["seqs"] * S / full,
+        "ms_per_step_extrapolated": full * 1e3,
+        "sample_ms": (t_chain + t_adam) * 1e3,
+        "cores": nthreads,
+        "sample": f"{n_seqs} of {cfg_kw['seqs']} sequences x 2048 tokens through all {L} layers in fp32 "
+                  f"({t_chain:.2f} s) + Adam on 1/32 of 596M params ({t_adam:.2f} s), {nthreads} threads; step time = chain x "
+                  f"{cfg_kw['seqs'] // n_seqs} + Adam x 32",
+    }
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg_kw = {"layers": args.layers, "seqs": args.seqs}
+    r = cpu_chain(cfg_kw, args.cpu_seqs, max(1, args.steps), max(0, min(args.warmup, 1)))
+    line = {
+        "impl": "reference",
+        "metric": "layer-op tokens/sec (Qwen3-0.6B non-matmul layer chain + Adam)",
+        "value": r["tokens_per_s"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": r["ms_per_step_extrapolated"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, args.gpus),
+        "cpu_baseline": {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+        "e2e": {"value": r["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, world):
+    return {
+        "workload": "configs[4]: Qwen3-0.6B non-matmul layer chain (28 layers, dim 1024, hidden 3072, GQA 16/8, "
+                    "head_dim 128, bf16 activations) + Adam on 596M fp32 params",
+        "sequences": args.seqs, "seq_len": 2048, "layers": args.layers, "micro_batch_per_gpu": args.micro_batch,
+        "parallelism": f"dp{world} (sequences sharded, ZeRO-1 Adam)",
+        "l2_policy": "inputs larger than L2: every operator reads per-layer buffers (64-192 MiB each) last touched "
+                     "hundreds of MiB of traffic earlier",
+    }
+
+
+# ------------------------------------------------------------------------------------- per-op table
+def per_op_table(torch, ops, device, peak_gbs):
+    """Achieved GB/s per operator on benchmark-sized bf16 tensors (algorithmic bytes / time)."""
+    res = {}
+    M, S, D, H, Qd, KVd, hd = 16, 2048, 1024, 3072, 2048, 1024, 128
+    bf = torch.bfloat16
+    NSET = 3
+
+    def mk(ch, dtype=bf, n=NSET, b=M):
+        return [torch.randn((b, ch, S), device=device, dtype=dtype) for _ in range(n)]
+
+    def timeit(fn, bytes_per_launch, iters=12):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for i in range(iters):
+            fn(i)
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / iters
+        gbs = bytes_per_launch / ms / 1e6
+        return {"ms": round(ms, 4), "GB/s": round(gbs, 1), "frac_measured": round(gbs / peak_gbs, 3),
+                "frac_8TBs": round(gbs / NOMINAL_HBM_GBS, 3), "bytes": bytes_per_launch}
+
+    T = M * S
+    w = torch.ones(D, device=device)
+    wq = torch.ones(hd, device=device)
+    dw = torch.zeros(D, device=device)
+    dwq = torch.zeros(hd, device=device)
+    xs, ys, zs, os_ = mk(D), mk(D), mk(D), mk(D)
+    res["rmsnorm"] = timeit(lambda i: ops.rmsnorm(xs[i % NSET], w, out=os_[i % NSET]), 2 * D * T * 2)
+    res["rmsnorm_bwd"] = timeit(lambda i: ops.rmsnorm_bwd(ys[i % NSET], xs[i % NSET], w, dw, out=os_[i % NSET]), 3 * D * T * 2)
+    res["rmsnorm_bwd_add"] = timeit(lambda i: ops.rmsnorm_bwd(ys[i % NSET], xs[i % NSET], w, dw, add=zs[i % NSET], out=os_[i % NSET]), 4 * D * T * 2)
+    o2 = mk(D)
+    res["residual_rmsnorm"] = timeit(lambda i: ops.residual_rmsnorm(xs[i % NSET], ys[i % NSET], w, 0.13, x2=os_[i % NSET], x2norm=o2[i % NSET]), 4 * D * T * 2)
+    res["residual"] = timeit(lambda i: ops.residual(xs[i % NSET], ys[i % NSET], 0.13, out=os_[i % NSET]), 3 * D * T * 2)
+    del zs, o2
+    h1, h3, dd, g1, g3 = mk(H), mk(H), mk(H), mk(H), mk(H)
+    res["swiglu"] = timeit(lambda i: ops.swiglu(h1[i % NSET], h3[i % NSET], out=g1[i % NSET]), 3 * H * T * 2)
+    res["swiglu_bwd"] = timeit(lambda i: ops.swiglu_bwd(h1[i % NSET], h3[i % NSET], dd[i % NSET], dh1=g1[i % NSET], dh3=g3[i % NSET]), 5 * H * T * 2)
+    del h1, h3, dd, g1, g3
+    q, dq, qo = mk(Qd), mk(Qd), mk(Qd)
+    res["rope"] = timeit(lambda i: ops.rope(q[i % NSET], hd, base=1e6, out=qo[i % NSET]), 2 * Qd * T * 2)
+    res["qknorm_rope(Q)"] = timeit(lambda i: ops.qknorm_rope(q[i % NSET], wq, hd, out=qo[i % NSET]), 2 * Qd * T * 2)
+    res["rope_qknorm_bwd(Q)"] = timeit(lambda i: ops.rope_qknorm_bwd(dq[i % NSET], q[i % NSET], wq, dwq, hd, out=qo[i % NSET]), 3 * Qd * T * 2)
+    del q, dq, qo
+    # embedding (config 4: 32 x 2048 tokens, table [151936, 1024] bf16)
+    V, Be = 151936, 32
+    table = (0.02 * torch.randn(V, D, device=device)).to(bf)
+    tok = torch.randint(0, V, (Be, S), device=device, dtype=torch.int32)
+    xe = [torch.empty((Be, D, S), device=device, dtype=bf) for _ in range(2)]
+    res["embed_lookup"] = timeit(lambda i: ops.embed_lookup(table, tok, out=xe[i % 2]), Be * S * 4 + 2 * D * Be * S * 2)
+    dE = torch.zeros(V, D, device=device)
+    uniq = int(torch.unique(tok).numel())
+    res["embed_backward"] = timeit(lambda i: ops.embed_backward(dE, xe[i % 2], tok), Be * S * 4 + D * Be * S * 2 + 2 * uniq * D * 4, iters=6)
+    del table, xe, dE
+    # cross-entropy (config 4 shape, 4 of the 32 sequences: 5 GB of fp32 logits, in place)
+    Bc = 4
+    logits = torch.randn((Bc, V, S), device=device)
+    tg = torch.randint(0, V, (Bc, S), device=device, dtype=torch.int32)
+    res["cross_entropy"] = timeit(lambda i: ops.cross_entropy(logits, tg, dlogits=logits), 2 * V * Bc * S * 4, iters=3)
+    del logits
+    # Adam over 596M params is timed inside the step; here 64M params for the table
+    n = 64 << 20
+    wv, gv, mv, vv = (torch.randn(n, device=device) * 0.01 for _ in range(4))
+    vv.abs_()
+    res["adam"] = timeit(lambda i: ops.adam(wv, gv, mv, vv, 1 + i, 3e-4, 0.9, 0.95, 1e-8, wd=0.1), 28 * n)
+    nsq = torch.zeros(1, device=device)
+    res["grad_norm_sq"] = timeit(lambda i: ops.grad_norm_sq(gv, 1.0, out=nsq), 4 * n)
+    torch.cuda.empty_cache()
+    return res
+
+
+# ------------------------------------------------------------------------------------- e2e (host buffers)
+def e2e_chain(torch, cfg, n_seqs, steps, warmup):
+    """The chain through the host-buffer entry points on page-locked host tensors.  Per-layer host
+    buffers are shared between layers (the CPU side only provides and receives bytes)."""
+    from ane_b200 import host_ops as hop
+
+    S, D, H, Qd, KVd, hd = cfg.seq, cfg.dim, cfg.hidden, cfg.q_dim, cfg.kv_dim, cfg.head_dim
+    B = n_seqs
+    bf = cfg.dtype
+
+    def pin(ch, fill=True):
+        t = torch.empty((B, ch, S), dtype=bf).pin_memory()
+        if fill:
+            t.normal_()
+        return t
+
+    x, o, f, h1, h3, q, k = pin(D), pin(D), pin(D), pin(H), pin(H), pin(Qd), pin(KVd)
+    xn, x2, x2n, gate, xo, qr, kr = (pin(c, False) for c in (D, D, D, H, D, Qd, KVd))
+    ds, dxf, dqi, dki, dxa, dy = pin(H), pin(D), pin(Qd), pin(KVd), pin(D), pin(D)
+    dh1, dh3, dx2, dq, dk, dyo = (pin(c, False) for c in (H, H, D, Qd, KVd, D))
+    w = torch.ones(D)
+    wq = torch.ones(hd)
+    dw = torch.zeros(D)
+    dwq = torch.zeros(hd)
+    e = 2
+    h2d = cfg.layers * e * B * S * ((D) + (Qd + KVd) + 2 * D + 2 * H + 2 * D + 3 * H + 3 * D + 2 * (Qd + KVd) + 3 * D) + e * B * S * (D + 2 * D)
+    d2h = cfg.layers * e * B * S * ((D) + (Qd + KVd) + 2 * D + H + D + 2 * H + D + (Qd + KVd) + D) + e * B * S * (D + D)
+
+    def step():
+        for _ in range(cfg.layers):
+            hop.rmsnorm(xn, x, w, cfg.eps)
+            hop.qknorm_rope(qr, q, wq, hd, cfg.qk_eps, cfg.rope_base)
+            hop.qknorm_rope(kr, k, wq, hd, cfg.qk_eps, cfg.rope_base)
+            hop.residual_rmsnorm(x2, x2n, x, o, w, cfg.alpha, cfg.eps)
+            hop.swiglu(gate, h1, h3)
+            hop.residual(xo, x2, f, cfg.alpha)
+        hop.rmsnorm(xn, xo, w, cfg.eps)
+        hop.rmsnorm_bwd(dyo, dw, dy, xo, w, eps=cfg.eps)
+        for _ in range(cfg.layers):
+            hop.swiglu_bwd(dh1, dh3, h1, h3, ds)
+            hop.rmsnorm_bwd(dx2, dw, dxf, x2, w, add=dyo, eps=cfg.eps)
+            hop.rope_qknorm_bwd(dq, dwq, dqi, q, wq, hd, cfg.qk_eps, cfg.rope_base)
+            hop.rope_qknorm_bwd(dk, dwq, dki, k, wq, hd, cfg.qk_eps, cfg.rope_base)
+            hop.rmsnorm_bwd(dyo, dw, dxa, x, w, add=dx2, eps=cfg.eps)
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / steps
+    return B * S / dt, h2d, d2h, dt
+
+
+# ------------------------------------------------------------------------------------- main (ours)
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from ane_b200 import dev_ops as ops
+    from ane_b200 import lib
+    from ane_b200.layer_chain import ChainConfig, FlatParams, LayerChain
+    from ane_b200.sharded import ShardedAdam, padded_length, shard_range
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs CUDA devices: libane_cuda has no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib.init(local)
+    peak_gbs, peak_kind = measured_peak()
+
+    cfg = ChainConfig(layers=args.layers, alpha=(2.0 * args.layers) ** -0.5)
+    lo, hi = shard_range(args.seqs, world, rank)
+    my_seqs = hi - lo
+    M = min(args.micro_batch, max(my_seqs, 1))
+    n_micro = (my_seqs + M - 1) // M
+    if my_seqs % M:
+        raise SystemExit(f"sequences per rank ({my_seqs}) must be a multiple of the micro-batch ({M})")
+
+    params = FlatParams(cfg, device, pad_to=world * 256)
+    params.init_random()
+    chain = LayerChain(cfg, M, params, device)
+    opt = ShardedAdam(params.w, params.g, params.m, params.v, params.n_decay, params.n, world, rank,
+                      lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0)
+    gscale = 1.0 / (10 * 256.0)       # 1/(accum_steps*loss_scale), train.m:750
+    tstep = [0]
+
+    def step():
+        params.zero_produced_grads()
+        for _ in range(n_micro):
+            chain.forward()
+            chain.backward()
+        tstep[0] += 1
+        opt.step(tstep[0], gscale)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    chain.timed_op = ("swiglu_bwd", [])
+    lib.reset_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    launches = lib.launch_count()
+    clocks = sampler.stop()
+    ms_total = e0.elapsed_time(e1)
+    t = torch.tensor([ms_total], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t[0]) / args.steps
+    tokens = args.seqs * cfg.seq
+    value = tokens / (ms_step * 1e-3)
+
+    # roofline of the dominant kernel, timed live inside the timed region
+    ev = chain.timed_op[1]
+    chain.timed_op = None
+    k_ms = statistics.mean(s.elapsed_time(e) for s, e in ev)
+    k_bytes = 5 * cfg.hidden * M * cfg.seq * 2
+    achieved = k_bytes / k_ms / 1e6
+    roofline = {"bound": "hbm", "kernel": "ew_vec_kernel<bf16,3,2,SwigluBwdOp> (swiglu_bwd)", "achieved": round(achieved, 1),
+                "peak": peak_gbs, "peak_kind": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650",
+                "unit": "GB/s", "frac": round(achieved / peak_gbs, 4), "frac_of_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
+                "traffic": None, "launch_ms": round(k_ms, 4), "launches_timed": len(ev), "algorithmic_bytes_per_launch": k_bytes}
+    prof = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(prof):
+        try:
+            with open(prof) as f:
+                tr = json.load(f)
+            roofline["traffic"] = tr.get("swiglu_bwd_dram_bytes_per_algorithmic_byte", None) and int(
+                tr["swiglu_bwd_dram_bytes_per_algorithmic_byte"] * k_bytes)
+        except Exception:
+            pass
+
+    chain_bytes = tokens * (cfg.layers * cfg.bytes_per_token_layer() + cfg.bytes_per_token_ends()) + 28 * params.n + 4 * params.n
+    line = {
+        "metric": "layer-op tokens/sec (Qwen3-0.6B non-matmul layer chain + Adam)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_step, 3), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16 activations / f32 math and optimizer", "data": "synthetic",
+        "config": workload_config(args, world),
+        "step_algorithmic_GB": round(chain_bytes / 1e9, 2),
+        "step_GBps_per_gpu": round(chain_bytes / world / (ms_step * 1e-3) / 1e9, 1),
+        "step_frac_of_measured_peak": round(chain_bytes / world / (ms_step * 1e-3) / 1e9 / peak_gbs, 4),
+        "roofline": roofline,
+        "clocks": clocks,
+        "gpu_launches": int(launches),
+    }
+
+    del chain
+    torch.cuda.empty_cache()
+    if not args.no_ops and rank == 0 and world == 1:
+        line["ops"] = per_op_table(torch, ops, device, peak_gbs)
+    if world > 1:
+        dist.barrier()
+
+    if not args.no_e2e:
+        e2e_seqs = 4
+        tps, h2d, d2h, dt = e2e_chain(torch, cfg, e2e_seqs, steps=1, warmup=1)
+        t = torch.tensor([tps], device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        line["e2e"] = {"value": round(float(t[0]), 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                       "note": f"chain through ane_cuda_*_host on pinned host tensors, {e2e_seqs} sequences x 2048 tokens per rank and step "
+                               f"({dt*1e3:.0f} ms); PCIe-bound"}
+
+    if rank == 0:
+        if not args.no_cpu and world == 1:
+            r = cpu_chain({"layers": args.layers, "seqs": args.seqs}, args.cpu_seqs, 1, 0)
+            line["cpu_baseline"] = {"value": round(r["tokens_per_s"], 1), "unit": "tokens/s", "cores": r["cores"], "kind": "port",
+                                    "sample": r["sample"]}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -85,6 +85,7 @@ class Oracle:
         L.orc_vocab_map_build.restype = C.c_int
         L.orc_num_threads.restype = C.c_int
         L.orc_set_num_threads.argtypes = [C.c_int]
+        L.orc_set_chunk.argtypes = [C.c_int]
 
     # --- norms -----------------------------------------------------------------------
     def rmsnorm(self, x, w, eps=1e-5):
@@ -237,6 +238,10 @@ class Oracle:
 
     def set_num_threads(self, n):
         self.lib.orc_set_num_threads(int(n))
+
+    def set_chunk(self, tokens):
+        """Timed-baseline work splitting (0 = off, the parity setting); see oracle_ops.c."""
+        self.lib.orc_set_chunk(int(tokens))
 
 
 def reference_available() -> bool:

@@ -35,24 +35,45 @@
  *   ss[t]   = sum_c x[c,t]^2                      (:9-12, accumulated channel by channel)
  *   ss[t]   = ss[t]*(1/d) + eps ; rrms = 1/sqrt   (:13-15, eps is the literal 1e-5 there)
  *   out     = (x * rrms) * w[c]                   (:16-19, in that order)               */
-ORC_API void orc_rmsnorm(float *out, const float *x, const float *w, int d, int S, float eps) {
-    float *ss = (float *)calloc((size_t)S, sizeof(float));
+/* `n` tokens starting at x, channel rows `stride` floats apart (stride == n for a whole sequence). */
+static void rmsnorm_s(float *out, const float *x, const float *w, int d, int n, size_t stride, float eps) {
+    float *ss = (float *)calloc((size_t)n, sizeof(float));
     for (int i = 0; i < d; i++)
-        for (int t = 0; t < S; t++) { float v = x[(size_t)i * S + t]; ss[t] += v * v; }
+        for (int t = 0; t < n; t++) { float v = x[(size_t)i * stride + t]; ss[t] += v * v; }
     const float invd = 1.0f / d;
-    for (int t = 0; t < S; t++) ss[t] = 1.0f / sqrtf(ss[t] * invd + eps);
+    for (int t = 0; t < n; t++) ss[t] = 1.0f / sqrtf(ss[t] * invd + eps);
     for (int i = 0; i < d; i++)
-        for (int t = 0; t < S; t++) {
-            float v = x[(size_t)i * S + t] * ss[t];
-            out[(size_t)i * S + t] = v * w[i];
+        for (int t = 0; t < n; t++) {
+            float v = x[(size_t)i * stride + t] * ss[t];
+            out[(size_t)i * stride + t] = v * w[i];
         }
     free(ss);
 }
+ORC_API void orc_rmsnorm(float *out, const float *x, const float *w, int d, int S, float eps) {
+    rmsnorm_s(out, x, w, d, S, (size_t)S, eps);
+}
+
+/* Work splitting for the timed CPU baseline only: with g_chunk > 0 the batched functions cut
+ * every sequence into blocks of g_chunk tokens and spread (sequence, block) pairs over the
+ * OpenMP threads.  Per-token results are unchanged; token-summed results (dw) then add block
+ * sums instead of one running sum, so parity runs keep g_chunk = 0 (the reference's order). */
+static int g_chunk = 0;
+ORC_API void orc_set_chunk(int tokens) { g_chunk = tokens > 0 ? tokens : 0; }
+static int n_blocks(int S) { return g_chunk > 0 ? (S + g_chunk - 1) / g_chunk : 1; }
+static void block_span(int S, int k, int *t0, int *n) {
+    if (g_chunk <= 0) { *t0 = 0; *n = S; return; }
+    *t0 = k * g_chunk;
+    *n = S - *t0 < g_chunk ? S - *t0 : g_chunk;
+}
 
 ORC_API void orc_rmsnorm_batched(float *out, const float *x, const float *w, int B, int d, int S, float eps) {
+    const int nb = n_blocks(S);
     #pragma omp parallel for schedule(static)
-    for (int b = 0; b < B; b++)
-        orc_rmsnorm(out + (size_t)b * d * S, x + (size_t)b * d * S, w, d, S, eps);
+    for (int it = 0; it < B * nb; it++) {
+        int b = it / nb, t0, n;
+        block_span(S, it % nb, &t0, &n);
+        rmsnorm_s(out + (size_t)b * d * S + t0, x + (size_t)b * d * S + t0, w, d, n, (size_t)S, eps);
+    }
 }
 
 /* ------------------------------------------------------------------ RMSNorm backward
@@ -65,25 +86,25 @@ ORC_API void orc_rmsnorm_batched(float *out, const float *x, const float *w, int
  * The reference multiplies BOTH terms of dx by w[c]; this differs from the analytic
  * gradient rrms*(w*dy - x*dot) when w != 1.  `exact` != 0 selects the analytic form, which
  * is what the MIL graph in training/ane_rmsnorm_bwd.h:56,70-74 computes.                 */
-ORC_API void orc_rmsnorm_bwd(float *dx, float *dw, const float *dy, const float *x, const float *w,
-                             int d, int S, float eps, int exact) {
+static void rmsnorm_bwd_s(float *dx, float *dw, const float *dy, const float *x, const float *w,
+                          int d, int S, size_t stride, float eps, int exact) {
     float *ss = (float *)calloc((size_t)S, sizeof(float));
     float *rrms = (float *)malloc((size_t)S * sizeof(float));
     float *dot = (float *)calloc((size_t)S, sizeof(float));
     for (int i = 0; i < d; i++)
-        for (int t = 0; t < S; t++) { float v = x[(size_t)i * S + t]; ss[t] += v * v; }
+        for (int t = 0; t < S; t++) { float v = x[(size_t)i * stride + t]; ss[t] += v * v; }
     const float invd = 1.0f / d;
     for (int t = 0; t < S; t++) rrms[t] = 1.0f / sqrtf(ss[t] * invd + eps);
     for (int i = 0; i < d; i++)
         for (int t = 0; t < S; t++) {
-            float p = dy[(size_t)i * S + t] * x[(size_t)i * S + t];
+            float p = dy[(size_t)i * stride + t] * x[(size_t)i * stride + t];
             dot[t] = p * w[i] + dot[t];
         }
     for (int t = 0; t < S; t++) { float r2 = rrms[t] * rrms[t]; r2 = r2 * invd; dot[t] = dot[t] * r2; }
     for (int i = 0; i < d; i++) {
         float s = 0.0f;
         for (int t = 0; t < S; t++) {
-            size_t k = (size_t)i * S + t;
+            size_t k = (size_t)i * stride + t;
             if (exact) {
                 float a = dy[k] * w[i];
                 float b = x[k] * dot[t];
@@ -101,14 +122,29 @@ ORC_API void orc_rmsnorm_bwd(float *dx, float *dw, const float *dy, const float 
     }
     free(ss); free(rrms); free(dot);
 }
+ORC_API void orc_rmsnorm_bwd(float *dx, float *dw, const float *dy, const float *x, const float *w,
+                             int d, int S, float eps, int exact) {
+    rmsnorm_bwd_s(dx, dw, dy, x, w, d, S, (size_t)S, eps, exact);
+}
 
 /* Batched form.  dw accumulates over the B sequences in order b = 0..B-1, as the reference's
  * accumulation steps would (training_dynamic/train.m:588,719 called once per step). */
 ORC_API void orc_rmsnorm_bwd_batched(float *dx, float *dw, const float *dy, const float *x, const float *w,
                                      int B, int d, int S, float eps, int exact) {
-    for (int b = 0; b < B; b++)
-        orc_rmsnorm_bwd(dx + (size_t)b * d * S, dw, dy + (size_t)b * d * S, x + (size_t)b * d * S,
-                        w, d, S, eps, exact);
+    /* per-sequence dw rows, then added in order b = 0..B-1: the same additions as accumulating
+     * into dw call after call, but the sequences can run on separate threads */
+    const int nb = n_blocks(S);
+    float *dwl = (float *)calloc((size_t)B * nb * d, sizeof(float));
+    #pragma omp parallel for schedule(static)
+    for (int it = 0; it < B * nb; it++) {
+        int b = it / nb, t0, n;
+        block_span(S, it % nb, &t0, &n);
+        size_t o = (size_t)b * d * S + t0;
+        rmsnorm_bwd_s(dx + o, dwl + (size_t)it * d, dy + o, x + o, w, d, n, (size_t)S, eps, exact);
+    }
+    for (int it = 0; it < B * nb; it++)
+        for (int i = 0; i < d; i++) dw[i] += dwl[(size_t)it * d + i];
+    free(dwl);
 }
 
 /* ------------------------------------------------------------------ DeepNet-alpha residual
@@ -116,14 +152,17 @@ ORC_API void orc_rmsnorm_bwd_batched(float *dx, float *dw, const float *dy, cons
  * training/training_dynamic/mil_dynamic.h:279-283  x_next = x2 + alpha*ffn_out
  * training/train_large.m:427,442 is the alpha = 1 case.                                  */
 ORC_API void orc_residual(float *out, const float *x, const float *f, float alpha, size_t n) {
+    #pragma omp parallel for schedule(static)
     for (size_t i = 0; i < n; i++) out[i] = f[i] * alpha + x[i];
 }
 /* train.m:523,595  y = alpha * x ;  train.m:497 dlogits *= loss_scale */
 ORC_API void orc_scale(float *out, const float *x, float alpha, size_t n) {
+    #pragma omp parallel for schedule(static)
     for (size_t i = 0; i < n; i++) out[i] = x[i] * alpha;
 }
 /* train.m:590,714,721  out = a + b */
 ORC_API void orc_add(float *out, const float *a, const float *b, size_t n) {
+    #pragma omp parallel for schedule(static)
     for (size_t i = 0; i < n; i++) out[i] = a[i] + b[i];
 }
 
@@ -131,6 +170,7 @@ ORC_API void orc_add(float *out, const float *a, const float *b, size_t n) {
  * training/forward.h:101  silu_f(x) = x / (1 + expf(-x));  :149-151  out = silu_f(h1) * h3
  * (the ANE graphs compute h1*sigmoid(h1)*h3: stories_mil.h:99-101, mil_dynamic.h:264-266) */
 ORC_API void orc_swiglu(float *out, const float *h1, const float *h3, size_t n) {
+    #pragma omp parallel for schedule(static)
     for (size_t i = 0; i < n; i++) {
         float s = h1[i] / (1.0f + expf(-h1[i]));
         out[i] = s * h3[i];
@@ -145,6 +185,7 @@ ORC_API void orc_swiglu(float *out, const float *h1, const float *h3, size_t n) 
  *   dh1  = (dsilu * h3) * t2                                                            */
 ORC_API void orc_swiglu_bwd(float *dh1, float *dh3, const float *h1, const float *h3,
                             const float *dsilu, size_t n) {
+    #pragma omp parallel for schedule(static)
     for (size_t i = 0; i < n; i++) {
         float e = expf(h1[i] * -1.0f);
         float sig = 1.0f / (e + 1.0f);
@@ -167,7 +208,7 @@ ORC_API void orc_swiglu_bwd(float *dh1, float *dh3, const float *h1, const float
  *   freq  = 1 / powf(base, 2*i/hd)   (cpu_ops.h:172, base is the literal 10000 there)
  *   theta = p * freq ; p counted from pos0 (0 in the reference)
  * inverse != 0 gives the backward (transposed) rotation (a cos + b sin, -a sin + b cos). */
-ORC_API void orc_rope(float *x, int seq, int dim, int hd, float base, int pos0, int inverse) {
+static void rope_s(float *x, int seq, size_t stride, int dim, int hd, float base, int pos0, int inverse) {
     int nheads = dim / hd;
     for (int h = 0; h < nheads; h++)
         for (int i = 0; i < hd / 2; i++) {
@@ -175,17 +216,25 @@ ORC_API void orc_rope(float *x, int seq, int dim, int hd, float base, int pos0, 
             for (int p = 0; p < seq; p++) {
                 float theta = (p + pos0) * freq;
                 float c = cosf(theta), s = sinf(theta);
-                size_t i0 = (size_t)(h * hd + 2 * i) * seq + p;
-                size_t i1 = (size_t)(h * hd + 2 * i + 1) * seq + p;
+                size_t i0 = (size_t)(h * hd + 2 * i) * stride + p;
+                size_t i1 = (size_t)(h * hd + 2 * i + 1) * stride + p;
                 float v0 = x[i0], v1 = x[i1];
                 if (inverse) { x[i0] = v0 * c + v1 * s;  x[i1] = -v0 * s + v1 * c; }
                 else         { x[i0] = v0 * c - v1 * s;  x[i1] = v0 * s + v1 * c; }
             }
         }
 }
+ORC_API void orc_rope(float *x, int seq, int dim, int hd, float base, int pos0, int inverse) {
+    rope_s(x, seq, (size_t)seq, dim, hd, base, pos0, inverse);
+}
 ORC_API void orc_rope_batched(float *x, int B, int seq, int dim, int hd, float base, int pos0, int inverse) {
+    const int nb = n_blocks(seq);
     #pragma omp parallel for schedule(static)
-    for (int b = 0; b < B; b++) orc_rope(x + (size_t)b * dim * seq, seq, dim, hd, base, pos0, inverse);
+    for (int it = 0; it < B * nb; it++) {
+        int b = it / nb, t0, n;
+        block_span(seq, it % nb, &t0, &n);
+        rope_s(x + (size_t)b * dim * seq + t0, n, (size_t)seq, dim, hd, base, pos0 + t0, inverse);
+    }
 }
 
 /* ------------------------------------------------------------------ per-head QK-RMSNorm
@@ -204,24 +253,47 @@ ORC_API void orc_qknorm_bwd(float *dx, float *dw, const float *dy, const float *
 /* Fused forward: out = rope(qknorm(x)); fused backward: dx = qknorm_bwd(rope^-1(dy), x). */
 ORC_API void orc_qknorm_rope_batched(float *out, const float *x, const float *w, int B, int heads, int hd,
                                      int S, float eps, float base, int pos0) {
+    const int nb = n_blocks(S);
     #pragma omp parallel for schedule(static)
-    for (int b = 0; b < B; b++) {
-        size_t o = (size_t)b * heads * hd * S;
-        orc_qknorm(out + o, x + o, w, heads, hd, S, eps);
-        orc_rope(out + o, S, heads * hd, hd, base, pos0, 0);
+    for (int it = 0; it < B * nb; it++) {
+        int b = it / nb, t0, n;
+        block_span(S, it % nb, &t0, &n);
+        size_t o = (size_t)b * heads * hd * S + t0;
+        for (int h = 0; h < heads; h++)
+            rmsnorm_s(out + o + (size_t)h * hd * S, x + o + (size_t)h * hd * S, w, hd, n, (size_t)S, eps);
+        rope_s(out + o, n, (size_t)S, heads * hd, hd, base, pos0 + t0, 0);
     }
 }
 ORC_API void orc_rope_qknorm_bwd_batched(float *dx, float *dw, const float *dy, const float *x, const float *w,
                                          int B, int heads, int hd, int S, float eps, float base, int pos0,
                                          int exact) {
-    size_t n = (size_t)heads * hd * S;
-    float *g = (float *)malloc(n * sizeof(float));
-    for (int b = 0; b < B; b++) {
-        memcpy(g, dy + (size_t)b * n, n * sizeof(float));
-        orc_rope(g, S, heads * hd, hd, base, pos0, 1);
-        orc_qknorm_bwd(dx + (size_t)b * n, dw, g, x + (size_t)b * n, w, heads, hd, S, eps, exact);
+    const size_t n = (size_t)heads * hd * S;
+    const int nb = n_blocks(S);
+    float *dwl = (float *)calloc((size_t)B * nb * heads * hd, sizeof(float));
+    #pragma omp parallel for schedule(static)
+    for (int it = 0; it < B * nb; it++) {
+        int b = it / nb, t0, m;
+        block_span(S, it % nb, &t0, &m);
+        /* g = rope^-1(dy) for this block, packed with row stride m */
+        float *g = (float *)malloc((size_t)heads * hd * m * sizeof(float));
+        for (int c = 0; c < heads * hd; c++)
+            memcpy(g + (size_t)c * m, dy + (size_t)b * n + (size_t)c * S + t0, (size_t)m * sizeof(float));
+        rope_s(g, m, (size_t)m, heads * hd, hd, base, pos0 + t0, 1);
+        /* the norm backward reads g with stride m and x / dx with stride S: go head by head through a
+         * strided copy of x so one routine serves both */
+        float *xb = (float *)malloc((size_t)hd * m * sizeof(float));
+        float *db = (float *)malloc((size_t)hd * m * sizeof(float));
+        for (int h = 0; h < heads; h++) {   /* one dw row per (sequence, block, head), summed in order below */
+            const size_t o = (size_t)b * n + (size_t)h * hd * S + t0;
+            for (int c = 0; c < hd; c++) memcpy(xb + (size_t)c * m, x + o + (size_t)c * S, (size_t)m * sizeof(float));
+            rmsnorm_bwd_s(db, dwl + ((size_t)it * heads + h) * hd, g + (size_t)h * hd * m, xb, w, hd, m, (size_t)m, eps, exact);
+            for (int c = 0; c < hd; c++) memcpy(dx + o + (size_t)c * S, db + (size_t)c * m, (size_t)m * sizeof(float));
+        }
+        free(g); free(xb); free(db);
     }
-    free(g);
+    for (size_t r = 0; r < (size_t)B * nb * heads; r++)
+        for (int i = 0; i < hd; i++) dw[i] += dwl[r * hd + i];
+    free(dwl);
 }
 
 /* ------------------------------------------------------------------ embedding gather / scatter-add
