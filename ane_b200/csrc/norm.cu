@@ -345,6 +345,77 @@ static int check_bcs(const char *fn, int B, int C, int S) {
     return ANE_CUDA_OK;
 }
 
+
+// ------------------------------------------------------------------ allocation-free backward
+// The backward kernel needs a [blocks][C] matrix of dw partials.  The regular entry point takes
+// it from the library's grow-only scratch range, i.e. it may call cudaMalloc.  Some callers
+// cannot tolerate that: a host process whose framework has already reserved the whole device
+// for its own caching pool (a cudaMalloc from a side library then fails or fragments the
+// pool), or a latency-critical loop that must never hit cudaMalloc's device-wide
+// synchronisation.  For them the same kernels run with the partials in a fixed array that is
+// part of the module image: every GPU that loads this library holds
+// STATIC_MAX_BLOCKS * STATIC_MAX_C * 4 bytes (2.3 MiB) of it from load until the process exits.
+constexpr int STATIC_MAX_C = 2048;
+constexpr int STATIC_MAX_BLOCKS = 296;   // two resident blocks per SM on a 148-SM part
+static __device__ __align__(256) float g_static_dw_partials[(size_t)STATIC_MAX_BLOCKS * STATIC_MAX_C];
+
+// In host code the array's name is only a handle for the runtime, not a device address; the
+// address has to be asked for, per device, with that device current.
+constexpr int STATIC_MAX_DEVICES = 64;
+static float *g_static_dw_addr[STATIC_MAX_DEVICES] = {};
+static int g_static_sm_count[STATIC_MAX_DEVICES] = {};
+
+static int static_scratch_for_current_device(float **addr, int *sm_count) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(ANE_CUDA_ERR_CUDA, "rmsnorm_bwd_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= STATIC_MAX_DEVICES) return fail(ANE_CUDA_ERR_UNSUPPORTED, "rmsnorm_bwd_static: device ordinal %d not supported", dev);
+    if (!g_static_dw_addr[dev]) {       // first call on this device: resolve and remember
+        int major = 0, sms = 0;
+        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return fail(ANE_CUDA_ERR_CUDA, "rmsnorm_bwd_static: cudaDeviceGetAttribute failed: %s", cudaGetErrorString(e));
+        if (major != 10) return fail(ANE_CUDA_ERR_UNSUPPORTED, "rmsnorm_bwd_static: device %d is not sm_100 (the kernels are built for sm_100a only)", dev);
+        float *p = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_static_dw_partials);
+        if (e != cudaSuccess || !p) return fail(ANE_CUDA_ERR_CUDA, "rmsnorm_bwd_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        g_static_sm_count[dev] = sms;
+        g_static_dw_addr[dev] = p;
+    }
+    *addr = g_static_dw_addr[dev];
+    *sm_count = g_static_sm_count[dev];
+    return ANE_CUDA_OK;
+}
+
+template <typename T, bool HAS_ADD>
+static int launch_rmsnorm_bwd_static(cudaStream_t st, float *partial, int sm_count, int B, int C, int S, void *dx, float *dw,
+                                     const void *dy, const void *x, const float *w, const void *add, float eps, unsigned flags) {
+    constexpr int VEC = Elt<T>::VEC;
+    const bool vec = (S % VEC == 0) && aligned16(dx) && aligned16(dy) && aligned16(x) && (!HAS_ADD || aligned16(add));
+    const size_t smem = (size_t)C * sizeof(float);
+    int cap = 2 * sm_count;
+    if (cap > STATIC_MAX_BLOCKS) cap = STATIC_MAX_BLOCKS;
+    int grid;
+    if (vec) {
+        constexpr int LG = 8;
+        const int tps = (S + LG * VEC - 1) / (LG * VEC);
+        const int ntiles = B * tps;
+        grid = ntiles < cap ? ntiles : cap;
+        rmsnorm_bwd_kernel<T, VEC, LG, HAS_ADD><<<grid, NORM_THREADS, smem, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w,
+                                                                                 (const T *)add, C, S, tps, ntiles, eps, flags);
+    } else {
+        constexpr int LG = 32;
+        const int tps = (S + LG - 1) / LG;
+        const int ntiles = B * tps;
+        grid = ntiles < cap ? ntiles : cap;
+        rmsnorm_bwd_kernel<T, 1, LG, HAS_ADD><<<grid, NORM_THREADS, smem, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w,
+                                                                               (const T *)add, C, S, tps, ntiles, eps, flags);
+    }
+    dw_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(dw, partial, grid, C);
+    ANE_LAUNCH_OK(2);
+    return ANE_CUDA_OK;
+}
+
 }  // namespace ane
 
 using namespace ane;
@@ -379,6 +450,32 @@ int ane_cuda_rmsnorm_bwd_dev(void *stream, ane_dtype dtype, int B, int C, int S,
     ANE_REQUIRE(flags == ANE_NORM_BWD_REFERENCE || flags == ANE_NORM_BWD_EXACT, "%s: bad flags %u", __func__, flags);
     if (int rc = check_bcs(__func__, B, C, S)) return rc;
     return rmsnorm_bwd_any((cudaStream_t)stream, dtype, B, C, S, dx, dw, dy, x, w, add, eps, flags);
+}
+
+int ane_cuda_rmsnorm_bwd_static_dev(void *stream, ane_dtype dtype, int B, int C, int S, void *dx, float *dw, const void *dy,
+                                    const void *x, const float *w, const void *add, float eps, unsigned flags) {
+    // Deliberately independent of ane_cuda_init(): that call allocates, this path must not.
+    ANE_REQUIRE(dx && dw && dy && x && w, "%s: null pointer", __func__);
+    ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
+    ANE_REQUIRE(flags == ANE_NORM_BWD_REFERENCE || flags == ANE_NORM_BWD_EXACT, "%s: bad flags %u", __func__, flags);
+    ANE_REQUIRE(B >= 1 && C >= 1 && S >= 1, "%s: B, C, S must be positive (got %d, %d, %d)", __func__, B, C, S);
+    if (C > STATIC_MAX_C)
+        return fail(ANE_CUDA_ERR_UNSUPPORTED, "%s: C = %d exceeds the built-in scratch (at most %d channels); use ane_cuda_rmsnorm_bwd_dev",
+                    __func__, C, STATIC_MAX_C);
+    if ((long long)B * ((S + 7) / 8) > 0x7fffffffLL) return fail(ANE_CUDA_ERR_UNSUPPORTED, "%s: too many token tiles", __func__);
+    float *partial = nullptr;
+    int sms = 0;
+    if (int rc = static_scratch_for_current_device(&partial, &sms)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    // Nothing in the scratch has to start at zero: every block overwrites its whole row of
+    // partials before the column sums read rows 0 .. grid-1, so leftovers of earlier calls are
+    // never read.
+    if (add) {
+        ANE_DISPATCH_DTYPE(dtype, T, return (launch_rmsnorm_bwd_static<T, true>(st, partial, sms, B, C, S, dx, dw, dy, x, w, add, eps, flags)));
+    } else {
+        ANE_DISPATCH_DTYPE(dtype, T, return (launch_rmsnorm_bwd_static<T, false>(st, partial, sms, B, C, S, dx, dw, dy, x, w, nullptr, eps, flags)));
+    }
+    return ANE_CUDA_OK;
 }
 
 }  // extern "C"

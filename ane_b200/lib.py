@@ -89,6 +89,7 @@ PROTOTYPES = {
     # device-resident operators
     "ane_cuda_rmsnorm_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _f]),
     "ane_cuda_rmsnorm_bwd_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _u]),
+    "ane_cuda_rmsnorm_bwd_static_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _u]),
     "ane_cuda_residual_dev": (_i, [_vp, _i, _sz, _vp, _vp, _vp, _f]),
     "ane_cuda_scale_dev": (_i, [_vp, _i, _sz, _vp, _vp, _f]),
     "ane_cuda_residual_rmsnorm_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _f]),

@@ -169,6 +169,25 @@ int ane_cuda_rmsnorm_dev(void *stream, ane_dtype dtype, int B, int C, int S,
 int ane_cuda_rmsnorm_bwd_dev(void *stream, ane_dtype dtype, int B, int C, int S,
                              void *dx, float *dw, const void *dy, const void *x, const float *w,
                              const void *add, float eps, unsigned flags);
+/* Same operator and arguments as ane_cuda_rmsnorm_bwd_dev, for callers that must not cause a
+ * device allocation -- e.g. a process whose framework has reserved the whole GPU for its own
+ * memory pool, so that a cudaMalloc from this library would fail or fragment the pool, or a
+ * latency-critical loop that cannot take cudaMalloc's device-wide synchronisation.  It has no
+ * counterpart in the reference (whose rmsnorm_bwd mallocs its scratch on every call,
+ * stories_cpu_ops.h:24-25).  The dw partials live in a fixed 2.3 MiB array inside the library
+ * image (held on every GPU that loads the library until the process exits), so:
+ *   - C must be <= 2048 (ANE_CUDA_ERR_UNSUPPORTED otherwise; B and S are not limited);
+ *   - it does not need ane_cuda_init(), and calls no cudaMalloc / cudaFree or any allocating
+ *     library routine; the caller passes inputs and outputs on the CURRENT device;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress) -- make that first call before any stream capture;
+ *   - all calls share the one array: calls that may overlap on the GPU (different streams,
+ *     or other threads) race on it.  Keep them on one stream, or order them with events.
+ * Results: dx is bit-identical to ane_cuda_rmsnorm_bwd_dev; dw may differ in the last bits
+ * (the partials are split over at most 296 blocks, a different fixed summation order). */
+int ane_cuda_rmsnorm_bwd_static_dev(void *stream, ane_dtype dtype, int B, int C, int S,
+                                    void *dx, float *dw, const void *dy, const void *x, const float *w,
+                                    const void *add, float eps, unsigned flags);
 /* a3: out = f*alpha + x (flat, n elements)                            train.m:460, mil_dynamic.h:279-283 */
 int ane_cuda_residual_dev(void *stream, ane_dtype dtype, size_t n, void *out, const void *x, const void *f,
                           float alpha);
