@@ -34,6 +34,16 @@ int fail(int code, const char *fmt, ...) {
 
 void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+struct Knob { char name[32]; int value; };
+static Knob g_knobs[32];
+static int g_nknobs = 0;
+
+int tuning(const char *name, int dflt) {
+    for (int i = 0; i < g_nknobs; i++)
+        if (strcmp(g_knobs[i].name, name) == 0) return g_knobs[i].value;
+    return dflt;
+}
+
 void *workspace(size_t bytes) {
     Context &c = g_ctx;
     if (bytes <= c.ws_bytes && c.ws) return c.ws;
@@ -93,6 +103,16 @@ using namespace ane;
 extern "C" {
 
 int ane_cuda_version(void) { return ANE_CUDA_VERSION; }
+
+int ane_cuda_set_tuning(const char *name, int value) {
+    if (!name || strlen(name) >= sizeof(g_knobs[0].name)) return fail(ANE_CUDA_ERR_INVALID, "ane_cuda_set_tuning: bad knob name");
+    for (int i = 0; i < g_nknobs; i++)
+        if (strcmp(g_knobs[i].name, name) == 0) { g_knobs[i].value = value; return ANE_CUDA_OK; }
+    if (g_nknobs >= 32) return fail(ANE_CUDA_ERR_INVALID, "ane_cuda_set_tuning: too many knobs");
+    strcpy(g_knobs[g_nknobs].name, name);
+    g_knobs[g_nknobs++].value = value;
+    return ANE_CUDA_OK;
+}
 
 const char *ane_cuda_last_error(void) { return g_err; }
 

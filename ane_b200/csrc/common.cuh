@@ -29,6 +29,8 @@ int fail(int code, const char *fmt, ...);
 void note_launch(int n = 1);
 // Returns a device scratch range of at least `bytes` (256-byte aligned) or nullptr.
 void *workspace(size_t bytes);
+// Kernel-selection knobs (ane_cuda_set_tuning); `dflt` when the knob was never set.
+int tuning(const char *name, int dflt);
 
 #define ANE_REQUIRE_INIT() do { if (!::ane::ctx().inited) return ::ane::fail(ANE_CUDA_ERR_NOT_INIT, "%s: call ane_cuda_init first", __func__); } while (0)
 #define ANE_REQUIRE(cond, ...) do { if (!(cond)) return ::ane::fail(ANE_CUDA_ERR_INVALID, __VA_ARGS__); } while (0)
@@ -64,6 +66,13 @@ template <> struct Elt<float> {
     __device__ __forceinline__ static uint4 pack(const float *f) {
         return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
     }
+    __device__ __forceinline__ static void unpack2(const uint4 &r, float2 *p) {
+        p[0] = make_float2(__uint_as_float(r.x), __uint_as_float(r.y));
+        p[1] = make_float2(__uint_as_float(r.z), __uint_as_float(r.w));
+    }
+    __device__ __forceinline__ static uint4 pack2(const float2 *p) {
+        return make_uint4(__float_as_uint(p[0].x), __float_as_uint(p[0].y), __float_as_uint(p[1].x), __float_as_uint(p[1].y));
+    }
 };
 template <> struct Elt<__nv_bfloat16> {
     static constexpr int VEC = 8;
@@ -83,6 +92,20 @@ template <> struct Elt<__nv_bfloat16> {
         for (int i = 0; i < 4; i++) {
             __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
             w[i] = *reinterpret_cast<uint32_t *>(&p);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ __forceinline__ static void unpack2(const uint4 &r, float2 *p) {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) p[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+    }
+    __device__ __forceinline__ static uint4 pack2(const float2 *p) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            __nv_bfloat162 q = __floats2bfloat162_rn(p[i].x, p[i].y);
+            w[i] = *reinterpret_cast<uint32_t *>(&q);
         }
         return make_uint4(w[0], w[1], w[2], w[3]);
     }
@@ -109,7 +132,127 @@ template <> struct Elt<__half> {
         }
         return make_uint4(w[0], w[1], w[2], w[3]);
     }
+    __device__ __forceinline__ static void unpack2(const uint4 &r, float2 *p) {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) p[i] = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+    }
+    __device__ __forceinline__ static uint4 pack2(const float2 *p) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            __half2 q = __floats2half2_rn(p[i].x, p[i].y);
+            w[i] = *reinterpret_cast<uint32_t *>(&q);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
 };
+
+// ------------------------------------------------------------------ packed fp32 lanes
+// Blackwell issues two fp32 operations per instruction on register pairs (add/sub/mul/fma
+// .f32x2).  The reduction kernels are close to issue-bound in bf16 (about 20 B of HBM traffic per
+// SM and clock against 4 issue slots), so their per-element math runs on V<N>: N fp32 lanes
+// held as N/2 pairs.  Every packed operation rounds each lane exactly like the scalar IEEE
+// operation, so results do not depend on the packing.
+__device__ __forceinline__ float2 f2_fma(float2 a, float2 b, float2 c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long *>(&a)),
+        "l"(*reinterpret_cast<unsigned long long *>(&b)), "l"(*reinterpret_cast<unsigned long long *>(&c)));
+    return *reinterpret_cast<float2 *>(&d);
+}
+__device__ __forceinline__ float2 f2_mul(float2 a, float2 b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long *>(&a)),
+        "l"(*reinterpret_cast<unsigned long long *>(&b)));
+    return *reinterpret_cast<float2 *>(&d);
+}
+__device__ __forceinline__ float2 f2_add(float2 a, float2 b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long *>(&a)),
+        "l"(*reinterpret_cast<unsigned long long *>(&b)));
+    return *reinterpret_cast<float2 *>(&d);
+}
+__device__ __forceinline__ float2 f2_sub(float2 a, float2 b) {
+    unsigned long long d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long *>(&a)),
+        "l"(*reinterpret_cast<unsigned long long *>(&b)));
+    return *reinterpret_cast<float2 *>(&d);
+}
+
+template <int N> struct V {
+    static_assert(N % 2 == 0, "V<N> holds pairs");
+    float2 p[N / 2];
+    __device__ __forceinline__ static V splat(float s) {
+        V r;
+#pragma unroll
+        for (int i = 0; i < N / 2; i++) r.p[i] = make_float2(s, s);
+        return r;
+    }
+    __device__ __forceinline__ float get(int j) const { return (j & 1) ? p[j >> 1].y : p[j >> 1].x; }
+    __device__ __forceinline__ void set(int j, float v) { if (j & 1) p[j >> 1].y = v; else p[j >> 1].x = v; }
+    __device__ __forceinline__ float hsum() const {
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < N / 2; i++) { s += p[i].x; s += p[i].y; }
+        return s;
+    }
+};
+template <> struct V<1> {
+    float a;
+    __device__ __forceinline__ static V splat(float s) { V r; r.a = s; return r; }
+    __device__ __forceinline__ float get(int) const { return a; }
+    __device__ __forceinline__ void set(int, float v) { a = v; }
+    __device__ __forceinline__ float hsum() const { return a; }
+};
+template <int N> __device__ __forceinline__ V<N> vmul(const V<N> &a, const V<N> &b) {
+    V<N> r;
+#pragma unroll
+    for (int i = 0; i < N / 2; i++) r.p[i] = f2_mul(a.p[i], b.p[i]);
+    return r;
+}
+template <int N> __device__ __forceinline__ V<N> vadd(const V<N> &a, const V<N> &b) {
+    V<N> r;
+#pragma unroll
+    for (int i = 0; i < N / 2; i++) r.p[i] = f2_add(a.p[i], b.p[i]);
+    return r;
+}
+template <int N> __device__ __forceinline__ V<N> vsub(const V<N> &a, const V<N> &b) {
+    V<N> r;
+#pragma unroll
+    for (int i = 0; i < N / 2; i++) r.p[i] = f2_sub(a.p[i], b.p[i]);
+    return r;
+}
+template <int N> __device__ __forceinline__ V<N> vfma(const V<N> &a, const V<N> &b, const V<N> &c) {
+    V<N> r;
+#pragma unroll
+    for (int i = 0; i < N / 2; i++) r.p[i] = f2_fma(a.p[i], b.p[i], c.p[i]);
+    return r;
+}
+template <> __device__ __forceinline__ V<1> vmul<1>(const V<1> &a, const V<1> &b) { V<1> r; r.a = __fmul_rn(a.a, b.a); return r; }
+template <> __device__ __forceinline__ V<1> vadd<1>(const V<1> &a, const V<1> &b) { V<1> r; r.a = __fadd_rn(a.a, b.a); return r; }
+template <> __device__ __forceinline__ V<1> vsub<1>(const V<1> &a, const V<1> &b) { V<1> r; r.a = __fsub_rn(a.a, b.a); return r; }
+template <> __device__ __forceinline__ V<1> vfma<1>(const V<1> &a, const V<1> &b, const V<1> &c) { V<1> r; r.a = fmaf(a.a, b.a, c.a); return r; }
+
+// Shared-memory transfer of the N lanes of a V<N> as 16-byte words: a quarter-warp of such
+// stores covers one contiguous run, so rows of per-token partials are written without bank
+// conflicts (scalar stores of lane j from 8 lanes x 4 row groups would collide 8 ways).
+template <int N> __device__ __forceinline__ void lanes_to_smem(float *dst, const V<N> &v) {
+#pragma unroll
+    for (int i = 0; i < N / 4; i++)
+        *reinterpret_cast<float4 *>(dst + 4 * i) = make_float4(v.p[2 * i].x, v.p[2 * i].y, v.p[2 * i + 1].x, v.p[2 * i + 1].y);
+}
+template <> __device__ __forceinline__ void lanes_to_smem<1>(float *dst, const V<1> &v) { dst[0] = v.a; }
+template <int N> __device__ __forceinline__ V<N> lanes_from_smem(const float *src) {
+    V<N> v;
+#pragma unroll
+    for (int i = 0; i < N / 4; i++) {
+        const float4 q = *reinterpret_cast<const float4 *>(src + 4 * i);
+        v.p[2 * i] = make_float2(q.x, q.y);
+        v.p[2 * i + 1] = make_float2(q.z, q.w);
+    }
+    return v;
+}
+template <> __device__ __forceinline__ V<1> lanes_from_smem<1>(const float *src) { V<1> v; v.a = src[0]; return v; }
 
 // A group of VEC consecutive elements held raw: one 16-byte word when VEC is the full vector
 // width of T, one element when VEC == 1 (the path for shapes that break 16-byte alignment).
@@ -122,6 +265,8 @@ template <typename T> struct Raw<T, 1> {
     __device__ __forceinline__ void store_stream(T *p) const { __stcs(p, v); }
     __device__ __forceinline__ void unpack(float *f) const { f[0] = Elt<T>::to_f(v); }
     __device__ __forceinline__ void pack(const float *f) { v = Elt<T>::from_f(f[0]); }
+    __device__ __forceinline__ V<1> get() const { V<1> r; r.a = Elt<T>::to_f(v); return r; }
+    __device__ __forceinline__ void put(const V<1> &x) { v = Elt<T>::from_f(x.a); }
 };
 #define ANE_RAW_FULL(T)                                                                                   \
     template <> struct Raw<T, Elt<T>::VEC> {                                                              \
@@ -132,6 +277,8 @@ template <typename T> struct Raw<T, 1> {
         __device__ __forceinline__ void store_stream(T *p) const { __stcs(reinterpret_cast<uint4 *>(p), v); } \
         __device__ __forceinline__ void unpack(float *f) const { Elt<T>::unpack(v, f); }                  \
         __device__ __forceinline__ void pack(const float *f) { v = Elt<T>::pack(f); }                     \
+        __device__ __forceinline__ V<Elt<T>::VEC> get() const { V<Elt<T>::VEC> r; Elt<T>::unpack2(v, r.p); return r; } \
+        __device__ __forceinline__ void put(const V<Elt<T>::VEC> &x) { v = Elt<T>::pack2(x.p); }          \
     };
 ANE_RAW_FULL(float)
 ANE_RAW_FULL(__nv_bfloat16)

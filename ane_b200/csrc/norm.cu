@@ -3,18 +3,22 @@
 // the backward.
 //
 // Data layout and work split.  S is the contiguous axis, the reduction runs over C with
-// stride S.  A block owns a token tile of LG*VEC tokens (one 128-byte line per channel row for
-// the vector paths) of one sequence: LG adjacent lanes cover the tile with 16-byte loads and
-// THREADS/LG "row groups" stride over the channels.  Per-token partial sums meet in shared
-// memory.  Each tensor is swept twice (reduce, then normalise); the tile of one block is at
-// most a few hundred KB, so the second sweep is served by the L2 cache and HBM sees every
-// input byte once.
+// stride S.  A block owns a token tile of LG*VEC tokens of one sequence: LG adjacent lanes
+// cover the tile with 16-byte loads and THREADS/LG "row groups" stride over the channels.
+// Per-token partial sums meet in shared memory.  Two families:
+//   * two-sweep kernels (this file): each tensor is swept twice (reduce, then normalise); a
+//     block's tile is at most a few hundred KB, so the second sweep is served by L2 and HBM
+//     sees every input byte once.  Any C, any alignment (VEC = 1 path).
+//   * register-resident kernels (norm_rr.cuh): the whole tile stays in registers between
+//     the reduction and the store; used when C fits the per-thread budget.
+// The per-element math runs on packed fp32 pairs (V<VEC>, common.cuh).
 //
 // dw (a sum over all tokens) is made deterministic without float atomics: the backward kernel
 // is persistent, every block keeps dw partials for its tiles in shared memory in a fixed tile
 // order, writes them to a scratch matrix [blocks][C], and a second kernel adds the rows in
 // block order.
 #include "common.cuh"
+#include "norm_rr.cuh"
 
 namespace ane {
 
@@ -27,19 +31,19 @@ rmsnorm_fwd_kernel(T *out, T *x2out, const T *x, const T *f,
                    const float *__restrict__ w, int C, int S, int tiles_per_seq, float alpha, float eps) {
     constexpr int R = NORM_THREADS / LG;
     constexpr int TW = LG * VEC;
-    __shared__ float red[R][TW];
-    __shared__ float tot[TW];
+    __shared__ __align__(16) float red[R][TW];
+    __shared__ __align__(16) float tot[TW];
 
     const int b = blockIdx.x / tiles_per_seq;
     const int t0 = (blockIdx.x % tiles_per_seq) * TW;
     const int lg = threadIdx.x % LG, rg = threadIdx.x / LG;
     const int t = t0 + lg * VEC;
     const bool active = t < S;
-    const size_t base = (size_t)b * C * S + t;
+    const size_t base = (size_t)b * C * S + t + (size_t)rg * S;
+    const size_t step = (size_t)R * S;
+    const V<VEC> valpha = V<VEC>::splat(alpha);
 
-    float ss[VEC];
-#pragma unroll
-    for (int j = 0; j < VEC; j++) ss[j] = 0.0f;
+    V<VEC> ss = V<VEC>::splat(0.0f);
 
     // sweep 1: sum of squares (and, when fused, x2 = f*alpha + x written out)
     for (int cb = 0; cb < C; cb += R * NORM_U) {
@@ -48,11 +52,12 @@ rmsnorm_fwd_kernel(T *out, T *x2out, const T *x, const T *f,
         for (int u = 0; u < NORM_U; u++) {
             const int c = cb + u * R + rg;
             if (active && c < C) {
+                const size_t o = base + (size_t)(cb / R + u) * step;
                 if (FUSE_RES) {
-                    rx[u].load_stream(x + base + (size_t)c * S);
-                    rf[u].load_stream(f + base + (size_t)c * S);
+                    rx[u].load_stream(x + o);
+                    rf[u].load_stream(f + o);
                 } else {
-                    rx[u].load(x + base + (size_t)c * S);
+                    rx[u].load(x + o);
                 }
             }
         }
@@ -60,36 +65,28 @@ rmsnorm_fwd_kernel(T *out, T *x2out, const T *x, const T *f,
         for (int u = 0; u < NORM_U; u++) {
             const int c = cb + u * R + rg;
             if (active && c < C) {
-                float v[VEC];
-                rx[u].unpack(v);
+                V<VEC> v = rx[u].get();
                 if (FUSE_RES) {
-                    float fv[VEC];
-                    rf[u].unpack(fv);
-#pragma unroll
-                    for (int j = 0; j < VEC; j++) v[j] = round_through<T>(__fadd_rn(__fmul_rn(fv[j], alpha), v[j]));
+                    v = vadd(vmul(rf[u].get(), valpha), v);              // train.m:460, two roundings
                     Raw<T, VEC> o;
-                    o.pack(v);
-                    o.store(x2out + base + (size_t)c * S);   // stays in L2 for sweep 2
+                    o.put(v);
+                    o.store(x2out + base + (size_t)(cb / R + u) * step);   // stays in L2 for sweep 2
+                    v = o.get();                                          // the stored (rounded) value
                 }
-#pragma unroll
-                for (int j = 0; j < VEC; j++) ss[j] += v[j] * v[j];
+                ss = vfma(v, v, ss);
             }
         }
     }
-#pragma unroll
-    for (int j = 0; j < VEC; j++) red[rg][lg * VEC + j] = ss[j];
+    lanes_to_smem<VEC>(&red[rg][lg * VEC], ss);
     __syncthreads();
-    if (threadIdx.x < TW) {
+    if (threadIdx.x < TW) {       // one thread per token: column sum, then rrms once for everybody
         float s = 0.0f;
 #pragma unroll 8
         for (int r = 0; r < R; r++) s += red[r][threadIdx.x];
-        tot[threadIdx.x] = s;
+        tot[threadIdx.x] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s, 1.0f / (float)C), eps));
     }
     __syncthreads();
-    const float invd = 1.0f / (float)C;
-    float rr[VEC];
-#pragma unroll
-    for (int j = 0; j < VEC; j++) rr[j] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(tot[lg * VEC + j], invd), eps));
+    const V<VEC> rr = lanes_from_smem<VEC>(&tot[lg * VEC]);
 
     // sweep 2: out = (x * rrms) * w[c]          (stories_cpu_ops.h:16-19, in that order)
     const T *src = FUSE_RES ? x2out : x;
@@ -99,41 +96,39 @@ rmsnorm_fwd_kernel(T *out, T *x2out, const T *x, const T *f,
         for (int u = 0; u < NORM_U; u++) {
             const int c = cb + u * R + rg;
             if (active && c < C) {
-                if (FUSE_RES) rx[u].load(src + base + (size_t)c * S);
-                else rx[u].load_stream(src + base + (size_t)c * S);
+                const size_t o = base + (size_t)(cb / R + u) * step;
+                if (FUSE_RES) rx[u].load(src + o);
+                else rx[u].load_stream(src + o);
             }
         }
 #pragma unroll
         for (int u = 0; u < NORM_U; u++) {
             const int c = cb + u * R + rg;
             if (active && c < C) {
-                float v[VEC];
-                rx[u].unpack(v);
-                const float wc = __ldg(w + c);
-#pragma unroll
-                for (int j = 0; j < VEC; j++) v[j] = (v[j] * rr[j]) * wc;
+                const V<VEC> v = vmul(vmul(rx[u].get(), rr), V<VEC>::splat(__ldg(w + c)));
                 Raw<T, VEC> o;
-                o.pack(v);
-                o.store_stream(out + base + (size_t)c * S);
+                o.put(v);
+                o.store_stream(out + base + (size_t)(cb / R + u) * step);
             }
         }
     }
 }
 
 template <typename T, int VEC, int LG, bool HAS_ADD>
-__global__ void __launch_bounds__(NORM_THREADS)
+__global__ void __launch_bounds__(NORM_THREADS, 2)
 rmsnorm_bwd_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *x,
                    const float *__restrict__ w, const T *add, int C, int S, int tiles_per_seq,
                    int ntiles, float eps, unsigned flags) {
     constexpr int R = NORM_THREADS / LG;
     constexpr int TW = LG * VEC;
-    __shared__ float red[2][R][TW];
-    __shared__ float tot[2][TW];
+    __shared__ __align__(16) float red[2][R][TW];
+    __shared__ __align__(16) float tot[2][TW];
     extern __shared__ float dwacc[];  // [C]
 
     const int lg = threadIdx.x % LG, rg = threadIdx.x / LG;
     const float invd = 1.0f / (float)C;
     const bool exact = (flags & ANE_NORM_BWD_EXACT) != 0;
+    const size_t step = (size_t)R * S;
 
     for (int c = threadIdx.x; c < C; c += NORM_THREADS) dwacc[c] = 0.0f;
     __syncthreads();
@@ -142,11 +137,9 @@ rmsnorm_bwd_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *x,
         const int b = tile / tiles_per_seq;
         const int t = (tile % tiles_per_seq) * TW + lg * VEC;
         const bool active = t < S;
-        const size_t base = (size_t)b * C * S + t;
+        const size_t base = (size_t)b * C * S + t + (size_t)rg * S;
 
-        float ss[VEC], dot[VEC];
-#pragma unroll
-        for (int j = 0; j < VEC; j++) { ss[j] = 0.0f; dot[j] = 0.0f; }
+        V<VEC> ss = V<VEC>::splat(0.0f), dot = V<VEC>::splat(0.0f);
 
         // sweep 1: ss = sum x^2 ; dot = sum (dy*x)*w       (stories_cpu_ops.h:26-38)
         for (int cb = 0; cb < C; cb += R * NORM_U) {
@@ -155,45 +148,36 @@ rmsnorm_bwd_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *x,
             for (int u = 0; u < NORM_U; u++) {
                 const int c = cb + u * R + rg;
                 if (active && c < C) {
-                    rx[u].load(x + base + (size_t)c * S);
-                    rd[u].load(dy + base + (size_t)c * S);
+                    const size_t o = base + (size_t)(cb / R + u) * step;
+                    rx[u].load(x + o);
+                    rd[u].load(dy + o);
                 }
             }
 #pragma unroll
             for (int u = 0; u < NORM_U; u++) {
                 const int c = cb + u * R + rg;
                 if (active && c < C) {
-                    float xv[VEC], dv[VEC];
-                    rx[u].unpack(xv);
-                    rd[u].unpack(dv);
-                    const float wc = __ldg(w + c);
-#pragma unroll
-                    for (int j = 0; j < VEC; j++) {
-                        ss[j] += xv[j] * xv[j];
-                        dot[j] += (dv[j] * xv[j]) * wc;
-                    }
+                    const V<VEC> xv = rx[u].get(), dv = rd[u].get();
+                    ss = vfma(xv, xv, ss);
+                    dot = vfma(vmul(dv, xv), V<VEC>::splat(__ldg(w + c)), dot);
                 }
             }
         }
-#pragma unroll
-        for (int j = 0; j < VEC; j++) { red[0][rg][lg * VEC + j] = ss[j]; red[1][rg][lg * VEC + j] = dot[j]; }
+        lanes_to_smem<VEC>(&red[0][rg][lg * VEC], ss);
+        lanes_to_smem<VEC>(&red[1][rg][lg * VEC], dot);
         __syncthreads();
-        if (threadIdx.x < 2 * TW) {
-            const int which = threadIdx.x / TW, col = threadIdx.x % TW;
-            float s = 0.0f;
+        if (threadIdx.x < TW) {   // one thread per token: both column sums, then rrms and coef once
+            float s0 = 0.0f, s1 = 0.0f;
 #pragma unroll 8
-            for (int r = 0; r < R; r++) s += red[which][r][col];
-            tot[which][col] = s;
+            for (int r = 0; r < R; r++) { s0 += red[0][r][threadIdx.x]; s1 += red[1][r][threadIdx.x]; }
+            const float r1 = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s0, invd), eps));
+            float r2 = r1 * r1;
+            r2 = r2 * invd;
+            tot[0][threadIdx.x] = r1;
+            tot[1][threadIdx.x] = s1 * r2;                    // stories_cpu_ops.h:39-41
         }
         __syncthreads();
-        float rr[VEC], coef[VEC];
-#pragma unroll
-        for (int j = 0; j < VEC; j++) {
-            rr[j] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(tot[0][lg * VEC + j], invd), eps));
-            float r2 = rr[j] * rr[j];
-            r2 = r2 * invd;
-            coef[j] = tot[1][lg * VEC + j] * r2;          // stories_cpu_ops.h:39-41
-        }
+        const V<VEC> rr = lanes_from_smem<VEC>(&tot[0][lg * VEC]), coef = lanes_from_smem<VEC>(&tot[1][lg * VEC]);
 
         // sweep 2: dx and the dw partials (inputs come back from L2)
         for (int cb = 0; cb < C; cb += R * NORM_U) {
@@ -202,9 +186,10 @@ rmsnorm_bwd_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *x,
             for (int u = 0; u < NORM_U; u++) {
                 const int c = cb + u * R + rg;
                 if (active && c < C) {
-                    rx[u].load_stream(x + base + (size_t)c * S);
-                    rd[u].load_stream(dy + base + (size_t)c * S);
-                    if (HAS_ADD) ra[u].load_stream(add + base + (size_t)c * S);
+                    const size_t o = base + (size_t)(cb / R + u) * step;
+                    rx[u].load_stream(x + o);
+                    rd[u].load_stream(dy + o);
+                    if (HAS_ADD) ra[u].load_stream(add + o);
                 }
             }
 #pragma unroll
@@ -212,31 +197,16 @@ rmsnorm_bwd_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *x,
                 const int c = cb + u * R + rg;
                 float dwp = 0.0f;
                 if (active && c < C) {
-                    float xv[VEC], dv[VEC], o[VEC];
-                    rx[u].unpack(xv);
-                    rd[u].unpack(dv);
-                    const float wc = __ldg(w + c);
-#pragma unroll
-                    for (int j = 0; j < VEC; j++) {
-                        if (exact) {
-                            o[j] = __fmul_rn(__fsub_rn(__fmul_rn(dv[j], wc), __fmul_rn(xv[j], coef[j])), rr[j]);
-                        } else {
-                            float tmp = __fmul_rn(xv[j], coef[j]);      // stories_cpu_ops.h:43-46
-                            tmp = __fsub_rn(dv[j], tmp);
-                            tmp = tmp * rr[j];
-                            o[j] = tmp * wc;
-                        }
-                        dwp += (dv[j] * xv[j]) * rr[j];                 // stories_cpu_ops.h:47-50
-                    }
-                    if (HAS_ADD) {
-                        float av[VEC];
-                        ra[u].unpack(av);
-#pragma unroll
-                        for (int j = 0; j < VEC; j++) o[j] = o[j] + av[j];   // train.m:590,721
-                    }
+                    const V<VEC> xv = rx[u].get(), dv = rd[u].get();
+                    const V<VEC> wc = V<VEC>::splat(__ldg(w + c));
+                    V<VEC> o;
+                    if (exact) o = vmul(vsub(vmul(dv, wc), vmul(xv, coef)), rr);
+                    else o = vmul(vmul(vsub(dv, vmul(xv, coef)), rr), wc);     // stories_cpu_ops.h:43-46
+                    dwp = vmul(vmul(dv, xv), rr).hsum();                        // stories_cpu_ops.h:47-50
+                    if (HAS_ADD) o = vadd(o, ra[u].get());                      // train.m:590,721
                     Raw<T, VEC> ro;
-                    ro.pack(o);
-                    ro.store_stream(dx + base + (size_t)c * S);
+                    ro.put(o);
+                    ro.store_stream(dx + base + (size_t)(cb / R + u) * step);
                 }
                 // sum over the LG lanes that share channel c (the loop is uniform across the warp)
 #pragma unroll
@@ -264,6 +234,31 @@ static int launch_rmsnorm_fwd(cudaStream_t st, int B, int C, int S, void *out, v
     constexpr int VEC = Elt<T>::VEC;
     const bool vec = (S % VEC == 0) && aligned16(out) && aligned16(x) && (!FUSE_RES || (aligned16(x2) && aligned16(f)));
     if (vec) {
+        // register-resident path: tile shape by knob, NV = channels per thread (compile-time bound)
+#define ANE_FWD_RR(LGv, THv, NVv)                                                                                   \
+        do {                                                                                                        \
+            const int tps_ = (S + (LGv) * VEC - 1) / ((LGv) * VEC);                                                  \
+            rmsnorm_fwd_rr_kernel<T, LGv, THv, NVv, FUSE_RES><<<(unsigned)(B * tps_), THv, 0, st>>>(                 \
+                (T *)out, (T *)x2, (const T *)x, (const T *)f, w, C, S, tps_, alpha, eps);                          \
+            ANE_LAUNCH_OK(1);                                                                                       \
+            return ANE_CUDA_OK;                                                                                     \
+        } while (0)
+#define ANE_FWD_RR_NV(LGv, THv)                                                                                     \
+        do {                                                                                                        \
+            const int nv_ = (C + (THv) / (LGv) - 1) / ((THv) / (LGv));                                               \
+            if (nv_ <= 4) ANE_FWD_RR(LGv, THv, 4);                                                                  \
+            else if (nv_ <= 8) ANE_FWD_RR(LGv, THv, 8);                                                             \
+            else if (nv_ <= 12) ANE_FWD_RR(LGv, THv, 12);                                                           \
+            else if (nv_ <= 16) ANE_FWD_RR(LGv, THv, 16);                                                           \
+        } while (0)
+        switch (tuning("norm_fwd", 2)) {
+            case 2: ANE_FWD_RR_NV(4, 256); break;        // C <= 1024
+            case 3: ANE_FWD_RR_NV(4, 512); break;        // C <= 2048
+            case 4: ANE_FWD_RR_NV(8, 512); break;        // C <= 1024, 128-byte row segments
+            default: break;
+        }
+#undef ANE_FWD_RR_NV
+#undef ANE_FWD_RR
         constexpr int LG = 8;
         const int tps = (S + LG * VEC - 1) / (LG * VEC);
         rmsnorm_fwd_kernel<T, VEC, LG, FUSE_RES><<<(unsigned)(B * tps), NORM_THREADS, 0, st>>>(
@@ -279,9 +274,9 @@ static int launch_rmsnorm_fwd(cudaStream_t st, int B, int C, int S, void *out, v
 }
 
 template <typename KernelT>
-static int persistent_grid(KernelT kernel, size_t dyn_smem, int ntiles) {
+static int persistent_grid(KernelT kernel, int threads, size_t dyn_smem, int ntiles) {
     int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, NORM_THREADS, dyn_smem) != cudaSuccess || per_sm < 1)
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, dyn_smem) != cudaSuccess || per_sm < 1)
         per_sm = 1;
     long g = (long)per_sm * ctx().sm_count;
     if (g > ntiles) g = ntiles;
@@ -298,11 +293,37 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
     int grid, ntiles;
     float *partial;
     if (vec) {
+#define ANE_BWD_RR(LGv, THv, NVv)                                                                                   \
+        do {                                                                                                        \
+            auto k_ = rmsnorm_bwd_rr_kernel<T, LGv, THv, NVv, HAS_ADD>;                                              \
+            const int tps_ = (S + (LGv) * VEC - 1) / ((LGv) * VEC);                                                  \
+            ntiles = B * tps_;                                                                                      \
+            grid = persistent_grid(k_, THv, smem, ntiles);                                                          \
+            partial = static_cast<float *>(workspace((size_t)grid * C * sizeof(float)));                            \
+            if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", grid, C); \
+            k_<<<grid, THv, smem, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags); \
+            dw_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(dw, partial, grid, C);                              \
+            ANE_LAUNCH_OK(2);                                                                                       \
+            return ANE_CUDA_OK;                                                                                     \
+        } while (0)
+#define ANE_BWD_RR_NV(LGv, THv)                                                                                     \
+        do {                                                                                                        \
+            const int nv_ = (C + (THv) / (LGv) - 1) / ((THv) / (LGv));                                               \
+            if (nv_ <= 4) ANE_BWD_RR(LGv, THv, 4);                                                                  \
+            else if (nv_ <= 8) ANE_BWD_RR(LGv, THv, 8);                                                             \
+        } while (0)
+        switch (tuning("norm_bwd", 0)) {
+            case 2: ANE_BWD_RR_NV(4, 512); break;        // C <= 1024
+            case 3: ANE_BWD_RR_NV(8, 512); break;        // C <= 512
+            default: break;
+        }
+#undef ANE_BWD_RR_NV
+#undef ANE_BWD_RR
         constexpr int LG = 8;
         auto k = rmsnorm_bwd_kernel<T, VEC, LG, HAS_ADD>;
         const int tps = (S + LG * VEC - 1) / (LG * VEC);
         ntiles = B * tps;
-        grid = persistent_grid(k, smem, ntiles);
+        grid = persistent_grid(k, NORM_THREADS, smem, ntiles);
         partial = static_cast<float *>(workspace((size_t)grid * C * sizeof(float)));
         if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", grid, C);
         k<<<grid, NORM_THREADS, smem, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps,
@@ -312,7 +333,7 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
         auto k = rmsnorm_bwd_kernel<T, 1, LG, HAS_ADD>;
         const int tps = (S + LG - 1) / LG;
         ntiles = B * tps;
-        grid = persistent_grid(k, smem, ntiles);
+        grid = persistent_grid(k, NORM_THREADS, smem, ntiles);
         partial = static_cast<float *>(workspace((size_t)grid * C * sizeof(float)));
         if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", grid, C);
         k<<<grid, NORM_THREADS, smem, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps,

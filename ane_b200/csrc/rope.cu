@@ -32,60 +32,81 @@ rope_kernel(T *out, const T *x, int heads, int hd, int S, int tiles_per_seq, int
     if (t >= S) return;
     const int C = heads * hd;
     const size_t base = (size_t)b * C * S + t;
+    const size_t hstep = (size_t)hd * S;
     for (int i = blockIdx.y * R + rg; i < hd / 2; i += gridDim.y * R) {
-        float cs[VEC], sn[VEC];
+        V<VEC> cs, sn;
         const float fr = freq.f[i];
 #pragma unroll
         for (int j = 0; j < VEC; j++) {
             const float theta = (float)(pos0 + t + j) * fr;
-            cs[j] = cosf(theta);
-            sn[j] = inverse ? -sinf(theta) : sinf(theta);
+            cs.set(j, cosf(theta));
+            sn.set(j, inverse ? -sinf(theta) : sinf(theta));
         }
-        for (int h = 0; h < heads; h++) {
-            const size_t o0 = base + (size_t)(h * hd + 2 * i) * S;
+        const size_t o0 = base + (size_t)(2 * i) * S;
+        int h = 0;
+        for (; h + 2 <= heads; h += 2) {          // two heads (four rows) in flight
+            Raw<T, VEC> r0, r1, r2, r3;
+            const size_t o = o0 + h * hstep;
+            r0.load_stream(x + o);
+            r1.load_stream(x + o + S);
+            r2.load_stream(x + o + hstep);
+            r3.load_stream(x + o + hstep + S);
+            const V<VEC> a0 = r0.get(), b0 = r1.get(), a1 = r2.get(), b1 = r3.get();
+            r0.put(vsub(vmul(a0, cs), vmul(b0, sn)));
+            r1.put(vfma(a0, sn, vmul(b0, cs)));
+            r2.put(vsub(vmul(a1, cs), vmul(b1, sn)));
+            r3.put(vfma(a1, sn, vmul(b1, cs)));
+            r0.store_stream(out + o);
+            r1.store_stream(out + o + S);
+            r2.store_stream(out + o + hstep);
+            r3.store_stream(out + o + hstep + S);
+        }
+        for (; h < heads; h++) {
             Raw<T, VEC> r0, r1;
-            r0.load_stream(x + o0);
-            r1.load_stream(x + o0 + S);
-            float a[VEC], bb[VEC], ya[VEC], yb[VEC];
-            r0.unpack(a);
-            r1.unpack(bb);
-#pragma unroll
-            for (int j = 0; j < VEC; j++) {
-                ya[j] = __fsub_rn(__fmul_rn(a[j], cs[j]), __fmul_rn(bb[j], sn[j]));
-                yb[j] = __fadd_rn(__fmul_rn(a[j], sn[j]), __fmul_rn(bb[j], cs[j]));
-            }
-            r0.pack(ya);
-            r1.pack(yb);
-            r0.store_stream(out + o0);
-            r1.store_stream(out + o0 + S);
+            const size_t o = o0 + h * hstep;
+            r0.load_stream(x + o);
+            r1.load_stream(x + o + S);
+            const V<VEC> a0 = r0.get(), b0 = r1.get();
+            r0.put(vsub(vmul(a0, cs), vmul(b0, sn)));
+            r1.put(vfma(a0, sn, vmul(b0, cs)));
+            r0.store_stream(out + o);
+            r1.store_stream(out + o + S);
         }
     }
 }
 
 // ------------------------------------------------------------------ fused per-head kernels
-// hd == RPT * (QK_THREADS / LG); thread (rg, lg) holds channels rg*RPT .. rg*RPT+RPT-1.
-template <typename T, int VEC, int LG, int RPT, bool ROPE>
-__global__ void __launch_bounds__(QK_THREADS)
+// hd == RPT * 32; a block of 256 threads owns a tile of 8*VEC tokens and walks over the heads,
+// HB heads per step.  Thread (rg, lg) holds channels rg*RPT .. rg*RPT+RPT-1 of each head of the
+// step (both channels of a rotation pair sit in one thread) for its VEC tokens, in registers,
+// from the load to the store.  sin/cos for the thread's pairs and tokens are computed once per
+// tile and reused for every head.
+constexpr int QK_LG = 8;
+constexpr int QK_R = QK_THREADS / QK_LG;   // 32 row groups
+
+template <typename T, int RPT, bool ROPE, int HB>
+__global__ void __launch_bounds__(QK_THREADS, 2)
 qk_fwd_kernel(T *__restrict__ out, const T *__restrict__ x, const float *__restrict__ w, int heads, int S,
               int tiles_per_seq, float eps, int pos0, const __grid_constant__ RopeFreq freq) {
-    constexpr int R = QK_THREADS / LG;
-    constexpr int TW = LG * VEC;
-    constexpr int HD = RPT * R;
-    __shared__ float red[2][R][TW];
-    __shared__ float tot[2][TW];
+    constexpr int VEC = Elt<T>::VEC;
+    constexpr int TW = QK_LG * VEC;
+    constexpr int HD = RPT * QK_R;
+    __shared__ __align__(16) float red[2][HB][QK_R][TW];
+    __shared__ __align__(16) float tot[2][HB][TW];
 
     const int b = blockIdx.x / tiles_per_seq;
-    const int lg = threadIdx.x % LG, rg = threadIdx.x / LG;
+    const int lg = threadIdx.x % QK_LG, rg = threadIdx.x / QK_LG;
     const int t = (blockIdx.x % tiles_per_seq) * TW + lg * VEC;
     const bool active = t < S;
-    const size_t base = (size_t)b * heads * HD * S + t;
+    const size_t base = (size_t)b * heads * HD * S + t + (size_t)(rg * RPT) * S;
+    const size_t hstep = (size_t)HD * S;
     const float invd = 1.0f / (float)HD;
 
-    float wc[RPT];
+    V<VEC> wc[RPT];
 #pragma unroll
-    for (int k = 0; k < RPT; k++) wc[k] = __ldg(w + rg * RPT + k);
+    for (int k = 0; k < RPT; k++) wc[k] = V<VEC>::splat(__ldg(w + rg * RPT + k));
 
-    float cs[RPT / 2][VEC], sn[RPT / 2][VEC];
+    V<VEC> cs[RPT / 2], sn[RPT / 2];
     if (ROPE) {
 #pragma unroll
         for (int p = 0; p < RPT / 2; p++) {
@@ -93,97 +114,95 @@ qk_fwd_kernel(T *__restrict__ out, const T *__restrict__ x, const float *__restr
 #pragma unroll
             for (int j = 0; j < VEC; j++) {
                 const float theta = (float)(pos0 + t + j) * fr;
-                cs[p][j] = cosf(theta);
-                sn[p][j] = sinf(theta);
+                cs[p].set(j, cosf(theta));
+                sn[p].set(j, sinf(theta));
             }
         }
     }
 
-    for (int h = 0; h < heads; h++) {
-        const int buf = h & 1;
-        Raw<T, VEC> r[RPT];
-        float v[RPT][VEC];
-        const size_t hb = base + (size_t)(h * HD + rg * RPT) * S;
-        if (active) {
+    int it = 0;
+    for (int h0 = 0; h0 < heads; h0 += HB, it++) {
+        const int buf = it & 1;
+        Raw<T, VEC> r[HB][RPT];
 #pragma unroll
-            for (int k = 0; k < RPT; k++) r[k].load_stream(x + hb + (size_t)k * S);
-        }
-        float ss[VEC];
+        for (int hh = 0; hh < HB; hh++)
+            if (active && h0 + hh < heads) {
 #pragma unroll
-        for (int j = 0; j < VEC; j++) ss[j] = 0.0f;
-        if (active) {
-#pragma unroll
-            for (int k = 0; k < RPT; k++) {
-                r[k].unpack(v[k]);
-#pragma unroll
-                for (int j = 0; j < VEC; j++) ss[j] += v[k][j] * v[k][j];
+                for (int k = 0; k < RPT; k++) r[hh][k].load_stream(x + base + (h0 + hh) * hstep + (size_t)k * S);
             }
-        }
 #pragma unroll
-        for (int j = 0; j < VEC; j++) red[buf][rg][lg * VEC + j] = ss[j];
+        for (int hh = 0; hh < HB; hh++) {
+            V<VEC> ss = V<VEC>::splat(0.0f);
+            if (active && h0 + hh < heads) {
+#pragma unroll
+                for (int k = 0; k < RPT; k++) { const V<VEC> v = r[hh][k].get(); ss = vfma(v, v, ss); }
+            }
+            lanes_to_smem<VEC>(&red[buf][hh][rg][lg * VEC], ss);
+        }
         __syncthreads();
-        if (threadIdx.x < TW) {
+        if (threadIdx.x < HB * TW) {      // one thread per (head, token): column sum, then rrms once
+            const int hh = threadIdx.x / TW, col = threadIdx.x % TW;
             float s = 0.0f;
 #pragma unroll 8
-            for (int q = 0; q < R; q++) s += red[buf][q][threadIdx.x];
-            tot[buf][threadIdx.x] = s;
+            for (int q = 0; q < QK_R; q++) s += red[buf][hh][q][col];
+            tot[buf][hh][col] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s, invd), eps));
         }
         __syncthreads();
-        if (active) {
-            float rr[VEC];
 #pragma unroll
-            for (int j = 0; j < VEC; j++) rr[j] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(tot[buf][lg * VEC + j], invd), eps));
+        for (int hh = 0; hh < HB; hh++) {
+            if (active && h0 + hh < heads) {
+                const V<VEC> rr = lanes_from_smem<VEC>(&tot[buf][hh][lg * VEC]);
+                V<VEC> v[RPT];
 #pragma unroll
-            for (int k = 0; k < RPT; k++)
+                for (int k = 0; k < RPT; k++) v[k] = vmul(vmul(r[hh][k].get(), rr), wc[k]);
+                if (ROPE) {
 #pragma unroll
-                for (int j = 0; j < VEC; j++) v[k][j] = (v[k][j] * rr[j]) * wc[k];
-            if (ROPE) {
-#pragma unroll
-                for (int p = 0; p < RPT / 2; p++)
-#pragma unroll
-                    for (int j = 0; j < VEC; j++) {
-                        const float a = v[2 * p][j], bb = v[2 * p + 1][j];
-                        v[2 * p][j] = __fsub_rn(__fmul_rn(a, cs[p][j]), __fmul_rn(bb, sn[p][j]));
-                        v[2 * p + 1][j] = __fadd_rn(__fmul_rn(a, sn[p][j]), __fmul_rn(bb, cs[p][j]));
+                    for (int p = 0; p < RPT / 2; p++) {
+                        const V<VEC> a = v[2 * p], bb = v[2 * p + 1];
+                        v[2 * p] = vsub(vmul(a, cs[p]), vmul(bb, sn[p]));
+                        v[2 * p + 1] = vfma(a, sn[p], vmul(bb, cs[p]));
                     }
-            }
+                }
 #pragma unroll
-            for (int k = 0; k < RPT; k++) {
-                Raw<T, VEC> o;
-                o.pack(v[k]);
-                o.store_stream(out + hb + (size_t)k * S);
+                for (int k = 0; k < RPT; k++) {
+                    Raw<T, VEC> o;
+                    o.put(v[k]);
+                    o.store_stream(out + base + (h0 + hh) * hstep + (size_t)k * S);
+                }
             }
         }
     }
 }
 
-template <typename T, int VEC, int LG, int RPT, bool ROPE>
-__global__ void __launch_bounds__(QK_THREADS)
+template <typename T, int RPT, bool ROPE, int HB>
+__global__ void __launch_bounds__(QK_THREADS, (HB == 1 ? 2 : 1))
 qk_bwd_kernel(T *__restrict__ dx, float *__restrict__ partial, const T *__restrict__ dy, const T *__restrict__ x,
               const float *__restrict__ w, int heads, int S, int tiles_per_seq, int ntiles, float eps, int pos0,
               unsigned flags, const __grid_constant__ RopeFreq freq) {
-    constexpr int R = QK_THREADS / LG;
-    constexpr int TW = LG * VEC;
-    constexpr int HD = RPT * R;
-    __shared__ float red[2][2][R][TW];
-    __shared__ float tot[2][2][TW];
+    constexpr int VEC = Elt<T>::VEC;
+    constexpr int TW = QK_LG * VEC;
+    constexpr int HD = RPT * QK_R;
+    __shared__ __align__(16) float red[2][HB][2][QK_R][TW];
+    __shared__ __align__(16) float tot[2][HB][2][TW];
 
-    const int lg = threadIdx.x % LG, rg = threadIdx.x / LG;
+    const int lg = threadIdx.x % QK_LG, rg = threadIdx.x / QK_LG;
     const float invd = 1.0f / (float)HD;
     const bool exact = (flags & ANE_NORM_BWD_EXACT) != 0;
+    const size_t hstep = (size_t)HD * S;
 
-    float wc[RPT], dwacc[RPT];
+    V<VEC> wc[RPT];
+    float dwacc[RPT];
 #pragma unroll
-    for (int k = 0; k < RPT; k++) { wc[k] = __ldg(w + rg * RPT + k); dwacc[k] = 0.0f; }
+    for (int k = 0; k < RPT; k++) { wc[k] = V<VEC>::splat(__ldg(w + rg * RPT + k)); dwacc[k] = 0.0f; }
 
     int it = 0;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
         const int b = tile / tiles_per_seq;
         const int t = (tile % tiles_per_seq) * TW + lg * VEC;
         const bool active = t < S;
-        const size_t base = (size_t)b * heads * HD * S + t;
+        const size_t base = (size_t)b * heads * HD * S + t + (size_t)(rg * RPT) * S;
 
-        float cs[RPT / 2][VEC], sn[RPT / 2][VEC];
+        V<VEC> cs[RPT / 2], sn[RPT / 2];
         if (ROPE) {
 #pragma unroll
             for (int p = 0; p < RPT / 2; p++) {
@@ -191,88 +210,88 @@ qk_bwd_kernel(T *__restrict__ dx, float *__restrict__ partial, const T *__restri
 #pragma unroll
                 for (int j = 0; j < VEC; j++) {
                     const float theta = (float)(pos0 + t + j) * fr;
-                    cs[p][j] = cosf(theta);
-                    sn[p][j] = sinf(theta);
+                    cs[p].set(j, cosf(theta));
+                    sn[p].set(j, sinf(theta));
                 }
             }
         }
 
-        for (int h = 0; h < heads; h++, it++) {
+        for (int h0 = 0; h0 < heads; h0 += HB, it++) {
             const int buf = it & 1;
-            Raw<T, VEC> rxr[RPT], rdr[RPT];
-            float xv[RPT][VEC], g[RPT][VEC];
-            const size_t hb = base + (size_t)(h * HD + rg * RPT) * S;
-            if (active) {
+            Raw<T, VEC> rxr[HB][RPT], rdr[HB][RPT];
 #pragma unroll
-                for (int k = 0; k < RPT; k++) {
-                    rxr[k].load_stream(x + hb + (size_t)k * S);
-                    rdr[k].load_stream(dy + hb + (size_t)k * S);
-                }
-            }
-            float ss[VEC], dot[VEC];
+            for (int hh = 0; hh < HB; hh++)
+                if (active && h0 + hh < heads) {
 #pragma unroll
-            for (int j = 0; j < VEC; j++) { ss[j] = 0.0f; dot[j] = 0.0f; }
-            if (active) {
-#pragma unroll
-                for (int k = 0; k < RPT; k++) { rxr[k].unpack(xv[k]); rdr[k].unpack(g[k]); }
-                if (ROPE) {   // g = rope^-1(dy): (a cos + b sin, -a sin + b cos)   cpu_ops.h:178-181
-#pragma unroll
-                    for (int p = 0; p < RPT / 2; p++)
-#pragma unroll
-                        for (int j = 0; j < VEC; j++) {
-                            const float a = g[2 * p][j], bb = g[2 * p + 1][j];
-                            g[2 * p][j] = __fadd_rn(__fmul_rn(a, cs[p][j]), __fmul_rn(bb, sn[p][j]));
-                            g[2 * p + 1][j] = __fadd_rn(__fmul_rn(-a, sn[p][j]), __fmul_rn(bb, cs[p][j]));
-                        }
-                }
-#pragma unroll
-                for (int k = 0; k < RPT; k++)
-#pragma unroll
-                    for (int j = 0; j < VEC; j++) {
-                        ss[j] += xv[k][j] * xv[k][j];
-                        dot[j] += (g[k][j] * xv[k][j]) * wc[k];
+                    for (int k = 0; k < RPT; k++) {
+                        rxr[hh][k].load_stream(x + base + (h0 + hh) * hstep + (size_t)k * S);
+                        rdr[hh][k].load_stream(dy + base + (h0 + hh) * hstep + (size_t)k * S);
                     }
-            }
+                }
+            // g = rope^-1(dy): (a cos + b sin, -a sin + b cos)   cpu_ops.h:178-181 ; kept packed in rdr
 #pragma unroll
-            for (int j = 0; j < VEC; j++) { red[buf][0][rg][lg * VEC + j] = ss[j]; red[buf][1][rg][lg * VEC + j] = dot[j]; }
+            for (int hh = 0; hh < HB; hh++) {
+                V<VEC> ss = V<VEC>::splat(0.0f), dot = V<VEC>::splat(0.0f);
+                if (active && h0 + hh < heads) {
+#pragma unroll
+                    for (int p = 0; p < RPT / 2; p++) {
+                        V<VEC> g0 = rdr[hh][2 * p].get(), g1 = rdr[hh][2 * p + 1].get();
+                        if (ROPE) {
+                            const V<VEC> a = g0, bb = g1;
+                            g0 = vfma(a, cs[p], vmul(bb, sn[p]));
+                            g1 = vsub(vmul(bb, cs[p]), vmul(a, sn[p]));
+                        }
+                        const V<VEC> x0 = rxr[hh][2 * p].get(), x1 = rxr[hh][2 * p + 1].get();
+                        ss = vfma(x0, x0, ss);
+                        ss = vfma(x1, x1, ss);
+                        dot = vfma(vmul(g0, x0), wc[2 * p], dot);
+                        dot = vfma(vmul(g1, x1), wc[2 * p + 1], dot);
+                    }
+                }
+                lanes_to_smem<VEC>(&red[buf][hh][0][rg][lg * VEC], ss);
+                lanes_to_smem<VEC>(&red[buf][hh][1][rg][lg * VEC], dot);
+            }
             __syncthreads();
-            if (threadIdx.x < 2 * TW) {
-                const int which = threadIdx.x / TW, col = threadIdx.x % TW;
-                float s = 0.0f;
+            if (threadIdx.x < HB * TW) {  // one thread per (head, token): both sums, then rrms and coef once
+                const int hh = threadIdx.x / TW, col = threadIdx.x % TW;
+                float s0 = 0.0f, s1 = 0.0f;
 #pragma unroll 8
-                for (int q = 0; q < R; q++) s += red[buf][which][q][col];
-                tot[buf][which][col] = s;
+                for (int q = 0; q < QK_R; q++) { s0 += red[buf][hh][0][q][col]; s1 += red[buf][hh][1][q][col]; }
+                const float r1 = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s0, invd), eps));
+                float r2 = r1 * r1;
+                r2 = r2 * invd;
+                tot[buf][hh][0][col] = r1;
+                tot[buf][hh][1][col] = s1 * r2;
             }
             __syncthreads();
-            if (active) {
-                float rr[VEC], coef[VEC];
 #pragma unroll
-                for (int j = 0; j < VEC; j++) {
-                    rr[j] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(tot[buf][0][lg * VEC + j], invd), eps));
-                    float r2 = rr[j] * rr[j];
-                    r2 = r2 * invd;
-                    coef[j] = tot[buf][1][lg * VEC + j] * r2;
-                }
+            for (int hh = 0; hh < HB; hh++) {
+                if (active && h0 + hh < heads) {
+                    const V<VEC> rr = lanes_from_smem<VEC>(&tot[buf][hh][0][lg * VEC]);
+                    const V<VEC> coef = lanes_from_smem<VEC>(&tot[buf][hh][1][lg * VEC]);
 #pragma unroll
-                for (int k = 0; k < RPT; k++) {
-                    float o[VEC];
-                    float dwp = 0.0f;
-#pragma unroll
-                    for (int j = 0; j < VEC; j++) {
-                        if (exact) {
-                            o[j] = __fmul_rn(__fsub_rn(__fmul_rn(g[k][j], wc[k]), __fmul_rn(xv[k][j], coef[j])), rr[j]);
-                        } else {
-                            float tmp = __fmul_rn(xv[k][j], coef[j]);
-                            tmp = __fsub_rn(g[k][j], tmp);
-                            tmp = tmp * rr[j];
-                            o[j] = tmp * wc[k];
+                    for (int p = 0; p < RPT / 2; p++) {
+                        V<VEC> g[2];
+                        g[0] = rdr[hh][2 * p].get();
+                        g[1] = rdr[hh][2 * p + 1].get();
+                        if (ROPE) {     // recomputed rather than kept: registers are the scarcer resource
+                            const V<VEC> a = g[0], bb = g[1];
+                            g[0] = vfma(a, cs[p], vmul(bb, sn[p]));
+                            g[1] = vsub(vmul(bb, cs[p]), vmul(a, sn[p]));
                         }
-                        dwp += (g[k][j] * xv[k][j]) * rr[j];
+#pragma unroll
+                        for (int q = 0; q < 2; q++) {
+                            const int k = 2 * p + q;
+                            const V<VEC> xv = rxr[hh][k].get();
+                            V<VEC> o;
+                            if (exact) o = vmul(vsub(vmul(g[q], wc[k]), vmul(xv, coef)), rr);
+                            else o = vmul(vmul(vsub(g[q], vmul(xv, coef)), rr), wc[k]);
+                            dwacc[k] += vmul(vmul(g[q], xv), rr).hsum();
+                            Raw<T, VEC> ro;
+                            ro.put(o);
+                            ro.store_stream(dx + base + (h0 + hh) * hstep + (size_t)k * S);
+                        }
                     }
-                    dwacc[k] += dwp;
-                    Raw<T, VEC> ro;
-                    ro.pack(o);
-                    ro.store_stream(dx + hb + (size_t)k * S);
                 }
             }
         }
@@ -282,7 +301,7 @@ qk_bwd_kernel(T *__restrict__ dx, float *__restrict__ partial, const T *__restri
     for (int k = 0; k < RPT; k++) {
         float s = dwacc[k];
 #pragma unroll
-        for (int off = LG / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        for (int off = QK_LG / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
         if (lg == 0) partial[(size_t)blockIdx.x * HD + rg * RPT + k] = s;
     }
 }
@@ -440,10 +459,18 @@ static int launch_rope(cudaStream_t st, int B, int heads, int hd, int S, void *o
     constexpr int VEC = Elt<T>::VEC;
     const bool vec = (S % VEC == 0) && aligned16(out) && aligned16(x);
     if (vec) {
-        constexpr int LG = 8;
-        const int tps = (S + LG * VEC - 1) / (LG * VEC);
-        dim3 grid((unsigned)(B * tps), (unsigned)((hd / 2 + (QK_THREADS / LG) - 1) / (QK_THREADS / LG)));
-        rope_kernel<T, VEC, LG><<<grid, QK_THREADS, 0, st>>>((T *)out, (const T *)x, heads, hd, S, tps, pos0, inverse, fq);
+#define ANE_ROPE_LG(LGv)                                                                                             \
+        do {                                                                                                         \
+            const int tps_ = (S + (LGv) * VEC - 1) / ((LGv) * VEC);                                                   \
+            dim3 grid_((unsigned)(B * tps_), (unsigned)((hd / 2 + (QK_THREADS / (LGv)) - 1) / (QK_THREADS / (LGv)))); \
+            rope_kernel<T, VEC, LGv><<<grid_, QK_THREADS, 0, st>>>((T *)out, (const T *)x, heads, hd, S, tps_, pos0, inverse, fq); \
+        } while (0)
+        switch (tuning("rope_lg", 8)) {
+            case 32: ANE_ROPE_LG(32); break;
+            case 16: ANE_ROPE_LG(16); break;
+            default: ANE_ROPE_LG(8); break;
+        }
+#undef ANE_ROPE_LG
     } else {
         constexpr int LG = 32;
         const int tps = (S + LG - 1) / LG;
@@ -474,13 +501,13 @@ template <typename T, bool ROPE>
 static int launch_qk_fwd(cudaStream_t st, int B, int heads, int hd, int S, void *out, const void *x, const float *w,
                          float eps, int pos0, const RopeFreq &fq) {
     constexpr int VEC = Elt<T>::VEC;
-    constexpr int LG = 8;
-    const int tps = (S + LG * VEC - 1) / (LG * VEC);
+    const int tps = (S + QK_LG * VEC - 1) / (QK_LG * VEC);
     const unsigned grid = (unsigned)(B * tps);
-    if (hd == 128)
-        qk_fwd_kernel<T, VEC, LG, 4, ROPE><<<grid, QK_THREADS, 0, st>>>((T *)out, (const T *)x, w, heads, S, tps, eps, pos0, fq);
-    else
-        qk_fwd_kernel<T, VEC, LG, 2, ROPE><<<grid, QK_THREADS, 0, st>>>((T *)out, (const T *)x, w, heads, S, tps, eps, pos0, fq);
+    const int hb = tuning("qk_fwd", 2);
+#define ANE_QKF(RPTv, HBv) qk_fwd_kernel<T, RPTv, ROPE, HBv><<<grid, QK_THREADS, 0, st>>>((T *)out, (const T *)x, w, heads, S, tps, eps, pos0, fq)
+    if (hd == 128) { if (hb == 1) ANE_QKF(4, 1); else ANE_QKF(4, 2); }
+    else { if (hb == 1) ANE_QKF(2, 1); else ANE_QKF(2, 2); }
+#undef ANE_QKF
     ANE_LAUNCH_OK(1);
     return ANE_CUDA_OK;
 }
@@ -489,24 +516,23 @@ template <typename T, bool ROPE>
 static int launch_qk_bwd(cudaStream_t st, int B, int heads, int hd, int S, void *dx, float *dw, const void *dy,
                          const void *x, const float *w, float eps, int pos0, unsigned flags, const RopeFreq &fq) {
     constexpr int VEC = Elt<T>::VEC;
-    constexpr int LG = 8;
-    const int tps = (S + LG * VEC - 1) / (LG * VEC);
+    const int tps = (S + QK_LG * VEC - 1) / (QK_LG * VEC);
     const int ntiles = B * tps;
-    int grid;
-    float *partial;
-    if (hd == 128) {
-        auto k = qk_bwd_kernel<T, VEC, LG, 4, ROPE>;
-        grid = qk_persistent_grid(k, ntiles);
-        partial = static_cast<float *>(workspace((size_t)grid * hd * sizeof(float)));
-        if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "qknorm_bwd: no scratch");
-        k<<<grid, QK_THREADS, 0, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, heads, S, tps, ntiles, eps, pos0, flags, fq);
-    } else {
-        auto k = qk_bwd_kernel<T, VEC, LG, 2, ROPE>;
-        grid = qk_persistent_grid(k, ntiles);
-        partial = static_cast<float *>(workspace((size_t)grid * hd * sizeof(float)));
-        if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "qknorm_bwd: no scratch");
-        k<<<grid, QK_THREADS, 0, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, heads, S, tps, ntiles, eps, pos0, flags, fq);
-    }
+    const int hb = tuning("qk_bwd", 1);
+    int grid = 0;
+    float *partial = nullptr;
+#define ANE_QKB(RPTv, HBv)                                                                                          \
+    do {                                                                                                            \
+        auto k = qk_bwd_kernel<T, RPTv, ROPE, HBv>;                                                                  \
+        grid = qk_persistent_grid(k, ntiles);                                                                       \
+        partial = static_cast<float *>(workspace((size_t)grid * hd * sizeof(float)));                               \
+        if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "qknorm_bwd: no scratch");                                    \
+        k<<<grid, QK_THREADS, 0, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, heads, S, tps, ntiles, eps, pos0, flags, fq); \
+    } while (0)
+    (void)hb;       // one head per step: two would need more than 48 KiB of static shared memory
+    if (hd == 128) ANE_QKB(4, 1);
+    else ANE_QKB(2, 1);
+#undef ANE_QKB
     qk_dw_finalize_kernel<<<(hd + 127) / 128, 128, 0, st>>>(dw, partial, grid, hd);
     ANE_LAUNCH_OK(2);
     return ANE_CUDA_OK;

@@ -53,6 +53,7 @@ PROTOTYPES = {
     "ane_cuda_last_error": (C.c_char_p, []),
     "ane_cuda_launch_count": (C.c_longlong, []),
     "ane_cuda_reset_launch_count": (None, []),
+    "ane_cuda_set_tuning": (_i, [C.c_char_p, _i]),
     "ane_cuda_alloc": (_vp, [_sz]),
     "ane_cuda_write": (_i, [_vp, _sz, _vp, _sz]),
     "ane_cuda_read": (_i, [_vp, _sz, _vp, _sz]),
@@ -136,6 +137,14 @@ def check(rc: int) -> None:
 
 def init(device: int = 0) -> None:
     check(load().ane_cuda_init(int(device)))
+    # ANE_CUDA_TUNING="knob=value,knob=value": kernel-selection knobs for benchmarking
+    for item in filter(None, os.environ.get("ANE_CUDA_TUNING", "").split(",")):
+        name, _, value = item.partition("=")
+        set_tuning(name.strip(), int(value))
+
+
+def set_tuning(name: str, value: int) -> None:
+    check(load().ane_cuda_set_tuning(name.encode(), int(value)))
 
 
 def launch_count() -> int:

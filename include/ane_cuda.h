@@ -89,6 +89,10 @@ const char *ane_cuda_last_error(void);
 long long ane_cuda_launch_count(void);
 void ane_cuda_reset_launch_count(void);
 
+/* Kernel-selection knobs for benchmarking (tile shapes; every setting computes the same result
+ * up to the summation order of dw).  Unknown names are stored and ignored. */
+int ane_cuda_set_tuning(const char *name, int value);
+
 ANECudaBuf *ane_cuda_alloc(size_t bytes);                       /* NULL on failure */
 int ane_cuda_write(ANECudaBuf *buf, size_t offset, const void *host, size_t bytes);  /* ane_bridge_write_input */
 int ane_cuda_read(ANECudaBuf *buf, size_t offset, void *host, size_t bytes);         /* ane_bridge_read_output */
