@@ -4,6 +4,7 @@
 // the overwrite / accumulate behaviour of training/stories_cpu_ops.h and
 // training/training_dynamic/cpu_ops.h.
 #include "common.cuh"
+#include "tma.cuh"
 
 #include <atomic>
 #include <cstdarg>
@@ -33,6 +34,39 @@ int fail(int code, const char *fmt, ...) {
 }
 
 void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// cuTensorMapEncodeTiled is a driver entry point; it is resolved through the runtime so that the
+// library does not link against libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode_tiled = nullptr;
+
+int make_bcs_tensor_map(CUtensorMap *map, ane_dtype dtype, const void *base, int B, int C, int S, int box_s, int box_c) {
+    if (!g_encode_tiled) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn ||
+            q != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            return fail(ANE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        }
+        g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    const size_t e = dtype_size(dtype);
+    if (!aligned16(base) || ((size_t)S * e) % 16 || ((size_t)box_s * e) % 16 || box_s > 256 || box_c > 256 || box_s < 1 || box_c < 1)
+        return fail(ANE_CUDA_ERR_INVALID, "tensor map: unsupported alignment or box (S=%d box %dx%d)", S, box_s, box_c);
+    const CUtensorMapDataType dt = dtype == ANE_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == ANE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const cuuint64_t dims[3] = {(cuuint64_t)S, (cuuint64_t)C, (cuuint64_t)B};
+    const cuuint64_t strides[2] = {(cuuint64_t)S * e, (cuuint64_t)C * S * e};
+    const cuuint32_t box[3] = {(cuuint32_t)box_s, (cuuint32_t)box_c, 1u};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    const CUresult r = g_encode_tiled(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ANE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return ANE_CUDA_OK;
+}
 
 struct Knob { char name[32]; int value; };
 static Knob g_knobs[32];
@@ -155,6 +189,7 @@ void ane_cuda_shutdown(void) {
     if (!c.inited) return;
     cudaDeviceSynchronize();
     pipe_destroy();
+    rope_tables_release();
     if (c.ws) cudaFree(c.ws);
     if (c.stage) cudaFree(c.stage);
     if (c.status) cudaFree(c.status);

@@ -31,6 +31,8 @@ void note_launch(int n = 1);
 void *workspace(size_t bytes);
 // Kernel-selection knobs (ane_cuda_set_tuning); `dflt` when the knob was never set.
 int tuning(const char *name, int dflt);
+// Frees the cached RoPE cos/sin tables (rope.cu).
+void rope_tables_release();
 
 #define ANE_REQUIRE_INIT() do { if (!::ane::ctx().inited) return ::ane::fail(ANE_CUDA_ERR_NOT_INIT, "%s: call ane_cuda_init first", __func__); } while (0)
 #define ANE_REQUIRE(cond, ...) do { if (!(cond)) return ::ane::fail(ANE_CUDA_ERR_INVALID, __VA_ARGS__); } while (0)
@@ -228,6 +230,23 @@ template <int N> __device__ __forceinline__ V<N> vfma(const V<N> &a, const V<N> 
     for (int i = 0; i < N / 2; i++) r.p[i] = f2_fma(a.p[i], b.p[i], c.p[i]);
     return r;
 }
+// a * (s, s): the per-channel weight lives in one register pair, not in N lanes
+template <int N> __device__ __forceinline__ V<N> vscale(const V<N> &a, float s) {
+    V<N> r;
+    const float2 s2 = make_float2(s, s);
+#pragma unroll
+    for (int i = 0; i < N / 2; i++) r.p[i] = f2_mul(a.p[i], s2);
+    return r;
+}
+template <int N> __device__ __forceinline__ V<N> vfma_s(const V<N> &a, float s, const V<N> &c) {
+    V<N> r;
+    const float2 s2 = make_float2(s, s);
+#pragma unroll
+    for (int i = 0; i < N / 2; i++) r.p[i] = f2_fma(a.p[i], s2, c.p[i]);
+    return r;
+}
+template <> __device__ __forceinline__ V<1> vscale<1>(const V<1> &a, float s) { V<1> r; r.a = __fmul_rn(a.a, s); return r; }
+template <> __device__ __forceinline__ V<1> vfma_s<1>(const V<1> &a, float s, const V<1> &c) { V<1> r; r.a = fmaf(a.a, s, c.a); return r; }
 template <> __device__ __forceinline__ V<1> vmul<1>(const V<1> &a, const V<1> &b) { V<1> r; r.a = __fmul_rn(a.a, b.a); return r; }
 template <> __device__ __forceinline__ V<1> vadd<1>(const V<1> &a, const V<1> &b) { V<1> r; r.a = __fadd_rn(a.a, b.a); return r; }
 template <> __device__ __forceinline__ V<1> vsub<1>(const V<1> &a, const V<1> &b) { V<1> r; r.a = __fsub_rn(a.a, b.a); return r; }
@@ -253,6 +272,24 @@ template <int N> __device__ __forceinline__ V<N> lanes_from_smem(const float *sr
     return v;
 }
 template <> __device__ __forceinline__ V<1> lanes_from_smem<1>(const float *src) { V<1> v; v.a = src[0]; return v; }
+
+// Column sums of a shared-memory matrix red[R][COLS] with ALL `THREADS` threads of the block
+// (THREADS == COLS * P): thread tid adds R/P rows of column tid / P, the P partial sums meet
+// through warp shuffles, and every thread of the group returns the column total.  Compared with
+// one thread per column this shortens the serial chain from R to R/P loads while the rest of the
+// block would only wait at the next barrier.  The summation order is fixed.
+template <int R, int COLS, int THREADS>
+__device__ __forceinline__ float block_column_sum(const float *red, int tid) {
+    constexpr int P = THREADS / COLS;
+    static_assert(P >= 1 && P <= 32 && (P & (P - 1)) == 0 && COLS * P == THREADS && R % P == 0, "bad reduction shape");
+    const int col = tid / P, part = tid % P;
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < R / P; i++) s += red[(part * (R / P) + i) * COLS + col];
+#pragma unroll
+    for (int off = P / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    return s;
+}
 
 // A group of VEC consecutive elements held raw: one 16-byte word when VEC is the full vector
 // width of T, one element when VEC == 1 (the path for shapes that break 16-byte alignment).

@@ -41,8 +41,7 @@ rmsnorm_fwd_kernel(T *out, T *x2out, const T *x, const T *f,
     const bool active = t < S;
     const size_t base = (size_t)b * C * S + t + (size_t)rg * S;
     const size_t step = (size_t)R * S;
-    const V<VEC> valpha = V<VEC>::splat(alpha);
-
+    
     V<VEC> ss = V<VEC>::splat(0.0f);
 
     // sweep 1: sum of squares (and, when fused, x2 = f*alpha + x written out)
@@ -67,7 +66,7 @@ rmsnorm_fwd_kernel(T *out, T *x2out, const T *x, const T *f,
             if (active && c < C) {
                 V<VEC> v = rx[u].get();
                 if (FUSE_RES) {
-                    v = vadd(vmul(rf[u].get(), valpha), v);              // train.m:460, two roundings
+                    v = vadd(vscale(rf[u].get(), alpha), v);              // train.m:460, two roundings
                     Raw<T, VEC> o;
                     o.put(v);
                     o.store(x2out + base + (size_t)(cb / R + u) * step);   // stays in L2 for sweep 2
@@ -79,11 +78,10 @@ rmsnorm_fwd_kernel(T *out, T *x2out, const T *x, const T *f,
     }
     lanes_to_smem<VEC>(&red[rg][lg * VEC], ss);
     __syncthreads();
-    if (threadIdx.x < TW) {       // one thread per token: column sum, then rrms once for everybody
-        float s = 0.0f;
-#pragma unroll 8
-        for (int r = 0; r < R; r++) s += red[r][threadIdx.x];
-        tot[threadIdx.x] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s, 1.0f / (float)C), eps));
+    {   // column sums with the whole block, then rrms once per token
+        constexpr int P = NORM_THREADS / TW;
+        const float s = block_column_sum<R, TW, NORM_THREADS>(&red[0][0], threadIdx.x);
+        if (threadIdx.x % P == 0) tot[threadIdx.x / P] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s, 1.0f / (float)C), eps));
     }
     __syncthreads();
     const V<VEC> rr = lanes_from_smem<VEC>(&tot[lg * VEC]);
@@ -105,7 +103,7 @@ rmsnorm_fwd_kernel(T *out, T *x2out, const T *x, const T *f,
         for (int u = 0; u < NORM_U; u++) {
             const int c = cb + u * R + rg;
             if (active && c < C) {
-                const V<VEC> v = vmul(vmul(rx[u].get(), rr), V<VEC>::splat(__ldg(w + c)));
+                const V<VEC> v = vscale(vmul(rx[u].get(), rr), __ldg(w + c));
                 Raw<T, VEC> o;
                 o.put(v);
                 o.store_stream(out + base + (size_t)(cb / R + u) * step);
@@ -159,22 +157,24 @@ rmsnorm_bwd_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *x,
                 if (active && c < C) {
                     const V<VEC> xv = rx[u].get(), dv = rd[u].get();
                     ss = vfma(xv, xv, ss);
-                    dot = vfma(vmul(dv, xv), V<VEC>::splat(__ldg(w + c)), dot);
+                    dot = vfma_s(vmul(dv, xv), __ldg(w + c), dot);
                 }
             }
         }
         lanes_to_smem<VEC>(&red[0][rg][lg * VEC], ss);
         lanes_to_smem<VEC>(&red[1][rg][lg * VEC], dot);
         __syncthreads();
-        if (threadIdx.x < TW) {   // one thread per token: both column sums, then rrms and coef once
-            float s0 = 0.0f, s1 = 0.0f;
-#pragma unroll 8
-            for (int r = 0; r < R; r++) { s0 += red[0][r][threadIdx.x]; s1 += red[1][r][threadIdx.x]; }
-            const float r1 = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s0, invd), eps));
-            float r2 = r1 * r1;
-            r2 = r2 * invd;
-            tot[0][threadIdx.x] = r1;
-            tot[1][threadIdx.x] = s1 * r2;                    // stories_cpu_ops.h:39-41
+        {   // column sums with the whole block, then rrms and coef once per token
+            constexpr int P = NORM_THREADS / TW;
+            const float s0 = block_column_sum<R, TW, NORM_THREADS>(&red[0][0][0], threadIdx.x);
+            const float s1 = block_column_sum<R, TW, NORM_THREADS>(&red[1][0][0], threadIdx.x);
+            if (threadIdx.x % P == 0) {
+                const float r1 = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s0, invd), eps));
+                float r2 = r1 * r1;
+                r2 = r2 * invd;
+                tot[0][threadIdx.x / P] = r1;
+                tot[1][threadIdx.x / P] = s1 * r2;            // stories_cpu_ops.h:39-41
+            }
         }
         __syncthreads();
         const V<VEC> rr = lanes_from_smem<VEC>(&tot[0][lg * VEC]), coef = lanes_from_smem<VEC>(&tot[1][lg * VEC]);
@@ -198,10 +198,10 @@ rmsnorm_bwd_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *x,
                 float dwp = 0.0f;
                 if (active && c < C) {
                     const V<VEC> xv = rx[u].get(), dv = rd[u].get();
-                    const V<VEC> wc = V<VEC>::splat(__ldg(w + c));
+                    const float wc = __ldg(w + c);
                     V<VEC> o;
-                    if (exact) o = vmul(vsub(vmul(dv, wc), vmul(xv, coef)), rr);
-                    else o = vmul(vmul(vsub(dv, vmul(xv, coef)), rr), wc);     // stories_cpu_ops.h:43-46
+                    if (exact) o = vmul(vsub(vscale(dv, wc), vmul(xv, coef)), rr);
+                    else o = vscale(vmul(vsub(dv, vmul(xv, coef)), rr), wc);     // stories_cpu_ops.h:43-46
                     dwp = vmul(vmul(dv, xv), rr).hsum();                        // stories_cpu_ops.h:47-50
                     if (HAS_ADD) o = vadd(o, ra[u].get());                      // train.m:590,721
                     Raw<T, VEC> ro;

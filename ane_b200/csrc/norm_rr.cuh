@@ -42,8 +42,7 @@ rmsnorm_fwd_rr_kernel(T *out, T *x2out, const T *x, const T *f, const float *__r
             if (active && k * R + rg < C) { const V<VEC> v = r[k].get(); ss = vfma(v, v, ss); }
     } else {
         constexpr int UB = NV < 8 ? NV : 8;          // x and f in batches of UB channels
-        const V<VEC> valpha = V<VEC>::splat(alpha);
-#pragma unroll
+        #pragma unroll
         for (int k0 = 0; k0 < NV; k0 += UB) {
             Raw<T, VEC> rf[UB];
 #pragma unroll
@@ -58,7 +57,7 @@ rmsnorm_fwd_rr_kernel(T *out, T *x2out, const T *x, const T *f, const float *__r
             for (int u = 0; u < UB; u++) {
                 const int k = k0 + u;
                 if (k < NV && active && k * R + rg < C) {
-                    r[k].put(vadd(vmul(rf[u].get(), valpha), r[k].get()));      // train.m:460, two roundings
+                    r[k].put(vadd(vscale(rf[u].get(), alpha), r[k].get()));      // train.m:460, two roundings
                     r[k].store_stream(x2out + base + k * step);
                     const V<VEC> v = r[k].get();                                  // the stored (rounded) value
                     ss = vfma(v, v, ss);
@@ -68,11 +67,10 @@ rmsnorm_fwd_rr_kernel(T *out, T *x2out, const T *x, const T *f, const float *__r
     }
     lanes_to_smem<VEC>(&red[rg][lg * VEC], ss);
     __syncthreads();
-    if (threadIdx.x < TW) {       // one thread per token: column sum, then rrms once for everybody
-        float s = 0.0f;
-#pragma unroll 8
-        for (int q = 0; q < R; q++) s += red[q][threadIdx.x];
-        tot[threadIdx.x] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s, 1.0f / (float)C), eps));
+    {   // column sums with the whole block, then rrms once per token
+        constexpr int P = THREADS / TW;
+        const float s = block_column_sum<R, TW, THREADS>(&red[0][0], threadIdx.x);
+        if (threadIdx.x % P == 0) tot[threadIdx.x / P] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s, 1.0f / (float)C), eps));
     }
     __syncthreads();
     if (!active) return;
@@ -82,7 +80,7 @@ rmsnorm_fwd_rr_kernel(T *out, T *x2out, const T *x, const T *f, const float *__r
         const int c = k * R + rg;
         if (c < C) {
             Raw<T, VEC> o;
-            o.put(vmul(vmul(r[k].get(), rr), V<VEC>::splat(__ldg(w + c))));      // stories_cpu_ops.h:16-19
+            o.put(vscale(vmul(r[k].get(), rr), __ldg(w + c)));      // stories_cpu_ops.h:16-19
             o.store_stream(out + base + k * step);
         }
     }
@@ -129,21 +127,23 @@ rmsnorm_bwd_rr_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *
             if (active && c < C) {
                 const V<VEC> xv = rx[k].get(), dv = rd[k].get();
                 ss = vfma(xv, xv, ss);
-                dot = vfma(vmul(dv, xv), V<VEC>::splat(__ldg(w + c)), dot);      // stories_cpu_ops.h:35-38
+                dot = vfma_s(vmul(dv, xv), __ldg(w + c), dot);      // stories_cpu_ops.h:35-38
             }
         }
         lanes_to_smem<VEC>(&red[0][rg][lg * VEC], ss);
         lanes_to_smem<VEC>(&red[1][rg][lg * VEC], dot);
         __syncthreads();
-        if (threadIdx.x < TW) {   // one thread per token: both column sums, then rrms and coef once
-            float s0 = 0.0f, s1 = 0.0f;
-#pragma unroll 8
-            for (int q = 0; q < R; q++) { s0 += red[0][q][threadIdx.x]; s1 += red[1][q][threadIdx.x]; }
-            const float r1 = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s0, invd), eps));
-            float r2 = r1 * r1;
-            r2 = r2 * invd;
-            tot[0][threadIdx.x] = r1;
-            tot[1][threadIdx.x] = s1 * r2;                                         // stories_cpu_ops.h:39-41
+        {   // column sums with the whole block, then rrms and coef once per token
+            constexpr int P = THREADS / TW;
+            const float s0 = block_column_sum<R, TW, THREADS>(&red[0][0][0], threadIdx.x);
+            const float s1 = block_column_sum<R, TW, THREADS>(&red[1][0][0], threadIdx.x);
+            if (threadIdx.x % P == 0) {
+                const float r1 = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s0, invd), eps));
+                float r2 = r1 * r1;
+                r2 = r2 * invd;
+                tot[0][threadIdx.x / P] = r1;
+                tot[1][threadIdx.x / P] = s1 * r2;                                 // stories_cpu_ops.h:39-41
+            }
         }
         __syncthreads();
         const V<VEC> rr = lanes_from_smem<VEC>(&tot[0][lg * VEC]), coef = lanes_from_smem<VEC>(&tot[1][lg * VEC]);
@@ -155,10 +155,10 @@ rmsnorm_bwd_rr_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *
                 Raw<T, VEC> ra;
                 if (HAS_ADD) ra.load_stream(add + base + k * step);
                 const V<VEC> xv = rx[k].get(), dv = rd[k].get();
-                const V<VEC> wc = V<VEC>::splat(__ldg(w + c));
+                const float wc = __ldg(w + c);
                 V<VEC> o;
-                if (exact) o = vmul(vsub(vmul(dv, wc), vmul(xv, coef)), rr);
-                else o = vmul(vmul(vsub(dv, vmul(xv, coef)), rr), wc);             // stories_cpu_ops.h:43-46
+                if (exact) o = vmul(vsub(vscale(dv, wc), vmul(xv, coef)), rr);
+                else o = vscale(vmul(vsub(dv, vmul(xv, coef)), rr), wc);             // stories_cpu_ops.h:43-46
                 dwp = vmul(vmul(dv, xv), rr).hsum();                                // stories_cpu_ops.h:47-50
                 if (HAS_ADD) o = vadd(o, ra.get());                                 // train.m:590,721
                 Raw<T, VEC> ro;

@@ -7,8 +7,10 @@
 // per-token reduction and the write: every byte crosses HBM once.  sin/cos for the thread's
 // pairs and tokens are computed once per tile and reused for every head.
 #include "common.cuh"
+#include "tma.cuh"
 
 #include <math.h>
+#include <type_traits>
 
 namespace ane {
 
@@ -17,6 +19,50 @@ int rmsnorm_bwd_any(cudaStream_t st, ane_dtype dtype, int B, int C, int S, void 
                     const void *x, const float *w, const void *add, float eps, unsigned flags);
 
 constexpr int QK_THREADS = 256;
+
+// ------------------------------------------------------------------ cos / sin table
+// theta(t, i) = (pos0 + t) * freq[i] depends on neither the head nor the sequence, but evaluating
+// cosf / sinf per thread and tile costs as many instructions as all the rest of a fused kernel.
+// The values are therefore computed once, by the same expressions, into a table
+// cos[i][t], sin[i][t] (i < hd/2, t < S) that stays L2-resident, and cached per
+// (hd, S, base, pos0) on the device.
+__global__ void rope_table_kernel(float *__restrict__ cosT, float *__restrict__ sinT, int S, int half, int pos0,
+                                  const __grid_constant__ RopeFreq freq) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= S * half) return;
+    const int i = idx / S, t = idx % S;
+    const float theta = (float)(pos0 + t) * freq.f[i];
+    cosT[idx] = cosf(theta);
+    sinT[idx] = sinf(theta);
+}
+
+struct RopeTable { int hd, S, pos0; float base; float *dev; size_t bytes; unsigned long long stamp; };
+static RopeTable g_tables[4] = {};
+static unsigned long long g_table_clock = 0;
+
+void rope_tables_release() {
+    for (auto &t : g_tables) { if (t.dev) cudaFree(t.dev); t = RopeTable(); }
+}
+
+// Returns cos table (sin table follows at + S*hd/2 floats) or nullptr on failure.
+static const float *rope_table(cudaStream_t st, int hd, int S, float base, int pos0, const RopeFreq &fq) {
+    RopeTable *slot = &g_tables[0];
+    for (auto &t : g_tables) {
+        if (t.dev && t.hd == hd && t.S == S && t.pos0 == pos0 && t.base == base) { t.stamp = ++g_table_clock; return t.dev; }
+        if (t.stamp < slot->stamp) slot = &t;
+    }
+    const size_t n = (size_t)S * (hd / 2);
+    const size_t bytes = 2 * n * sizeof(float);
+    if (slot->dev && slot->bytes < bytes) { cudaFree(slot->dev); slot->dev = nullptr; }
+    if (!slot->dev) {
+        if (cudaMalloc(reinterpret_cast<void **>(&slot->dev), bytes) != cudaSuccess) { cudaGetLastError(); slot->dev = nullptr; return nullptr; }
+        slot->bytes = bytes;
+    }
+    slot->hd = hd; slot->S = S; slot->pos0 = pos0; slot->base = base; slot->stamp = ++g_table_clock;
+    rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(slot->dev, slot->dev + n, S, hd / 2, pos0, fq);
+    note_launch(1);
+    return slot->dev;
+}
 
 // ------------------------------------------------------------------ stand-alone RoPE
 // One thread: one pair index i, VEC tokens, all heads.   cpu_ops.h:168-184 / forward.h:55-70
@@ -81,13 +127,25 @@ rope_kernel(T *out, const T *x, int heads, int hd, int S, int tiles_per_seq, int
 // step (both channels of a rotation pair sit in one thread) for its VEC tokens, in registers,
 // from the load to the store.  sin/cos for the thread's pairs and tokens are computed once per
 // tile and reused for every head.
+// N consecutive table entries (16-byte aligned) as packed lanes.
+template <int N> __device__ __forceinline__ V<N> table_lanes(const float *p) {
+    V<N> v;
+#pragma unroll
+    for (int i = 0; i < N / 4; i++) {
+        const float4 q = __ldg(reinterpret_cast<const float4 *>(p) + i);
+        v.p[2 * i] = make_float2(q.x, q.y);
+        v.p[2 * i + 1] = make_float2(q.z, q.w);
+    }
+    return v;
+}
+
 constexpr int QK_LG = 8;
 constexpr int QK_R = QK_THREADS / QK_LG;   // 32 row groups
 
 template <typename T, int RPT, bool ROPE, int HB>
 __global__ void __launch_bounds__(QK_THREADS, 2)
 qk_fwd_kernel(T *__restrict__ out, const T *__restrict__ x, const float *__restrict__ w, int heads, int S,
-              int tiles_per_seq, float eps, int pos0, const __grid_constant__ RopeFreq freq) {
+              int tiles_per_seq, float eps, const float *__restrict__ cosT, const float *__restrict__ sinT) {
     constexpr int VEC = Elt<T>::VEC;
     constexpr int TW = QK_LG * VEC;
     constexpr int HD = RPT * QK_R;
@@ -102,21 +160,16 @@ qk_fwd_kernel(T *__restrict__ out, const T *__restrict__ x, const float *__restr
     const size_t hstep = (size_t)HD * S;
     const float invd = 1.0f / (float)HD;
 
-    V<VEC> wc[RPT];
+    float wc[RPT];
 #pragma unroll
-    for (int k = 0; k < RPT; k++) wc[k] = V<VEC>::splat(__ldg(w + rg * RPT + k));
+    for (int k = 0; k < RPT; k++) wc[k] = __ldg(w + rg * RPT + k);
 
     V<VEC> cs[RPT / 2], sn[RPT / 2];
-    if (ROPE) {
+    if (ROPE && active) {
 #pragma unroll
         for (int p = 0; p < RPT / 2; p++) {
-            const float fr = freq.f[rg * (RPT / 2) + p];
-#pragma unroll
-            for (int j = 0; j < VEC; j++) {
-                const float theta = (float)(pos0 + t + j) * fr;
-                cs[p].set(j, cosf(theta));
-                sn[p].set(j, sinf(theta));
-            }
+            cs[p] = table_lanes<VEC>(cosT + (size_t)(rg * (RPT / 2) + p) * S + t);
+            sn[p] = table_lanes<VEC>(sinT + (size_t)(rg * (RPT / 2) + p) * S + t);
         }
     }
 
@@ -140,12 +193,11 @@ qk_fwd_kernel(T *__restrict__ out, const T *__restrict__ x, const float *__restr
             lanes_to_smem<VEC>(&red[buf][hh][rg][lg * VEC], ss);
         }
         __syncthreads();
-        if (threadIdx.x < HB * TW) {      // one thread per (head, token): column sum, then rrms once
-            const int hh = threadIdx.x / TW, col = threadIdx.x % TW;
-            float s = 0.0f;
-#pragma unroll 8
-            for (int q = 0; q < QK_R; q++) s += red[buf][hh][q][col];
-            tot[buf][hh][col] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s, invd), eps));
+#pragma unroll
+        for (int hh = 0; hh < HB; hh++) {     // column sums with the whole block, then rrms once per token
+            constexpr int P = QK_THREADS / TW;
+            const float s = block_column_sum<QK_R, TW, QK_THREADS>(&red[buf][hh][0][0], threadIdx.x);
+            if (threadIdx.x % P == 0) tot[buf][hh][threadIdx.x / P] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s, invd), eps));
         }
         __syncthreads();
 #pragma unroll
@@ -154,7 +206,7 @@ qk_fwd_kernel(T *__restrict__ out, const T *__restrict__ x, const float *__restr
                 const V<VEC> rr = lanes_from_smem<VEC>(&tot[buf][hh][lg * VEC]);
                 V<VEC> v[RPT];
 #pragma unroll
-                for (int k = 0; k < RPT; k++) v[k] = vmul(vmul(r[hh][k].get(), rr), wc[k]);
+                for (int k = 0; k < RPT; k++) v[k] = vscale(vmul(r[hh][k].get(), rr), wc[k]);
                 if (ROPE) {
 #pragma unroll
                     for (int p = 0; p < RPT / 2; p++) {
@@ -177,8 +229,8 @@ qk_fwd_kernel(T *__restrict__ out, const T *__restrict__ x, const float *__restr
 template <typename T, int RPT, bool ROPE, int HB>
 __global__ void __launch_bounds__(QK_THREADS, (HB == 1 ? 2 : 1))
 qk_bwd_kernel(T *__restrict__ dx, float *__restrict__ partial, const T *__restrict__ dy, const T *__restrict__ x,
-              const float *__restrict__ w, int heads, int S, int tiles_per_seq, int ntiles, float eps, int pos0,
-              unsigned flags, const __grid_constant__ RopeFreq freq) {
+              const float *__restrict__ w, int heads, int S, int tiles_per_seq, int ntiles, float eps,
+              unsigned flags, const float *__restrict__ cosT, const float *__restrict__ sinT) {
     constexpr int VEC = Elt<T>::VEC;
     constexpr int TW = QK_LG * VEC;
     constexpr int HD = RPT * QK_R;
@@ -190,10 +242,9 @@ qk_bwd_kernel(T *__restrict__ dx, float *__restrict__ partial, const T *__restri
     const bool exact = (flags & ANE_NORM_BWD_EXACT) != 0;
     const size_t hstep = (size_t)HD * S;
 
-    V<VEC> wc[RPT];
-    float dwacc[RPT];
+    float wc[RPT], dwacc[RPT];
 #pragma unroll
-    for (int k = 0; k < RPT; k++) { wc[k] = V<VEC>::splat(__ldg(w + rg * RPT + k)); dwacc[k] = 0.0f; }
+    for (int k = 0; k < RPT; k++) { wc[k] = __ldg(w + rg * RPT + k); dwacc[k] = 0.0f; }
 
     int it = 0;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
@@ -203,16 +254,11 @@ qk_bwd_kernel(T *__restrict__ dx, float *__restrict__ partial, const T *__restri
         const size_t base = (size_t)b * heads * HD * S + t + (size_t)(rg * RPT) * S;
 
         V<VEC> cs[RPT / 2], sn[RPT / 2];
-        if (ROPE) {
+        if (ROPE && active) {
 #pragma unroll
             for (int p = 0; p < RPT / 2; p++) {
-                const float fr = freq.f[rg * (RPT / 2) + p];
-#pragma unroll
-                for (int j = 0; j < VEC; j++) {
-                    const float theta = (float)(pos0 + t + j) * fr;
-                    cs[p].set(j, cosf(theta));
-                    sn[p].set(j, sinf(theta));
-                }
+                cs[p] = table_lanes<VEC>(cosT + (size_t)(rg * (RPT / 2) + p) * S + t);
+                sn[p] = table_lanes<VEC>(sinT + (size_t)(rg * (RPT / 2) + p) * S + t);
             }
         }
 
@@ -244,24 +290,26 @@ qk_bwd_kernel(T *__restrict__ dx, float *__restrict__ partial, const T *__restri
                         const V<VEC> x0 = rxr[hh][2 * p].get(), x1 = rxr[hh][2 * p + 1].get();
                         ss = vfma(x0, x0, ss);
                         ss = vfma(x1, x1, ss);
-                        dot = vfma(vmul(g0, x0), wc[2 * p], dot);
-                        dot = vfma(vmul(g1, x1), wc[2 * p + 1], dot);
+                        dot = vfma_s(vmul(g0, x0), wc[2 * p], dot);
+                        dot = vfma_s(vmul(g1, x1), wc[2 * p + 1], dot);
                     }
                 }
                 lanes_to_smem<VEC>(&red[buf][hh][0][rg][lg * VEC], ss);
                 lanes_to_smem<VEC>(&red[buf][hh][1][rg][lg * VEC], dot);
             }
             __syncthreads();
-            if (threadIdx.x < HB * TW) {  // one thread per (head, token): both sums, then rrms and coef once
-                const int hh = threadIdx.x / TW, col = threadIdx.x % TW;
-                float s0 = 0.0f, s1 = 0.0f;
-#pragma unroll 8
-                for (int q = 0; q < QK_R; q++) { s0 += red[buf][hh][0][q][col]; s1 += red[buf][hh][1][q][col]; }
-                const float r1 = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s0, invd), eps));
-                float r2 = r1 * r1;
-                r2 = r2 * invd;
-                tot[buf][hh][0][col] = r1;
-                tot[buf][hh][1][col] = s1 * r2;
+#pragma unroll
+            for (int hh = 0; hh < HB; hh++) {  // column sums with the whole block, then rrms and coef once per token
+                constexpr int P = QK_THREADS / TW;
+                const float s0 = block_column_sum<QK_R, TW, QK_THREADS>(&red[buf][hh][0][0][0], threadIdx.x);
+                const float s1 = block_column_sum<QK_R, TW, QK_THREADS>(&red[buf][hh][1][0][0], threadIdx.x);
+                if (threadIdx.x % P == 0) {
+                    const float r1 = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s0, invd), eps));
+                    float r2 = r1 * r1;
+                    r2 = r2 * invd;
+                    tot[buf][hh][0][threadIdx.x / P] = r1;
+                    tot[buf][hh][1][threadIdx.x / P] = s1 * r2;
+                }
             }
             __syncthreads();
 #pragma unroll
@@ -284,8 +332,8 @@ qk_bwd_kernel(T *__restrict__ dx, float *__restrict__ partial, const T *__restri
                             const int k = 2 * p + q;
                             const V<VEC> xv = rxr[hh][k].get();
                             V<VEC> o;
-                            if (exact) o = vmul(vsub(vmul(g[q], wc[k]), vmul(xv, coef)), rr);
-                            else o = vmul(vmul(vsub(g[q], vmul(xv, coef)), rr), wc[k]);
+                            if (exact) o = vmul(vsub(vscale(g[q], wc[k]), vmul(xv, coef)), rr);
+                            else o = vscale(vmul(vsub(g[q], vmul(xv, coef)), rr), wc[k]);
                             dwacc[k] += vmul(vmul(g[q], xv), rr).hsum();
                             Raw<T, VEC> ro;
                             ro.put(o);
@@ -303,6 +351,254 @@ qk_bwd_kernel(T *__restrict__ dx, float *__restrict__ partial, const T *__restri
 #pragma unroll
         for (int off = QK_LG / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
         if (lg == 0) partial[(size_t)blockIdx.x * HD + rg * RPT + k] = s;
+    }
+}
+
+// ------------------------------------------------------------------ TMA-fed variants
+// Same thread layout and arithmetic as qk_fwd_kernel / qk_bwd_kernel, but the head tiles
+// ([HD channels x 8*VEC tokens], 16 KiB in bf16) are brought into a ring of NST shared-memory
+// stages by the tensor copy engine, several tiles ahead of the math: loads stay in flight all the
+// time and cost no registers.  A block is persistent over token tiles; within a tile it walks
+// over the heads.  Thread 0 issues the copies; a stage is refilled right after the block-wide
+// barrier that follows everybody's read of it (the barrier the reduction needs anyway).
+// Waits on the copy barriers are bounded: on a give-up the block records it in the status words
+// and returns.
+template <typename T, int RPT, bool ROPE, int NST>
+__global__ void __launch_bounds__(QK_THREADS)
+qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap, const float *__restrict__ w, int heads,
+                  int S, int tiles_per_seq, int ntiles, float eps, ane_cuda_status *status,
+                  const float *__restrict__ cosT, const float *__restrict__ sinT) {
+    constexpr int VEC = Elt<T>::VEC;
+    constexpr int TW = QK_LG * VEC;
+    constexpr int HD = RPT * QK_R;
+    constexpr uint32_t STAGE_BYTES = HD * TW * sizeof(T);
+    extern __shared__ unsigned char stages_raw[];
+    unsigned char *stages = stages_raw + ((128u - (smem_u32(stages_raw) & 127u)) & 127u);   // 128-byte aligned copy targets
+    __shared__ __align__(8) uint64_t full[NST];
+    __shared__ __align__(16) float red[2][QK_R][TW];
+    __shared__ __align__(16) float tot[2][TW];
+    __shared__ int give_up;
+
+    const int lg = threadIdx.x % QK_LG, rg = threadIdx.x / QK_LG;
+    const float invd = 1.0f / (float)HD;
+    const size_t hstep = (size_t)HD * S;
+    const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int n_items = my_tiles * heads;
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < NST; s++) mbar_init(&full[s], 1);
+        mbar_init_fence();
+        give_up = 0;
+    }
+    __syncthreads();
+
+    auto issue = [&](int j) {
+        const int tl = (int)blockIdx.x + (j / heads) * (int)gridDim.x;
+        const int s = j % NST;
+        mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+        tma_load_3d(stages + (size_t)s * STAGE_BYTES, &xmap, (tl % tiles_per_seq) * TW, (j % heads) * HD, tl / tiles_per_seq, &full[s]);
+    };
+    if (threadIdx.x == 0)
+        for (int j = 0; j < NST && j < n_items; j++) issue(j);
+
+    float wc[RPT];
+#pragma unroll
+    for (int k = 0; k < RPT; k++) wc[k] = __ldg(w + rg * RPT + k);
+    V<VEC> cs[RPT / 2], sn[RPT / 2];
+
+    for (int j = 0; j < n_items; j++) {
+        const int tl = (int)blockIdx.x + (j / heads) * (int)gridDim.x;
+        const int h = j % heads;
+        const int b = tl / tiles_per_seq;
+        const int t = (tl % tiles_per_seq) * TW + lg * VEC;
+        const bool active = t < S;
+        const int s = j % NST, buf = j & 1;
+        if (ROPE && h == 0 && active) {
+#pragma unroll
+            for (int p = 0; p < RPT / 2; p++) {
+                cs[p] = table_lanes<VEC>(cosT + (size_t)(rg * (RPT / 2) + p) * S + t);
+                sn[p] = table_lanes<VEC>(sinT + (size_t)(rg * (RPT / 2) + p) * S + t);
+            }
+        }
+        if (!mbar_wait_bounded(&full[s], (uint32_t)(j / NST) & 1u)) give_up = 1;
+        const T *tile = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES);
+        Raw<T, VEC> r[RPT];
+        V<VEC> ss = V<VEC>::splat(0.0f);
+#pragma unroll
+        for (int k = 0; k < RPT; k++) {
+            r[k].load(tile + (rg * RPT + k) * TW + lg * VEC);
+            const V<VEC> v = r[k].get();
+            ss = vfma(v, v, ss);
+        }
+        lanes_to_smem<VEC>(&red[buf][rg][lg * VEC], ss);
+        __syncthreads();                                   // every thread has its part of stage s in registers
+        if (give_up) {
+            if (threadIdx.x == 0) atomicAdd(&status->wait_giveups, 1);
+            return;
+        }
+        if (threadIdx.x == 0 && j + NST < n_items) { fence_proxy_async(); issue(j + NST); }
+        {
+            constexpr int P = QK_THREADS / TW;
+            const float sum = block_column_sum<QK_R, TW, QK_THREADS>(&red[buf][0][0], threadIdx.x);
+            if (threadIdx.x % P == 0) tot[buf][threadIdx.x / P] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(sum, invd), eps));
+        }
+        __syncthreads();
+        if (active) {
+            const V<VEC> rr = lanes_from_smem<VEC>(&tot[buf][lg * VEC]);
+            V<VEC> v[RPT];
+#pragma unroll
+            for (int k = 0; k < RPT; k++) v[k] = vscale(vmul(r[k].get(), rr), wc[k]);
+            if (ROPE) {
+#pragma unroll
+                for (int p = 0; p < RPT / 2; p++) {
+                    const V<VEC> a = v[2 * p], bb = v[2 * p + 1];
+                    v[2 * p] = vsub(vmul(a, cs[p]), vmul(bb, sn[p]));
+                    v[2 * p + 1] = vfma(a, sn[p], vmul(bb, cs[p]));
+                }
+            }
+            const size_t o = (size_t)b * heads * hstep + h * hstep + (size_t)(rg * RPT) * S + t;
+#pragma unroll
+            for (int k = 0; k < RPT; k++) {
+                Raw<T, VEC> ro;
+                ro.put(v[k]);
+                ro.store_stream(out + o + (size_t)k * S);
+            }
+        }
+    }
+}
+
+template <typename T, int RPT, bool ROPE, int NST>
+__global__ void __launch_bounds__(QK_THREADS)
+qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_constant__ CUtensorMap dymap,
+                  const __grid_constant__ CUtensorMap xmap, const float *__restrict__ w, int heads, int S, int tiles_per_seq,
+                  int ntiles, float eps, unsigned flags, ane_cuda_status *status,
+                  const float *__restrict__ cosT, const float *__restrict__ sinT) {
+    constexpr int VEC = Elt<T>::VEC;
+    constexpr int TW = QK_LG * VEC;
+    constexpr int HD = RPT * QK_R;
+    constexpr uint32_t TILE_BYTES = HD * TW * sizeof(T);
+    constexpr uint32_t STAGE_BYTES = 2 * TILE_BYTES;       // x tile, then dy tile
+    extern __shared__ unsigned char stages_raw[];
+    unsigned char *stages = stages_raw + ((128u - (smem_u32(stages_raw) & 127u)) & 127u);   // 128-byte aligned copy targets
+    __shared__ __align__(8) uint64_t full[NST];
+    __shared__ __align__(16) float red[2][2][QK_R][TW];
+    __shared__ __align__(16) float tot[2][2][TW];
+    __shared__ int give_up;
+
+    const int lg = threadIdx.x % QK_LG, rg = threadIdx.x / QK_LG;
+    const float invd = 1.0f / (float)HD;
+    const bool exact = (flags & ANE_NORM_BWD_EXACT) != 0;
+    const size_t hstep = (size_t)HD * S;
+    const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int n_items = my_tiles * heads;
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < NST; s++) mbar_init(&full[s], 1);
+        mbar_init_fence();
+        give_up = 0;
+    }
+    __syncthreads();
+
+    auto issue = [&](int j) {
+        const int tl = (int)blockIdx.x + (j / heads) * (int)gridDim.x;
+        const int s = j % NST;
+        unsigned char *dst = stages + (size_t)s * STAGE_BYTES;
+        mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+        tma_load_3d(dst, &xmap, (tl % tiles_per_seq) * TW, (j % heads) * HD, tl / tiles_per_seq, &full[s]);
+        tma_load_3d(dst + TILE_BYTES, &dymap, (tl % tiles_per_seq) * TW, (j % heads) * HD, tl / tiles_per_seq, &full[s]);
+    };
+    if (threadIdx.x == 0)
+        for (int j = 0; j < NST && j < n_items; j++) issue(j);
+
+    float wc[RPT], dwacc[RPT];
+#pragma unroll
+    for (int k = 0; k < RPT; k++) { wc[k] = __ldg(w + rg * RPT + k); dwacc[k] = 0.0f; }
+    V<VEC> cs[RPT / 2], sn[RPT / 2];
+
+    for (int j = 0; j < n_items; j++) {
+        const int tl = (int)blockIdx.x + (j / heads) * (int)gridDim.x;
+        const int h = j % heads;
+        const int b = tl / tiles_per_seq;
+        const int t = (tl % tiles_per_seq) * TW + lg * VEC;
+        const bool active = t < S;
+        const int s = j % NST, buf = j & 1;
+        if (ROPE && h == 0 && active) {
+#pragma unroll
+            for (int p = 0; p < RPT / 2; p++) {
+                cs[p] = table_lanes<VEC>(cosT + (size_t)(rg * (RPT / 2) + p) * S + t);
+                sn[p] = table_lanes<VEC>(sinT + (size_t)(rg * (RPT / 2) + p) * S + t);
+            }
+        }
+        if (!mbar_wait_bounded(&full[s], (uint32_t)(j / NST) & 1u)) give_up = 1;
+        const T *xt = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES);
+        const T *dt = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES + TILE_BYTES);
+        V<VEC> xv[RPT], g[RPT];
+        V<VEC> ss = V<VEC>::splat(0.0f), dot = V<VEC>::splat(0.0f);
+#pragma unroll
+        for (int k = 0; k < RPT; k++) {
+            Raw<T, VEC> a, c;
+            a.load(xt + (rg * RPT + k) * TW + lg * VEC);
+            c.load(dt + (rg * RPT + k) * TW + lg * VEC);
+            xv[k] = a.get();
+            g[k] = c.get();
+        }
+#pragma unroll
+        for (int p = 0; p < RPT / 2; p++) {
+            if (ROPE) {       // g = rope^-1(dy): (a cos + b sin, -a sin + b cos)   cpu_ops.h:178-181
+                const V<VEC> a = g[2 * p], bb = g[2 * p + 1];
+                g[2 * p] = vfma(a, cs[p], vmul(bb, sn[p]));
+                g[2 * p + 1] = vsub(vmul(bb, cs[p]), vmul(a, sn[p]));
+            }
+            ss = vfma(xv[2 * p], xv[2 * p], ss);
+            ss = vfma(xv[2 * p + 1], xv[2 * p + 1], ss);
+            dot = vfma_s(vmul(g[2 * p], xv[2 * p]), wc[2 * p], dot);
+            dot = vfma_s(vmul(g[2 * p + 1], xv[2 * p + 1]), wc[2 * p + 1], dot);
+        }
+        lanes_to_smem<VEC>(&red[buf][0][rg][lg * VEC], ss);
+        lanes_to_smem<VEC>(&red[buf][1][rg][lg * VEC], dot);
+        __syncthreads();                                   // stage s is in registers everywhere
+        if (give_up) {
+            if (threadIdx.x == 0) atomicAdd(&status->wait_giveups, 1);
+            break;
+        }
+        if (threadIdx.x == 0 && j + NST < n_items) { fence_proxy_async(); issue(j + NST); }
+        {
+            constexpr int P = QK_THREADS / TW;
+            const float s0 = block_column_sum<QK_R, TW, QK_THREADS>(&red[buf][0][0][0], threadIdx.x);
+            const float s1 = block_column_sum<QK_R, TW, QK_THREADS>(&red[buf][1][0][0], threadIdx.x);
+            if (threadIdx.x % P == 0) {
+                const float r1 = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s0, invd), eps));
+                float r2 = r1 * r1;
+                r2 = r2 * invd;
+                tot[buf][0][threadIdx.x / P] = r1;
+                tot[buf][1][threadIdx.x / P] = s1 * r2;
+            }
+        }
+        __syncthreads();
+        if (active) {
+            const V<VEC> rr = lanes_from_smem<VEC>(&tot[buf][0][lg * VEC]);
+            const V<VEC> coef = lanes_from_smem<VEC>(&tot[buf][1][lg * VEC]);
+            const size_t o = (size_t)b * heads * hstep + h * hstep + (size_t)(rg * RPT) * S + t;
+#pragma unroll
+            for (int k = 0; k < RPT; k++) {
+                V<VEC> ov;
+                if (exact) ov = vmul(vsub(vscale(g[k], wc[k]), vmul(xv[k], coef)), rr);
+                else ov = vscale(vmul(vsub(g[k], vmul(xv[k], coef)), rr), wc[k]);
+                dwacc[k] += vmul(vmul(g[k], xv[k]), rr).hsum();
+                Raw<T, VEC> ro;
+                ro.put(ov);
+                ro.store_stream(dx + o + (size_t)k * S);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < RPT; k++) {
+        float sum = dwacc[k];
+#pragma unroll
+        for (int off = QK_LG / 2; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        if (lg == 0) partial[(size_t)blockIdx.x * HD + rg * RPT + k] = sum;
     }
 }
 
@@ -465,7 +761,7 @@ static int launch_rope(cudaStream_t st, int B, int heads, int hd, int S, void *o
             dim3 grid_((unsigned)(B * tps_), (unsigned)((hd / 2 + (QK_THREADS / (LGv)) - 1) / (QK_THREADS / (LGv)))); \
             rope_kernel<T, VEC, LGv><<<grid_, QK_THREADS, 0, st>>>((T *)out, (const T *)x, heads, hd, S, tps_, pos0, inverse, fq); \
         } while (0)
-        switch (tuning("rope_lg", 8)) {
+        switch (tuning("rope_lg", 16)) {
             case 32: ANE_ROPE_LG(32); break;
             case 16: ANE_ROPE_LG(16); break;
             default: ANE_ROPE_LG(8); break;
@@ -499,12 +795,40 @@ static bool qk_fast_ok(int hd, int S, const void *a, const void *b, const void *
 
 template <typename T, bool ROPE>
 static int launch_qk_fwd(cudaStream_t st, int B, int heads, int hd, int S, void *out, const void *x, const float *w,
-                         float eps, int pos0, const RopeFreq &fq) {
+                         float eps, float base, int pos0, const RopeFreq &fq) {
     constexpr int VEC = Elt<T>::VEC;
+    const float *cosT = nullptr, *sinT = nullptr;
+    if (ROPE) {
+        cosT = rope_table(st, hd, S, base, pos0, fq);
+        if (!cosT) return fail(ANE_CUDA_ERR_NOMEM, "qknorm_rope: no memory for the cos/sin table");
+        sinT = cosT + (size_t)S * (hd / 2);
+    }
     const int tps = (S + QK_LG * VEC - 1) / (QK_LG * VEC);
     const unsigned grid = (unsigned)(B * tps);
-    const int hb = tuning("qk_fwd", 2);
-#define ANE_QKF(RPTv, HBv) qk_fwd_kernel<T, RPTv, ROPE, HBv><<<grid, QK_THREADS, 0, st>>>((T *)out, (const T *)x, w, heads, S, tps, eps, pos0, fq)
+    const int hb = tuning("qk_fwd", 3);
+    if (hb >= 3) {       // TMA-fed ring of hb stages
+        CUtensorMap xmap;
+        if (int rc = make_bcs_tensor_map(&xmap, sizeof(T) == 4 ? ANE_F32 : (std::is_same<T, __half>::value ? ANE_F16 : ANE_BF16), x, B,
+                                         heads * hd, S, QK_LG * VEC, hd)) return rc;
+        const int ntiles = B * tps;
+#define ANE_QKF_TMA(RPTv, NSTv)                                                                                      \
+        do {                                                                                                         \
+            auto k = qk_fwd_tma_kernel<T, RPTv, ROPE, NSTv>;                                                          \
+            const size_t smem = (size_t)NSTv * (RPTv * QK_R) * (QK_LG * VEC) * sizeof(T) + 128;                             \
+            ANE_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));           \
+            int per_sm = 0;                                                                                          \
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, QK_THREADS, smem) != cudaSuccess || per_sm < 1) per_sm = 1; \
+            int g = per_sm * ctx().sm_count;                                                                         \
+            if (g > ntiles) g = ntiles;                                                                              \
+            k<<<g, QK_THREADS, smem, st>>>((T *)out, xmap, w, heads, S, tps, ntiles, eps, ctx().status, cosT, sinT);   \
+        } while (0)
+        if (hd == 128) { if (hb == 3) ANE_QKF_TMA(4, 3); else if (hb == 4) ANE_QKF_TMA(4, 4); else ANE_QKF_TMA(4, 6); }
+        else { if (hb == 3) ANE_QKF_TMA(2, 3); else if (hb == 4) ANE_QKF_TMA(2, 4); else ANE_QKF_TMA(2, 6); }
+#undef ANE_QKF_TMA
+        ANE_LAUNCH_OK(1);
+        return ANE_CUDA_OK;
+    }
+#define ANE_QKF(RPTv, HBv) qk_fwd_kernel<T, RPTv, ROPE, HBv><<<grid, QK_THREADS, 0, st>>>((T *)out, (const T *)x, w, heads, S, tps, eps, cosT, sinT)
     if (hd == 128) { if (hb == 1) ANE_QKF(4, 1); else ANE_QKF(4, 2); }
     else { if (hb == 1) ANE_QKF(2, 1); else ANE_QKF(2, 2); }
 #undef ANE_QKF
@@ -514,20 +838,51 @@ static int launch_qk_fwd(cudaStream_t st, int B, int heads, int hd, int S, void 
 
 template <typename T, bool ROPE>
 static int launch_qk_bwd(cudaStream_t st, int B, int heads, int hd, int S, void *dx, float *dw, const void *dy,
-                         const void *x, const float *w, float eps, int pos0, unsigned flags, const RopeFreq &fq) {
+                         const void *x, const float *w, float eps, float base, int pos0, unsigned flags, const RopeFreq &fq) {
     constexpr int VEC = Elt<T>::VEC;
+    const float *cosT = nullptr, *sinT = nullptr;
+    if (ROPE) {
+        cosT = rope_table(st, hd, S, base, pos0, fq);
+        if (!cosT) return fail(ANE_CUDA_ERR_NOMEM, "rope_qknorm_bwd: no memory for the cos/sin table");
+        sinT = cosT + (size_t)S * (hd / 2);
+    }
     const int tps = (S + QK_LG * VEC - 1) / (QK_LG * VEC);
     const int ntiles = B * tps;
-    const int hb = tuning("qk_bwd", 1);
+    const int hb = tuning("qk_bwd", 3);
     int grid = 0;
     float *partial = nullptr;
+    if (hb >= 3) {       // TMA-fed ring of hb stages
+        const ane_dtype dte = sizeof(T) == 4 ? ANE_F32 : (std::is_same<T, __half>::value ? ANE_F16 : ANE_BF16);
+        CUtensorMap xmap, dymap;
+        if (int rc = make_bcs_tensor_map(&xmap, dte, x, B, heads * hd, S, QK_LG * VEC, hd)) return rc;
+        if (int rc = make_bcs_tensor_map(&dymap, dte, dy, B, heads * hd, S, QK_LG * VEC, hd)) return rc;
+#define ANE_QKB_TMA(RPTv, NSTv)                                                                                      \
+        do {                                                                                                         \
+            auto k = qk_bwd_tma_kernel<T, RPTv, ROPE, NSTv>;                                                          \
+            const size_t smem = (size_t)NSTv * 2 * (RPTv * QK_R) * (QK_LG * VEC) * sizeof(T) + 128;                         \
+            ANE_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));           \
+            int per_sm = 0;                                                                                          \
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, QK_THREADS, smem) != cudaSuccess || per_sm < 1) per_sm = 1; \
+            grid = per_sm * ctx().sm_count;                                                                          \
+            if (grid > ntiles) grid = ntiles;                                                                        \
+            partial = static_cast<float *>(workspace((size_t)grid * hd * sizeof(float)));                            \
+            if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "qknorm_bwd: no scratch");                                 \
+            k<<<grid, QK_THREADS, smem, st>>>((T *)dx, partial, dymap, xmap, w, heads, S, tps, ntiles, eps, flags, ctx().status, cosT, sinT); \
+        } while (0)
+        if (hd == 128) { if (hb == 3) ANE_QKB_TMA(4, 3); else ANE_QKB_TMA(4, 4); }
+        else { if (hb == 3) ANE_QKB_TMA(2, 3); else ANE_QKB_TMA(2, 4); }
+#undef ANE_QKB_TMA
+        qk_dw_finalize_kernel<<<(hd + 127) / 128, 128, 0, st>>>(dw, partial, grid, hd);
+        ANE_LAUNCH_OK(2);
+        return ANE_CUDA_OK;
+    }
 #define ANE_QKB(RPTv, HBv)                                                                                          \
     do {                                                                                                            \
         auto k = qk_bwd_kernel<T, RPTv, ROPE, HBv>;                                                                  \
         grid = qk_persistent_grid(k, ntiles);                                                                       \
         partial = static_cast<float *>(workspace((size_t)grid * hd * sizeof(float)));                               \
         if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "qknorm_bwd: no scratch");                                    \
-        k<<<grid, QK_THREADS, 0, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, heads, S, tps, ntiles, eps, pos0, flags, fq); \
+        k<<<grid, QK_THREADS, 0, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, heads, S, tps, ntiles, eps, flags, cosT, sinT); \
     } while (0)
     (void)hb;       // one head per step: two would need more than 48 KiB of static shared memory
     if (hd == 128) ANE_QKB(4, 1);
@@ -574,7 +929,7 @@ int ane_cuda_qknorm_dev(void *stream, ane_dtype dtype, int B, int heads, int hd,
     cudaStream_t st = (cudaStream_t)stream;
     RopeFreq fq = {};
     ANE_DISPATCH_DTYPE(dtype, T,
-        if (qk_fast_ok<T, false>(hd, S, out, x, nullptr)) return (launch_qk_fwd<T, false>(st, B, heads, hd, S, out, x, w, eps, 0, fq)));
+        if (qk_fast_ok<T, false>(hd, S, out, x, nullptr)) return (launch_qk_fwd<T, false>(st, B, heads, hd, S, out, x, w, eps, 0.0f, 0, fq)));
     return rmsnorm_fwd_any(st, dtype, B * heads, hd, S, out, x, w, eps);
 }
 
@@ -588,7 +943,7 @@ int ane_cuda_qknorm_bwd_dev(void *stream, ane_dtype dtype, int B, int heads, int
     cudaStream_t st = (cudaStream_t)stream;
     RopeFreq fq = {};
     ANE_DISPATCH_DTYPE(dtype, T,
-        if (qk_fast_ok<T, false>(hd, S, dx, dy, x)) return (launch_qk_bwd<T, false>(st, B, heads, hd, S, dx, dw, dy, x, w, eps, 0, flags, fq)));
+        if (qk_fast_ok<T, false>(hd, S, dx, dy, x)) return (launch_qk_bwd<T, false>(st, B, heads, hd, S, dx, dw, dy, x, w, eps, 0.0f, 0, flags, fq)));
     return rmsnorm_bwd_any(st, dtype, B * heads, hd, S, dx, dw, dy, x, w, nullptr, eps, flags);
 }
 
@@ -602,7 +957,7 @@ int ane_cuda_qknorm_rope_dev(void *stream, ane_dtype dtype, int B, int heads, in
     RopeFreq fq;
     if (int rc = fill_freq(fq, hd, base)) return rc;
     ANE_DISPATCH_DTYPE(dtype, T,
-        if (qk_fast_ok<T, true>(hd, S, out, x, nullptr)) return (launch_qk_fwd<T, true>(st, B, heads, hd, S, out, x, w, eps, pos0, fq)));
+        if (qk_fast_ok<T, true>(hd, S, out, x, nullptr)) return (launch_qk_fwd<T, true>(st, B, heads, hd, S, out, x, w, eps, base, pos0, fq)));
     // other head widths and unaligned shapes
     ANE_DISPATCH_DTYPE(dtype, T, return (launch_qk_rope_fwd_generic<T>(st, B, heads, hd, S, out, x, w, eps, pos0, fq)));
     return ANE_CUDA_OK;
@@ -620,7 +975,7 @@ int ane_cuda_rope_qknorm_bwd_dev(void *stream, ane_dtype dtype, int B, int heads
     RopeFreq fq;
     if (int rc = fill_freq(fq, hd, base)) return rc;
     ANE_DISPATCH_DTYPE(dtype, T,
-        if (qk_fast_ok<T, true>(hd, S, dx, dy, x)) return (launch_qk_bwd<T, true>(st, B, heads, hd, S, dx, dw, dy, x, w, eps, pos0, flags, fq)));
+        if (qk_fast_ok<T, true>(hd, S, dx, dy, x)) return (launch_qk_bwd<T, true>(st, B, heads, hd, S, dx, dw, dy, x, w, eps, base, pos0, flags, fq)));
     // other head widths and unaligned shapes
     ANE_DISPATCH_DTYPE(dtype, T, return (launch_qk_rope_bwd_generic<T>(st, B, heads, hd, S, dx, dw, dy, x, w, eps, pos0, flags, fq)));
     return ANE_CUDA_OK;

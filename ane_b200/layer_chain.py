@@ -245,6 +245,26 @@ class LayerChain:
         ops.embed_backward(p.embed(grad=True), dy, self.tokens)
         self.dy_out = dy
 
+    # ------------------------------------------------------------------ CUDA graph replay
+    def capture(self):
+        """Record forward() + backward() of one micro-batch into a CUDA graph.  The operator
+        chain is a fixed sequence of a few hundred short kernels, so replaying it as a graph removes
+        the per-launch host cost and most of the gap between kernels.  One eager pass runs first so
+        that the library's scratch range has reached its final size (no allocation may happen while
+        a stream is being captured)."""
+        self.forward()
+        self.backward()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.forward()
+            self.backward()
+        self.graph = g
+        return g
+
+    def replay(self):
+        self.graph.replay()
+
     def launches_per_microbatch(self) -> int:
         """Kernels of this library launched by forward() + backward()."""
         L = self.cfg.layers

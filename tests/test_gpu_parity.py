@@ -333,7 +333,8 @@ def test_embed_backward_skips_out_of_range(dev, oracle):
 
 
 @pytest.mark.parametrize("idt", ["int32", "uint16"])
-@pytest.mark.parametrize("B,V,S,gs", [(1, 32000, 256, 1.0), (2, 1000, 37, 256.0), (1, 151936, 64, 1.0), (3, 17, 4, 1.0), (1, 9200, 256, 1.0)])
+@pytest.mark.parametrize("B,V,S,gs", [(1, 32000, 256, 1.0), (2, 1000, 37, 256.0), (1, 151936, 64, 1.0), (3, 17, 4, 1.0), (1, 9200, 256, 1.0),
+                                       (5, 9200, 256, 1.0), (2, 32000, 520, 256.0)])   # the last two take the whole-grid wave kernel
 def test_cross_entropy(dev, oracle, B, V, S, gs, idt):
     torch = _torch()
     if idt == "uint16" and V > 65536:
@@ -599,3 +600,64 @@ def test_full_size_properties(dev):
     loss, dl = dev.cross_entropy(logits, tg)
     assert float(dl.double().sum(dim=1).abs().max()) <= 1e-6          # sum_v (p - onehot) = 0 per token
     assert abs(float(loss[0]) - (np.log(Vs) + 0.5)) < 0.2              # E[loss] = log V + sigma^2/2 for N(0,1) logits
+
+
+def test_layer_chain_matches_oracle_and_graph_replay(dev, oracle):
+    """The whole operator chain of a micro-batch (ane_b200.layer_chain, the order of
+    training_dynamic/train.m:405-728) on a tiny fp32 model: every product of the chain equals the
+    same sequence of oracle operators, and replaying the captured CUDA graph gives the eager result
+    bit for bit."""
+    torch = _torch()
+    from ane_b200.layer_chain import ChainConfig, FlatParams, LayerChain
+    cfg = ChainConfig(layers=2, dim=64, hidden=96, heads=2, kv_heads=1, head_dim=64, seq=32, vocab=50,
+                      dtype=torch.float32, alpha=0.5, rope_base=1e4)
+    p = FlatParams(cfg, "cuda")
+    p.init_random(seed=3)
+    p.zero_produced_grads()
+    ch = LayerChain(cfg, 2, p, "cuda", rotate=2, seed=5)
+    ch.forward()
+    ch.backward()
+    torch.cuda.synchronize()
+
+    def n(t):
+        return t.detach().float().cpu().numpy().copy()
+
+    # --- oracle replay of the same chain
+    tok = n(ch.tokens).astype(np.int32)
+    x, _ = oracle.embed_lookup(n(ch.table), tok)
+    xs, x2s = [x], []
+    for L in range(cfg.layers):
+        assert rel_err(n(ch.layer_in[L]), xs[L]) <= TOL32
+        x2 = oracle.residual(xs[L], n(ch.o_out[L]), cfg.alpha)
+        x2s.append(x2)
+        assert rel_err(n(ch.x2[L]), x2) <= TOL32
+        xs.append(oracle.residual(x2, n(ch.ffn_out[L]), cfg.alpha))
+    assert rel_err(n(ch.x_final), oracle.rmsnorm(xs[-1], n(p.norm_w("final")), cfg.eps)) <= TOL32
+    r = (cfg.layers - 1) % ch.R
+    assert rel_err(n(ch.q_r[r]), oracle.qknorm_rope(n(ch.q[cfg.layers - 1]), n(p.norm_w("q", cfg.layers - 1)), 64, cfg.qk_eps, cfg.rope_base)) <= TOL32
+    assert rel_err(n(ch.gate[r]), oracle.swiglu(n(ch.h1[cfg.layers - 1]), n(ch.h3[cfg.layers - 1]))) <= TOL32
+    dy, gfin = oracle.rmsnorm_bwd(n(ch.dy_cls), xs[-1], n(p.norm_w("final")), eps=cfg.eps)
+    assert rel_err(n(p.norm_w("final", grad=True)), gfin) <= TOL32
+    for L in range(cfg.layers - 1, -1, -1):
+        r = L % ch.R
+        d2, gffn = oracle.rmsnorm_bwd(n(ch.dx_ffn[r]), x2s[L], n(p.norm_w("ffn", L)), eps=cfg.eps)
+        dx2 = oracle.add(d2, dy)
+        d1, gatt = oracle.rmsnorm_bwd(n(ch.dx_attn[r]), xs[L], n(p.norm_w("att", L)), eps=cfg.eps)
+        dy = oracle.add(d1, dx2)
+        assert rel_err(n(p.norm_w("ffn", L, grad=True)), gffn) <= TOL32
+        assert rel_err(n(p.norm_w("att", L, grad=True)), gatt) <= TOL32
+        _, gq = oracle.rope_qknorm_bwd(n(ch.dq_in[r]), n(ch.q[L]), n(p.norm_w("q", L)), 64, eps=cfg.qk_eps, base=cfg.rope_base)
+        assert rel_err(n(p.norm_w("q", L, grad=True)), gq) <= TOL32
+    assert rel_err(n(ch.dy_out), dy) <= TOL32
+    dE, _ = oracle.embed_backward(np.zeros((cfg.vocab, cfg.dim), np.float32), dy, tok)
+    assert rel_err(n(p.embed(grad=True)), dE) <= TOL32
+
+    # --- graph replay == eager
+    eager = {k: n(v) for k, v in (("dy", ch.dy_out), ("xf", ch.x_final), ("g", p.g[p.n_matrix:p.n]))}
+    p.zero_produced_grads()
+    ch.capture()              # runs one eager pass, then records
+    p.zero_produced_grads()
+    ch.replay()
+    torch.cuda.synchronize()
+    assert np.array_equal(n(ch.dy_out), eager["dy"]) and np.array_equal(n(ch.x_final), eager["xf"])
+    assert np.array_equal(n(p.g[p.n_matrix:p.n]), eager["g"])
