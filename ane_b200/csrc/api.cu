@@ -42,7 +42,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static EncodeTiledFn g_encode_tiled = nullptr;
 
-int make_bcs_tensor_map(CUtensorMap *map, ane_dtype dtype, const void *base, int B, int C, int S, int box_s, int box_c) {
+int make_bcs_tensor_map(CUtensorMap *map, ane_dtype dtype, const void *base, int B, int C, int S, int box_s, int box_c,
+                        int l2_promotion_bytes) {
     if (!g_encode_tiled) {
         void *fn = nullptr;
         cudaDriverEntryPointQueryResult q;
@@ -62,8 +63,11 @@ int make_bcs_tensor_map(CUtensorMap *map, ane_dtype dtype, const void *base, int
     const cuuint64_t strides[2] = {(cuuint64_t)S * e, (cuuint64_t)C * S * e};
     const cuuint32_t box[3] = {(cuuint32_t)box_s, (cuuint32_t)box_c, 1u};
     const cuuint32_t estr[3] = {1u, 1u, 1u};
+    const CUtensorMapL2promotion promo = l2_promotion_bytes >= 256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+                                       : l2_promotion_bytes >= 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                       : l2_promotion_bytes >= 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B : CU_TENSOR_MAP_L2_PROMOTION_NONE;
     const CUresult r = g_encode_tiled(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                                      CU_TENSOR_MAP_SWIZZLE_NONE, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(ANE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return ANE_CUDA_OK;
 }

@@ -16,7 +16,10 @@ namespace ane {
 // [B][C][S] tensor of `dtype` elements seen as a 3-D map (S innermost); the box is
 // box_s tokens x box_c channels x 1 sequence.  Requirements checked here: 16-byte aligned base,
 // S*elt a multiple of 16 bytes, box_s*elt a multiple of 16 bytes, box dims <= 256.
-int make_bcs_tensor_map(CUtensorMap *map, ane_dtype dtype, const void *base, int B, int C, int S, int box_s, int box_c);
+// l2_promotion_bytes (0, 64, 128, 256): granularity the copy engine may widen L2 fills to; keep it no
+// wider than a box row, or every row costs a wider DRAM fetch than it uses.
+int make_bcs_tensor_map(CUtensorMap *map, ane_dtype dtype, const void *base, int B, int C, int S, int box_s, int box_c,
+                        int l2_promotion_bytes = 128);
 
 #ifdef __CUDACC__
 // ------------------------------------------------------------------ device primitives

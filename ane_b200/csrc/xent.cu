@@ -9,13 +9,28 @@
 // twice: an online (max, sum) pass, then the pass that writes dlogits.  Loss terms go to a
 // per-token scratch array and are summed per sequence in a fixed order by a second kernel.
 #include "common.cuh"
+#include "tma.cuh"
 
+#include <cooperative_groups.h>
 #include <math.h>
+
+namespace cg = cooperative_groups;
 
 namespace ane {
 
 constexpr int XE_THREADS = 256;
 constexpr int XE_U = 4;
+
+// exp(x) on the special-function unit: 2^(x*log2(e)), relative error about 2^-22 plus the rounding of
+// the scaled argument -- below 2e-6 for |x| < 40, inside the 1e-5 contract.  The accurate expf costs
+// ~20 instructions per element, which made this operator issue-bound instead of memory-bound.
+constexpr float XC_LOG2E = 1.4426950408889634f;
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 
 template <typename ID, int VEC, int LG>
 __global__ void __launch_bounds__(XE_THREADS)
@@ -61,13 +76,13 @@ xent_kernel(float *dlogits, const float *logits, const void *__restrict__ target
         }
 #pragma unroll
         for (int j = 0; j < VEC; j++) {
-            if (gm[j] > m[j]) { s[j] = s[j] * expf(m[j] - gm[j]); m[j] = gm[j]; }   // exp(-inf) = 0 on the first group
+            if (gm[j] > m[j]) { s[j] = s[j] * ex2_approx((m[j] - gm[j]) * XC_LOG2E); m[j] = gm[j]; }   // 2^-inf = 0 on the first group
         }
 #pragma unroll
         for (int u = 0; u < XE_U; u++) {
             if (ok[u]) {
 #pragma unroll
-                for (int j = 0; j < VEC; j++) s[j] += expf(l[u][j] - m[j]);
+                for (int j = 0; j < VEC; j++) s[j] += ex2_approx(fmaf(l[u][j], XC_LOG2E, -m[j] * XC_LOG2E));
             }
         }
     }
@@ -87,12 +102,12 @@ xent_kernel(float *dlogits, const float *logits, const void *__restrict__ target
     }
     __syncthreads();
 
-    float negM[VEC], inv[VEC];
+    float negML[VEC], inv[VEC], scale[VEC];
     int tgt[VEC];
     const float invS = 1.0f / (float)S;
 #pragma unroll
     for (int j = 0; j < VEC; j++) {
-        negM[j] = -tot_m[lg * VEC + j];
+        negML[j] = -tot_m[lg * VEC + j] * XC_LOG2E;
         inv[j] = tot_is[lg * VEC + j];
         tgt[j] = -1;
         if (active) {
@@ -103,6 +118,10 @@ xent_kernel(float *dlogits, const float *logits, const void *__restrict__ target
                 loss_tok[(size_t)b * S + t + j] = 0.0f;        // no loss term (stories_cpu_ops.h:98)
             }
         }
+        float sc = inv[j];
+        if (tgt[j] >= 0) sc = sc * invS;                       // an out-of-range target keeps the plain softmax
+        if (grad_scale != 1.0f) sc = sc * grad_scale;
+        scale[j] = sc;
     }
 
     // sweep 2: p = exp(l - M) * inv_sum ; target row: loss and -1 ; then *1/S (and grad_scale)
@@ -123,17 +142,16 @@ xent_kernel(float *dlogits, const float *logits, const void *__restrict__ target
                 r[u].unpack(l);
 #pragma unroll
                 for (int j = 0; j < VEC; j++) {
-                    float p = expf(l[j] + negM[j]) * inv[j];
-                    if (tgt[j] >= 0) {
-                        if (v == tgt[j]) {
-                            const float lt = -logf(p + 1e-10f);
-                            loss_tok[(size_t)b * S + t + j] = lt;
-                            if (!isfinite(lt)) atomicAdd(&status->nonfinite, 1);
-                            p -= 1.0f;
-                        }
-                        p = p * invS;
+                    const float e = ex2_approx(fmaf(l[j], XC_LOG2E, negML[j]));
+                    float p = e * scale[j];
+                    if (v == tgt[j]) {
+                        const float pr = e * inv[j];
+                        const float lt = -logf(pr + 1e-10f);                       // stories_cpu_ops.h:99
+                        loss_tok[(size_t)b * S + t + j] = lt;
+                        if (!isfinite(lt)) atomicAdd(&status->nonfinite, 1);
+                        p = (pr - 1.0f) * invS;
+                        if (grad_scale != 1.0f) p = p * grad_scale;
                     }
-                    if (grad_scale != 1.0f) p = p * grad_scale;
                     l[j] = p;
                 }
                 Raw<float, VEC> o;
@@ -144,214 +162,280 @@ xent_kernel(float *dlogits, const float *logits, const void *__restrict__ target
     }
 }
 
-// ------------------------------------------------------------------ L2-resident wave kernel
-// With V = 151936 one token's column is 608 KB: a token stripe does not fit on chip, and a block
-// that sweeps its stripe twice reads it twice from HBM.  Here the WHOLE grid works on one "wave"
-// of XW_W = 32 tokens (a 128-byte line per vocabulary row, 19 MB for V = 151936) at a time, each
-// block owning a fixed slice of the vocabulary rows:
-//   phase 1 (wave w)   stream the slice, online (max, sum) per token, block partial -> scratch;
-//                      the last block to arrive merges all partials into (max, 1/sum) per token
-//                      and raises flag[w];
-//   phase 2 (wave w)   after flag[w]: stream the slice again -- still in L2, only about three
-//                      waves (58 MB) are live at any time -- and write dlogits.
-// Blocks run phase 1 of wave w+1 BEFORE phase 2 of wave w, so the merge of wave w is hidden
-// behind real work and nobody idles at a grid-wide barrier.  The kernel is launched
-// cooperatively (all blocks co-resident); the flag wait is bounded and reports a give-up in the
-// status words instead of spinning forever.
-constexpr int XW_THREADS = 256;
-constexpr int XW_LG = 8;
-constexpr int XW_VEC = 4;
-constexpr int XW_W = XW_LG * XW_VEC;      // 32 tokens per wave
-constexpr int XW_R = XW_THREADS / XW_LG;  // 32 vocabulary rows per sweep step
-constexpr int XW_U = 4;
-constexpr int XW_BUFS = 3;
+// ------------------------------------------------------------------ cluster kernel
+// One token's column is V*4 bytes (152 KB for V = 37984, 608 KB for V = 151936): a block cannot keep
+// its stripe on chip, and with one block per stripe the whole GPU has hundreds of stripes (GBs) in
+// flight, so the second sweep always comes from HBM again (3 bytes moved per 2 needed).
+// Here a thread-block CLUSTER of XC_CL blocks owns a 16-token stripe (64-byte rows); block r of the
+// cluster takes vocabulary rows [r*rows_per_cta, (r+1)*rows_per_cta):
+//   1. one thread asks the copy engine (TMA) for the first `rows_res` rows of the slice, 256-row
+//      boxes, each signalling its own mbarrier -- up to 192 KB per SM in flight with no register
+//      staging; the rows that do not fit (if any) stream through registers meanwhile;
+//   2. online (max, sum) per token over the slice; warp shuffles, then shared memory, give the
+//      block's pair; the cluster exchanges the XC_CL pairs through distributed shared memory
+//      (hardware cluster barrier -- no flags in global memory, no cooperative launch);
+//   3. the slice is swept again FROM SHARED MEMORY to write dlogits; only the non-resident rows
+//      are read a second time (from L2 when the slices in flight fit there).
+// With V = 37984 about two thirds of every slice never leaves the SM between the sweeps.
+constexpr int XC_CL = 8;               // blocks per cluster (portable maximum)
+constexpr int XC_LG = 4;               // 16-byte lanes per row: 16 tokens, 64-byte rows
+constexpr int XC_TW = XC_LG * 4;
+constexpr int XC_BOXR = 256;           // rows per copy-engine box (16 KB)
+constexpr int XC_MAXBOX = 13;
+constexpr int XC_U = 4;
 
-struct XentWaveScratch {
-    float2 *partial;     // [XW_BUFS][grid][XW_W]  (max, sum) per block and token
-    float2 *final_ms;    // [XW_BUFS][XW_W]        (max, 1/sum) per token
-    unsigned *counter;   // [nwaves] blocks arrived
-    unsigned *flag;      // [nwaves] merged
+// running (max, sum) of four tokens; ml = max * log2(e)
+struct Ms4 { float m[4], s[4]; };
+
+__device__ __forceinline__ void ms_init(Ms4 &a) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) { a.m[j] = -INFINITY; a.s[j] = 0.0f; }
+}
+__device__ __forceinline__ void ms_raise(Ms4 &a, const float (&gm)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+        if (gm[j] > a.m[j]) { a.s[j] = a.s[j] * ex2_approx((a.m[j] - gm[j]) * XC_LOG2E); a.m[j] = gm[j]; }   // 2^-inf = 0 the first time
+}
+// fold U rows (held as float4) into the running (max, sum): one rescale per group
+template <int U>
+__device__ __forceinline__ void ms_fold(Ms4 &a, const float4 (&r)[U], const bool (&ok)[U]) {
+    float gm[4] = {a.m[0], a.m[1], a.m[2], a.m[3]};
+#pragma unroll
+    for (int u = 0; u < U; u++)
+        if (ok[u]) {
+            gm[0] = fmaxf(gm[0], r[u].x); gm[1] = fmaxf(gm[1], r[u].y);
+            gm[2] = fmaxf(gm[2], r[u].z); gm[3] = fmaxf(gm[3], r[u].w);
+        }
+    ms_raise(a, gm);
+    const float n0 = -a.m[0] * XC_LOG2E, n1 = -a.m[1] * XC_LOG2E, n2 = -a.m[2] * XC_LOG2E, n3 = -a.m[3] * XC_LOG2E;
+#pragma unroll
+    for (int u = 0; u < U; u++)
+        if (ok[u]) {
+            a.s[0] += ex2_approx(fmaf(r[u].x, XC_LOG2E, n0)); a.s[1] += ex2_approx(fmaf(r[u].y, XC_LOG2E, n1));
+            a.s[2] += ex2_approx(fmaf(r[u].z, XC_LOG2E, n2)); a.s[3] += ex2_approx(fmaf(r[u].w, XC_LOG2E, n3));
+        }
+}
+__device__ __forceinline__ void ms_merge(float &m, float &s, float m2, float s2) {
+    const float M = fmaxf(m, m2);
+    float acc = 0.0f;
+    if (m > -INFINITY) acc += s * expf(m - M);
+    if (m2 > -INFINITY) acc += s2 * expf(m2 - M);
+    m = M;
+    s = acc;
+}
+
+// Per-thread constants of the second sweep.  p = softmax probability of a row; the row that is a
+// token's target takes the slow path (stories_cpu_ops.h:97-103).
+struct XentRowOut {
+    float scale[4];       // (1/sum) * (1/S) * grad_scale   (out-of-range target: no 1/S, stories_cpu_ops.h:98)
+    float inv[4];         // 1/sum
+    int tgt[4];
+    float invS, grad_scale;
+    float *loss_tok;      // already offset to this thread's first token
+    ane_cuda_status *status;
 };
+// e[j] = exp(l - M) (or exp(l - m_t) with the difference folded into scale/inv); v = vocabulary row
+__device__ __forceinline__ float4 xent_finish(const float (&e)[4], int v, const XentRowOut &o) {
+    float p[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) p[j] = e[j] * o.scale[j];
+    if (v == o.tgt[0] || v == o.tgt[1] || v == o.tgt[2] || v == o.tgt[3]) {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (v == o.tgt[j]) {
+                const float pr = e[j] * o.inv[j];
+                const float lt = -logf(pr + 1e-10f);                                // stories_cpu_ops.h:99
+                o.loss_tok[j] = lt;
+                if (!isfinite(lt)) atomicAdd(&o.status->nonfinite, 1);
+                float q = (pr - 1.0f) * o.invS;
+                if (o.grad_scale != 1.0f) q = q * o.grad_scale;
+                p[j] = q;
+            }
+    }
+    return make_float4(p[0], p[1], p[2], p[3]);
+}
 
-template <typename ID>
-__global__ void __launch_bounds__(XW_THREADS)
-xent_wave_kernel(float *dlogits, const float *logits, const void *__restrict__ targets, float *__restrict__ loss_tok,
-                 int V, int S, int waves_per_seq, int nwaves, float grad_scale, XentWaveScratch sc, ane_cuda_status *status) {
-    __shared__ __align__(16) float red_m[XW_R][XW_W];
-    __shared__ __align__(16) float red_s[XW_R][XW_W];
-    __shared__ float mrg_m[XW_THREADS / 32][XW_W];
-    __shared__ float mrg_s[XW_THREADS / 32][XW_W];
-    __shared__ int is_last, give_up;
+template <typename ID, int THREADS>
+__global__ void __cluster_dims__(XC_CL, 1, 1) __launch_bounds__(THREADS, 1024 / THREADS)
+xent_cluster_kernel(const __grid_constant__ CUtensorMap lmap, float *dlogits, const float *logits,
+                    const void *__restrict__ targets, float *__restrict__ loss_tok, int V, int S, int stripes_per_seq,
+                    int rows_per_cta, int rows_res, float grad_scale, ane_cuda_status *status) {
+    constexpr int R = THREADS / XC_LG;
+    constexpr int NW = THREADS / 32;
+    extern __shared__ uint8_t xc_raw[];
+    __shared__ uint64_t bar[XC_MAXBOX];
+    __shared__ float2 red[NW][XC_TW];
+    __shared__ float2 part[XC_TW];        // this block's (max, sum) per token; peers read it
+    __shared__ float2 fin[XC_TW];         // (max, 1/sum) over the whole vocabulary
+    __shared__ int gave_up;
 
-    const int G = gridDim.x;
-    const int lg = threadIdx.x % XW_LG, rg = threadIdx.x / XW_LG;
-    const int rows_per = (V + G - 1) / G;
-    const int v0 = blockIdx.x * rows_per;
-    const int v1 = v0 + rows_per < V ? v0 + rows_per : V;
-    const float invS = 1.0f / (float)S;
-    if (threadIdx.x == 0) give_up = 0;
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned rank = cluster.block_rank();
+    float4 *res = reinterpret_cast<float4 *>((reinterpret_cast<uintptr_t>(xc_raw) + 127) & ~(uintptr_t)127);   // [rows][XC_LG]
+
+    const int stripe = blockIdx.x / XC_CL;
+    const int b = stripe / stripes_per_seq;
+    const int t0 = (stripe % stripes_per_seq) * XC_TW;
+    const int lg = threadIdx.x % XC_LG, rg = threadIdx.x / XC_LG;
+    const int t = t0 + lg * 4;
+    const bool active = t < S;
+    const int v0 = (int)rank * rows_per_cta;
+    const int v1 = v0 + rows_per_cta < V ? v0 + rows_per_cta : V;
+    const int rows = v1 > v0 ? v1 - v0 : 0;
+    const int nres = rows < rows_res ? rows : rows_res;
+    const int nbox = (nres + XC_BOXR - 1) / XC_BOXR;
+    const size_t base = (size_t)b * V * S + t;
+
+    if (threadIdx.x == 0) {
+        gave_up = 0;
+        for (int k = 0; k < nbox; k++) mbar_init(&bar[k], 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int k = 0; k < nbox; k++) {
+            mbar_arrive_expect_tx(&bar[k], XC_BOXR * XC_TW * 4);
+            tma_load_3d(res + (size_t)k * XC_BOXR * XC_LG, &lmap, t0, v0 + k * XC_BOXR, b, &bar[k]);
+        }
+    }
+
+    // ---- sweep 1a: rows that do not fit in shared memory, through registers (they stay in L2)
+    Ms4 ms;
+    ms_init(ms);
+    for (int vb = v0 + nres; vb < v1; vb += R * XC_U) {
+        float4 r[XC_U];
+        bool ok[XC_U];
+#pragma unroll
+        for (int u = 0; u < XC_U; u++) {
+            const int v = vb + u * R + rg;
+            ok[u] = active && v < v1;
+            if (ok[u]) r[u] = *reinterpret_cast<const float4 *>(logits + base + (size_t)v * S);
+        }
+        ms_fold<XC_U>(ms, r, ok);
+    }
+    // ---- sweep 1b: maximum over this thread's resident rows, as their boxes land
+    bool bad = false;
+    float gm[4] = {ms.m[0], ms.m[1], ms.m[2], ms.m[3]};
+    for (int k = 0; k < nbox; k++) {
+        if (!mbar_wait_bounded(&bar[k], 0)) { bad = true; break; }
+        const int lim = nres - k * XC_BOXR < XC_BOXR ? nres - k * XC_BOXR : XC_BOXR;
+        const float4 *bx = res + (size_t)k * XC_BOXR * XC_LG;
+#pragma unroll 2
+        for (int q = rg; q < lim; q += R) {
+            const float4 r = bx[q * XC_LG + lg];
+            gm[0] = fmaxf(gm[0], r.x); gm[1] = fmaxf(gm[1], r.y); gm[2] = fmaxf(gm[2], r.z); gm[3] = fmaxf(gm[3], r.w);
+        }
+    }
+    if (bad) gave_up = 1;       // benign race: every writer stores 1
+    ms_raise(ms, gm);
+    // ---- sweep 1c: e = exp(l - m_thread) replaces l in shared memory; the sum accumulates
+    if (!bad) {
+        const float n0 = -ms.m[0] * XC_LOG2E, n1 = -ms.m[1] * XC_LOG2E, n2 = -ms.m[2] * XC_LOG2E, n3 = -ms.m[3] * XC_LOG2E;
+#pragma unroll 4
+        for (int q = rg; q < nres; q += R) {
+            float4 r = res[q * XC_LG + lg];
+            r.x = ex2_approx(fmaf(r.x, XC_LOG2E, n0)); r.y = ex2_approx(fmaf(r.y, XC_LOG2E, n1));
+            r.z = ex2_approx(fmaf(r.z, XC_LOG2E, n2)); r.w = ex2_approx(fmaf(r.w, XC_LOG2E, n3));
+            ms.s[0] += r.x; ms.s[1] += r.y; ms.s[2] += r.z; ms.s[3] += r.w;
+            res[q * XC_LG + lg] = r;                 // only this thread ever touches this entry again
+        }
+    }
+    const float mt[4] = {ms.m[0], ms.m[1], ms.m[2], ms.m[3]};      // the reference point of this thread's e values
+
+    // ---- block (max, sum): row groups of a warp by shuffles, warps through shared memory
+#pragma unroll
+    for (int off = XC_LG; off < 32; off <<= 1) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float m2 = __shfl_xor_sync(0xffffffffu, ms.m[j], off);
+            const float s2 = __shfl_xor_sync(0xffffffffu, ms.s[j], off);
+            ms_merge(ms.m[j], ms.s[j], m2, s2);
+        }
+    }
+    if ((threadIdx.x & 31) < XC_LG) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) red[threadIdx.x >> 5][lg * 4 + j] = make_float2(ms.m[j], ms.s[j]);
+    }
+    __syncthreads();
+    if (threadIdx.x < XC_TW) {
+        float m = -INFINITY, s = 0.0f;
+        for (int q = 0; q < NW; q++) ms_merge(m, s, red[q][threadIdx.x].x, red[q][threadIdx.x].y);
+        part[threadIdx.x] = make_float2(m, s);
+    }
+    cluster.sync();                                   // every block's pair is published
+    if (threadIdx.x < XC_TW) {
+        float m = -INFINITY, s = 0.0f;
+        for (unsigned q = 0; q < XC_CL; q++) {        // fixed rank order: all blocks get the same bits
+            const float2 pq = cluster.map_shared_rank(part, q)[threadIdx.x];
+            ms_merge(m, s, pq.x, pq.y);
+        }
+        fin[threadIdx.x] = make_float2(m, 1.0f / s);                                 // inv_sum, stories_cpu_ops.h:91-92
+    }
+    cluster.barrier_arrive();                         // done reading peers; matched by the wait before exit
     __syncthreads();
 
-    for (int w = 0; w <= nwaves; w++) {
-        // ---------------- phase 1 of wave w
-        if (w < nwaves) {
-            const int b = w / waves_per_seq;
-            const int t = (w % waves_per_seq) * XW_W + lg * XW_VEC;
-            const bool active = t < S;
-            const size_t base = (size_t)b * V * S + t;
-            float m[XW_VEC], s[XW_VEC];
+    if (gave_up) {
+        if (threadIdx.x == 0) atomicAdd(&status->wait_giveups, 1);
+    } else {
+        XentRowOut o;
+        float negML[4], rel[4];
+        o.invS = 1.0f / (float)S;
+        o.grad_scale = grad_scale;
+        o.status = status;
+        o.loss_tok = loss_tok + (size_t)b * S + t;
 #pragma unroll
-            for (int j = 0; j < XW_VEC; j++) { m[j] = -INFINITY; s[j] = 0.0f; }
-            for (int vb = v0; vb < v1; vb += XW_R * XW_U) {
-                float4 r[XW_U];
-                bool ok[XW_U];
-#pragma unroll
-                for (int u = 0; u < XW_U; u++) {
-                    const int v = vb + u * XW_R + rg;
-                    ok[u] = active && v < v1;
-                    if (ok[u]) r[u] = *reinterpret_cast<const float4 *>(logits + base + (size_t)v * S);   // stays in L2 for phase 2
+        for (int j = 0; j < 4; j++) {
+            const float2 f = fin[lg * 4 + j];
+            negML[j] = -f.x * XC_LOG2E;
+            rel[j] = mt[j] > -INFINITY ? ex2_approx((mt[j] - f.x) * XC_LOG2E) : 0.0f;   // exp(m_thread - M)
+            o.inv[j] = f.y;
+            o.tgt[j] = -1;
+            if (active) {
+                const int id = (int)reinterpret_cast<const ID *>(targets)[(size_t)b * S + t + j];
+                if (id >= 0 && id < V) o.tgt[j] = id;
+                else if (rg == 0 && rank == 0) {                  // one thread per token reports it
+                    atomicAdd(&status->oor_ids, 1);
+                    o.loss_tok[j] = 0.0f;                         // no loss term (stories_cpu_ops.h:98)
                 }
-                float gm[XW_VEC];
-#pragma unroll
-                for (int j = 0; j < XW_VEC; j++) gm[j] = m[j];
-#pragma unroll
-                for (int u = 0; u < XW_U; u++)
-                    if (ok[u]) {
-                        gm[0] = fmaxf(gm[0], r[u].x); gm[1] = fmaxf(gm[1], r[u].y);
-                        gm[2] = fmaxf(gm[2], r[u].z); gm[3] = fmaxf(gm[3], r[u].w);
-                    }
-#pragma unroll
-                for (int j = 0; j < XW_VEC; j++)
-                    if (gm[j] > m[j]) { s[j] = s[j] * expf(m[j] - gm[j]); m[j] = gm[j]; }
-#pragma unroll
-                for (int u = 0; u < XW_U; u++)
-                    if (ok[u]) {
-                        s[0] += expf(r[u].x - m[0]); s[1] += expf(r[u].y - m[1]);
-                        s[2] += expf(r[u].z - m[2]); s[3] += expf(r[u].w - m[3]);
-                    }
             }
-            *reinterpret_cast<float4 *>(&red_m[rg][lg * XW_VEC]) = make_float4(m[0], m[1], m[2], m[3]);
-            *reinterpret_cast<float4 *>(&red_s[rg][lg * XW_VEC]) = make_float4(s[0], s[1], s[2], s[3]);
-            __syncthreads();
-            if (threadIdx.x < XW_W) {
-                float M = -INFINITY;
-                for (int q = 0; q < XW_R; q++) M = fmaxf(M, red_m[q][threadIdx.x]);
-                float sum = 0.0f;
-                for (int q = 0; q < XW_R; q++) {
-                    const float mq = red_m[q][threadIdx.x];
-                    if (mq > -INFINITY) sum += red_s[q][threadIdx.x] * expf(mq - M);
-                }
-                sc.partial[((size_t)(w % XW_BUFS) * G + blockIdx.x) * XW_W + threadIdx.x] = make_float2(M, sum);
-                __threadfence();
-            }
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                const unsigned ticket = atomicAdd(&sc.counter[w], 1u);
-                is_last = ticket == (unsigned)(G - 1);
-                if (is_last) __threadfence();
-            }
-            __syncthreads();
-            if (is_last) {      // merge the G partials of every token: warp `part` takes blocks part, part+8, ...
-                const int tok = threadIdx.x % XW_W, part = threadIdx.x / XW_W;
-                constexpr int PARTS = XW_THREADS / XW_W;
-                const float2 *pp = sc.partial + (size_t)(w % XW_BUFS) * G * XW_W;
-                float M = -INFINITY;
-                for (int i = part; i < G; i += PARTS) M = fmaxf(M, __ldcg(&pp[(size_t)i * XW_W + tok]).x);
-                mrg_m[part][tok] = M;
-                __syncthreads();
-                M = -INFINITY;
+            float sc = o.inv[j];
+            if (o.tgt[j] >= 0) sc = sc * o.invS;
+            if (grad_scale != 1.0f) sc = sc * grad_scale;
+            o.scale[j] = sc;
+        }
+        // ---- sweep 2a: non-resident rows again (read first: they were touched longest ago)
+        for (int vb = v0 + nres; vb < v1; vb += R * XC_U) {
+            float4 r[XC_U];
+            bool ok[XC_U];
 #pragma unroll
-                for (int q = 0; q < PARTS; q++) M = fmaxf(M, mrg_m[q][tok]);
-                float sum = 0.0f;
-                for (int i = part; i < G; i += PARTS) {
-                    const float2 ms = __ldcg(&pp[(size_t)i * XW_W + tok]);
-                    if (ms.x > -INFINITY) sum += ms.y * expf(ms.x - M);
-                }
-                mrg_s[part][tok] = sum;
-                __syncthreads();
-                if (part == 0) {
-                    sum = 0.0f;
+            for (int u = 0; u < XC_U; u++) {
+                const int v = vb + u * R + rg;
+                ok[u] = active && v < v1;
+                if (ok[u]) r[u] = __ldcs(reinterpret_cast<const float4 *>(logits + base + (size_t)v * S));
+            }
 #pragma unroll
-                    for (int q = 0; q < PARTS; q++) sum += mrg_s[q][tok];
-                    sc.final_ms[(w % XW_BUFS) * XW_W + tok] = make_float2(M, 1.0f / sum);     // inv_sum, stories_cpu_ops.h:91-92
-                    __threadfence();
+            for (int u = 0; u < XC_U; u++) {
+                const int v = vb + u * R + rg;
+                if (ok[u]) {
+                    const float e[4] = {ex2_approx(fmaf(r[u].x, XC_LOG2E, negML[0])), ex2_approx(fmaf(r[u].y, XC_LOG2E, negML[1])),
+                                        ex2_approx(fmaf(r[u].z, XC_LOG2E, negML[2])), ex2_approx(fmaf(r[u].w, XC_LOG2E, negML[3]))};
+                    __stcs(reinterpret_cast<float4 *>(dlogits + base + (size_t)v * S), xent_finish(e, v, o));
                 }
-                __syncthreads();
-                if (threadIdx.x == 0) atomicExch(&sc.flag[w], 1u);
             }
         }
-        // ---------------- phase 2 of wave w-1
-        if (w >= 1) {
-            const int pw = w - 1;
-            if (threadIdx.x == 0) {
-                unsigned spins = 0;
-                while (atomicAdd(&sc.flag[pw], 0u) == 0u) {
-                    __nanosleep(64);
-                    if (++spins > (1u << 22)) { give_up = 1; break; }
-                }
-                __threadfence();
-            }
-            __syncthreads();
-            if (give_up) {
-                if (threadIdx.x == 0) atomicAdd(&status->wait_giveups, 1);
-                return;
-            }
-            const int b = pw / waves_per_seq;
-            const int t = (pw % waves_per_seq) * XW_W + lg * XW_VEC;
-            const bool active = t < S;
-            const size_t base = (size_t)b * V * S + t;
-            float negM[XW_VEC], inv[XW_VEC];
-            int tgt[XW_VEC];
+        // ---- sweep 2b: resident rows from shared memory: e values relative to this thread's maximum
+        if (active) {
 #pragma unroll
-            for (int j = 0; j < XW_VEC; j++) {
-                const float2 ms = __ldcg(&sc.final_ms[(pw % XW_BUFS) * XW_W + lg * XW_VEC + j]);
-                negM[j] = -ms.x;
-                inv[j] = ms.y;
-                tgt[j] = -1;
-                if (active) {
-                    const int id = (int)reinterpret_cast<const ID *>(targets)[(size_t)b * S + t + j];
-                    if (id >= 0 && id < V) tgt[j] = id;
-                    else if (rg == 0 && blockIdx.x == 0) {        // one thread per token reports it
-                        atomicAdd(&status->oor_ids, 1);
-                        loss_tok[(size_t)b * S + t + j] = 0.0f;   // no loss term (stories_cpu_ops.h:98)
-                    }
-                }
-            }
-            for (int vb = v0; vb < v1; vb += XW_R * XW_U) {
-                float4 r[XW_U];
-                bool ok[XW_U];
-#pragma unroll
-                for (int u = 0; u < XW_U; u++) {
-                    const int v = vb + u * XW_R + rg;
-                    ok[u] = active && v < v1;
-                    if (ok[u]) r[u] = __ldcs(reinterpret_cast<const float4 *>(logits + base + (size_t)v * S));
-                }
-#pragma unroll
-                for (int u = 0; u < XW_U; u++) {
-                    const int v = vb + u * XW_R + rg;
-                    if (ok[u]) {
-                        float l[XW_VEC] = {r[u].x, r[u].y, r[u].z, r[u].w};
-#pragma unroll
-                        for (int j = 0; j < XW_VEC; j++) {
-                            float p = expf(l[j] + negM[j]) * inv[j];
-                            if (tgt[j] >= 0) {
-                                if (v == tgt[j]) {
-                                    const float lt = -logf(p + 1e-10f);
-                                    loss_tok[(size_t)b * S + t + j] = lt;
-                                    if (!isfinite(lt)) atomicAdd(&status->nonfinite, 1);
-                                    p -= 1.0f;
-                                }
-                                p = p * invS;
-                            }
-                            if (grad_scale != 1.0f) p = p * grad_scale;
-                            l[j] = p;
-                        }
-                        __stcs(reinterpret_cast<float4 *>(dlogits + base + (size_t)v * S), make_float4(l[0], l[1], l[2], l[3]));
-                    }
-                }
+            for (int j = 0; j < 4; j++) { o.scale[j] *= rel[j]; o.inv[j] *= rel[j]; }
+#pragma unroll 4
+            for (int q = rg; q < nres; q += R) {
+                const float4 r = res[q * XC_LG + lg];
+                const float e[4] = {r.x, r.y, r.z, r.w};
+                __stcs(reinterpret_cast<float4 *>(dlogits + base + (size_t)(v0 + q) * S), xent_finish(e, v0 + q, o));
             }
         }
     }
+    cluster.barrier_wait();                           // peers may still be reading `part`
 }
 
 // loss_seq[b] = (sum_t loss_tok[b][t]) / S, fixed summation tree.
@@ -388,37 +472,37 @@ int ane_cuda_cross_entropy_dev(void *stream, ane_idtype idtype, int B, int V, in
     if (!loss_tok) return fail(ANE_CUDA_ERR_NOMEM, "%s: no scratch", __func__);
     ane_cuda_status *status = ctx().status;
     const bool vec = (S % 4 == 0) && aligned16(dlogits) && aligned16(logits);
-    if (vec && tuning("xent_wave", 1) && V >= 8192 && (long long)B * S >= 1024) {
-        // whole-grid waves of 32 tokens kept in L2 between the two sweeps (cooperative launch)
-        int per_sm = 0;
-        auto kern = idtype == ANE_ID_U16 ? xent_wave_kernel<uint16_t> : xent_wave_kernel<int32_t>;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, XW_THREADS, 0) == cudaSuccess && per_sm >= 1) {
-            if (per_sm > 2) per_sm = 2;
-            int G = per_sm * ctx().sm_count;
-            const int wps = (S + XW_W - 1) / XW_W;
-            int nwaves = B * wps;
-            const size_t off_part = round_up((size_t)B * S * sizeof(float), 256);
-            const size_t off_final = off_part + round_up((size_t)XW_BUFS * G * XW_W * sizeof(float2), 256);
-            const size_t off_cnt = off_final + round_up((size_t)XW_BUFS * XW_W * sizeof(float2), 256);
-            const size_t off_flag = off_cnt + round_up((size_t)nwaves * sizeof(unsigned), 256);
-            const size_t total = off_flag + round_up((size_t)nwaves * sizeof(unsigned), 256);
-            char *ws = static_cast<char *>(workspace(total));
-            if (!ws) return fail(ANE_CUDA_ERR_NOMEM, "%s: no scratch", __func__);
-            loss_tok = reinterpret_cast<float *>(ws);
-            XentWaveScratch sc;
-            sc.partial = reinterpret_cast<float2 *>(ws + off_part);
-            sc.final_ms = reinterpret_cast<float2 *>(ws + off_final);
-            sc.counter = reinterpret_cast<unsigned *>(ws + off_cnt);
-            sc.flag = reinterpret_cast<unsigned *>(ws + off_flag);
-            ANE_CUDA_TRY(cudaMemsetAsync(ws + off_cnt, 0, total - off_cnt, st));
-            void *args[] = {&dlogits, &logits, &targets, &loss_tok, &V, &S, (void *)&wps, &nwaves, &grad_scale, &sc, &status};
-            ANE_CUDA_TRY(cudaLaunchCooperativeKernel((const void *)kern, dim3(G), dim3(XW_THREADS), args, 0, st));
+    if (vec && tuning("xent_cluster", 1) && V >= 4096 && S % XC_TW == 0) {
+        // a cluster of 8 blocks per 16-token stripe, most of the stripe resident in shared memory
+        const int threads = tuning("xent_threads", 1024) == 512 ? 512 : 1024;
+        const int sps = S / XC_TW;
+        const long long nstripes = (long long)B * sps;
+        const int rows_per_cta = (V + XC_CL - 1) / XC_CL;
+        int rows_res = ((rows_per_cta + XC_BOXR - 1) / XC_BOXR) * XC_BOXR;
+        const int cap = tuning("xent_boxes", threads == 512 ? 6 : 12);  // 12 boxes = 192 KB
+        if (rows_res > cap * XC_BOXR) rows_res = cap * XC_BOXR;
+        const size_t smem = (size_t)rows_res * XC_TW * sizeof(float) + 128;
+        CUtensorMap lmap;
+        if (nstripes * XC_CL < 0x7fffffffLL && cap >= 0 && cap <= XC_MAXBOX - 1 &&
+            make_bcs_tensor_map(&lmap, ANE_F32, logits, B, V, S, XC_TW, XC_BOXR, 64) == ANE_CUDA_OK) {
+            void (*kern)(const CUtensorMap, float *, const float *, const void *, float *, int, int, int, int, int, float, ane_cuda_status *);
+            if (threads == 512) kern = idtype == ANE_ID_U16 ? xent_cluster_kernel<uint16_t, 512> : xent_cluster_kernel<int32_t, 512>;
+            else kern = idtype == ANE_ID_U16 ? xent_cluster_kernel<uint16_t, 1024> : xent_cluster_kernel<int32_t, 1024>;
+            ANE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            kern<<<(unsigned)(nstripes * XC_CL), threads, smem, st>>>(lmap, dlogits, logits, targets, loss_tok, V, S, sps, rows_per_cta,
+                                                                    rows_res, grad_scale, status);
             xent_loss_kernel<<<B, 256, 0, st>>>(loss_seq, loss_tok, S);
             ANE_LAUNCH_OK(2);
             return ANE_CUDA_OK;
         }
     }
-    if (vec) {
+    if (vec && tuning("xent_lg", 8) == 4) {
+        constexpr int LG = 4, VEC = 4;
+        const int tps = (S + LG * VEC - 1) / (LG * VEC);
+        const unsigned grid = (unsigned)(B * tps);
+        if (idtype == ANE_ID_U16) xent_kernel<uint16_t, VEC, LG><<<grid, XE_THREADS, 0, st>>>(dlogits, logits, targets, loss_tok, V, S, tps, grad_scale, status);
+        else xent_kernel<int32_t, VEC, LG><<<grid, XE_THREADS, 0, st>>>(dlogits, logits, targets, loss_tok, V, S, tps, grad_scale, status);
+    } else if (vec) {
         constexpr int LG = 8, VEC = 4;
         const int tps = (S + LG * VEC - 1) / (LG * VEC);
         const unsigned grid = (unsigned)(B * tps);

@@ -252,8 +252,11 @@ class LayerChain:
         the per-launch host cost and most of the gap between kernels.  One eager pass runs first so
         that the library's scratch range has reached its final size (no allocation may happen while
         a stream is being captured)."""
+        from . import lib as _lib
+        before = _lib.launch_count()
         self.forward()
         self.backward()
+        self.launches_measured = _lib.launch_count() - before
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
@@ -266,8 +269,5 @@ class LayerChain:
         self.graph.replay()
 
     def launches_per_microbatch(self) -> int:
-        """Kernels of this library launched by forward() + backward()."""
-        L = self.cfg.layers
-        fwd = 1 + L * 6 + 1
-        bwd = 2 + L * (1 + 2 + 2 + 2 + 2) + 4
-        return fwd + bwd
+        """Kernels of this library launched by forward() + backward() (counted during capture())."""
+        return getattr(self, "launches_measured", 0)

@@ -1,0 +1,193 @@
+"""Per-operator micro-benchmark: achieved GB/s of each device-resident operator on benchmark-sized
+tensors, computed from ALGORITHMIC bytes (compulsory HBM traffic with perfect on-chip reuse) and the
+CUDA-event time of a launch.
+
+    python -m ane_b200.opbench                       # the whole table, one JSON object
+    python -m ane_b200.opbench --op cross_entropy    # one operator (what a profiler run wraps)
+    python -m ane_b200.opbench --op rmsnorm --batch 64 --iters 3 --tuning norm_fwd=0
+
+Every operator rotates through several input/output sets so that consecutive launches do not find
+their operands in the 126 MB L2 (each set is 64 MiB or more at the default batch).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+NOMINAL_HBM_GBS = 8000.0
+S, D, H, QD, KVD, HD, VOCAB = 2048, 1024, 3072, 2048, 1024, 128, 151936
+NSET = 3
+
+
+def _cases(torch, ops, device, M):
+    """name -> (builder) ; builder() returns (fn(i), algorithmic bytes per launch, default iterations)."""
+    bf = torch.bfloat16
+    T = M * S
+
+    def mk(ch, dtype=bf, n=NSET, b=M):
+        return [torch.randn((b, ch, S), device=device, dtype=dtype) for _ in range(n)]
+
+    def norm_w():
+        return torch.ones(D, device=device), torch.zeros(D, device=device)
+
+    def head_w():
+        return torch.ones(HD, device=device), torch.zeros(HD, device=device)
+
+    def rmsnorm():
+        (w, _), xs, os_ = norm_w(), mk(D), mk(D)
+        return (lambda i: ops.rmsnorm(xs[i % NSET], w, out=os_[i % NSET])), 2 * D * T * 2, 12
+
+    def rmsnorm_bwd():
+        (w, dw), xs, ys, os_ = norm_w(), mk(D), mk(D), mk(D)
+        return (lambda i: ops.rmsnorm_bwd(ys[i % NSET], xs[i % NSET], w, dw, out=os_[i % NSET])), 3 * D * T * 2, 12
+
+    def rmsnorm_bwd_add():
+        (w, dw), xs, ys, zs, os_ = norm_w(), mk(D), mk(D), mk(D), mk(D)
+        return (lambda i: ops.rmsnorm_bwd(ys[i % NSET], xs[i % NSET], w, dw, add=zs[i % NSET], out=os_[i % NSET])), 4 * D * T * 2, 12
+
+    def residual_rmsnorm():
+        (w, _), xs, ys, os_, o2 = norm_w(), mk(D), mk(D), mk(D), mk(D)
+        return (lambda i: ops.residual_rmsnorm(xs[i % NSET], ys[i % NSET], w, 0.13, x2=os_[i % NSET], x2norm=o2[i % NSET])), 4 * D * T * 2, 12
+
+    def residual():
+        xs, ys, os_ = mk(D), mk(D), mk(D)
+        return (lambda i: ops.residual(xs[i % NSET], ys[i % NSET], 0.13, out=os_[i % NSET])), 3 * D * T * 2, 12
+
+    def swiglu():
+        h1, h3, g1 = mk(H), mk(H), mk(H)
+        return (lambda i: ops.swiglu(h1[i % NSET], h3[i % NSET], out=g1[i % NSET])), 3 * H * T * 2, 12
+
+    def swiglu_bwd():
+        h1, h3, dd, g1, g3 = mk(H), mk(H), mk(H), mk(H), mk(H)
+        return (lambda i: ops.swiglu_bwd(h1[i % NSET], h3[i % NSET], dd[i % NSET], dh1=g1[i % NSET], dh3=g3[i % NSET])), 5 * H * T * 2, 12
+
+    def rope():
+        q, qo = mk(QD), mk(QD)
+        return (lambda i: ops.rope(q[i % NSET], HD, base=1e6, out=qo[i % NSET])), 2 * QD * T * 2, 12
+
+    def qknorm_rope():
+        (wq, _), q, qo = head_w(), mk(QD), mk(QD)
+        return (lambda i: ops.qknorm_rope(q[i % NSET], wq, HD, out=qo[i % NSET])), 2 * QD * T * 2, 12
+
+    def rope_qknorm_bwd():
+        (wq, dwq), q, dq, qo = head_w(), mk(QD), mk(QD), mk(QD)
+        return (lambda i: ops.rope_qknorm_bwd(dq[i % NSET], q[i % NSET], wq, dwq, HD, out=qo[i % NSET])), 3 * QD * T * 2, 12
+
+    # embedding: 2 x batch sequences of 2048 tokens, table [151936, 1024] bf16
+    def _embed_common():
+        Be = 2 * M
+        table = (0.02 * torch.randn(VOCAB, D, device=device)).to(bf)
+        tok = torch.randint(0, VOCAB, (Be, S), device=device, dtype=torch.int32)
+        xe = [torch.empty((Be, D, S), device=device, dtype=bf) for _ in range(2)]
+        return Be, table, tok, xe
+
+    def embed_lookup():
+        Be, table, tok, xe = _embed_common()
+        return (lambda i: ops.embed_lookup(table, tok, out=xe[i % 2])), Be * S * 4 + 2 * D * Be * S * 2, 12
+
+    def embed_backward():
+        Be, table, tok, xe = _embed_common()
+        ops.embed_lookup(table, tok, out=xe[0])
+        ops.embed_lookup(table, tok, out=xe[1])
+        del table
+        dE = torch.zeros(VOCAB, D, device=device)
+        uniq = int(torch.unique(tok).numel())
+        return (lambda i: ops.embed_backward(dE, xe[i % 2], tok)), Be * S * 4 + D * Be * S * 2 + 2 * uniq * D * 4, 6
+
+    # cross-entropy: fp32 logits [batch/4][151936][2048] (5 GB at the default batch), written in place
+    def cross_entropy():
+        Bc = max(1, M // 4)
+        logits = torch.randn((Bc, VOCAB, S), device=device)
+        tg = torch.randint(0, VOCAB, (Bc, S), device=device, dtype=torch.int32)
+        return (lambda i: ops.cross_entropy(logits, tg, dlogits=logits)), 2 * VOCAB * Bc * S * 4, 3
+
+    # the vocabulary after compaction to the ids a corpus uses (a quarter of the full one here)
+    def cross_entropy_compact():
+        Vc = VOCAB // 4
+        logits = torch.randn((M, Vc, S), device=device)
+        tg = torch.randint(0, Vc, (M, S), device=device, dtype=torch.int32)
+        return (lambda i: ops.cross_entropy(logits, tg, dlogits=logits)), 2 * Vc * M * S * 4, 3
+
+    def _flat():
+        n = 4 * M << 20
+        wv, gv, mv, vv = (torch.randn(n, device=device) * 0.01 for _ in range(4))
+        vv.abs_()
+        return n, wv, gv, mv, vv
+
+    def adam():
+        n, wv, gv, mv, vv = _flat()
+        return (lambda i: ops.adam(wv, gv, mv, vv, 1 + i, 3e-4, 0.9, 0.95, 1e-8, wd=0.1)), 28 * n, 12
+
+    def grad_norm_sq():
+        n, wv, gv, mv, vv = _flat()
+        del wv, mv, vv
+        nsq = torch.zeros(1, device=device)
+        return (lambda i: ops.grad_norm_sq(gv, 1.0, out=nsq)), 4 * n, 12
+
+    return {
+        "rmsnorm": rmsnorm, "rmsnorm_bwd": rmsnorm_bwd, "rmsnorm_bwd_add": rmsnorm_bwd_add,
+        "residual_rmsnorm": residual_rmsnorm, "residual": residual, "swiglu": swiglu, "swiglu_bwd": swiglu_bwd,
+        "rope": rope, "qknorm_rope(Q)": qknorm_rope, "rope_qknorm_bwd(Q)": rope_qknorm_bwd,
+        "embed_lookup": embed_lookup, "embed_backward": embed_backward,
+        "cross_entropy": cross_entropy, "cross_entropy_compact": cross_entropy_compact,
+        "adam": adam, "grad_norm_sq": grad_norm_sq,
+    }
+
+
+def time_op(torch, builder, peak_gbs, iters=None, warmup=3):
+    fn, nbytes, default_iters = builder()
+    iters = iters or default_iters
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for i in range(iters):
+        fn(i)
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / iters
+    gbs = nbytes / ms / 1e6
+    return {"ms": round(ms, 4), "GB/s": round(gbs, 1), "frac_measured": round(gbs / peak_gbs, 3),
+            "frac_8TBs": round(gbs / NOMINAL_HBM_GBS, 3), "bytes": nbytes}
+
+
+def per_op_table(torch, ops, device, peak_gbs, batch=16, only=None, iters=None, warmup=3):
+    """Achieved GB/s per operator on benchmark-sized bf16 tensors (algorithmic bytes / time)."""
+    res = {}
+    for name, builder in _cases(torch, ops, device, batch).items():
+        if only and name not in only:
+            continue
+        res[name] = time_op(torch, builder, peak_gbs, iters, warmup)
+        torch.cuda.empty_cache()
+    return res
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--op", action="append", help="operator name (repeatable); default: all")
+    ap.add_argument("--batch", type=int, default=16, help="sequences of 2048 tokens per launch")
+    ap.add_argument("--iters", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--peak-gbs", type=float, default=None, help="roofline denominator (default: MEASURED_PEAKS.json)")
+    ap.add_argument("--tuning", default="", help="comma-separated knob=value pairs")
+    a = ap.parse_args(argv)
+    import torch
+    from . import dev_ops as ops, lib
+    from .peaks import hbm_peak_gbs
+
+    if not torch.cuda.is_available():
+        raise SystemExit("opbench needs a CUDA device")
+    lib.init(0)
+    for item in filter(None, a.tuning.split(",")):
+        k, _, v = item.partition("=")
+        lib.set_tuning(k, int(v))
+    peak, kind = hbm_peak_gbs()
+    if a.peak_gbs:
+        peak, kind = a.peak_gbs, "given"
+    table = per_op_table(torch, ops, torch.device("cuda:0"), peak, a.batch, a.op, a.iters, a.warmup)
+    print(json.dumps({"batch": a.batch, "peak_gbs": peak, "peak_kind": kind, "ops": table}))
+
+
+if __name__ == "__main__":
+    main()

@@ -58,12 +58,8 @@ def parse_args():
 
 
 def measured_peak():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    try:
-        with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
-    except Exception:
-        return FALLBACK_HBM_GBS, "fallback"
+    from ane_b200.peaks import hbm_peak_gbs
+    return hbm_peak_gbs()
 
 
 # ------------------------------------------------------------------------------------- clocks
@@ -250,81 +246,6 @@ def workload_config(args, world):
     }
 
 
-# ------------------------------------------------------------------------------------- per-op table
-def per_op_table(torch, ops, device, peak_gbs):
-    """Achieved GB/s per operator on benchmark-sized bf16 tensors (algorithmic bytes / time)."""
-    res = {}
-    M, S, D, H, Qd, KVd, hd = 16, 2048, 1024, 3072, 2048, 1024, 128
-    bf = torch.bfloat16
-    NSET = 3
-
-    def mk(ch, dtype=bf, n=NSET, b=M):
-        return [torch.randn((b, ch, S), device=device, dtype=dtype) for _ in range(n)]
-
-    def timeit(fn, bytes_per_launch, iters=12):
-        for i in range(3):
-            fn(i)
-        torch.cuda.synchronize()
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        for i in range(iters):
-            fn(i)
-        e.record()
-        torch.cuda.synchronize()
-        ms = s.elapsed_time(e) / iters
-        gbs = bytes_per_launch / ms / 1e6
-        return {"ms": round(ms, 4), "GB/s": round(gbs, 1), "frac_measured": round(gbs / peak_gbs, 3),
-                "frac_8TBs": round(gbs / NOMINAL_HBM_GBS, 3), "bytes": bytes_per_launch}
-
-    T = M * S
-    w = torch.ones(D, device=device)
-    wq = torch.ones(hd, device=device)
-    dw = torch.zeros(D, device=device)
-    dwq = torch.zeros(hd, device=device)
-    xs, ys, zs, os_ = mk(D), mk(D), mk(D), mk(D)
-    res["rmsnorm"] = timeit(lambda i: ops.rmsnorm(xs[i % NSET], w, out=os_[i % NSET]), 2 * D * T * 2)
-    res["rmsnorm_bwd"] = timeit(lambda i: ops.rmsnorm_bwd(ys[i % NSET], xs[i % NSET], w, dw, out=os_[i % NSET]), 3 * D * T * 2)
-    res["rmsnorm_bwd_add"] = timeit(lambda i: ops.rmsnorm_bwd(ys[i % NSET], xs[i % NSET], w, dw, add=zs[i % NSET], out=os_[i % NSET]), 4 * D * T * 2)
-    o2 = mk(D)
-    res["residual_rmsnorm"] = timeit(lambda i: ops.residual_rmsnorm(xs[i % NSET], ys[i % NSET], w, 0.13, x2=os_[i % NSET], x2norm=o2[i % NSET]), 4 * D * T * 2)
-    res["residual"] = timeit(lambda i: ops.residual(xs[i % NSET], ys[i % NSET], 0.13, out=os_[i % NSET]), 3 * D * T * 2)
-    del zs, o2
-    h1, h3, dd, g1, g3 = mk(H), mk(H), mk(H), mk(H), mk(H)
-    res["swiglu"] = timeit(lambda i: ops.swiglu(h1[i % NSET], h3[i % NSET], out=g1[i % NSET]), 3 * H * T * 2)
-    res["swiglu_bwd"] = timeit(lambda i: ops.swiglu_bwd(h1[i % NSET], h3[i % NSET], dd[i % NSET], dh1=g1[i % NSET], dh3=g3[i % NSET]), 5 * H * T * 2)
-    del h1, h3, dd, g1, g3
-    q, dq, qo = mk(Qd), mk(Qd), mk(Qd)
-    res["rope"] = timeit(lambda i: ops.rope(q[i % NSET], hd, base=1e6, out=qo[i % NSET]), 2 * Qd * T * 2)
-    res["qknorm_rope(Q)"] = timeit(lambda i: ops.qknorm_rope(q[i % NSET], wq, hd, out=qo[i % NSET]), 2 * Qd * T * 2)
-    res["rope_qknorm_bwd(Q)"] = timeit(lambda i: ops.rope_qknorm_bwd(dq[i % NSET], q[i % NSET], wq, dwq, hd, out=qo[i % NSET]), 3 * Qd * T * 2)
-    del q, dq, qo
-    # embedding (config 4: 32 x 2048 tokens, table [151936, 1024] bf16)
-    V, Be = 151936, 32
-    table = (0.02 * torch.randn(V, D, device=device)).to(bf)
-    tok = torch.randint(0, V, (Be, S), device=device, dtype=torch.int32)
-    xe = [torch.empty((Be, D, S), device=device, dtype=bf) for _ in range(2)]
-    res["embed_lookup"] = timeit(lambda i: ops.embed_lookup(table, tok, out=xe[i % 2]), Be * S * 4 + 2 * D * Be * S * 2)
-    dE = torch.zeros(V, D, device=device)
-    uniq = int(torch.unique(tok).numel())
-    res["embed_backward"] = timeit(lambda i: ops.embed_backward(dE, xe[i % 2], tok), Be * S * 4 + D * Be * S * 2 + 2 * uniq * D * 4, iters=6)
-    del table, xe, dE
-    # cross-entropy (config 4 shape, 4 of the 32 sequences: 5 GB of fp32 logits, in place)
-    Bc = 4
-    logits = torch.randn((Bc, V, S), device=device)
-    tg = torch.randint(0, V, (Bc, S), device=device, dtype=torch.int32)
-    res["cross_entropy"] = timeit(lambda i: ops.cross_entropy(logits, tg, dlogits=logits), 2 * V * Bc * S * 4, iters=3)
-    del logits
-    # Adam over 596M params is timed inside the step; here 64M params for the table
-    n = 64 << 20
-    wv, gv, mv, vv = (torch.randn(n, device=device) * 0.01 for _ in range(4))
-    vv.abs_()
-    res["adam"] = timeit(lambda i: ops.adam(wv, gv, mv, vv, 1 + i, 3e-4, 0.9, 0.95, 1e-8, wd=0.1), 28 * n)
-    nsq = torch.zeros(1, device=device)
-    res["grad_norm_sq"] = timeit(lambda i: ops.grad_norm_sq(gv, 1.0, out=nsq), 4 * n)
-    torch.cuda.empty_cache()
-    return res
-
-
 # ------------------------------------------------------------------------------------- e2e (host buffers)
 def e2e_chain(torch, cfg, n_seqs, steps, warmup):
     """The chain through the host-buffer entry points on page-locked host tensors.  Per-layer host
@@ -504,7 +425,8 @@ def run_ours(args):
     del chain
     torch.cuda.empty_cache()
     if not args.no_ops and rank == 0 and world == 1:
-        line["ops"] = per_op_table(torch, ops, device, peak_gbs)
+        from ane_b200.opbench import per_op_table
+        line["ops"] = per_op_table(torch, ops, device, peak_gbs, batch=min(16, args.micro_batch))
     if world > 1:
         dist.barrier()
 
