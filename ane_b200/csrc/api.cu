@@ -194,6 +194,7 @@ void ane_cuda_shutdown(void) {
     cudaDeviceSynchronize();
     pipe_destroy();
     rope_tables_release();
+    embed_side_release();
     if (c.ws) cudaFree(c.ws);
     if (c.stage) cudaFree(c.stage);
     if (c.status) cudaFree(c.status);

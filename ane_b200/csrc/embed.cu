@@ -70,6 +70,127 @@ embed_lookup_kernel(U *__restrict__ x, const U *__restrict__ table, const void *
     }
 }
 
+// ---------------------------------------------------------------- vectorised tiles
+// The kernels above move one element per thread and instruction; at 2 bytes per element that is
+// instruction-bound long before it is memory-bound.  The tiled forms below move 16 bytes per
+// instruction on both sides.  The shared tile holds 32-bit words, tile[d][wc]: for 32-bit elements
+// a word column wc is a token, for 16-bit elements it is a PAIR of adjacent tokens (low half = even
+// token), so both the row side (32 bytes of one table row per thread) and the column side (16 bytes
+// = 4 word columns of one channel per thread) are whole vectors.  A block covers 32 word columns
+// (32 or 64 tokens) x DCW channels; row stride 36 words keeps 16-byte alignment and spreads banks.
+constexpr int ET_WC = 32;           // word columns per tile
+constexpr int ET_STRIDE = 36;       // words per tile row
+
+template <int ESZ> struct EtGeom;
+template <> struct EtGeom<2> { static constexpr int TOK = 64, DC = 128, CH = 16; };   // tokens, channels per tile, channels per 32-byte chunk
+template <> struct EtGeom<4> { static constexpr int TOK = 32, DC = 64, CH = 8; };
+
+// two 16-bit rows (8 channels each as uint4) -> 8 words, word j = (a[j], b[j])
+__device__ __forceinline__ void interleave16(const uint4 a, const uint4 b, uint32_t (&w)[8]) {
+    w[0] = __byte_perm(a.x, b.x, 0x5410); w[1] = __byte_perm(a.x, b.x, 0x7632);
+    w[2] = __byte_perm(a.y, b.y, 0x5410); w[3] = __byte_perm(a.y, b.y, 0x7632);
+    w[4] = __byte_perm(a.z, b.z, 0x5410); w[5] = __byte_perm(a.z, b.z, 0x7632);
+    w[6] = __byte_perm(a.w, b.w, 0x5410); w[7] = __byte_perm(a.w, b.w, 0x7632);
+}
+// inverse of interleave16
+__device__ __forceinline__ void deinterleave16(const uint32_t (&w)[8], uint4 &a, uint4 &b) {
+    a.x = __byte_perm(w[0], w[1], 0x5410); b.x = __byte_perm(w[0], w[1], 0x7632);
+    a.y = __byte_perm(w[2], w[3], 0x5410); b.y = __byte_perm(w[2], w[3], 0x7632);
+    a.z = __byte_perm(w[4], w[5], 0x5410); b.z = __byte_perm(w[4], w[5], 0x7632);
+    a.w = __byte_perm(w[6], w[7], 0x5410); b.w = __byte_perm(w[6], w[7], 0x7632);
+}
+
+// Gather.  Requirements (checked by the launcher): S % 8 == 0 (16-bit) or S % 4 == 0 (32-bit),
+// D a multiple of the 32-byte chunk, 16-byte aligned x and table.
+template <int ESZ, typename ID>
+__global__ void __launch_bounds__(EMB_THREADS)
+embed_lookup_tiled_kernel(void *__restrict__ xv, const void *__restrict__ tablev, const void *__restrict__ tokens, int D, int S,
+                          int tiles_per_seq, int vocab, bool zero_oor, ane_cuda_status *status) {
+    using G = EtGeom<ESZ>;
+    constexpr int NCH = G::DC / G::CH;                 // 32-byte chunks per tile row: 8
+    static_assert(NCH * ET_WC == EMB_THREADS, "one (word column, chunk) item per thread");
+    __shared__ __align__(16) uint32_t tile[G::DC * ET_STRIDE];
+    __shared__ int ids[G::TOK];
+    __shared__ int any_skip;
+    const int b = blockIdx.x / tiles_per_seq;
+    const int t0 = (blockIdx.x % tiles_per_seq) * G::TOK;
+    const int d0 = blockIdx.y * G::DC;
+    const char *table = static_cast<const char *>(tablev);
+    char *x = static_cast<char *>(xv);
+
+    if (threadIdx.x == 0) any_skip = 0;
+    __syncthreads();
+    if (threadIdx.x < G::TOK) {
+        const int t = t0 + threadIdx.x;
+        int id = -1;
+        if (t < S) {
+            id = load_id<ID>(tokens, (size_t)b * S + t);
+            if (id < 0 || id >= vocab) {
+                id = -1;
+                if (blockIdx.y == 0) atomicAdd(&status->oor_ids, 1);
+                if (!zero_oor) any_skip = 1;
+            }
+        }
+        ids[threadIdx.x] = id;
+    }
+    __syncthreads();
+    {   // rows -> tile: lanes along word columns, one 32-byte chunk per warp
+        const int wc = threadIdx.x % ET_WC, ch = threadIdx.x / ET_WC;
+        const int d = d0 + ch * G::CH;
+        if (d < D) {
+            uint32_t w[8 * (ESZ == 2 ? 2 : 1)];
+            if constexpr (ESZ == 2) {
+                const int ia = ids[2 * wc], ib = ids[2 * wc + 1];
+                uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0, b0 = a0, b1 = a0;
+                if (ia >= 0) {
+                    const uint4 *p = reinterpret_cast<const uint4 *>(table + ((size_t)ia * D + d) * 2);
+                    a0 = __ldg(p); a1 = __ldg(p + 1);
+                }
+                if (ib >= 0) {
+                    const uint4 *p = reinterpret_cast<const uint4 *>(table + ((size_t)ib * D + d) * 2);
+                    b0 = __ldg(p); b1 = __ldg(p + 1);
+                }
+                uint32_t lo[8], hi[8];
+                interleave16(a0, b0, lo);
+                interleave16(a1, b1, hi);
+#pragma unroll
+                for (int j = 0; j < 8; j++) { w[j] = lo[j]; w[8 + j] = hi[j]; }
+            } else {
+                const int ia = ids[wc];
+                uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0;
+                if (ia >= 0) {
+                    const uint4 *p = reinterpret_cast<const uint4 *>(table + ((size_t)ia * D + d) * 4);
+                    a0 = __ldg(p); a1 = __ldg(p + 1);
+                }
+                w[0] = a0.x; w[1] = a0.y; w[2] = a0.z; w[3] = a0.w; w[4] = a1.x; w[5] = a1.y; w[6] = a1.z; w[7] = a1.w;
+            }
+#pragma unroll
+            for (int j = 0; j < G::CH; j++) tile[(ch * G::CH + j) * ET_STRIDE + wc] = w[j];
+        }
+    }
+    __syncthreads();
+    // tile -> columns: 16 bytes (4 word columns) of one channel per thread
+    constexpr int TPW = ESZ == 2 ? 2 : 1;              // tokens per word
+    for (int item = threadIdx.x; item < G::DC * (ET_WC / 4); item += EMB_THREADS) {
+        const int dl = item / (ET_WC / 4), k = item % (ET_WC / 4);
+        const int t = t0 + k * 4 * TPW;
+        if (d0 + dl >= D || t >= S) continue;
+        const uint4 v = *reinterpret_cast<const uint4 *>(&tile[dl * ET_STRIDE + 4 * k]);
+        char *dst = x + (((size_t)b * D + d0 + dl) * S + t) * ESZ;
+        if (!any_skip) {
+            __stcs(reinterpret_cast<uint4 *>(dst), v);
+        } else {        // some token of this tile keeps its stale column: element-wise stores
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4 * TPW; q++) {
+                if (ids[k * 4 * TPW + q] < 0) continue;
+                if constexpr (ESZ == 2) reinterpret_cast<uint16_t *>(dst)[q] = (uint16_t)(w[q / 2] >> (16 * (q & 1)));
+                else reinterpret_cast<uint32_t *>(dst)[q] = w[q];
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------- scatter-add
 template <typename ID>
 __global__ void eb_prepare_kernel(int *__restrict__ keys, int *__restrict__ vals, const void *__restrict__ tokens,
@@ -139,6 +260,343 @@ eb_reduce_kernel(float *__restrict__ d_embed, const T *__restrict__ stage, const
     }
 }
 
+// Gather, row-walking form (the mirror image of eb_stage_rows_kernel below): a block takes 32 tokens
+// (16 word columns) x up to 512 channels; a WARP owns a word column and walks its table row(s) with
+// consecutive lanes on consecutive channels (one sequential 1-2 KB burst per row), the column side
+// writes 64-byte segments of x.
+constexpr int ER_WC = 16, ER_DC = 512, ER_STRIDE = 17, ER_THREADS = 32 * ER_WC;
+
+template <int ESZ, typename ID>
+__global__ void __launch_bounds__(ER_THREADS)
+embed_lookup_rows_kernel(void *__restrict__ xv, const void *__restrict__ tablev, const void *__restrict__ tokens, int D, int S,
+                         int tiles_per_seq, int vocab, bool zero_oor, ane_cuda_status *status) {
+    constexpr int TPW = ESZ == 2 ? 2 : 1;
+    constexpr int TOK = ER_WC * TPW;
+    __shared__ uint32_t tile[ER_DC * ER_STRIDE];
+    __shared__ int ids[TOK];
+    __shared__ int any_skip;
+    const int b = blockIdx.x / tiles_per_seq;
+    const int t0 = (blockIdx.x % tiles_per_seq) * TOK;
+    const int d0 = blockIdx.y * ER_DC;
+    const int dcount = D - d0 < ER_DC ? D - d0 : ER_DC;
+    const char *table = static_cast<const char *>(tablev);
+    char *x = static_cast<char *>(xv);
+
+    if (threadIdx.x == 0) any_skip = 0;
+    __syncthreads();
+    if (threadIdx.x < TOK) {
+        const int t = t0 + threadIdx.x;
+        int id = -1;
+        if (t < S) {
+            id = load_id<ID>(tokens, (size_t)b * S + t);
+            if (id < 0 || id >= vocab) {
+                id = -1;
+                if (blockIdx.y == 0) atomicAdd(&status->oor_ids, 1);
+                if (!zero_oor) any_skip = 1;
+            }
+        }
+        ids[threadIdx.x] = id;
+    }
+    __syncthreads();
+    {   // rows -> tile: four channels per lane and step
+        const int wc = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int nquad = dcount >> 2;
+        if constexpr (ESZ == 2) {
+            const int ia = ids[2 * wc], ib = ids[2 * wc + 1];
+            const uint2 *ra = reinterpret_cast<const uint2 *>(table + ((size_t)(ia < 0 ? 0 : ia) * D + d0) * 2);
+            const uint2 *rb = reinterpret_cast<const uint2 *>(table + ((size_t)(ib < 0 ? 0 : ib) * D + d0) * 2);
+#pragma unroll 4
+            for (int cq = lane; cq < nquad; cq += 32) {
+                uint2 a = make_uint2(0, 0), c = make_uint2(0, 0);
+                if (ia >= 0) a = __ldg(ra + cq);
+                if (ib >= 0) c = __ldg(rb + cq);
+                uint32_t *col = &tile[(4 * cq) * ER_STRIDE + wc];
+                col[0] = __byte_perm(a.x, c.x, 0x5410);
+                col[ER_STRIDE] = __byte_perm(a.x, c.x, 0x7632);
+                col[2 * ER_STRIDE] = __byte_perm(a.y, c.y, 0x5410);
+                col[3 * ER_STRIDE] = __byte_perm(a.y, c.y, 0x7632);
+            }
+        } else {
+            const int ia = ids[wc];
+            const uint4 *ra = reinterpret_cast<const uint4 *>(table + ((size_t)(ia < 0 ? 0 : ia) * D + d0) * 4);
+#pragma unroll 4
+            for (int cq = lane; cq < nquad; cq += 32) {
+                uint4 a = make_uint4(0, 0, 0, 0);
+                if (ia >= 0) a = __ldg(ra + cq);
+                uint32_t *col = &tile[(4 * cq) * ER_STRIDE + wc];
+                col[0] = a.x; col[ER_STRIDE] = a.y; col[2 * ER_STRIDE] = a.z; col[3 * ER_STRIDE] = a.w;
+            }
+        }
+    }
+    __syncthreads();
+    constexpr int VPR = ER_WC / 4;                       // 16-byte vectors per tile row
+    for (int item = threadIdx.x; item < dcount * VPR; item += ER_THREADS) {
+        const int dl = item / VPR, k = item % VPR;
+        const int t = t0 + k * 4 * TPW;
+        if (t >= S) continue;
+        const uint32_t *row = &tile[dl * ER_STRIDE + 4 * k];
+        const uint32_t w[4] = {row[0], row[1], row[2], row[3]};
+        char *dst = x + (((size_t)b * D + d0 + dl) * S + t) * ESZ;
+        if (!any_skip) {
+            __stcs(reinterpret_cast<uint4 *>(dst), make_uint4(w[0], w[1], w[2], w[3]));
+        } else {        // some token of this tile keeps its stale column: element-wise stores
+#pragma unroll
+            for (int q = 0; q < 4 * TPW; q++) {
+                if (ids[k * 4 * TPW + q] < 0) continue;
+                if constexpr (ESZ == 2) reinterpret_cast<uint16_t *>(dst)[q] = (uint16_t)(w[q / 2] >> (16 * (q & 1)));
+                else reinterpret_cast<uint32_t *>(dst)[q] = w[q];
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- vectorised scatter-add
+// Staging kernel destinations:
+//   dest >= 0       row `dest` (= the position b*S + t itself) of the staging matrix: the id occurs more
+//                   than once and its rows are added in position order by eb_reduce_runs_kernel;
+//   EB_SKIP         out-of-range id, dropped (stories_cpu_ops.h:126);
+//   otherwise       -(id + 2): the id occurs exactly once, so its column is added straight onto
+//                   d_embed[id] -- a single addition has no order to preserve, and the staging
+//                   round trip (one write and one read of the column) is saved.
+// Only the reduction of repeated ids needs the positions sorted by id; that sort depends on the
+// tokens alone and runs on a side stream while the staging kernel moves the data.
+constexpr int EB_SKIP = -1;
+
+// sort keys: out-of-range ids sort behind every valid id
+template <typename ID>
+__global__ void eb_keys_kernel(int *__restrict__ keys, int *__restrict__ vals, const void *__restrict__ tokens, int n, int vocab) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int id = load_id<ID>(tokens, i);
+    if (id < 0 || id >= vocab) id = vocab;
+    keys[i] = id;
+    vals[i] = i;
+}
+
+// starts of runs longer than one go to a work list (its order does not matter: runs are independent)
+__global__ void eb_runs_kernel(int *__restrict__ run_start, int *__restrict__ run_count, const int *__restrict__ keys, int n, int vocab) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n) return;
+    const int key = keys[r];
+    if (key >= vocab) return;
+    const bool first = r == 0 || keys[r - 1] != key;
+    const bool last = r == n - 1 || keys[r + 1] != key;
+    if (first && !last) run_start[atomicAdd(run_count, 1)] = r;
+}
+
+template <typename T> __device__ __forceinline__ float raw16_to_f(uint32_t h);
+template <> __device__ __forceinline__ float raw16_to_f<__nv_bfloat16>(uint32_t h) { return __uint_as_float(h << 16); }
+template <> __device__ __forceinline__ float raw16_to_f<__half>(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
+
+// Staging kernel.  Random 64-byte read-modify-writes of d_embed (every lane of a warp on a different
+// row, what a 64-token x 128-channel tile leads to) ran at a tenth of the HBM rate: each touches its own
+// DRAM page.  Here a block takes 32 tokens (16 word columns) x up to 512 channels, and a WARP owns a
+// word column: it walks its half of the d_embed (or staging) row with consecutive lanes on consecutive
+// channels, so every row piece is one sequential 1-2 KB burst.  The column side reads 64-byte segments
+// of dx (32-byte segments cost a 64-byte DRAM fetch each).
+
+// occurrences of every id (count must be zero on entry); out-of-range ids are reported, not counted
+template <typename ID>
+__global__ void eb_count_kernel(int *__restrict__ count, const void *__restrict__ tokens, int n, int vocab, ane_cuda_status *status) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int id = load_id<ID>(tokens, i);
+    if (id < 0 || id >= vocab) atomicAdd(&status->oor_ids, 1);
+    else atomicAdd(&count[id], 1);
+}
+
+// Destination of a position, from the occurrence counts alone (no sort needed): an id that occurs once
+// goes straight to d_embed, any other to the staging row of its own position.
+template <typename ID>
+__device__ __forceinline__ int eb_dest(const void *tokens, const int *count, size_t pos, int vocab) {
+    const int id = load_id<ID>(tokens, pos);
+    if (id < 0 || id >= vocab) return EB_SKIP;
+    return count[id] == 1 ? -(id + 2) : (int)pos;
+}
+
+template <typename T, int ESZ, typename ID>
+__global__ void __launch_bounds__(ER_THREADS)
+eb_stage_rows_kernel(void *__restrict__ stagev, float *__restrict__ d_embed, const void *__restrict__ dxv,
+                     const void *__restrict__ tokens, const int *__restrict__ count, int vocab, int D, int S, int tiles_per_seq) {
+    constexpr int TPW = ESZ == 2 ? 2 : 1;
+    constexpr int TOK = ER_WC * TPW;
+    __shared__ uint32_t tile[ER_DC * ER_STRIDE];
+    __shared__ int dst[TOK];
+    const int b = blockIdx.x / tiles_per_seq;
+    const int t0 = (blockIdx.x % tiles_per_seq) * TOK;
+    const int d0 = blockIdx.y * ER_DC;
+    const int dcount = D - d0 < ER_DC ? D - d0 : ER_DC;
+    const char *dx = static_cast<const char *>(dxv);
+
+    if (threadIdx.x < TOK) {
+        const int t = t0 + threadIdx.x;
+        dst[threadIdx.x] = t < S ? eb_dest<ID>(tokens, count, (size_t)b * S + t, vocab) : EB_SKIP;
+    }
+    constexpr int VPR = ER_WC / 4;                       // 16-byte vectors per tile row
+    for (int item = threadIdx.x; item < dcount * VPR; item += ER_THREADS) {
+        const int dl = item / VPR, k = item % VPR;
+        const int t = t0 + k * 4 * TPW;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (t < S) v = __ldcs(reinterpret_cast<const uint4 *>(dx + (((size_t)b * D + d0 + dl) * S + t) * ESZ));
+        uint32_t *row = &tile[dl * ER_STRIDE + 4 * k];
+        row[0] = v.x; row[1] = v.y; row[2] = v.z; row[3] = v.w;
+    }
+    __syncthreads();
+    const int wc = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int npair = dcount >> 1;                       // channel pairs
+#pragma unroll
+    for (int q = 0; q < TPW; q++) {
+        const int dsel = dst[wc * TPW + q];
+        if (dsel == EB_SKIP) continue;
+        // value pair (channels 2cp, 2cp+1) of this token
+        auto fetch = [&](int cp, float &f0, float &f1, uint32_t &raw) {
+            const uint32_t w0 = tile[(2 * cp) * ER_STRIDE + wc], w1 = tile[(2 * cp + 1) * ER_STRIDE + wc];
+            if constexpr (ESZ == 2) {
+                raw = __byte_perm(w0, w1, q == 0 ? 0x5410 : 0x7632);
+                f0 = raw16_to_f<T>(raw & 0xffffu);
+                f1 = raw16_to_f<T>(raw >> 16);
+            } else {
+                raw = 0;
+                f0 = __uint_as_float(w0);
+                f1 = __uint_as_float(w1);
+            }
+        };
+        if (dsel >= 0) {
+            char *srow = static_cast<char *>(stagev) + ((size_t)dsel * D + d0) * ESZ;
+            for (int cp = lane; cp < npair; cp += 32) {
+                float f0, f1;
+                uint32_t raw;
+                fetch(cp, f0, f1, raw);
+                if constexpr (ESZ == 2) reinterpret_cast<uint32_t *>(srow)[cp] = raw;
+                else reinterpret_cast<float2 *>(srow)[cp] = make_float2(f0, f1);
+            }
+        } else {
+            float2 *erow = reinterpret_cast<float2 *>(d_embed + (size_t)(-(dsel + 2)) * D + d0);
+            constexpr int UN = 8;
+            for (int cb = lane; cb < npair; cb += 32 * UN) {
+                float2 cur[UN];
+#pragma unroll
+                for (int u = 0; u < UN; u++)
+                    if (cb + u * 32 < npair) cur[u] = erow[cb + u * 32];
+#pragma unroll
+                for (int u = 0; u < UN; u++) {
+                    const int cp = cb + u * 32;
+                    if (cp < npair) {
+                        float f0, f1;
+                        uint32_t raw;
+                        fetch(cp, f0, f1, raw);
+                        erow[cp] = make_float2(cur[u].x + f0, cur[u].y + f1);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Runs of equal ids (length >= 2): a WARP per run adds the staging rows in sorted (= position) order
+// onto the d_embed row, four channels per lane and step.  With one warp per run all runs are in flight
+// at once, which hides the chain of dependent loads (keys, positions, rows) each of them is.
+constexpr int RR_THREADS = 256, RR_J = 8;
+template <typename T, int ESZ>
+__device__ __forceinline__ void rr_add(float4 &acc, const uint4 raw) {
+    if constexpr (ESZ == 2) {
+        acc.x += raw16_to_f<T>(raw.x & 0xffffu); acc.y += raw16_to_f<T>(raw.x >> 16);
+        acc.z += raw16_to_f<T>(raw.y & 0xffffu); acc.w += raw16_to_f<T>(raw.y >> 16);
+    } else {
+        acc.x += __uint_as_float(raw.x); acc.y += __uint_as_float(raw.y);
+        acc.z += __uint_as_float(raw.z); acc.w += __uint_as_float(raw.w);
+    }
+}
+template <int ESZ>
+__device__ __forceinline__ uint4 rr_load(const char *src) {
+    if constexpr (ESZ == 2) {
+        const uint2 v = *reinterpret_cast<const uint2 *>(src);
+        return make_uint4(v.x, v.y, 0, 0);
+    } else {
+        return *reinterpret_cast<const uint4 *>(src);
+    }
+}
+
+template <typename T, int ESZ>
+__global__ void __launch_bounds__(RR_THREADS)
+eb_reduce_runs_kernel(float *__restrict__ d_embed, const void *__restrict__ stagev, const int *__restrict__ keys,
+                      const int *__restrict__ sorted_pos, const int *__restrict__ run_start, const int *__restrict__ run_count,
+                      int n, int D) {
+    const char *stage = static_cast<const char *>(stagev);
+    const int lane = threadIdx.x & 31;
+    const int wi = blockIdx.x * (RR_THREADS / 32) + (threadIdx.x >> 5);
+    if (wi >= *run_count) return;
+    const int r = run_start[wi];
+    const int key = keys[r];
+    float *erow = d_embed + (size_t)key * D;
+    for (int d0 = 0; d0 < D; d0 += 128 * RR_J) {
+        float4 acc[RR_J];
+#pragma unroll
+        for (int j = 0; j < RR_J; j++) {
+            const int d = d0 + (j * 32 + lane) * 4;
+            if (d < D) acc[j] = *reinterpret_cast<const float4 *>(erow + d);
+        }
+        for (int q0 = r;; q0 += 32) {                    // 32 positions of the run per round
+            const int idx = q0 + lane;
+            const bool same = idx < n && keys[idx] == key;
+            const unsigned m = __ballot_sync(0xffffffffu, same);
+            const int cnt = m == 0xffffffffu ? 32 : __ffs(~m) - 1;
+            const int mypos = same ? sorted_pos[idx] : 0;
+            for (int u = 0; u < cnt; u += 2) {           // two rows (16 loads) in flight; added in order
+                const size_t row0 = (size_t)__shfl_sync(0xffffffffu, mypos, u) * D;
+                const size_t row1 = (size_t)__shfl_sync(0xffffffffu, mypos, (u + 1) & 31) * D;
+                const bool two = u + 1 < cnt;
+                uint4 v0[RR_J], v1[RR_J];
+#pragma unroll
+                for (int j = 0; j < RR_J; j++) {
+                    const int d = d0 + (j * 32 + lane) * 4;
+                    if (d < D) {
+                        v0[j] = rr_load<ESZ>(stage + (row0 + d) * ESZ);
+                        if (two) v1[j] = rr_load<ESZ>(stage + (row1 + d) * ESZ);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < RR_J; j++) {
+                    const int d = d0 + (j * 32 + lane) * 4;
+                    if (d < D) {
+                        rr_add<T, ESZ>(acc[j], v0[j]);
+                        if (two) rr_add<T, ESZ>(acc[j], v1[j]);
+                    }
+                }
+            }
+            if (cnt < 32) break;
+        }
+#pragma unroll
+        for (int j = 0; j < RR_J; j++) {
+            const int d = d0 + (j * 32 + lane) * 4;
+            if (d < D) *reinterpret_cast<float4 *>(erow + d) = acc[j];
+        }
+    }
+}
+
+// Side stream for the sort (created on first use, destroyed at shutdown).
+struct EmbedSide { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; bool ok = false; };
+static EmbedSide g_side;
+static EmbedSide *embed_side() {
+    if (g_side.ok) return &g_side;
+    int lo = 0, hi = 0;                                  // the short sort kernels must not queue behind the data movement
+    cudaDeviceGetStreamPriorityRange(&lo, &hi);
+    if (cudaStreamCreateWithPriority(&g_side.stream, cudaStreamNonBlocking, hi) != cudaSuccess ||
+        cudaEventCreateWithFlags(&g_side.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&g_side.join, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    g_side.ok = true;
+    return &g_side;
+}
+void embed_side_release() {
+    if (g_side.stream) cudaStreamDestroy(g_side.stream);
+    if (g_side.fork) cudaEventDestroy(g_side.fork);
+    if (g_side.join) cudaEventDestroy(g_side.join);
+    g_side = EmbedSide();
+}
+
 static int sort_bits(int vocab) {
     int bits = 1;
     while ((1ll << bits) <= (long long)vocab) bits++;   // keys go up to `vocab` (the out-of-range sentinel)
@@ -162,7 +620,33 @@ int ane_cuda_embed_lookup_dev(void *stream, ane_dtype dtype, ane_idtype idtype, 
     cudaStream_t st = (cudaStream_t)stream;
     const bool zero = flags == ANE_OOR_ZERO;
     ane_cuda_status *status = ctx().status;
-    if (dtype == ANE_F32) {
+    const size_t esz = dtype_size(dtype);
+    const bool tiled = tuning("embed_tiled", 1) && aligned16(x) && aligned16(table) && S % (16 / (int)esz) == 0 &&
+                       D % (32 / (int)esz) == 0;
+    if (tiled && tuning("embed_rows", 1) && D % 4 == 0) {
+        const int TOKr = ER_WC * (esz == 2 ? 2 : 1);
+        const int tps = (S + TOKr - 1) / TOKr;
+        dim3 grid((unsigned)(B * tps), (unsigned)((D + ER_DC - 1) / ER_DC));
+        if (esz == 2) {
+            if (idtype == ANE_ID_U16) embed_lookup_rows_kernel<2, uint16_t><<<grid, ER_THREADS, 0, st>>>(x, table, tokens, D, S, tps, vocab, zero, status);
+            else embed_lookup_rows_kernel<2, int32_t><<<grid, ER_THREADS, 0, st>>>(x, table, tokens, D, S, tps, vocab, zero, status);
+        } else {
+            if (idtype == ANE_ID_U16) embed_lookup_rows_kernel<4, uint16_t><<<grid, ER_THREADS, 0, st>>>(x, table, tokens, D, S, tps, vocab, zero, status);
+            else embed_lookup_rows_kernel<4, int32_t><<<grid, ER_THREADS, 0, st>>>(x, table, tokens, D, S, tps, vocab, zero, status);
+        }
+    } else if (tiled && esz == 2) {
+        using G = EtGeom<2>;
+        const int tps = (S + G::TOK - 1) / G::TOK;
+        dim3 grid((unsigned)(B * tps), (unsigned)((D + G::DC - 1) / G::DC));
+        if (idtype == ANE_ID_U16) embed_lookup_tiled_kernel<2, uint16_t><<<grid, EMB_THREADS, 0, st>>>(x, table, tokens, D, S, tps, vocab, zero, status);
+        else embed_lookup_tiled_kernel<2, int32_t><<<grid, EMB_THREADS, 0, st>>>(x, table, tokens, D, S, tps, vocab, zero, status);
+    } else if (tiled) {
+        using G = EtGeom<4>;
+        const int tps = (S + G::TOK - 1) / G::TOK;
+        dim3 grid((unsigned)(B * tps), (unsigned)((D + G::DC - 1) / G::DC));
+        if (idtype == ANE_ID_U16) embed_lookup_tiled_kernel<4, uint16_t><<<grid, EMB_THREADS, 0, st>>>(x, table, tokens, D, S, tps, vocab, zero, status);
+        else embed_lookup_tiled_kernel<4, int32_t><<<grid, EMB_THREADS, 0, st>>>(x, table, tokens, D, S, tps, vocab, zero, status);
+    } else if (dtype == ANE_F32) {
         constexpr int TT = 32, DC = 32;
         const int tps = (S + TT - 1) / TT;
         dim3 grid((unsigned)(B * tps), (unsigned)((D + DC - 1) / DC));
@@ -194,44 +678,82 @@ int ane_cuda_embed_backward_dev(void *stream, ane_dtype dtype, ane_idtype idtype
     cudaStream_t st = (cudaStream_t)stream;
     const int n = B * S;
     const size_t esz = dtype_size(dtype);
+    const bool u16 = idtype == ANE_ID_U16;
 
     size_t cub_bytes = 0;
     cub::DoubleBuffer<int> kb(nullptr, nullptr), vb(nullptr, nullptr);
     ANE_CUDA_TRY(cub::DeviceRadixSort::SortPairs(nullptr, cub_bytes, kb, vb, n, 0, sort_bits(vocab), st));
     const size_t ints = round_up((size_t)n * sizeof(int), 256);
-    const size_t off_k0 = 0, off_k1 = ints, off_v0 = 2 * ints, off_v1 = 3 * ints, off_rank = 4 * ints;
-    const size_t off_cub = 5 * ints;
+    const size_t off_k0 = 0, off_k1 = ints, off_v0 = 2 * ints, off_v1 = 3 * ints, off_aux = 4 * ints;   // aux: rank_of_pos or run_start
+    const size_t off_cnt = 5 * ints;                                                                   // run_count, then count[vocab]
+    const size_t off_cub = off_cnt + round_up(((size_t)vocab + 64) * sizeof(int), 256);
     const size_t off_stage = off_cub + round_up(cub_bytes, 256);
     const size_t total = off_stage + round_up((size_t)n * D * esz, 256);
     char *ws = static_cast<char *>(workspace(total));
     if (!ws) return fail(ANE_CUDA_ERR_NOMEM, "%s: no scratch (%zu bytes)", __func__, total);
     int *k0 = (int *)(ws + off_k0), *k1 = (int *)(ws + off_k1), *v0 = (int *)(ws + off_v0), *v1 = (int *)(ws + off_v1);
-    int *rank_of_pos = (int *)(ws + off_rank);
-
-    const int pb = (n + 255) / 256;
-    if (idtype == ANE_ID_U16) eb_prepare_kernel<uint16_t><<<pb, 256, 0, st>>>(k0, v0, tokens, n, vocab, ctx().status);
-    else eb_prepare_kernel<int32_t><<<pb, 256, 0, st>>>(k0, v0, tokens, n, vocab, ctx().status);
+    int *aux = (int *)(ws + off_aux);
+    void *stage = ws + off_stage;
     kb = cub::DoubleBuffer<int>(k0, k1);
     vb = cub::DoubleBuffer<int>(v0, v1);
+    const int pb = (n + 255) / 256;
+
+    const bool tiled = tuning("embed_tiled", 1) && aligned16(dx) && aligned16(d_embed) && S % (16 / (int)esz) == 0 && D % 4 == 0;
+    if (tiled) {
+        EmbedSide *side = embed_side();
+        if (!side) return fail(ANE_CUDA_ERR_CUDA, "%s: cannot create the side stream", __func__);
+        int *run_count = (int *)(ws + off_cnt), *count = run_count + 64, *run_start = aux;
+        ANE_CUDA_TRY(cudaMemsetAsync(run_count, 0, ((size_t)vocab + 64) * sizeof(int), st));
+        // fork: keys -> sort -> run starts, beside the data movement
+        ANE_CUDA_TRY(cudaEventRecord(side->fork, st));
+        ANE_CUDA_TRY(cudaStreamWaitEvent(side->stream, side->fork, 0));
+        if (u16) eb_keys_kernel<uint16_t><<<pb, 256, 0, side->stream>>>(k0, v0, tokens, n, vocab);
+        else eb_keys_kernel<int32_t><<<pb, 256, 0, side->stream>>>(k0, v0, tokens, n, vocab);
+        ANE_CUDA_TRY(cub::DeviceRadixSort::SortPairs(ws + off_cub, cub_bytes, kb, vb, n, 0, sort_bits(vocab), side->stream));
+        eb_runs_kernel<<<pb, 256, 0, side->stream>>>(run_start, run_count, kb.Current(), n, vocab);
+        ANE_CUDA_TRY(cudaEventRecord(side->join, side->stream));
+        // main: occurrence counts, then every column to d_embed (single occurrence) or to its staging row
+        if (u16) eb_count_kernel<uint16_t><<<pb, 256, 0, st>>>(count, tokens, n, vocab, ctx().status);
+        else eb_count_kernel<int32_t><<<pb, 256, 0, st>>>(count, tokens, n, vocab, ctx().status);
+        const int TOKr = ER_WC * (esz == 2 ? 2 : 1);
+        const int tps = (S + TOKr - 1) / TOKr;
+        dim3 grid((unsigned)(B * tps), (unsigned)((D + ER_DC - 1) / ER_DC));
+        const int rblocks = ((n + 1) / 2 + RR_THREADS / 32 - 1) / (RR_THREADS / 32);   // a run has two positions or more
+#define ANE_EB_ROWS(Tv, ESZv)                                                                                                         \
+        do {                                                                                                                          \
+            if (u16) eb_stage_rows_kernel<Tv, ESZv, uint16_t><<<grid, ER_THREADS, 0, st>>>(stage, d_embed, dx, tokens, count, vocab, D, S, tps); \
+            else eb_stage_rows_kernel<Tv, ESZv, int32_t><<<grid, ER_THREADS, 0, st>>>(stage, d_embed, dx, tokens, count, vocab, D, S, tps);      \
+            ANE_CUDA_TRY(cudaStreamWaitEvent(st, side->join, 0));                                                                     \
+            eb_reduce_runs_kernel<Tv, ESZv><<<rblocks, RR_THREADS, 0, st>>>(d_embed, stage, kb.Current(), vb.Current(), run_start, run_count, n, D); \
+        } while (0)
+        if (dtype == ANE_F32) ANE_EB_ROWS(float, 4);
+        else if (dtype == ANE_BF16) ANE_EB_ROWS(__nv_bfloat16, 2);
+        else ANE_EB_ROWS(__half, 2);
+#undef ANE_EB_ROWS
+        ANE_LAUNCH_OK(5);
+        return ANE_CUDA_OK;
+    }
+
+    // element-wise form for unaligned shapes
+    if (u16) eb_prepare_kernel<uint16_t><<<pb, 256, 0, st>>>(k0, v0, tokens, n, vocab, ctx().status);
+    else eb_prepare_kernel<int32_t><<<pb, 256, 0, st>>>(k0, v0, tokens, n, vocab, ctx().status);
     ANE_CUDA_TRY(cub::DeviceRadixSort::SortPairs(ws + off_cub, cub_bytes, kb, vb, n, 0, sort_bits(vocab), st));
     const int *keys = kb.Current();
-    const int *sorted_pos = vb.Current();
-    eb_inverse_kernel<<<pb, 256, 0, st>>>(rank_of_pos, sorted_pos, n);
+    int *rank_of_pos = aux;
+    eb_inverse_kernel<<<pb, 256, 0, st>>>(rank_of_pos, vb.Current(), n);
     if (dtype == ANE_F32) {
         constexpr int TT = 32, DC = 32;
         const int tps = (S + TT - 1) / TT;
         dim3 grid((unsigned)(B * tps), (unsigned)((D + DC - 1) / DC));
-        eb_stage_kernel<uint32_t, TT, DC><<<grid, EMB_THREADS, 0, st>>>((uint32_t *)(ws + off_stage), (const uint32_t *)dx, rank_of_pos, D, S, tps);
-        eb_reduce_kernel<float><<<n, 128, 0, st>>>(d_embed, (const float *)(ws + off_stage), keys, n, D, vocab);
+        eb_stage_kernel<uint32_t, TT, DC><<<grid, EMB_THREADS, 0, st>>>((uint32_t *)stage, (const uint32_t *)dx, rank_of_pos, D, S, tps);
+        eb_reduce_kernel<float><<<n, 128, 0, st>>>(d_embed, (const float *)stage, keys, n, D, vocab);
     } else {
         constexpr int TT = 64, DC = 64;
         const int tps = (S + TT - 1) / TT;
         dim3 grid((unsigned)(B * tps), (unsigned)((D + DC - 1) / DC));
-        eb_stage_kernel<uint16_t, TT, DC><<<grid, EMB_THREADS, 0, st>>>((uint16_t *)(ws + off_stage), (const uint16_t *)dx, rank_of_pos, D, S, tps);
-        if (dtype == ANE_BF16)
-            eb_reduce_kernel<__nv_bfloat16><<<n, 128, 0, st>>>(d_embed, (const __nv_bfloat16 *)(ws + off_stage), keys, n, D, vocab);
-        else
-            eb_reduce_kernel<__half><<<n, 128, 0, st>>>(d_embed, (const __half *)(ws + off_stage), keys, n, D, vocab);
+        eb_stage_kernel<uint16_t, TT, DC><<<grid, EMB_THREADS, 0, st>>>((uint16_t *)stage, (const uint16_t *)dx, rank_of_pos, D, S, tps);
+        if (dtype == ANE_BF16) eb_reduce_kernel<__nv_bfloat16><<<n, 128, 0, st>>>(d_embed, (const __nv_bfloat16 *)stage, keys, n, D, vocab);
+        else eb_reduce_kernel<__half><<<n, 128, 0, st>>>(d_embed, (const __half *)stage, keys, n, D, vocab);
     }
     ANE_LAUNCH_OK(4);
     return ANE_CUDA_OK;

@@ -472,7 +472,7 @@ int ane_cuda_cross_entropy_dev(void *stream, ane_idtype idtype, int B, int V, in
     if (!loss_tok) return fail(ANE_CUDA_ERR_NOMEM, "%s: no scratch", __func__);
     ane_cuda_status *status = ctx().status;
     const bool vec = (S % 4 == 0) && aligned16(dlogits) && aligned16(logits);
-    if (vec && tuning("xent_cluster", 1) && V >= 4096 && S % XC_TW == 0) {
+    if (vec && tuning("xent_cluster", 0) && V >= 4096 && S % XC_TW == 0) {
         // a cluster of 8 blocks per 16-token stripe, most of the stripe resident in shared memory
         const int threads = tuning("xent_threads", 1024) == 512 ? 512 : 1024;
         const int sps = S / XC_TW;
@@ -496,7 +496,9 @@ int ane_cuda_cross_entropy_dev(void *stream, ane_idtype idtype, int B, int V, in
             return ANE_CUDA_OK;
         }
     }
-    if (vec && tuning("xent_lg", 8) == 4) {
+    // 32-token stripes (128-byte rows) unless that leaves fewer than four blocks per SM: then 16-token stripes
+    const int lg_auto = (long long)B * ((S + 31) / 32) < 4LL * ctx().sm_count ? 4 : 8;
+    if (vec && tuning("xent_lg", lg_auto) == 4) {
         constexpr int LG = 4, VEC = 4;
         const int tps = (S + LG * VEC - 1) / (LG * VEC);
         const unsigned grid = (unsigned)(B * tps);
