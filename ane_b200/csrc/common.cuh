@@ -293,6 +293,20 @@ __device__ __forceinline__ float block_column_sum(const float *red, int tid) {
     return s;
 }
 
+// lane-wise sum over the row groups of a warp (lanes with equal lane % LG), every lane gets the total
+template <int N, int LG>
+__device__ __forceinline__ V<N> warp_rowgroup_sum(V<N> v) {
+#pragma unroll
+    for (int off = LG; off < 32; off <<= 1) {
+#pragma unroll
+        for (int i = 0; i < N / 2; i++) {
+            v.p[i].x += __shfl_xor_sync(0xffffffffu, v.p[i].x, off);
+            v.p[i].y += __shfl_xor_sync(0xffffffffu, v.p[i].y, off);
+        }
+    }
+    return v;
+}
+
 // A group of VEC consecutive elements held raw: one 16-byte word when VEC is the full vector
 // width of T, one element when VEC == 1 (the path for shapes that break 16-byte alignment).
 template <typename T, int VEC> struct Raw;

@@ -459,9 +459,28 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
             if (nv_ <= 4) ANE_BWD_RR(LGv, THv, 4);                                                                  \
             else if (nv_ <= 8) ANE_BWD_RR(LGv, THv, 8);                                                             \
         } while (0)
-        // Measured on B200: with the extra `add` stream the split statistics/apply pair is fastest, without it
-        // the two-sweep kernel.
-        const int knob_b = tuning("norm_bwd", HAS_ADD ? 5 : 0);
+        // Measured on B200 (C = 1024, bf16, 32-64 sequences): the block-pair kernel reaches 57-66 % of the copy
+        // rate, the two-sweep kernel 41-58 %, the split statistics/apply pair 42-57 %.
+        const int knob_b = tuning("norm_bwd", 8);
+        if (knob_b == 8 && (size_t)C * 66 <= 200 * 1024 && C >= 64) {      // channel halves on a pair of blocks, 64-byte rows
+            constexpr int LGs = 4;
+            const int tps_ = (S + LGs * VEC - 1) / (LGs * VEC);
+            ntiles = B * tps_;
+            const int half = (C + 1) / 2;
+            const size_t smem_st = (size_t)2 * half * LGs * 16 + (size_t)half * sizeof(float);
+            auto k_ = rmsnorm_bwd_pair_kernel<T, LGs, HAS_ADD>;
+            ANE_CUDA_TRY(cudaFuncSetAttribute(k_, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_st));
+            int per_sm = (int)((220 * 1024) / (smem_st + 5 * 1024));
+            per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+            int npairs = per_sm * ctx().sm_count / 2;
+            if (npairs > ntiles) npairs = ntiles;
+            partial = static_cast<float *>(workspace((size_t)npairs * C * sizeof(float)));
+            if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", npairs, C);
+            k_<<<(unsigned)(2 * npairs), ST_THREADS, smem_st, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags);
+            dw_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(dw, partial, npairs, C);
+            ANE_LAUNCH_OK(2);
+            return ANE_CUDA_OK;
+        }
         if ((knob_b == 6 || knob_b == 7) && (size_t)C * 132 <= 200 * 1024) {   // shared-memory-resident strips of x and dy
             const int LGs = knob_b == 6 ? 2 : 4;                               // 32- or 64-byte rows
             const int tps_ = (S + LGs * VEC - 1) / (LGs * VEC);

@@ -12,7 +12,11 @@
 #pragma once
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
 namespace ane {
+
+namespace cgx = cooperative_groups;
 
 constexpr int ST_THREADS = 256;
 
@@ -203,6 +207,141 @@ rmsnorm_bwd_st_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *
     }
     __syncthreads();
     for (int c = threadIdx.x; c < C; c += ST_THREADS) partial[(size_t)blockIdx.x * C + c] = dwacc[c];
+}
+
+// Backward on a PAIR of blocks (a thread-block cluster of two): the channels are split between the
+// two blocks, so the x and dy strips of a 64-byte-wide token tile take C/2 * 128 bytes of shared
+// memory per block (64 KiB for C = 1024: three blocks per SM) instead of C * 128.  Each block reduces
+// its half of sum(x^2) and sum(dy*x*w) per token, the halves are exchanged through distributed
+// shared memory behind one cluster barrier per tile, and both blocks finish their channels.  The
+// pairs are persistent (pair i takes tiles i, i+pairs, ...) so dw leaves as one row per pair.
+// Rows of 64 bytes, not 32: a 32-byte segment costs a 64-byte DRAM fetch.
+template <typename T, int LG, bool HAS_ADD>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ST_THREADS, 3)
+rmsnorm_bwd_pair_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *x, const float *__restrict__ w,
+                        const T *add, int C, int S, int tiles_per_seq, int ntiles, float eps, unsigned flags) {
+    constexpr int VEC = Elt<T>::VEC;
+    constexpr int R = ST_THREADS / LG;
+    constexpr int TW = LG * VEC;
+    constexpr int NW = ST_THREADS / 32;
+    static_assert(TW <= ST_THREADS, "one thread per token for the exchange");
+    extern __shared__ uint4 strip[];                 // x: [Cn][LG], dy: [Cn][LG], then dw accumulators float[Cn]
+    __shared__ __align__(16) float red[2][NW][TW];
+    __shared__ __align__(16) float tot[2][TW];
+    __shared__ float xch[2][2][TW];                  // [tile parity][sum][token]: this block's halves, read by the peer
+
+    cgx::cluster_group cluster = cgx::this_cluster();
+    const unsigned rank = cluster.block_rank();
+    const int half = (C + 1) / 2;
+    const int c0 = (int)rank * half;
+    const int Cn = (C - c0 < half ? C - c0 : half) > 0 ? (C - c0 < half ? C - c0 : half) : 0;
+    uint4 *sx = strip, *sd = strip + (size_t)half * LG;
+    float *dwacc = reinterpret_cast<float *>(strip + (size_t)2 * half * LG);
+    const float *peer_xch = cluster.map_shared_rank(&xch[0][0][0], rank ^ 1u);
+
+    const int lg = threadIdx.x % LG, rg = threadIdx.x / LG;
+    const float invd = 1.0f / (float)C;
+    const bool exact = (flags & ANE_NORM_BWD_EXACT) != 0;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+    for (int c = threadIdx.x; c < Cn; c += ST_THREADS) dwacc[c] = 0.0f;
+    __syncthreads();
+
+    int it = 0;
+    for (int tile = pair; tile < ntiles; tile += npairs, it ^= 1) {
+        const int b = tile / tiles_per_seq;
+        const int t = (tile % tiles_per_seq) * TW + lg * VEC;
+        const bool active = t < S;
+        const size_t base = ((size_t)b * C + c0) * S + t;
+
+        if (active)
+            for (int c = rg; c < Cn; c += R) {
+                cp_async16(&sx[c * LG + lg], x + base + (size_t)c * S);
+                cp_async16(&sd[c * LG + lg], dy + base + (size_t)c * S);
+            }
+        cp_async_commit();
+        cp_async_wait_all();             // each thread reads back only what it copied itself
+
+        V<VEC> ss = V<VEC>::splat(0.0f), dot = V<VEC>::splat(0.0f);
+        if (active) {
+#pragma unroll 4
+            for (int c = rg; c < Cn; c += R) {
+                Raw<T, VEC> rx, rd;
+                rx.v = sx[c * LG + lg];
+                rd.v = sd[c * LG + lg];
+                const V<VEC> xv = rx.get(), dv = rd.get();
+                ss = vfma(xv, xv, ss);
+                dot = vfma_s(vmul(dv, xv), __ldg(w + c0 + c), dot);                // stories_cpu_ops.h:35-38
+            }
+        }
+        ss = warp_rowgroup_sum<VEC, LG>(ss);
+        dot = warp_rowgroup_sum<VEC, LG>(dot);
+        if ((threadIdx.x & 31) < LG) {
+            lanes_to_smem<VEC>(&red[0][threadIdx.x >> 5][lg * VEC], ss);
+            lanes_to_smem<VEC>(&red[1][threadIdx.x >> 5][lg * VEC], dot);
+        }
+        __syncthreads();
+        if (threadIdx.x < TW) {          // this block's halves, warps in fixed order
+            float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+            for (int q = 0; q < NW; q++) { s0 += red[0][q][threadIdx.x]; s1 += red[1][q][threadIdx.x]; }
+            xch[it][0][threadIdx.x] = s0;
+            xch[it][1][threadIdx.x] = s1;
+        }
+        cluster.sync();                  // both halves published (also a block barrier)
+        if (threadIdx.x < TW) {
+            const float m0 = xch[it][0][threadIdx.x], m1 = xch[it][1][threadIdx.x];
+            const float p0 = peer_xch[(it * 2 + 0) * TW + threadIdx.x], p1 = peer_xch[(it * 2 + 1) * TW + threadIdx.x];
+            const float s0 = rank == 0 ? m0 + p0 : p0 + m0;        // lower channels first in both blocks: same bits
+            const float s1 = rank == 0 ? m1 + p1 : p1 + m1;
+            const float r1 = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s0, invd), eps));
+            float r2 = r1 * r1;
+            r2 = r2 * invd;
+            tot[0][threadIdx.x] = r1;
+            tot[1][threadIdx.x] = s1 * r2;                                         // stories_cpu_ops.h:39-41
+        }
+        __syncthreads();
+        const V<VEC> rr = lanes_from_smem<VEC>(&tot[0][lg * VEC]), coef = lanes_from_smem<VEC>(&tot[1][lg * VEC]);
+        constexpr int U = 4;
+        for (int cb = 0; cb < Cn; cb += R * U) {      // uniform trip count: the shuffles below need every lane
+            Raw<T, VEC> ra[U];
+            if (HAS_ADD) {
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int c = cb + u * R + rg;
+                    if (active && c < Cn) ra[u].load_stream(add + base + (size_t)c * S);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int c = cb + u * R + rg;
+                float dwp = 0.0f;
+                if (active && c < Cn) {
+                    Raw<T, VEC> rx, rd;
+                    rx.v = sx[c * LG + lg];
+                    rd.v = sd[c * LG + lg];
+                    const V<VEC> xv = rx.get(), dv = rd.get();
+                    const float wc = __ldg(w + c0 + c);
+                    V<VEC> o;
+                    if (exact) o = vmul(vsub(vscale(dv, wc), vmul(xv, coef)), rr);
+                    else o = vscale(vmul(vsub(dv, vmul(xv, coef)), rr), wc);      // stories_cpu_ops.h:43-46
+                    dwp = vmul(vmul(dv, xv), rr).hsum();                           // stories_cpu_ops.h:47-50
+                    if (HAS_ADD) o = vadd(o, ra[u].get());                         // train.m:590,721
+                    Raw<T, VEC> ro;
+                    ro.put(o);
+                    ro.store_stream(dx + base + (size_t)c * S);
+                }
+#pragma unroll
+                for (int off = LG / 2; off > 0; off >>= 1) dwp += __shfl_xor_sync(0xffffffffu, dwp, off);
+                if (lg == 0 && c < Cn) dwacc[c] += dwp;  // row group rg is the only writer of channel c
+            }
+        }
+        // the strips are rewritten by this thread's own copies only; red/tot/xch[it] are next written
+        // after the following tile's barriers, which every thread of the pair reaches after this point
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < Cn; c += ST_THREADS) partial[(size_t)pair * C + c0 + c] = dwacc[c];
+    cluster.sync();                      // the peer may still be reading xch
 }
 
 }  // namespace ane

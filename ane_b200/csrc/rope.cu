@@ -363,6 +363,29 @@ qk_bwd_kernel(T *__restrict__ dx, float *__restrict__ partial, const T *__restri
 // barrier that follows everybody's read of it (the barrier the reduction needs anyway).
 // Waits on the copy barriers are bounded: on a give-up the block records it in the status words
 // and returns.
+struct ItemMap {
+    int heads, grid, bid, n_full, lo, n_items, first_left_tile;
+    __device__ ItemMap(int ntiles, int heads_, int grid_, int bid_) : heads(heads_), grid(grid_), bid(bid_) {
+        const int rounds = ntiles / grid;
+        n_full = rounds * heads;
+        first_left_tile = rounds * grid;
+        const int left = (ntiles - first_left_tile) * heads;            // items of the partial round
+        const int per = (left + grid - 1) / grid;
+        lo = bid * per;
+        int hi = lo + per < left ? lo + per : left;
+        n_items = n_full + (hi > lo ? hi - lo : 0);
+    }
+    // (tile, head) of item 0, then of item j_next given those of item j_next - 1: no division per item
+    __device__ __forceinline__ void first(int &tl, int &h) const {
+        if (n_full > 0) { tl = bid; h = 0; }
+        else { tl = first_left_tile + lo / heads; h = lo % heads; }
+    }
+    __device__ __forceinline__ void next(int j_next, int &tl, int &h) const {
+        if (j_next == n_full) { tl = first_left_tile + lo / heads; h = lo % heads; return; }
+        if (++h == heads) { h = 0; tl += j_next < n_full ? grid : 1; }
+    }
+};
+
 template <typename T, int RPT, bool ROPE, int NST>
 __global__ void __launch_bounds__(QK_THREADS)
 qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap, const float *__restrict__ w, int heads,
@@ -382,8 +405,12 @@ qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap,
     const int lg = threadIdx.x % QK_LG, rg = threadIdx.x / QK_LG;
     const float invd = 1.0f / (float)HD;
     const size_t hstep = (size_t)HD * S;
-    const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int n_items = my_tiles * heads;
+    // Work items are (token tile, head) pairs.  Full rounds: block i takes tile r*grid + i with all its
+    // heads, so the blocks running at one time sit on neighbouring token tiles of the same rows (DRAM page
+    // locality).  The tiles left after the last full round are shared out head by head, so no block idles
+    // for a whole tile.
+    const ItemMap im(ntiles, heads, (int)gridDim.x, (int)blockIdx.x);
+    const int n_items = im.n_items;
 
     if (threadIdx.x == 0) {
 #pragma unroll
@@ -393,11 +420,15 @@ qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap,
     }
     __syncthreads();
 
+    int ptl, ph, ctl, ch;                // producer (thread 0) and consumer positions
+    im.first(ctl, ch);
+    im.first(ptl, ph);
     auto issue = [&](int j) {
-        const int tl = (int)blockIdx.x + (j / heads) * (int)gridDim.x;
+        const int tl = ptl;
         const int s = j % NST;
         mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-        tma_load_3d(stages + (size_t)s * STAGE_BYTES, &xmap, (tl % tiles_per_seq) * TW, (j % heads) * HD, tl / tiles_per_seq, &full[s]);
+        tma_load_3d(stages + (size_t)s * STAGE_BYTES, &xmap, (tl % tiles_per_seq) * TW, ph * HD, tl / tiles_per_seq, &full[s]);
+        im.next(j + 1, ptl, ph);
     };
     if (threadIdx.x == 0)
         for (int j = 0; j < NST && j < n_items; j++) issue(j);
@@ -408,13 +439,13 @@ qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap,
     V<VEC> cs[RPT / 2], sn[RPT / 2];
 
     for (int j = 0; j < n_items; j++) {
-        const int tl = (int)blockIdx.x + (j / heads) * (int)gridDim.x;
-        const int h = j % heads;
+        const int tl = ctl, h = ch;
+        im.next(j + 1, ctl, ch);
         const int b = tl / tiles_per_seq;
         const int t = (tl % tiles_per_seq) * TW + lg * VEC;
         const bool active = t < S;
         const int s = j % NST, buf = j & 1;
-        if (ROPE && h == 0 && active) {
+        if (ROPE && (h == 0 || j == 0 || j == im.n_full) && active) {
 #pragma unroll
             for (int p = 0; p < RPT / 2; p++) {
                 cs[p] = table_lanes<VEC>(cosT + (size_t)(rg * (RPT / 2) + p) * S + t);
@@ -469,7 +500,7 @@ qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap,
 }
 
 template <typename T, int RPT, bool ROPE, int NST>
-__global__ void __launch_bounds__(QK_THREADS)
+__global__ void __launch_bounds__(QK_THREADS, 2)
 qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_constant__ CUtensorMap dymap,
                   const __grid_constant__ CUtensorMap xmap, const float *__restrict__ w, int heads, int S, int tiles_per_seq,
                   int ntiles, float eps, unsigned flags, ane_cuda_status *status,
@@ -482,7 +513,8 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
     extern __shared__ unsigned char stages_raw[];
     unsigned char *stages = stages_raw + ((128u - (smem_u32(stages_raw) & 127u)) & 127u);   // 128-byte aligned copy targets
     __shared__ __align__(8) uint64_t full[NST];
-    __shared__ __align__(16) float red[2][2][QK_R][TW];
+    constexpr int NWARP = QK_THREADS / 32;
+    __shared__ __align__(16) float red[2][2][NWARP][TW];       // per-warp sums (row groups of a warp are added by shuffles)
     __shared__ __align__(16) float tot[2][2][TW];
     __shared__ int give_up;
 
@@ -490,8 +522,12 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
     const float invd = 1.0f / (float)HD;
     const bool exact = (flags & ANE_NORM_BWD_EXACT) != 0;
     const size_t hstep = (size_t)HD * S;
-    const int my_tiles = (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int n_items = my_tiles * heads;
+    // Work items are (token tile, head) pairs.  Full rounds: block i takes tile r*grid + i with all its
+    // heads, so the blocks running at one time sit on neighbouring token tiles of the same rows (DRAM page
+    // locality).  The tiles left after the last full round are shared out head by head, so no block idles
+    // for a whole tile.
+    const ItemMap im(ntiles, heads, (int)gridDim.x, (int)blockIdx.x);
+    const int n_items = im.n_items;
 
     if (threadIdx.x == 0) {
 #pragma unroll
@@ -501,13 +537,17 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
     }
     __syncthreads();
 
+    int ptl, ph, ctl, ch;                // producer (thread 0) and consumer positions
+    im.first(ctl, ch);
+    im.first(ptl, ph);
     auto issue = [&](int j) {
-        const int tl = (int)blockIdx.x + (j / heads) * (int)gridDim.x;
+        const int tl = ptl;
         const int s = j % NST;
         unsigned char *dst = stages + (size_t)s * STAGE_BYTES;
         mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-        tma_load_3d(dst, &xmap, (tl % tiles_per_seq) * TW, (j % heads) * HD, tl / tiles_per_seq, &full[s]);
-        tma_load_3d(dst + TILE_BYTES, &dymap, (tl % tiles_per_seq) * TW, (j % heads) * HD, tl / tiles_per_seq, &full[s]);
+        tma_load_3d(dst, &xmap, (tl % tiles_per_seq) * TW, ph * HD, tl / tiles_per_seq, &full[s]);
+        tma_load_3d(dst + TILE_BYTES, &dymap, (tl % tiles_per_seq) * TW, ph * HD, tl / tiles_per_seq, &full[s]);
+        im.next(j + 1, ptl, ph);
     };
     if (threadIdx.x == 0)
         for (int j = 0; j < NST && j < n_items; j++) issue(j);
@@ -518,13 +558,13 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
     V<VEC> cs[RPT / 2], sn[RPT / 2];
 
     for (int j = 0; j < n_items; j++) {
-        const int tl = (int)blockIdx.x + (j / heads) * (int)gridDim.x;
-        const int h = j % heads;
+        const int tl = ctl, h = ch;
+        im.next(j + 1, ctl, ch);
         const int b = tl / tiles_per_seq;
         const int t = (tl % tiles_per_seq) * TW + lg * VEC;
         const bool active = t < S;
         const int s = j % NST, buf = j & 1;
-        if (ROPE && h == 0 && active) {
+        if (ROPE && (h == 0 || j == 0 || j == im.n_full) && active) {
 #pragma unroll
             for (int p = 0; p < RPT / 2; p++) {
                 cs[p] = table_lanes<VEC>(cosT + (size_t)(rg * (RPT / 2) + p) * S + t);
@@ -534,40 +574,51 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
         if (!mbar_wait_bounded(&full[s], (uint32_t)(j / NST) & 1u)) give_up = 1;
         const T *xt = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES);
         const T *dt = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES + TILE_BYTES);
-        V<VEC> xv[RPT], g[RPT];
+        // Sweep 1 keeps nothing but the two sums; sweep 2 reads the tile again from shared memory and
+        // redoes the inverse rotation (a few packed operations) -- the register file then allows two
+        // blocks per SM.
+        auto load_pair = [&](int p, V<VEC> &x0, V<VEC> &x1, V<VEC> &g0, V<VEC> &g1) {
+            Raw<T, VEC> a0, a1, c0, c1;
+            a0.load(xt + (rg * RPT + 2 * p) * TW + lg * VEC);
+            a1.load(xt + (rg * RPT + 2 * p + 1) * TW + lg * VEC);
+            c0.load(dt + (rg * RPT + 2 * p) * TW + lg * VEC);
+            c1.load(dt + (rg * RPT + 2 * p + 1) * TW + lg * VEC);
+            x0 = a0.get();
+            x1 = a1.get();
+            g0 = c0.get();
+            g1 = c1.get();
+            if (ROPE) {       // g = rope^-1(dy): (a cos + b sin, -a sin + b cos)   cpu_ops.h:178-181
+                const V<VEC> a = g0, bb = g1;
+                g0 = vfma(a, cs[p], vmul(bb, sn[p]));
+                g1 = vsub(vmul(bb, cs[p]), vmul(a, sn[p]));
+            }
+        };
         V<VEC> ss = V<VEC>::splat(0.0f), dot = V<VEC>::splat(0.0f);
 #pragma unroll
-        for (int k = 0; k < RPT; k++) {
-            Raw<T, VEC> a, c;
-            a.load(xt + (rg * RPT + k) * TW + lg * VEC);
-            c.load(dt + (rg * RPT + k) * TW + lg * VEC);
-            xv[k] = a.get();
-            g[k] = c.get();
-        }
-#pragma unroll
         for (int p = 0; p < RPT / 2; p++) {
-            if (ROPE) {       // g = rope^-1(dy): (a cos + b sin, -a sin + b cos)   cpu_ops.h:178-181
-                const V<VEC> a = g[2 * p], bb = g[2 * p + 1];
-                g[2 * p] = vfma(a, cs[p], vmul(bb, sn[p]));
-                g[2 * p + 1] = vsub(vmul(bb, cs[p]), vmul(a, sn[p]));
-            }
-            ss = vfma(xv[2 * p], xv[2 * p], ss);
-            ss = vfma(xv[2 * p + 1], xv[2 * p + 1], ss);
-            dot = vfma_s(vmul(g[2 * p], xv[2 * p]), wc[2 * p], dot);
-            dot = vfma_s(vmul(g[2 * p + 1], xv[2 * p + 1]), wc[2 * p + 1], dot);
+            V<VEC> x0, x1, g0, g1;
+            load_pair(p, x0, x1, g0, g1);
+            ss = vfma(x0, x0, ss);
+            ss = vfma(x1, x1, ss);
+            dot = vfma_s(vmul(g0, x0), wc[2 * p], dot);
+            dot = vfma_s(vmul(g1, x1), wc[2 * p + 1], dot);
         }
-        lanes_to_smem<VEC>(&red[buf][0][rg][lg * VEC], ss);
-        lanes_to_smem<VEC>(&red[buf][1][rg][lg * VEC], dot);
-        __syncthreads();                                   // stage s is in registers everywhere
+        ss = warp_rowgroup_sum<VEC, QK_LG>(ss);
+        dot = warp_rowgroup_sum<VEC, QK_LG>(dot);
+        if ((threadIdx.x & 31) < QK_LG) {
+            lanes_to_smem<VEC>(&red[buf][0][threadIdx.x >> 5][lg * VEC], ss);
+            lanes_to_smem<VEC>(&red[buf][1][threadIdx.x >> 5][lg * VEC], dot);
+        }
+        __syncthreads();                                   // every thread has left sweep 2 of item j-1
         if (give_up) {
             if (threadIdx.x == 0) atomicAdd(&status->wait_giveups, 1);
             break;
         }
-        if (threadIdx.x == 0 && j + NST < n_items) { fence_proxy_async(); issue(j + NST); }
+        if (threadIdx.x == 0 && j >= 1 && j - 1 + NST < n_items) { fence_proxy_async(); issue(j - 1 + NST); }   // refill the stage of item j-1
         {
             constexpr int P = QK_THREADS / TW;
-            const float s0 = block_column_sum<QK_R, TW, QK_THREADS>(&red[buf][0][0][0], threadIdx.x);
-            const float s1 = block_column_sum<QK_R, TW, QK_THREADS>(&red[buf][1][0][0], threadIdx.x);
+            const float s0 = block_column_sum<NWARP, TW, QK_THREADS>(&red[buf][0][0][0], threadIdx.x);
+            const float s1 = block_column_sum<NWARP, TW, QK_THREADS>(&red[buf][1][0][0], threadIdx.x);
             if (threadIdx.x % P == 0) {
                 const float r1 = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s0, invd), eps));
                 float r2 = r1 * r1;
@@ -582,14 +633,20 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
             const V<VEC> coef = lanes_from_smem<VEC>(&tot[buf][1][lg * VEC]);
             const size_t o = (size_t)b * heads * hstep + h * hstep + (size_t)(rg * RPT) * S + t;
 #pragma unroll
-            for (int k = 0; k < RPT; k++) {
-                V<VEC> ov;
-                if (exact) ov = vmul(vsub(vscale(g[k], wc[k]), vmul(xv[k], coef)), rr);
-                else ov = vscale(vmul(vsub(g[k], vmul(xv[k], coef)), rr), wc[k]);
-                dwacc[k] += vmul(vmul(g[k], xv[k]), rr).hsum();
-                Raw<T, VEC> ro;
-                ro.put(ov);
-                ro.store_stream(dx + o + (size_t)k * S);
+            for (int p = 0; p < RPT / 2; p++) {
+                V<VEC> xv[2], g[2];
+                load_pair(p, xv[0], xv[1], g[0], g[1]);
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    const int k = 2 * p + q;
+                    V<VEC> ov;
+                    if (exact) ov = vmul(vsub(vscale(g[q], wc[k]), vmul(xv[q], coef)), rr);
+                    else ov = vscale(vmul(vsub(g[q], vmul(xv[q], coef)), rr), wc[k]);
+                    dwacc[k] += vmul(vmul(g[q], xv[q]), rr).hsum();
+                    Raw<T, VEC> ro;
+                    ro.put(ov);
+                    ro.store_stream(dx + o + (size_t)k * S);
+                }
             }
         }
     }

@@ -7,7 +7,7 @@ CUDA-event time of a launch.
     python -m ane_b200.opbench --op rmsnorm --batch 64 --iters 3 --tuning norm_fwd=0
 
 Every operator rotates through several input/output sets so that consecutive launches do not find
-their operands in the 126 MB L2 (each set is 64 MiB or more at the default batch).
+their operands in the 126 MB L2 (each set is 128 MiB or more at the default batch of 32 sequences).
 """
 from __future__ import annotations
 
@@ -73,9 +73,9 @@ def _cases(torch, ops, device, M):
         (wq, dwq), q, dq, qo = head_w(), mk(QD), mk(QD), mk(QD)
         return (lambda i: ops.rope_qknorm_bwd(dq[i % NSET], q[i % NSET], wq, dwq, HD, out=qo[i % NSET])), 3 * QD * T * 2, 12
 
-    # embedding: 2 x batch sequences of 2048 tokens, table [151936, 1024] bf16
+    # embedding: batch sequences of 2048 tokens, table [151936, 1024] bf16
     def _embed_common():
-        Be = 2 * M
+        Be = M
         table = (0.02 * torch.randn(VOCAB, D, device=device)).to(bf)
         tok = torch.randint(0, VOCAB, (Be, S), device=device, dtype=torch.int32)
         xe = [torch.empty((Be, D, S), device=device, dtype=bf) for _ in range(2)]
@@ -94,7 +94,7 @@ def _cases(torch, ops, device, M):
         uniq = int(torch.unique(tok).numel())
         return (lambda i: ops.embed_backward(dE, xe[i % 2], tok)), Be * S * 4 + D * Be * S * 2 + 2 * uniq * D * 4, 6
 
-    # cross-entropy: fp32 logits [batch/4][151936][2048] (5 GB at the default batch), written in place
+    # cross-entropy: fp32 logits [batch/4][151936][2048] (10 GB at the default batch), written in place
     def cross_entropy():
         Bc = max(1, M // 4)
         logits = torch.randn((Bc, VOCAB, S), device=device)
@@ -109,7 +109,7 @@ def _cases(torch, ops, device, M):
         return (lambda i: ops.cross_entropy(logits, tg, dlogits=logits)), 2 * Vc * M * S * 4, 3
 
     def _flat():
-        n = 4 * M << 20
+        n = 2 * M << 20
         wv, gv, mv, vv = (torch.randn(n, device=device) * 0.01 for _ in range(4))
         vv.abs_()
         return n, wv, gv, mv, vv
@@ -152,7 +152,7 @@ def time_op(torch, builder, peak_gbs, iters=None, warmup=3):
             "frac_8TBs": round(gbs / NOMINAL_HBM_GBS, 3), "bytes": nbytes}
 
 
-def per_op_table(torch, ops, device, peak_gbs, batch=16, only=None, iters=None, warmup=3):
+def per_op_table(torch, ops, device, peak_gbs, batch=32, only=None, iters=None, warmup=3):
     """Achieved GB/s per operator on benchmark-sized bf16 tensors (algorithmic bytes / time)."""
     res = {}
     for name, builder in _cases(torch, ops, device, batch).items():
@@ -166,7 +166,7 @@ def per_op_table(torch, ops, device, peak_gbs, batch=16, only=None, iters=None, 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--op", action="append", help="operator name (repeatable); default: all")
-    ap.add_argument("--batch", type=int, default=16, help="sequences of 2048 tokens per launch")
+    ap.add_argument("--batch", type=int, default=32, help="sequences of 2048 tokens per launch")
     ap.add_argument("--iters", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--peak-gbs", type=float, default=None, help="roofline denominator (default: MEASURED_PEAKS.json)")

@@ -46,7 +46,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--micro-batch", type=int, default=16, help="sequences per micro-batch and GPU")
+    ap.add_argument("--micro-batch", type=int, default=64, help="sequences per micro-batch and GPU")
     ap.add_argument("--seqs", type=int, default=TOTAL_SEQS, help="sequences per step over all GPUs")
     ap.add_argument("--layers", type=int, default=28)
     ap.add_argument("--no-ops", action="store_true", help="skip the per-operator table")
@@ -241,8 +241,8 @@ def workload_config(args, world):
         "sequences": args.seqs, "seq_len": 2048, "layers": args.layers, "micro_batch_per_gpu": args.micro_batch,
         "parallelism": f"dp{world} (sequences sharded, ZeRO-1 Adam)",
         "launch": "host launches" if getattr(args, "no_graph", False) else "CUDA graph replay per micro-batch (first micro-batch of each step eager)",
-        "l2_policy": "inputs larger than L2: every operator reads per-layer buffers (64-192 MiB each) last touched "
-                     "hundreds of MiB of traffic earlier",
+        "l2_policy": f"inputs larger than L2: every operator reads per-layer buffers ({4 * min(args.micro_batch, max(1, args.seqs // world))}-"
+                     f"{12 * min(args.micro_batch, max(1, args.seqs // world))} MiB each) last touched GBs of traffic earlier",
     }
 
 
@@ -426,7 +426,7 @@ def run_ours(args):
     torch.cuda.empty_cache()
     if not args.no_ops and rank == 0 and world == 1:
         from ane_b200.opbench import per_op_table
-        line["ops"] = per_op_table(torch, ops, device, peak_gbs, batch=min(16, args.micro_batch))
+        line["ops"] = per_op_table(torch, ops, device, peak_gbs, batch=32)
     if world > 1:
         dist.barrier()
 

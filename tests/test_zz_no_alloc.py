@@ -56,8 +56,17 @@ def test_static_scratch_matches_regular_entry_point(dtype, with_add):
     assert _call(L, L.ane_cuda_rmsnorm_bwd_dev, dt, B, C, S, dx_ref, dw_ref, dy, x, w, add) == lib.OK
     torch.cuda.synchronize()
 
+    def same_dx(a, b):
+        # the two entry points may sum the per-token statistics in different orders: fp32 within 1e-5,
+        # 16-bit within one rounding step and 2e-3 in the L2 norm (the tolerances of test_gpu_parity)
+        a, b = a.float(), b.float()
+        scale = float(b.abs().max())
+        if dtype == "float32":
+            return float((a - b).abs().max()) <= 1e-5 * scale
+        return float((a - b).abs().max()) <= 2.0 ** -8 * scale and float((a - b).norm()) <= 2e-3 * float(b.norm())
+
     for dx, dw in outs:
-        assert torch.equal(dx, dx_ref)                                        # dx does not depend on the split
+        assert same_dx(dx, dx_ref)
         err = float((dw - dw_ref).abs().max()) / float(dw_ref.abs().max())
         assert err <= (1e-5 if dtype == "float32" else 1e-4)                  # the tolerances of test_gpu_parity
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
@@ -71,7 +80,7 @@ def test_static_scratch_matches_regular_entry_point(dtype, with_add):
     dxr, dwr = torch.empty_like(dxs), torch.zeros(C, device="cuda")
     assert _call(L, L.ane_cuda_rmsnorm_bwd_dev, dt, Bs, C, Ss, dxr, dwr, dys, xs, w, None) == lib.OK
     torch.cuda.synchronize()
-    assert torch.equal(dxs, dxr)
+    assert same_dx(dxs, dxr)
     assert float((dws - dwr).abs().max()) <= 1e-4 * float(dwr.abs().max())
 
 
