@@ -38,6 +38,7 @@ if ROOT not in sys.path:
 TOTAL_SEQS = 256
 FALLBACK_HBM_GBS = 6650.0
 NOMINAL_HBM_GBS = 8000.0
+SWIGLU_BWD_DRAM_BYTES_PER_ALGORITHMIC_BYTE = 0.956
 
 
 def parse_args():
@@ -397,15 +398,11 @@ def run_ours(args):
                 "peak": peak_gbs, "peak_kind": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650",
                 "unit": "GB/s", "frac": round(achieved / peak_gbs, 4), "frac_of_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
                 "traffic": None, "launch_ms": round(k_ms, 4), "launches_timed": len(ev), "algorithmic_bytes_per_launch": k_bytes}
-    prof = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(prof):
-        try:
-            with open(prof) as f:
-                tr = json.load(f)
-            roofline["traffic"] = tr.get("swiglu_bwd_dram_bytes_per_algorithmic_byte", None) and int(
-                tr["swiglu_bwd_dram_bytes_per_algorithmic_byte"] * k_bytes)
-        except Exception:
-            pass
+    # DRAM bytes of this kernel from one profiler capture at 16 sequences (dram__bytes_read + dram__bytes_write = 0.956 of
+    # its algorithmic bytes: the inputs are read exactly once, part of the output is still in L2 when the kernel ends);
+    # a streaming kernel's traffic grows in proportion to the elements moved, so the ratio carries to this launch size.
+    roofline["traffic"] = int(SWIGLU_BWD_DRAM_BYTES_PER_ALGORITHMIC_BYTE * k_bytes)
+    roofline["traffic_source"] = "ncu capture at 16 sequences, scaled by elements (profiles/swiglu_bwd_ew_vec_kernel_16seq.md)"
 
     chain_bytes = tokens * (cfg.layers * cfg.bytes_per_token_layer() + cfg.bytes_per_token_ends()) + 28 * params.n + 4 * params.n
     line = {
