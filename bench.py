@@ -241,7 +241,7 @@ def workload_config(args, world):
                     "head_dim 128, bf16 activations) + Adam on 596M fp32 params",
         "sequences": args.seqs, "seq_len": 2048, "layers": args.layers, "micro_batch_per_gpu": args.micro_batch,
         "parallelism": f"dp{world} (sequences sharded, ZeRO-1 Adam)",
-        "launch": "host launches" if getattr(args, "no_graph", False) else "CUDA graph replay per micro-batch (first micro-batch of each step eager)",
+        "launch": "host launches" if getattr(args, "no_graph", False) else "CUDA graph replay per micro-batch (the first micro-batch of the first timed step runs eagerly, with events around the dominant kernel)",
         "l2_policy": f"inputs larger than L2: every operator reads per-layer buffers ({4 * min(args.micro_batch, max(1, args.seqs // world))}-"
                      f"{12 * min(args.micro_batch, max(1, args.seqs // world))} MiB each) last touched GBs of traffic earlier",
     }
@@ -374,8 +374,11 @@ def run_ours(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    for _ in range(args.steps):
+    timed = chain.timed_op
+    for i in range(args.steps):
+        chain.timed_op = timed if i == 0 else None       # events around the dominant kernel in the first timed step only
         step()
+    chain.timed_op = timed
     e1.record()
     barrier()
     launches = lib.launch_count() + graph_launches[0]     # graph replays do not pass through the host-side counter
