@@ -173,3 +173,69 @@ def clip_factor(normsq, clip, out=None):
     out = torch.empty(1, dtype=torch.float32, device=normsq.device) if out is None else out
     _l.check(_l.load().ane_cuda_clip_factor_dev(_stream(), _p(normsq), normsq.numel(), clip, _p(out)))
     return out
+
+
+# ------------------------------------------------------------------ layout helpers
+def gqa_tile(x, kv_heads, ratio, out=None):
+    """[B][kv_heads*hd][S] -> [B][kv_heads*ratio*hd][S] (training_dynamic/io.h gqa_tile_kv)."""
+    B, Cn, S = _bcs(x)
+    hd = Cn // kv_heads
+    out = torch.empty((B, Cn * ratio, S), dtype=x.dtype, device=x.device) if out is None else out
+    _l.check(_l.load().ane_cuda_gqa_tile_dev(_stream(), _dt(x), B, kv_heads, ratio, hd, S, _p(out), _p(x)))
+    return out
+
+
+def gqa_reduce(x, kv_heads, ratio, out=None):
+    """[B][kv_heads*ratio*hd][S] -> [B][kv_heads*hd][S], heads summed in order (io.h gqa_reduce_kv)."""
+    B, Cn, S = _bcs(x)
+    hd = Cn // (kv_heads * ratio)
+    out = torch.empty((B, kv_heads * hd, S), dtype=x.dtype, device=x.device) if out is None else out
+    _l.check(_l.load().ane_cuda_gqa_reduce_dev(_stream(), _dt(x), B, kv_heads, ratio, hd, S, _p(out), _p(x)))
+    return out
+
+
+def convert(x, dtype, out=None):
+    """Element-wise cast between float32 / float16 / bfloat16 (stories_io.h cvt_f32_f16, cvt_f16_f32)."""
+    out = torch.empty(x.shape, dtype=dtype, device=x.device) if out is None else out
+    _l.check(_l.load().ane_cuda_convert_dev(_stream(), _dt(out), _dt(x), x.numel(), _p(out), _p(x)))
+    return out
+
+
+def pack_dyn(act, W, dtype=torch.float16, out=None):
+    """act [ic][seq] fp32, W [ic][oc] fp32 -> [ic][seq+oc] 16-bit (io.h io_write_dyn)."""
+    ic, seq = act.shape
+    oc = W.shape[1]
+    out = torch.empty((ic, seq + oc), dtype=dtype, device=act.device) if out is None else out
+    _l.check(_l.load().ane_cuda_pack_dyn_dev(_stream(), _dt(out), ic, seq, oc, _p(out), _p(act), _p(W)))
+    return out
+
+
+def vocab_map_build(tokens, full_vocab):
+    """-> (full_to_compact [V] int32, compact_to_full [V] int32 (first compact_vocab entries valid),
+    compact_vocab [1] int32), all on the device (cpu_ops.h vocab_map_build)."""
+    dev = tokens.device
+    f2c = torch.empty(full_vocab, dtype=torch.int32, device=dev)
+    c2f = torch.empty(full_vocab, dtype=torch.int32, device=dev)
+    cnt = torch.zeros(1, dtype=torch.int32, device=dev)
+    _l.check(_l.load().ane_cuda_vocab_map_build_dev(_stream(), _ID[tokens.dtype], tokens.numel(), _p(tokens), full_vocab,
+                                                   _p(f2c), _p(c2f), _p(cnt)))
+    return f2c, c2f, cnt
+
+
+def vocab_compact_embed(full_embed, c2f, cnt, compact_max, out=None):
+    V, dim = full_embed.shape
+    out = torch.empty((compact_max, dim), dtype=torch.float32, device=full_embed.device) if out is None else out
+    _l.check(_l.load().ane_cuda_vocab_compact_embed_dev(_stream(), _p(out), _p(full_embed), _p(c2f), _p(cnt), compact_max, dim, V))
+    return out
+
+
+def vocab_scatter_grads(full_gembed, compact_gembed, c2f, cnt, compact_max):
+    V, dim = full_gembed.shape
+    _l.check(_l.load().ane_cuda_vocab_scatter_grads_dev(_stream(), _p(full_gembed), _p(compact_gembed), _p(c2f), _p(cnt), compact_max, dim, V))
+    return full_gembed
+
+
+def vocab_update_full(full_embed, compact_embed, c2f, cnt, compact_max):
+    V, dim = full_embed.shape
+    _l.check(_l.load().ane_cuda_vocab_update_full_dev(_stream(), _p(full_embed), _p(compact_embed), _p(c2f), _p(cnt), compact_max, dim, V))
+    return full_embed

@@ -107,6 +107,15 @@ PROTOTYPES = {
     "ane_cuda_adam_dev": (_i, [_vp, _sz, _vp, _vp, _vp, _vp, _i, _f, _f, _f, _f, _f, _f, _vp, _u]),
     "ane_cuda_grad_norm_sq_dev": (_i, [_vp, _sz, _vp, _f, _vp]),
     "ane_cuda_clip_factor_dev": (_i, [_vp, _vp, _i, _f, _vp]),
+    # layout helpers
+    "ane_cuda_gqa_tile_dev": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "ane_cuda_gqa_reduce_dev": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "ane_cuda_convert_dev": (_i, [_vp, _i, _i, _sz, _vp, _vp]),
+    "ane_cuda_pack_dyn_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "ane_cuda_vocab_map_build_dev": (_i, [_vp, _i, _sz, _vp, _i, _vp, _vp, _vp]),
+    "ane_cuda_vocab_compact_embed_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
+    "ane_cuda_vocab_scatter_grads_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
+    "ane_cuda_vocab_update_full_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
 }
 
 _lib = None

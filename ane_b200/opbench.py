@@ -124,7 +124,33 @@ def _cases(torch, ops, device, M):
         nsq = torch.zeros(1, device=device)
         return (lambda i: ops.grad_norm_sq(gv, 1.0, out=nsq)), 4 * n, 12
 
+    # layout helpers beside the operators (GQA 16/8 heads of 128; fp32 -> bf16 cast; compact table of a quarter of the ids)
+    def gqa_tile():
+        k = mk(KVD)
+        o = [torch.empty((M, QD, S), dtype=bf, device=device) for _ in range(NSET)]
+        return (lambda i: ops.gqa_tile(k[i % NSET], 8, 2, out=o[i % NSET])), (KVD + QD) * T * 2, 12
+
+    def gqa_reduce():
+        q = mk(QD)
+        o = [torch.empty((M, KVD, S), dtype=bf, device=device) for _ in range(NSET)]
+        return (lambda i: ops.gqa_reduce(q[i % NSET], 8, 2, out=o[i % NSET])), (KVD + QD) * T * 2, 12
+
+    def convert_f32_bf16():
+        x = mk(D, dtype=torch.float32)
+        o = [torch.empty((M, D, S), dtype=bf, device=device) for _ in range(NSET)]
+        return (lambda i: ops.convert(x[i % NSET], bf, out=o[i % NSET])), 6 * D * T, 12
+
+    def vocab_compact_embed():
+        Vc = VOCAB // 4
+        full = torch.randn(VOCAB, D, device=device)
+        tok = (torch.randperm(VOCAB, device=device)[:Vc]).to(torch.int32).repeat(2)
+        f2c, c2f, cnt = ops.vocab_map_build(tok, VOCAB)
+        out = [torch.empty((Vc, D), device=device) for _ in range(2)]
+        return (lambda i: ops.vocab_compact_embed(full, c2f, cnt, Vc, out=out[i % 2])), 2 * Vc * D * 4 + Vc * 4, 12
+
     return {
+        "gqa_tile": gqa_tile, "gqa_reduce": gqa_reduce, "convert_f32_bf16": convert_f32_bf16,
+        "vocab_compact_embed": vocab_compact_embed,
         "rmsnorm": rmsnorm, "rmsnorm_bwd": rmsnorm_bwd, "rmsnorm_bwd_add": rmsnorm_bwd_add,
         "residual_rmsnorm": residual_rmsnorm, "residual": residual, "swiglu": swiglu, "swiglu_bwd": swiglu_bwd,
         "rope": rope, "qknorm_rope(Q)": qknorm_rope, "rope_qknorm_bwd(Q)": rope_qknorm_bwd,

@@ -250,6 +250,42 @@ int ane_cuda_grad_norm_sq_dev(void *stream, size_t n, const float *g, float gsca
  * n_terms partial squares at normsq_dev).                               train.m:788,809-810 */
 int ane_cuda_clip_factor_dev(void *stream, const float *normsq_dev, int n_terms, float clip, float *factor_dev);
 
+/* ---- layout helpers on either side of the operators in the reference's loop --------------------------
+ * GQA head tiling: x [B][kv_heads*hd][S] -> out [B][kv_heads*ratio*hd][S], every KV head repeated `ratio`
+ * times (query head kv*ratio + r reads KV head kv).       training_dynamic/io.h:330-337 (gqa_tile_kv) */
+int ane_cuda_gqa_tile_dev(void *stream, ane_dtype dtype, int B, int kv_heads, int ratio, int hd, int S,
+                          void *out, const void *in);
+/* GQA head sum: in [B][kv_heads*ratio*hd][S] -> out [B][kv_heads*hd][S], out = 0 + in[r=0] + in[r=1] + ...
+ * in head order (fp32 adds, one rounding on store).        training_dynamic/io.h:340-351 (gqa_reduce_kv) */
+int ane_cuda_gqa_reduce_dev(void *stream, ane_dtype dtype, int B, int kv_heads, int ratio, int hd, int S,
+                            void *out, const void *in);
+/* dst[i] = (dst type) src[i], round to nearest even; any pair of f32 / f16 / bf16.
+ *                                          stories_io.h:41-58, io.h:33-50 (cvt_f16_f32, cvt_f32_f16) */
+int ane_cuda_convert_dev(void *stream, ane_dtype dst_dtype, ane_dtype src_dtype, size_t n, void *dst, const void *src);
+/* Packed surface of the dynamic-weight matmul: row d of buf [ic][seq+oc] (16-bit) = act[d][0..seq) followed
+ * by W[d][0..oc), both converted from fp32.                                   io.h:79-88 (io_write_dyn).
+ * Reading a result back (io_read_dyn, io.h:91-95) is ane_cuda_convert_dev. */
+int ane_cuda_pack_dyn_dev(void *stream, ane_dtype dst_dtype, int ic, int seq, int oc, void *buf,
+                          const float *act, const float *W);
+/* Vocabulary compaction.  full_to_compact[v] = rank of v among the ids that occur in tokens, or -1;
+ * compact_to_full is its inverse (room for full_vocab entries); *compact_vocab = number of ids in use.
+ * All three outputs are device memory; ids outside [0, full_vocab) are counted in the status words.
+ *                                                                 cpu_ops.h:96-126 (vocab_map_build) */
+int ane_cuda_vocab_map_build_dev(void *stream, ane_idtype idtype, size_t n_tokens, const void *tokens, int full_vocab,
+                                 int *full_to_compact, int *compact_to_full, int *compact_vocab);
+/* Rows of `dim` floats moved between the full and the compact table.  The number of rows is
+ * min(*compact_vocab_dev, compact_vocab_max) when compact_vocab_dev is given (device pointer written by
+ * ane_cuda_vocab_map_build_dev: no host round trip), else compact_vocab_max.
+ *   compact_embed:  compact[c]          = full[compact_to_full[c]]        cpu_ops.h:129-134
+ *   scatter_grads:  full[compact_to_full[c]] += compact[c]                cpu_ops.h:137-143
+ *   update_full:    full[compact_to_full[c]]  = compact[c]                cpu_ops.h:146-149 */
+int ane_cuda_vocab_compact_embed_dev(void *stream, float *compact_embed, const float *full_embed, const int *compact_to_full,
+                                     const int *compact_vocab_dev, int compact_vocab_max, int dim, int full_vocab);
+int ane_cuda_vocab_scatter_grads_dev(void *stream, float *full_gembed, const float *compact_gembed, const int *compact_to_full,
+                                     const int *compact_vocab_dev, int compact_vocab_max, int dim, int full_vocab);
+int ane_cuda_vocab_update_full_dev(void *stream, float *full_embed, const float *compact_embed, const int *compact_to_full,
+                                   const int *compact_vocab_dev, int compact_vocab_max, int dim, int full_vocab);
+
 #ifdef __cplusplus
 }
 #endif

@@ -83,6 +83,15 @@ class Oracle:
         L.orc_clip_factor.restype = C.c_float
         L.orc_vocab_map_build.argtypes = [_i32p, C.c_size_t, C.c_int, _i32p, _i32p]
         L.orc_vocab_map_build.restype = C.c_int
+        for name in ("orc_vocab_compact_embed", "orc_vocab_scatter_grads", "orc_vocab_update_full"):
+            getattr(L, name).argtypes = [_f32p, _f32p, _i32p, C.c_int, C.c_int]
+            getattr(L, name).restype = None
+        for name in ("orc_gqa_tile_kv", "orc_gqa_reduce_kv"):
+            getattr(L, name).argtypes = [_f32p, _f32p, C.c_int, C.c_int, C.c_int, C.c_int]
+            getattr(L, name).restype = None
+        L.orc_cvt_f32_f16.argtypes = [_u16p, _f32p, C.c_size_t]
+        L.orc_cvt_f16_f32.argtypes = [_f32p, _u16p, C.c_size_t]
+        L.orc_pack_dyn_f16.argtypes = [_u16p, _f32p, C.c_int, C.c_int, _f32p, C.c_int]
         L.orc_num_threads.restype = C.c_int
         L.orc_set_num_threads.argtypes = [C.c_int]
         L.orc_set_chunk.argtypes = [C.c_int]
@@ -226,6 +235,61 @@ class Oracle:
     def clip_factor(self, norm_sq, clip):
         return float(self.lib.orc_clip_factor(norm_sq, clip))
 
+    # ---- layout helpers (training_dynamic/io.h, cpu_ops.h)
+    def vocab_compact_embed(self, full_embed, c2f, cv):
+        out = np.empty((cv, full_embed.shape[1]), np.float32)
+        self.lib.orc_vocab_compact_embed(_fp(out), _fp(np.ascontiguousarray(full_embed, np.float32)), _ip(c2f), cv, full_embed.shape[1])
+        return out
+
+    def vocab_scatter_grads(self, full_g, compact_g, c2f, cv):
+        out = np.ascontiguousarray(full_g, np.float32).copy()
+        self.lib.orc_vocab_scatter_grads(_fp(out), _fp(np.ascontiguousarray(compact_g, np.float32)), _ip(c2f), cv, full_g.shape[1])
+        return out
+
+    def vocab_update_full(self, full_embed, compact_embed, c2f, cv):
+        out = np.ascontiguousarray(full_embed, np.float32).copy()
+        self.lib.orc_vocab_update_full(_fp(out), _fp(np.ascontiguousarray(compact_embed, np.float32)), _ip(c2f), cv, full_embed.shape[1])
+        return out
+
+    def gqa_tile(self, x, kv_heads, ratio):
+        """x [B, kv_heads*hd, S] fp32 -> [B, kv_heads*ratio*hd, S]"""
+        x = np.ascontiguousarray(x, np.float32)
+        B, Cn, S = x.shape
+        hd = Cn // kv_heads
+        out = np.empty((B, Cn * ratio, S), np.float32)
+        for b in range(B):
+            self.lib.orc_gqa_tile_kv(_fp(out[b]), _fp(x[b]), kv_heads, ratio, hd, S)
+        return out
+
+    def gqa_reduce(self, x, kv_heads, ratio):
+        x = np.ascontiguousarray(x, np.float32)
+        B, Cn, S = x.shape
+        hd = Cn // (kv_heads * ratio)
+        out = np.empty((B, kv_heads * hd, S), np.float32)
+        for b in range(B):
+            self.lib.orc_gqa_reduce_kv(_fp(out[b]), _fp(x[b]), kv_heads, ratio, hd, S)
+        return out
+
+    def cvt_f32_f16(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape, np.uint16)
+        self.lib.orc_cvt_f32_f16(_up(out), _fp(x), x.size)
+        return out.view(np.float16)
+
+    def cvt_f16_f32(self, h):
+        h = np.ascontiguousarray(h, np.float16)
+        out = np.empty(h.shape, np.float32)
+        self.lib.orc_cvt_f16_f32(_fp(out), _up(h.view(np.uint16)), h.size)
+        return out
+
+    def pack_dyn(self, act, W):
+        act, W = np.ascontiguousarray(act, np.float32), np.ascontiguousarray(W, np.float32)
+        ic, seq = act.shape
+        oc = W.shape[1]
+        out = np.empty((ic, seq + oc), np.uint16)
+        self.lib.orc_pack_dyn_f16(_up(out), _fp(act), ic, seq, _fp(W), oc)
+        return out.view(np.float16)
+
     def vocab_map_build(self, data, full_vocab):
         d = np.ascontiguousarray(data.astype(np.int32).ravel())
         f2c = np.empty(full_vocab, np.int32)
@@ -272,6 +336,9 @@ class Reference:
         self.dy.ref_dynamic_rope_backward_inplace.argtypes = [_f32p, C.c_int, C.c_int, C.c_int]
         self.dy.ref_dynamic_vocab_map_build.argtypes = [_u16p, C.c_size_t, C.c_int, _i32p, _i32p]
         self.dy.ref_dynamic_vocab_map_build.restype = C.c_int
+        for name in ("ref_dynamic_vocab_compact_embed", "ref_dynamic_vocab_scatter_grads", "ref_dynamic_vocab_update_full"):
+            getattr(self.dy, name).argtypes = [_f32p, _f32p, _i32p, C.c_int, C.c_int]
+            getattr(self.dy, name).restype = None
         self.st.ref_stories_set_vocab.argtypes = [C.c_int]
 
     def _lib(self, variant):
@@ -325,6 +392,12 @@ class Reference:
     def rope_backward_inplace(self, dx, hd):
         out = dx.copy()
         self.dy.ref_dynamic_rope_backward_inplace(_fp(out), dx.shape[1], dx.shape[0], hd)
+        return out
+
+    def vocab_rows(self, which, a, b, c2f, cv):
+        """which in compact_embed / scatter_grads / update_full; a is the destination (copied), b the source."""
+        out = np.ascontiguousarray(a, np.float32).copy()
+        getattr(self.dy, "ref_dynamic_vocab_" + which)(_fp(out), _fp(np.ascontiguousarray(b, np.float32)), _ip(c2f), cv, b.shape[1])
         return out
 
     def vocab_map_build(self, data_u16, full_vocab):

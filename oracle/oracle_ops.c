@@ -411,6 +411,59 @@ ORC_API int orc_vocab_map_build(const int32_t *data, size_t n_tokens, int full_v
     return cid;
 }
 
+/* training_dynamic/cpu_ops.h:129-134: compact table = rows of the full table in compact order */
+ORC_API void orc_vocab_compact_embed(float *compact, const float *full_embed, const int32_t *compact_to_full, int compact_vocab, int dim) {
+    for (int c = 0; c < compact_vocab; c++)
+        memcpy(compact + (size_t)c * dim, full_embed + (size_t)compact_to_full[c] * dim, (size_t)dim * 4);
+}
+/* cpu_ops.h:137-143: full gradient rows += compact gradient rows */
+ORC_API void orc_vocab_scatter_grads(float *full_gembed, const float *compact_gembed, const int32_t *compact_to_full, int compact_vocab, int dim) {
+    for (int c = 0; c < compact_vocab; c++) {
+        const int fv = compact_to_full[c];
+        for (int d = 0; d < dim; d++) full_gembed[(size_t)fv * dim + d] += compact_gembed[(size_t)c * dim + d];
+    }
+}
+/* cpu_ops.h:146-149: full table rows = compact rows (after the optimizer step) */
+ORC_API void orc_vocab_update_full(float *full_embed, const float *compact_embed, const int32_t *compact_to_full, int compact_vocab, int dim) {
+    for (int c = 0; c < compact_vocab; c++)
+        memcpy(full_embed + (size_t)compact_to_full[c] * dim, compact_embed + (size_t)c * dim, (size_t)dim * 4);
+}
+
+/* ------------------------------------------------------------------ GQA helpers
+ * training_dynamic/io.h:330-337: every KV head copied to its `ratio` query heads. in [kv_heads*hd, seq] */
+ORC_API void orc_gqa_tile_kv(float *out, const float *in, int kv_heads, int ratio, int hd, int seq) {
+    for (int kv = 0; kv < kv_heads; kv++)
+        for (int r = 0; r < ratio; r++)
+            memcpy(out + (size_t)(kv * ratio + r) * hd * seq, in + (size_t)kv * hd * seq, (size_t)hd * seq * sizeof(float));
+}
+/* io.h:340-351: zero, then add the query heads of each KV head in head order */
+ORC_API void orc_gqa_reduce_kv(float *out, const float *in, int kv_heads, int ratio, int hd, int seq) {
+    memset(out, 0, (size_t)kv_heads * hd * seq * sizeof(float));
+    for (int kv = 0; kv < kv_heads; kv++)
+        for (int r = 0; r < ratio; r++) {
+            const float *src = in + (size_t)(kv * ratio + r) * hd * seq;
+            float *dst = out + (size_t)kv * hd * seq;
+            for (size_t i = 0; i < (size_t)hd * seq; i++) dst[i] += src[i];
+        }
+}
+
+/* ------------------------------------------------------------------ fp32 <-> fp16 and the packed surface
+ * stories_io.h:41-58 / io.h:33-50: element-wise casts (NEON vcvt = round to nearest even, as the C cast). */
+ORC_API void orc_cvt_f32_f16(uint16_t *dst, const float *src, size_t n) {
+    for (size_t i = 0; i < n; i++) { const _Float16 h = (_Float16)src[i]; memcpy(dst + i, &h, 2); }
+}
+ORC_API void orc_cvt_f16_f32(float *dst, const uint16_t *src, size_t n) {
+    for (size_t i = 0; i < n; i++) { _Float16 h; memcpy(&h, src + i, 2); dst[i] = (float)h; }
+}
+/* io.h:79-88 (io_write_dyn): row d = act[d][0..seq) then W[d][0..oc), fp16 */
+ORC_API void orc_pack_dyn_f16(uint16_t *buf, const float *act, int ic, int seq, const float *W, int oc) {
+    const int sp = seq + oc;
+    for (int d = 0; d < ic; d++) {
+        orc_cvt_f32_f16(buf + (size_t)d * sp, act + (size_t)d * seq, (size_t)seq);
+        orc_cvt_f32_f16(buf + (size_t)d * sp + seq, W + (size_t)d * oc, (size_t)oc);
+    }
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -37,3 +37,18 @@ int ref_dynamic_vocab_map_build(const uint16_t *data, size_t n_tokens, int full_
     free(vm.full_to_compact); free(vm.compact_to_full);
     return cv;
 }
+
+void ref_dynamic_vocab_compact_embed(float *compact, const float *full_embed, const int *compact_to_full, int compact_vocab, int dim) {
+    VocabMap vm = {compact_vocab, NULL, (int *)compact_to_full};
+    float *ce = vocab_compact_embed(full_embed, &vm, dim);
+    memcpy(compact, ce, (size_t)compact_vocab * dim * 4);
+    free(ce);
+}
+void ref_dynamic_vocab_scatter_grads(float *full_gembed, const float *compact_gembed, const int *compact_to_full, int compact_vocab, int dim) {
+    VocabMap vm = {compact_vocab, NULL, (int *)compact_to_full};
+    vocab_scatter_grads(full_gembed, compact_gembed, &vm, dim);
+}
+void ref_dynamic_vocab_update_full(float *full_embed, const float *compact_embed, const int *compact_to_full, int compact_vocab, int dim) {
+    VocabMap vm = {compact_vocab, NULL, (int *)compact_to_full};
+    vocab_update_full(full_embed, compact_embed, &vm, dim);
+}
