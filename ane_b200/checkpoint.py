@@ -1,0 +1,65 @@
+"""Checkpoints of the reference's training loops ("BLZT" files, version 2 of training/train_large.m and
+version 4 of training/training_dynamic/train.m) to and from flat device buffers, through the C ABI
+(`ane_cuda_ckpt_*`, implemented in csrc/ckpt.cu).
+
+Device layout ("weight order"): per layer Wq Wk Wv Wo W1 W2 W3 rms_att rms_ffn, then rms_final, then
+embed -- the file's order with the Adam moments taken out -- in three parallel fp32 buffers w, m, v.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import lib as _l
+
+MAGIC = 0x424C5A54
+
+
+class CkptHeader(C.Structure):
+    """training/stories_config.h:95-104 (version 2), training_dynamic/config.h:78-86 (version 4); 96 bytes."""
+    _fields_ = [("magic", C.c_int), ("version", C.c_int), ("step", C.c_int), ("total_steps", C.c_int),
+                ("n_layers", C.c_int), ("vocab_size", C.c_int), ("dim", C.c_int), ("hidden_dim", C.c_int),
+                ("n_heads", C.c_int), ("seq_len", C.c_int), ("lr", C.c_float), ("loss", C.c_float),
+                ("cum_compile", C.c_double), ("cum_train", C.c_double), ("cum_wall", C.c_double),
+                ("cum_steps", C.c_int), ("cum_batches", C.c_int), ("adam_t", C.c_int),
+                ("kv_heads", C.c_int), ("head_dim", C.c_int), ("q_dim", C.c_int)]
+
+    def as_dict(self):
+        return {n: getattr(self, n) for n, _ in self._fields_}
+
+
+def read_header(path: str) -> CkptHeader:
+    h = CkptHeader()
+    _l.check(_l.load().ane_cuda_ckpt_read_header(path.encode(), C.byref(h)))
+    return h
+
+
+def param_count(h: CkptHeader) -> int:
+    return int(_l.load().ane_cuda_ckpt_param_count(C.byref(h)))
+
+
+def layer_tensors(h: CkptHeader):
+    """(name, element count) of the nine per-layer tensors in file order."""
+    q_dim, kv_dim = (h.q_dim, h.kv_heads * h.head_dim) if h.version >= 4 else (h.dim, h.dim)
+    d, hid = h.dim, h.hidden_dim
+    return [("Wq", q_dim * d), ("Wk", kv_dim * d), ("Wv", kv_dim * d), ("Wo", d * q_dim), ("W1", hid * d), ("W2", d * hid),
+            ("W3", hid * d), ("rms_att", d), ("rms_ffn", d)]
+
+
+def load(path: str, with_moments: bool = True, device="cuda"):
+    """-> (header, w, m, v): flat fp32 CUDA tensors in weight order (m, v are None without moments)."""
+    import torch
+    h = read_header(path)
+    n = param_count(h)
+    w = torch.empty(n, dtype=torch.float32, device=device)
+    m = torch.empty_like(w) if with_moments else None
+    v = torch.empty_like(w) if with_moments else None
+    _l.check(_l.load().ane_cuda_ckpt_load(path.encode(), C.byref(h), w.data_ptr(), m.data_ptr() if with_moments else None,
+                                         v.data_ptr() if with_moments else None, n))
+    return h, w, m, v
+
+
+def save(path: str, h: CkptHeader, w, m, v) -> None:
+    for t in (w, m, v):
+        if not (t.is_cuda and t.is_contiguous() and t.dtype.is_floating_point and t.element_size() == 4):
+            raise ValueError("expected contiguous fp32 CUDA tensors")
+    _l.check(_l.load().ane_cuda_ckpt_save(path.encode(), C.byref(h), w.data_ptr(), m.data_ptr(), v.data_ptr(), w.numel()))

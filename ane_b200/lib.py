@@ -116,6 +116,11 @@ PROTOTYPES = {
     "ane_cuda_vocab_compact_embed_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "ane_cuda_vocab_scatter_grads_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "ane_cuda_vocab_update_full_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
+    # checkpoints
+    "ane_cuda_ckpt_read_header": (_i, [C.c_char_p, _vp]),
+    "ane_cuda_ckpt_param_count": (_sz, [_vp]),
+    "ane_cuda_ckpt_load": (_i, [C.c_char_p, _vp, _vp, _vp, _vp, _sz]),
+    "ane_cuda_ckpt_save": (_i, [C.c_char_p, _vp, _vp, _vp, _vp, _sz]),
 }
 
 _lib = None

@@ -286,6 +286,31 @@ int ane_cuda_vocab_scatter_grads_dev(void *stream, float *full_gembed, const flo
 int ane_cuda_vocab_update_full_dev(void *stream, float *full_embed, const float *compact_embed, const int *compact_to_full,
                                    const int *compact_vocab_dev, int compact_vocab_max, int dim, int full_vocab);
 
+/* ---- checkpoints of the reference's training loops ("BLZT" files) ------------------------------------
+ * Header as written by save_checkpoint: version 2 (training/stories_config.h:95-104, train_large.m:109-145;
+ * the last three ints are padding) and version 4 (training_dynamic/config.h:78-86, train.m:104-138). */
+typedef struct {
+    int magic;                 /* 0x424C5A54 */
+    int version;               /* 2 or 4 */
+    int step, total_steps;
+    int n_layers, vocab_size, dim, hidden_dim, n_heads, seq_len;
+    float lr, loss;
+    double cum_compile, cum_train, cum_wall;
+    int cum_steps, cum_batches, adam_t;
+    int kv_heads, head_dim, q_dim;   /* version 4; padding in version 2 */
+} ane_ckpt_header;
+/* Reads and validates the header only (no GPU needed). */
+int ane_cuda_ckpt_read_header(const char *path, ane_ckpt_header *hdr);
+/* Number of parameters the file holds = floats in each of the w / m / v buffers below. 0 for a bad header. */
+size_t ane_cuda_ckpt_param_count(const ane_ckpt_header *hdr);
+/* File -> device.  The three device buffers receive the weights and the two Adam moments in "weight order":
+ * per layer Wq Wk Wv Wo W1 W2 W3 rms_att rms_ffn, then rms_final, then embed -- the file's order with the
+ * moments taken out (load_checkpoint, train.m:140-172).  m_dev and v_dev may both be NULL (weights only). */
+int ane_cuda_ckpt_load(const char *path, ane_ckpt_header *hdr, float *w_dev, float *m_dev, float *v_dev, size_t n_floats);
+/* Device -> file, byte-identical to what the reference's save_checkpoint writes for the same values. */
+int ane_cuda_ckpt_save(const char *path, const ane_ckpt_header *hdr, const float *w_dev, const float *m_dev,
+                       const float *v_dev, size_t n_floats);
+
 #ifdef __cplusplus
 }
 #endif
