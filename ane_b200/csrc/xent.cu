@@ -215,25 +215,6 @@ __device__ __forceinline__ void ms_fold(Ms4 &a, const float4 (&r)[U], const bool
             a.s[2] += ex2_approx(fmaf(r[u].z, XC_LOG2E, n2)); a.s[3] += ex2_approx(fmaf(r[u].w, XC_LOG2E, n3));
         }
 }
-// same, the first n rows valid
-template <int U>
-__device__ __forceinline__ void ms_fold_n(Ms4 &a, const float4 (&r)[U], int n) {
-    float gm[4] = {a.m[0], a.m[1], a.m[2], a.m[3]};
-#pragma unroll
-    for (int u = 0; u < U; u++)
-        if (u < n) {
-            gm[0] = fmaxf(gm[0], r[u].x); gm[1] = fmaxf(gm[1], r[u].y);
-            gm[2] = fmaxf(gm[2], r[u].z); gm[3] = fmaxf(gm[3], r[u].w);
-        }
-    ms_raise(a, gm);
-    const float n0 = -a.m[0] * XC_LOG2E, n1 = -a.m[1] * XC_LOG2E, n2 = -a.m[2] * XC_LOG2E, n3 = -a.m[3] * XC_LOG2E;
-#pragma unroll
-    for (int u = 0; u < U; u++)
-        if (u < n) {
-            a.s[0] += ex2_approx(fmaf(r[u].x, XC_LOG2E, n0)); a.s[1] += ex2_approx(fmaf(r[u].y, XC_LOG2E, n1));
-            a.s[2] += ex2_approx(fmaf(r[u].z, XC_LOG2E, n2)); a.s[3] += ex2_approx(fmaf(r[u].w, XC_LOG2E, n3));
-        }
-}
 __device__ __forceinline__ void ms_merge(float &m, float &s, float m2, float s2) {
     const float M = fmaxf(m, m2);
     float acc = 0.0f;
@@ -457,189 +438,6 @@ xent_cluster_kernel(const __grid_constant__ CUtensorMap lmap, float *dlogits, co
     cluster.barrier_wait();                           // peers may still be reading `part`
 }
 
-// ------------------------------------------------------------------ whole-grid wave kernel
-// The only way to read the logits once AND keep every SM busy: the whole grid works on one "wave" of
-// W = 32*NSUB tokens at a time (V*W*4 bytes, sized to about 19 MB so that three waves fit in L2), each
-// block owning a fixed slice of the vocabulary rows:
-//   sweep 1 (wave w)   stream the slice (8 x 16-byte loads per thread in flight, 512 threads, two blocks
-//                      per SM), online (max, sum) per token, block pair -> scratch; the last block to
-//                      arrive merges all blocks' pairs into (max, 1/sum) per token and raises flag[w];
-//   sweep 2 (wave w)   after flag[w]: stream the slice again -- from L2 -- and write dlogits.
-// Blocks run sweep 1 of wave w+1 BEFORE sweep 2 of wave w, so the merge of wave w hides behind real
-// work.  Launched cooperatively (all blocks co-resident); the flag wait is bounded and reports a
-// give-up in the status words instead of spinning forever.
-constexpr int XW_THREADS = 256;
-constexpr int XW_LG = 8;                   // 128-byte rows: 32 tokens per sub-stripe
-constexpr int XW_SW = XW_LG * 4;
-constexpr int XW_R = XW_THREADS / XW_LG;   // 32 vocabulary rows per step
-constexpr int XW_U = 16;                   // 16-byte loads in flight per thread: 128 KB per SM with two blocks
-constexpr int XW_NW = XW_THREADS / 32;
-constexpr int XW_BUFS = 3;
-
-struct XentWaveScratch {
-    float2 *partial;     // [XW_BUFS][slices][W]  (max, sum) per row slice and token
-    float2 *final_ms;    // [XW_BUFS][W]          (max, 1/sum) per token
-    unsigned *counter;   // [nwaves] blocks arrived
-    unsigned *flag;      // [nwaves] merged
-};
-
-// Block b works on sub-stripe b % NSUB (32 tokens of the wave) and row slice b / NSUB.
-template <typename ID, int NSUB>
-__global__ void __launch_bounds__(XW_THREADS, 2)
-xent_wave_kernel(float *dlogits, const float *logits, const void *__restrict__ targets, float *__restrict__ loss_tok,
-                 int V, int S, int waves_per_seq, int nwaves, float grad_scale, XentWaveScratch sc, ane_cuda_status *status) {
-    constexpr int W = XW_SW * NSUB;
-    __shared__ float2 red[XW_NW][XW_SW];
-    __shared__ float mrg_m[XW_THREADS / W][W];
-    __shared__ float mrg_s[XW_THREADS / W][W];
-    __shared__ int is_last, give_up;
-
-    const int G = gridDim.x;
-    const int nslices = G / NSUB;                          // the launcher makes G a multiple of NSUB
-    const int sub = blockIdx.x % NSUB, slice = blockIdx.x / NSUB;
-    const int lg = threadIdx.x % XW_LG, rg = threadIdx.x / XW_LG;
-    const int rows_per = (V + nslices - 1) / nslices;
-    const int v0 = slice * rows_per;
-    const int v1 = v0 + rows_per < V ? v0 + rows_per : V;
-    if (threadIdx.x == 0) give_up = 0;
-    __syncthreads();
-
-    for (int w = 0; w <= nwaves; w++) {
-        // ---------------- sweep 1 of wave w
-        if (w < nwaves) {
-            const int b = w / waves_per_seq;
-            const int t = (w % waves_per_seq) * W + sub * XW_SW + lg * 4;
-            const bool active = t < S;
-            const size_t base = (size_t)b * V * S + t;
-            Ms4 ms;
-            ms_init(ms);
-            const size_t rstep = (size_t)XW_R * S;
-            for (int vb = v0 + rg; vb < v1; vb += XW_R * XW_U) {
-                float4 r[XW_U];
-                const int nv = active ? (v1 - vb + XW_R - 1) / XW_R : 0;      // valid rows of this step (may exceed XW_U)
-                const float *p = logits + base + (size_t)vb * S;
-#pragma unroll
-                for (int u = 0; u < XW_U; u++)
-                    if (u < nv) r[u] = *reinterpret_cast<const float4 *>(p + u * rstep);                  // stays in L2 for sweep 2
-                ms_fold_n<XW_U>(ms, r, nv);
-            }
-#pragma unroll
-            for (int off = XW_LG; off < 32; off <<= 1) {
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const float m2 = __shfl_xor_sync(0xffffffffu, ms.m[j], off);
-                    const float s2 = __shfl_xor_sync(0xffffffffu, ms.s[j], off);
-                    ms_merge(ms.m[j], ms.s[j], m2, s2);
-                }
-            }
-            if ((threadIdx.x & 31) < XW_LG) {
-#pragma unroll
-                for (int j = 0; j < 4; j++) red[threadIdx.x >> 5][lg * 4 + j] = make_float2(ms.m[j], ms.s[j]);
-            }
-            __syncthreads();
-            if (threadIdx.x < XW_SW) {
-                float m = -INFINITY, s = 0.0f;
-                for (int q = 0; q < XW_NW; q++) ms_merge(m, s, red[q][threadIdx.x].x, red[q][threadIdx.x].y);
-                sc.partial[((size_t)(w % XW_BUFS) * nslices + slice) * W + sub * XW_SW + threadIdx.x] = make_float2(m, s);
-                __threadfence();
-            }
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                const unsigned ticket = atomicAdd(&sc.counter[w], 1u);
-                is_last = ticket == (unsigned)(G - 1);
-                if (is_last) __threadfence();
-            }
-            __syncthreads();
-            if (is_last) {      // merge the pairs of every token over the row slices, in slice order per thread group
-                constexpr int PARTS = XW_THREADS / W;
-                const int tok = threadIdx.x % W, part = threadIdx.x / W;
-                const float2 *pp = sc.partial + (size_t)(w % XW_BUFS) * nslices * W;
-                float m = -INFINITY, s = 0.0f;
-                for (int i = part; i < nslices; i += PARTS) {
-                    const float2 q = __ldcg(&pp[(size_t)i * W + tok]);
-                    ms_merge(m, s, q.x, q.y);
-                }
-                mrg_m[part][tok] = m;
-                mrg_s[part][tok] = s;
-                __syncthreads();
-                if (part == 0) {
-                    m = -INFINITY;
-                    s = 0.0f;
-#pragma unroll
-                    for (int q = 0; q < PARTS; q++) ms_merge(m, s, mrg_m[q][tok], mrg_s[q][tok]);
-                    sc.final_ms[(w % XW_BUFS) * W + tok] = make_float2(m, 1.0f / s);          // inv_sum, stories_cpu_ops.h:91-92
-                    __threadfence();
-                }
-                __syncthreads();
-                if (threadIdx.x == 0) atomicExch(&sc.flag[w], 1u);
-            }
-        }
-        // ---------------- sweep 2 of wave w-1
-        if (w >= 1) {
-            const int pw = w - 1;
-            if (threadIdx.x == 0) {
-                unsigned spins = 0;
-                while (atomicAdd(&sc.flag[pw], 0u) == 0u) {
-                    __nanosleep(64);
-                    if (++spins > (1u << 22)) { give_up = 1; break; }
-                }
-                __threadfence();
-            }
-            __syncthreads();
-            if (give_up) {
-                if (threadIdx.x == 0) atomicAdd(&status->wait_giveups, 1);
-                return;
-            }
-            const int b = pw / waves_per_seq;
-            const int t = (pw % waves_per_seq) * W + sub * XW_SW + lg * 4;
-            const bool active = t < S;
-            const size_t base = (size_t)b * V * S + t;
-            XentRowOut o;
-            float negML[4];
-            o.invS = 1.0f / (float)S;
-            o.grad_scale = grad_scale;
-            o.status = status;
-            o.loss_tok = loss_tok + (size_t)b * S + t;
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float2 f = __ldcg(&sc.final_ms[(pw % XW_BUFS) * W + sub * XW_SW + lg * 4 + j]);
-                negML[j] = -f.x * XC_LOG2E;
-                o.inv[j] = f.y;
-                o.tgt[j] = -1;
-                if (active) {
-                    const int id = (int)reinterpret_cast<const ID *>(targets)[(size_t)b * S + t + j];
-                    if (id >= 0 && id < V) o.tgt[j] = id;
-                    else if (rg == 0 && slice == 0) {             // one thread per token reports it
-                        atomicAdd(&status->oor_ids, 1);
-                        o.loss_tok[j] = 0.0f;                     // no loss term (stories_cpu_ops.h:98)
-                    }
-                }
-                float scl = o.inv[j];
-                if (o.tgt[j] >= 0) scl = scl * o.invS;
-                if (grad_scale != 1.0f) scl = scl * grad_scale;
-                o.scale[j] = scl;
-            }
-            const size_t rstep = (size_t)XW_R * S;
-            for (int vb = v0 + rg; vb < v1; vb += XW_R * XW_U) {
-                float4 r[XW_U];
-                const int nv = active ? (v1 - vb + XW_R - 1) / XW_R : 0;
-                const float *p = logits + base + (size_t)vb * S;
-                float *q = dlogits + base + (size_t)vb * S;
-#pragma unroll
-                for (int u = 0; u < XW_U; u++)
-                    if (u < nv) r[u] = __ldcs(reinterpret_cast<const float4 *>(p + u * rstep));
-#pragma unroll
-                for (int u = 0; u < XW_U; u++)
-                    if (u < nv) {
-                        const float e[4] = {ex2_approx(fmaf(r[u].x, XC_LOG2E, negML[0])), ex2_approx(fmaf(r[u].y, XC_LOG2E, negML[1])),
-                                            ex2_approx(fmaf(r[u].z, XC_LOG2E, negML[2])), ex2_approx(fmaf(r[u].w, XC_LOG2E, negML[3]))};
-                        __stcs(reinterpret_cast<float4 *>(q + u * rstep), xent_finish(e, vb + u * XW_R, o));
-                    }
-            }
-        }
-    }
-}
-
 // loss_seq[b] = (sum_t loss_tok[b][t]) / S, fixed summation tree.
 __global__ void __launch_bounds__(256) xent_loss_kernel(float *__restrict__ loss_seq, const float *__restrict__ loss_tok, int S) {
     __shared__ float sh[8];
@@ -674,44 +472,6 @@ int ane_cuda_cross_entropy_dev(void *stream, ane_idtype idtype, int B, int V, in
     if (!loss_tok) return fail(ANE_CUDA_ERR_NOMEM, "%s: no scratch", __func__);
     ane_cuda_status *status = ctx().status;
     const bool vec = (S % 4 == 0) && aligned16(dlogits) && aligned16(logits);
-    if (vec && tuning("xent_wave", 0) && V >= 4096 && (long long)B * S >= 4096) {
-        // tokens per wave: about 19 MB of logits, so that three waves stay in L2
-        const long long per_token = (long long)V * 4;
-        const int nsub = tuning("xent_nsub", per_token * 128 <= (20ll << 20) ? 4 : (per_token * 64 <= (20ll << 20) ? 2 : 1));
-        const void *kern = nullptr;
-#define ANE_XW(IDT, NS) kern = (const void *)xent_wave_kernel<IDT, NS>
-        if (idtype == ANE_ID_U16) { if (nsub == 4) ANE_XW(uint16_t, 4); else if (nsub == 2) ANE_XW(uint16_t, 2); else ANE_XW(uint16_t, 1); }
-        else { if (nsub == 4) ANE_XW(int32_t, 4); else if (nsub == 2) ANE_XW(int32_t, 2); else ANE_XW(int32_t, 1); }
-#undef ANE_XW
-        const int Wt = XW_SW * (nsub == 4 ? 4 : (nsub == 2 ? 2 : 1));
-        int per_sm = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, XW_THREADS, 0) == cudaSuccess && per_sm >= 1) {
-            if (per_sm > 2) per_sm = 2;
-            const int nsub_eff = Wt / XW_SW;
-            int G = per_sm * ctx().sm_count / nsub_eff * nsub_eff;      // a whole number of row slices per sub-stripe
-            const int wps = (S + Wt - 1) / Wt;
-            int nwaves = B * wps;
-            const size_t off_part = round_up((size_t)B * S * sizeof(float), 256);
-            const size_t off_final = off_part + round_up((size_t)XW_BUFS * G * Wt * sizeof(float2), 256);
-            const size_t off_cnt = off_final + round_up((size_t)XW_BUFS * Wt * sizeof(float2), 256);
-            const size_t off_flag = off_cnt + round_up((size_t)nwaves * sizeof(unsigned), 256);
-            const size_t total = off_flag + round_up((size_t)nwaves * sizeof(unsigned), 256);
-            char *ws = static_cast<char *>(workspace(total));
-            if (!ws) return fail(ANE_CUDA_ERR_NOMEM, "%s: no scratch", __func__);
-            loss_tok = reinterpret_cast<float *>(ws);
-            XentWaveScratch sc;
-            sc.partial = reinterpret_cast<float2 *>(ws + off_part);
-            sc.final_ms = reinterpret_cast<float2 *>(ws + off_final);
-            sc.counter = reinterpret_cast<unsigned *>(ws + off_cnt);
-            sc.flag = reinterpret_cast<unsigned *>(ws + off_flag);
-            ANE_CUDA_TRY(cudaMemsetAsync(ws + off_cnt, 0, total - off_cnt, st));
-            void *args[] = {&dlogits, &logits, &targets, &loss_tok, &V, &S, (void *)&wps, &nwaves, &grad_scale, &sc, &status};
-            ANE_CUDA_TRY(cudaLaunchCooperativeKernel(kern, dim3(G), dim3(XW_THREADS), args, 0, st));
-            xent_loss_kernel<<<B, 256, 0, st>>>(loss_seq, loss_tok, S);
-            ANE_LAUNCH_OK(2);
-            return ANE_CUDA_OK;
-        }
-    }
     if (vec && tuning("xent_cluster", 0) && V >= 4096 && S % XC_TW == 0) {
         // a cluster of 8 blocks per 16-token stripe, most of the stripe resident in shared memory
         const int threads = tuning("xent_threads", 1024) == 512 ? 512 : 1024;

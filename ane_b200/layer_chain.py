@@ -208,42 +208,63 @@ class LayerChain:
             return r
         return fn()
 
-    def forward(self):
+    def fwd_layer(self, L):
         c, p = self.cfg, self.p
+        r = L % self.R
+        x = self.layer_in[L]
+        ops.rmsnorm(x, p.norm_w("att", L), c.eps, out=self.xnorm[r])
+        ops.qknorm_rope(self.q[L], p.norm_w("q", L), c.head_dim, c.qk_eps, c.rope_base, 0, out=self.q_r[r])
+        ops.qknorm_rope(self.k[L], p.norm_w("k", L), c.head_dim, c.qk_eps, c.rope_base, 0, out=self.k_r[r])
+        ops.residual_rmsnorm(x, self.o_out[L], p.norm_w("ffn", L), c.alpha, c.eps, x2=self.x2[L], x2norm=self.x2norm[r])
+        ops.swiglu(self.h1[L], self.h3[L], out=self.gate[r])
+        ops.residual(self.x2[L], self.ffn_out[L], c.alpha, out=self.layer_in[L + 1])
+
+    def fwd_begin(self):
         ops.embed_lookup(self.table, self.tokens, out=self.layer_in[0])
-        for L in range(c.layers):
-            r = L % self.R
-            x = self.layer_in[L]
-            ops.rmsnorm(x, p.norm_w("att", L), c.eps, out=self.xnorm[r])
-            ops.qknorm_rope(self.q[L], p.norm_w("q", L), c.head_dim, c.qk_eps, c.rope_base, 0, out=self.q_r[r])
-            ops.qknorm_rope(self.k[L], p.norm_w("k", L), c.head_dim, c.qk_eps, c.rope_base, 0, out=self.k_r[r])
-            ops.residual_rmsnorm(x, self.o_out[L], p.norm_w("ffn", L), c.alpha, c.eps, x2=self.x2[L], x2norm=self.x2norm[r])
-            ops.swiglu(self.h1[L], self.h3[L], out=self.gate[r])
-            ops.residual(self.x2[L], self.ffn_out[L], c.alpha, out=self.layer_in[L + 1])
+
+    def fwd_end(self):
+        c, p = self.cfg, self.p
         ops.rmsnorm(self.layer_in[c.layers], p.norm_w("final"), c.eps, out=self.x_final)
 
-    def backward(self):
+    def forward(self):
+        self.fwd_begin()
+        for L in range(self.cfg.layers):
+            self.fwd_layer(L)
+        self.fwd_end()
+
+    def bwd_begin(self):
+        c, p = self.cfg, self.p
+        self._cur = 0
+        self._dy = self.dy[0]
+        ops.rmsnorm_bwd(self.dy_cls, self.layer_in[c.layers], p.norm_w("final"), p.norm_w("final", grad=True), eps=c.eps,
+                        exact=c.exact_norm_bwd, out=self._dy)
+
+    def bwd_layer(self, L):
         c, p = self.cfg, self.p
         ex = c.exact_norm_bwd
-        dy = self.dy[0]
-        ops.rmsnorm_bwd(self.dy_cls, self.layer_in[c.layers], p.norm_w("final"), p.norm_w("final", grad=True), eps=c.eps,
-                        exact=ex, out=dy)
-        cur = 0
-        for L in range(c.layers - 1, -1, -1):
-            r = L % self.R
-            self._maybe_time("swiglu_bwd", lambda: ops.swiglu_bwd(self.h1[L], self.h3[L], self.dsilu[r], dh1=self.dh1[r], dh3=self.dh3[r]))
-            ops.rmsnorm_bwd(self.dx_ffn[r], self.x2[L], p.norm_w("ffn", L), p.norm_w("ffn", L, grad=True), add=dy, eps=c.eps,
-                            exact=ex, out=self.dx2)
-            ops.rope_qknorm_bwd(self.dq_in[r], self.q[L], p.norm_w("q", L), p.norm_w("q", L, grad=True), c.head_dim,
-                                c.qk_eps, c.rope_base, 0, exact=ex, out=self.dq[r])
-            ops.rope_qknorm_bwd(self.dk_in[r], self.k[L], p.norm_w("k", L), p.norm_w("k", L, grad=True), c.head_dim,
-                                c.qk_eps, c.rope_base, 0, exact=ex, out=self.dk[r])
-            nxt = self.dy[1 - cur]
-            ops.rmsnorm_bwd(self.dx_attn[r], self.layer_in[L], p.norm_w("att", L), p.norm_w("att", L, grad=True), add=self.dx2,
-                            eps=c.eps, exact=ex, out=nxt)
-            dy, cur = nxt, 1 - cur
-        ops.embed_backward(p.embed(grad=True), dy, self.tokens)
-        self.dy_out = dy
+        r = L % self.R
+        dy = self._dy
+        self._maybe_time("swiglu_bwd", lambda: ops.swiglu_bwd(self.h1[L], self.h3[L], self.dsilu[r], dh1=self.dh1[r], dh3=self.dh3[r]))
+        ops.rmsnorm_bwd(self.dx_ffn[r], self.x2[L], p.norm_w("ffn", L), p.norm_w("ffn", L, grad=True), add=dy, eps=c.eps,
+                        exact=ex, out=self.dx2)
+        ops.rope_qknorm_bwd(self.dq_in[r], self.q[L], p.norm_w("q", L), p.norm_w("q", L, grad=True), c.head_dim,
+                            c.qk_eps, c.rope_base, 0, exact=ex, out=self.dq[r])
+        ops.rope_qknorm_bwd(self.dk_in[r], self.k[L], p.norm_w("k", L), p.norm_w("k", L, grad=True), c.head_dim,
+                            c.qk_eps, c.rope_base, 0, exact=ex, out=self.dk[r])
+        nxt = self.dy[1 - self._cur]
+        ops.rmsnorm_bwd(self.dx_attn[r], self.layer_in[L], p.norm_w("att", L), p.norm_w("att", L, grad=True), add=self.dx2,
+                        eps=c.eps, exact=ex, out=nxt)
+        self._dy, self._cur = nxt, 1 - self._cur
+
+    def bwd_end(self):
+        ops.embed_backward(self.p.embed(grad=True), self._dy, self.tokens)
+        self.dy_out = self._dy
+
+    def backward(self):
+        self.bwd_begin()
+        for L in range(self.cfg.layers - 1, -1, -1):
+            self.bwd_layer(L)
+        self.bwd_end()
 
     # ------------------------------------------------------------------ CUDA graph replay
     def capture(self):

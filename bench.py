@@ -55,6 +55,7 @@ def parse_args():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     ap.add_argument("--cpu-seqs", type=int, default=2, help="sequences in the CPU sample")
+    ap.add_argument("--e2e-seqs", type=int, default=8, help="sequences per rank and step of the host-buffer (e2e) measurement")
     return ap.parse_args()
 
 
@@ -248,9 +249,28 @@ def workload_config(args, world):
 
 
 # ------------------------------------------------------------------------------------- e2e (host buffers)
-def e2e_chain(torch, cfg, n_seqs, steps, warmup):
-    """The chain through the host-buffer entry points on page-locked host tensors.  Per-layer host
-    buffers are shared between layers (the CPU side only provides and receives bytes)."""
+def e2e_chain(torch, cfg, params, device, n_seqs, steps, warmup):
+    """The chain with host buffers on the contraction side (ane_b200.host_chain.HostLayerChain): every tensor a matmul
+    or SDPA produces or consumes crosses PCIe inside the timed region, from / to page-locked host memory."""
+    from ane_b200.host_chain import HostLayerChain
+
+    hc = HostLayerChain(cfg, n_seqs, params, device)
+    for _ in range(warmup):
+        hc.step()
+    hc.synchronize()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        hc.step()
+    hc.synchronize()
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / steps
+    return n_seqs * cfg.seq / dt, hc.h2d_bytes_per_step, hc.d2h_bytes_per_step, dt
+
+
+def e2e_per_op(torch, cfg, n_seqs, steps, warmup):
+    """The same chain, every operator called on its own through the host-buffer entry points (ane_cuda_*_host): each call
+    stages its own inputs and outputs, so tensors the operators hand to each other cross PCIe too."""
     from ane_b200 import host_ops as hop
 
     S, D, H, Qd, KVd, hd = cfg.seq, cfg.dim, cfg.hidden, cfg.q_dim, cfg.kv_dim, cfg.head_dim
@@ -431,14 +451,21 @@ def run_ours(args):
         dist.barrier()
 
     if not args.no_e2e:
-        e2e_seqs = 4
-        tps, h2d, d2h, dt = e2e_chain(torch, cfg, e2e_seqs, steps=1, warmup=1)
+        e2e_seqs = args.e2e_seqs
+        tps, h2d, d2h, dt = e2e_chain(torch, cfg, params, device, e2e_seqs, steps=2, warmup=1)
         t = torch.tensor([tps], device=device)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.SUM)
         line["e2e"] = {"value": round(float(t[0]), 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                       "note": f"chain through ane_cuda_*_host on pinned host tensors, {e2e_seqs} sequences x 2048 tokens per rank and step "
-                               f"({dt*1e3:.0f} ms); PCIe-bound"}
+                       "note": f"HostLayerChain.step(): {e2e_seqs} sequences x 2048 tokens per rank and step ({dt*1e3:.0f} ms); every "
+                               "contraction-side tensor of every layer is copied from / to page-locked host memory inside the timed "
+                               f"region ({(h2d + d2h) / dt / 1e9:.1f} GB/s over PCIe, both directions); PCIe-bound"}
+        torch.cuda.empty_cache()
+        if rank == 0 and world == 1 and not args.no_ops:
+            tps2, h2d2, d2h2, dt2 = e2e_per_op(torch, cfg, 4, steps=1, warmup=1)
+            line["e2e_per_op_calls"] = {"value": round(tps2, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d2), "d2h_bytes_per_step": int(d2h2),
+                                        "note": "the same chain as one ane_cuda_*_host call per operator (4 sequences; each call stages its own "
+                                                "operands, also the ones operators hand to each other)"}
 
     if rank == 0:
         if not args.no_cpu and world == 1:

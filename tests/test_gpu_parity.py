@@ -661,3 +661,47 @@ def test_layer_chain_matches_oracle_and_graph_replay(dev, oracle):
     torch.cuda.synchronize()
     assert np.array_equal(n(ch.dy_out), eager["dy"]) and np.array_equal(n(ch.x_final), eager["xf"])
     assert np.array_equal(n(p.g[p.n_matrix:p.n]), eager["g"])
+
+
+@pytest.mark.gpu
+def test_host_layer_chain_equals_device_chain(dev):
+    """HostLayerChain.step() (contraction-side tensors in page-locked host memory, three streams) hands back
+    bit for bit what the device-resident chain computes from the same inputs, over two consecutive steps
+    (the second one reuses every buffer and event of the first)."""
+    torch = _torch()
+    from ane_b200.host_chain import HostLayerChain
+    from ane_b200.layer_chain import ChainConfig, FlatParams, LayerChain
+    cfg = ChainConfig(layers=5, dim=64, hidden=96, heads=2, kv_heads=1, head_dim=64, seq=32, vocab=50,
+                      dtype=torch.bfloat16, alpha=0.5, rope_base=1e4)
+    p = FlatParams(cfg, "cuda")
+    p.init_random(seed=3)
+    hc = HostLayerChain(cfg, 2, p, "cuda", rotate=2)
+    for _ in range(2):
+        p.zero_produced_grads()
+        hc.step()
+        hc.synchronize()
+        torch.cuda.synchronize()
+        g_host = p.g.clone()
+        # the same inputs through a device-resident chain (every layer sees the same host bytes)
+        p.zero_produced_grads()
+        ref = LayerChain(cfg, 2, p, "cuda", rotate=2)
+        ref.tokens.copy_(hc.h_tokens)
+        ref.dy_cls.copy_(hc.h_dy_cls)
+        for L in range(cfg.layers):
+            for k, h in hc.h_in_f.items():
+                getattr(ref, k)[L].copy_(h)
+        ref.forward()
+        torch.cuda.synchronize()
+        r_last = (cfg.layers - 1) % ref.R
+        for k, h in hc.h_out_f.items():                      # the shared host buffers hold the last layer's products
+            assert torch.equal(h.cuda(), getattr(ref, k)[r_last]), k
+        assert torch.equal(hc.h_x_final.cuda(), ref.x_final)
+        for r in range(ref.R):
+            for k, h in hc.h_in_b.items():
+                getattr(ref, k)[r].copy_(h)
+        ref.backward()
+        torch.cuda.synchronize()
+        for k, h in hc.h_out_b.items():                      # backward ends at layer 0
+            assert torch.equal(h.cuda(), getattr(ref, k)[0]), k
+        assert torch.equal(g_host, p.g)                      # norm-weight and embedding gradients
+    assert hc.h2d_bytes_per_step == 2 * 32 * 2 * (5 * (128 + 64 + 64 + 192 + 64 + 96 + 64 + 128 + 64 + 64) + 64) + 2 * 32 * 4
