@@ -247,19 +247,31 @@ rmsnorm_bwd_pair_kernel(T *dx, float *__restrict__ partial, const T *dy, const T
     for (int c = threadIdx.x; c < Cn; c += ST_THREADS) dwacc[c] = 0.0f;
     __syncthreads();
 
-    int it = 0;
-    for (int tile = pair; tile < ntiles; tile += npairs, it ^= 1) {
+    // The strips are software-pipelined across tiles without any extra barrier: a strip entry is only ever touched
+    // by the thread that copied it, so as soon as sweep 2 has read an entry the same thread issues the copy of the
+    // NEXT tile's element into it.  By the end of sweep 2 the whole next tile is in flight.
+    auto tile_base = [&](int tile, bool &act) -> size_t {
         const int b = tile / tiles_per_seq;
         const int t = (tile % tiles_per_seq) * TW + lg * VEC;
-        const bool active = t < S;
-        const size_t base = ((size_t)b * C + c0) * S + t;
-
-        if (active)
+        act = t < S;
+        return ((size_t)b * C + c0) * S + t;
+    };
+    {
+        bool act0;
+        const size_t base0 = pair < ntiles ? tile_base(pair, act0) : 0;
+        if (pair < ntiles && act0)
             for (int c = rg; c < Cn; c += R) {
-                cp_async16(&sx[c * LG + lg], x + base + (size_t)c * S);
-                cp_async16(&sd[c * LG + lg], dy + base + (size_t)c * S);
+                cp_async16(&sx[c * LG + lg], x + base0 + (size_t)c * S);
+                cp_async16(&sd[c * LG + lg], dy + base0 + (size_t)c * S);
             }
         cp_async_commit();
+    }
+    int it = 0;
+    for (int tile = pair; tile < ntiles; tile += npairs, it ^= 1) {
+        bool active, nactive = false;
+        const size_t base = tile_base(tile, active);
+        const bool has_next = tile + npairs < ntiles;
+        const size_t nbase = has_next ? tile_base(tile + npairs, nactive) : 0;
         cp_async_wait_all();             // each thread reads back only what it copied itself
 
         V<VEC> ss = V<VEC>::splat(0.0f), dot = V<VEC>::splat(0.0f);
@@ -321,6 +333,10 @@ rmsnorm_bwd_pair_kernel(T *dx, float *__restrict__ partial, const T *dy, const T
                     rx.v = sx[c * LG + lg];
                     rd.v = sd[c * LG + lg];
                     const V<VEC> xv = rx.get(), dv = rd.get();
+                    if (nactive) {       // this entry is free now: bring in the next tile's element
+                        cp_async16(&sx[c * LG + lg], x + nbase + (size_t)c * S);
+                        cp_async16(&sd[c * LG + lg], dy + nbase + (size_t)c * S);
+                    }
                     const float wc = __ldg(w + c0 + c);
                     V<VEC> o;
                     if (exact) o = vmul(vsub(vscale(dv, wc), vmul(xv, coef)), rr);
@@ -336,8 +352,15 @@ rmsnorm_bwd_pair_kernel(T *dx, float *__restrict__ partial, const T *dy, const T
                 if (lg == 0 && c < Cn) dwacc[c] += dwp;  // row group rg is the only writer of channel c
             }
         }
-        // the strips are rewritten by this thread's own copies only; red/tot/xch[it] are next written
-        // after the following tile's barriers, which every thread of the pair reaches after this point
+        if (!active && nactive) {        // this thread skipped sweep 2: issue its copies of the next tile here
+            for (int c = rg; c < Cn; c += R) {
+                cp_async16(&sx[c * LG + lg], x + nbase + (size_t)c * S);
+                cp_async16(&sd[c * LG + lg], dy + nbase + (size_t)c * S);
+            }
+        }
+        cp_async_commit();
+        // red/tot/xch[it] are next written after the following tile's barriers, which every thread of the pair
+        // reaches after this point
     }
     __syncthreads();
     for (int c = threadIdx.x; c < Cn; c += ST_THREADS) partial[(size_t)pair * C + c0 + c] = dwacc[c];
