@@ -9,7 +9,6 @@
 // twice: an online (max, sum) pass, then the pass that writes dlogits.  Loss terms go to a
 // per-token scratch array and are summed per sequence in a fixed order by a second kernel.
 #include "common.cuh"
-#include "tma.cuh"
 
 #include <cooperative_groups.h>
 #include <math.h>
@@ -255,128 +254,136 @@ __device__ __forceinline__ float4 xent_finish(const float (&e)[4], int v, const 
     return make_float4(p[0], p[1], p[2], p[3]);
 }
 
+__device__ __forceinline__ void xc_cp_async16(void *smem_dst, const void *gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void xc_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void xc_cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// Persistent clusters: cluster i takes stripes i, i + clusters, ...  The resident part of a block's slice is an
+// array of 16-byte entries, each touched by ONE thread only (it copies the entry in, sweeps it three times, and
+// -- as soon as the last sweep has read it -- copies the NEXT stripe's element into it), so the stripes are
+// software-pipelined without any barrier beyond the one cluster barrier per stripe.
 template <typename ID, int THREADS>
 __global__ void __cluster_dims__(XC_CL, 1, 1) __launch_bounds__(THREADS, 1024 / THREADS)
-xent_cluster_kernel(const __grid_constant__ CUtensorMap lmap, float *dlogits, const float *logits,
-                    const void *__restrict__ targets, float *__restrict__ loss_tok, int V, int S, int stripes_per_seq,
-                    int rows_per_cta, int rows_res, float grad_scale, ane_cuda_status *status) {
+xent_cluster_kernel(float *dlogits, const float *logits, const void *__restrict__ targets, float *__restrict__ loss_tok,
+                    int V, int S, int stripes_per_seq, int nstripes, int rows_per_cta, int rows_res, float grad_scale,
+                    ane_cuda_status *status) {
     constexpr int R = THREADS / XC_LG;
     constexpr int NW = THREADS / 32;
     extern __shared__ uint8_t xc_raw[];
-    __shared__ uint64_t bar[XC_MAXBOX];
     __shared__ float2 red[NW][XC_TW];
-    __shared__ float2 part[XC_TW];        // this block's (max, sum) per token; peers read it
+    __shared__ float2 part[2][XC_TW];     // [stripe parity]: this block's (max, sum) per token; peers read it
     __shared__ float2 fin[XC_TW];         // (max, 1/sum) over the whole vocabulary
-    __shared__ int gave_up;
 
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned rank = cluster.block_rank();
     float4 *res = reinterpret_cast<float4 *>((reinterpret_cast<uintptr_t>(xc_raw) + 127) & ~(uintptr_t)127);   // [rows][XC_LG]
 
-    const int stripe = blockIdx.x / XC_CL;
-    const int b = stripe / stripes_per_seq;
-    const int t0 = (stripe % stripes_per_seq) * XC_TW;
     const int lg = threadIdx.x % XC_LG, rg = threadIdx.x / XC_LG;
-    const int t = t0 + lg * 4;
-    const bool active = t < S;
     const int v0 = (int)rank * rows_per_cta;
     const int v1 = v0 + rows_per_cta < V ? v0 + rows_per_cta : V;
     const int rows = v1 > v0 ? v1 - v0 : 0;
     const int nres = rows < rows_res ? rows : rows_res;
-    const int nbox = (nres + XC_BOXR - 1) / XC_BOXR;
-    const size_t base = (size_t)b * V * S + t;
+    const int cid = blockIdx.x / XC_CL, ncl = gridDim.x / XC_CL;
 
-    if (threadIdx.x == 0) {
-        gave_up = 0;
-        for (int k = 0; k < nbox; k++) mbar_init(&bar[k], 1);
-        mbar_init_fence();
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int k = 0; k < nbox; k++) {
-            mbar_arrive_expect_tx(&bar[k], XC_BOXR * XC_TW * 4);
-            tma_load_3d(res + (size_t)k * XC_BOXR * XC_LG, &lmap, t0, v0 + k * XC_BOXR, b, &bar[k]);
+    auto stripe_base = [&](int stripe, bool &act, int &b, int &t) -> size_t {
+        b = stripe / stripes_per_seq;
+        t = (stripe % stripes_per_seq) * XC_TW + lg * 4;
+        act = t < S;
+        return (size_t)b * V * S + t;
+    };
+    {   // first stripe's resident rows
+        bool act;
+        int b, t;
+        if (cid < nstripes) {
+            const size_t base0 = stripe_base(cid, act, b, t);
+            if (act)
+                for (int q = rg; q < nres; q += R) xc_cp_async16(&res[q * XC_LG + lg], logits + base0 + (size_t)(v0 + q) * S);
         }
+        xc_cp_async_commit();
     }
 
-    // ---- sweep 1a: rows that do not fit in shared memory, through registers (they stay in L2)
-    Ms4 ms;
-    ms_init(ms);
-    for (int vb = v0 + nres; vb < v1; vb += R * XC_U) {
-        float4 r[XC_U];
-        bool ok[XC_U];
+    int par = 0;
+    for (int stripe = cid; stripe < nstripes; stripe += ncl, par ^= 1) {
+        bool active, nactive = false;
+        int b, t, nb, nt;
+        const size_t base = stripe_base(stripe, active, b, t);
+        const bool has_next = stripe + ncl < nstripes;
+        const size_t nbase = has_next ? stripe_base(stripe + ncl, nactive, nb, nt) : 0;
+
+        // ---- sweep 1a: rows that do not fit in shared memory, through registers (they stay in L2)
+        Ms4 ms;
+        ms_init(ms);
+        for (int vb = v0 + nres; vb < v1; vb += R * XC_U) {
+            float4 r[XC_U];
+            bool ok[XC_U];
 #pragma unroll
-        for (int u = 0; u < XC_U; u++) {
-            const int v = vb + u * R + rg;
-            ok[u] = active && v < v1;
-            if (ok[u]) r[u] = *reinterpret_cast<const float4 *>(logits + base + (size_t)v * S);
+            for (int u = 0; u < XC_U; u++) {
+                const int v = vb + u * R + rg;
+                ok[u] = active && v < v1;
+                if (ok[u]) r[u] = *reinterpret_cast<const float4 *>(logits + base + (size_t)v * S);
+            }
+            ms_fold<XC_U>(ms, r, ok);
         }
-        ms_fold<XC_U>(ms, r, ok);
-    }
-    // ---- sweep 1b: maximum over this thread's resident rows, as their boxes land
-    bool bad = false;
-    float gm[4] = {ms.m[0], ms.m[1], ms.m[2], ms.m[3]};
-    for (int k = 0; k < nbox; k++) {
-        if (!mbar_wait_bounded(&bar[k], 0)) { bad = true; break; }
-        const int lim = nres - k * XC_BOXR < XC_BOXR ? nres - k * XC_BOXR : XC_BOXR;
-        const float4 *bx = res + (size_t)k * XC_BOXR * XC_LG;
-#pragma unroll 2
-        for (int q = rg; q < lim; q += R) {
-            const float4 r = bx[q * XC_LG + lg];
-            gm[0] = fmaxf(gm[0], r.x); gm[1] = fmaxf(gm[1], r.y); gm[2] = fmaxf(gm[2], r.z); gm[3] = fmaxf(gm[3], r.w);
-        }
-    }
-    if (bad) gave_up = 1;       // benign race: every writer stores 1
-    ms_raise(ms, gm);
-    // ---- sweep 1c: e = exp(l - m_thread) replaces l in shared memory; the sum accumulates
-    if (!bad) {
-        const float n0 = -ms.m[0] * XC_LOG2E, n1 = -ms.m[1] * XC_LOG2E, n2 = -ms.m[2] * XC_LOG2E, n3 = -ms.m[3] * XC_LOG2E;
+        xc_cp_async_wait_all();           // this thread's resident entries have landed
+        // ---- sweep 1b: maximum over this thread's resident rows
+        float gm[4] = {ms.m[0], ms.m[1], ms.m[2], ms.m[3]};
+        if (active) {
 #pragma unroll 4
-        for (int q = rg; q < nres; q += R) {
-            float4 r = res[q * XC_LG + lg];
-            r.x = ex2_approx(fmaf(r.x, XC_LOG2E, n0)); r.y = ex2_approx(fmaf(r.y, XC_LOG2E, n1));
-            r.z = ex2_approx(fmaf(r.z, XC_LOG2E, n2)); r.w = ex2_approx(fmaf(r.w, XC_LOG2E, n3));
-            ms.s[0] += r.x; ms.s[1] += r.y; ms.s[2] += r.z; ms.s[3] += r.w;
-            res[q * XC_LG + lg] = r;                 // only this thread ever touches this entry again
+            for (int q = rg; q < nres; q += R) {
+                const float4 r = res[q * XC_LG + lg];
+                gm[0] = fmaxf(gm[0], r.x); gm[1] = fmaxf(gm[1], r.y); gm[2] = fmaxf(gm[2], r.z); gm[3] = fmaxf(gm[3], r.w);
+            }
         }
-    }
-    const float mt[4] = {ms.m[0], ms.m[1], ms.m[2], ms.m[3]};      // the reference point of this thread's e values
+        ms_raise(ms, gm);
+        // ---- sweep 1c: e = exp(l - m_thread) replaces l in shared memory; the sum accumulates
+        if (active) {
+            const float n0 = -ms.m[0] * XC_LOG2E, n1 = -ms.m[1] * XC_LOG2E, n2 = -ms.m[2] * XC_LOG2E, n3 = -ms.m[3] * XC_LOG2E;
+#pragma unroll 4
+            for (int q = rg; q < nres; q += R) {
+                float4 r = res[q * XC_LG + lg];
+                r.x = ex2_approx(fmaf(r.x, XC_LOG2E, n0)); r.y = ex2_approx(fmaf(r.y, XC_LOG2E, n1));
+                r.z = ex2_approx(fmaf(r.z, XC_LOG2E, n2)); r.w = ex2_approx(fmaf(r.w, XC_LOG2E, n3));
+                ms.s[0] += r.x; ms.s[1] += r.y; ms.s[2] += r.z; ms.s[3] += r.w;
+                res[q * XC_LG + lg] = r;
+            }
+        }
+        const float mt[4] = {ms.m[0], ms.m[1], ms.m[2], ms.m[3]};      // the reference point of this thread's e values
 
-    // ---- block (max, sum): row groups of a warp by shuffles, warps through shared memory
+        // ---- block (max, sum): row groups of a warp by shuffles, warps through shared memory
 #pragma unroll
-    for (int off = XC_LG; off < 32; off <<= 1) {
+        for (int off = XC_LG; off < 32; off <<= 1) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float m2 = __shfl_xor_sync(0xffffffffu, ms.m[j], off);
-            const float s2 = __shfl_xor_sync(0xffffffffu, ms.s[j], off);
-            ms_merge(ms.m[j], ms.s[j], m2, s2);
+            for (int j = 0; j < 4; j++) {
+                const float m2 = __shfl_xor_sync(0xffffffffu, ms.m[j], off);
+                const float s2 = __shfl_xor_sync(0xffffffffu, ms.s[j], off);
+                ms_merge(ms.m[j], ms.s[j], m2, s2);
+            }
         }
-    }
-    if ((threadIdx.x & 31) < XC_LG) {
+        if ((threadIdx.x & 31) < XC_LG) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) red[threadIdx.x >> 5][lg * 4 + j] = make_float2(ms.m[j], ms.s[j]);
-    }
-    __syncthreads();
-    if (threadIdx.x < XC_TW) {
-        float m = -INFINITY, s = 0.0f;
-        for (int q = 0; q < NW; q++) ms_merge(m, s, red[q][threadIdx.x].x, red[q][threadIdx.x].y);
-        part[threadIdx.x] = make_float2(m, s);
-    }
-    cluster.sync();                                   // every block's pair is published
-    if (threadIdx.x < XC_TW) {
-        float m = -INFINITY, s = 0.0f;
-        for (unsigned q = 0; q < XC_CL; q++) {        // fixed rank order: all blocks get the same bits
-            const float2 pq = cluster.map_shared_rank(part, q)[threadIdx.x];
-            ms_merge(m, s, pq.x, pq.y);
+            for (int j = 0; j < 4; j++) red[threadIdx.x >> 5][lg * 4 + j] = make_float2(ms.m[j], ms.s[j]);
         }
-        fin[threadIdx.x] = make_float2(m, 1.0f / s);                                 // inv_sum, stories_cpu_ops.h:91-92
-    }
-    cluster.barrier_arrive();                         // done reading peers; matched by the wait before exit
-    __syncthreads();
+        __syncthreads();
+        if (threadIdx.x < XC_TW) {
+            float m = -INFINITY, s = 0.0f;
+            for (int q = 0; q < NW; q++) ms_merge(m, s, red[q][threadIdx.x].x, red[q][threadIdx.x].y);
+            part[par][threadIdx.x] = make_float2(m, s);
+        }
+        cluster.sync();                                   // every block's pair is published (also a block barrier)
+        if (threadIdx.x < XC_TW) {
+            float m = -INFINITY, s = 0.0f;
+            for (unsigned q = 0; q < XC_CL; q++) {        // fixed rank order: all blocks get the same bits
+                const float2 pq = cluster.map_shared_rank(&part[0][0], q)[par * XC_TW + threadIdx.x];
+                ms_merge(m, s, pq.x, pq.y);
+            }
+            fin[threadIdx.x] = make_float2(m, 1.0f / s);                                 // inv_sum, stories_cpu_ops.h:91-92
+        }
+        __syncthreads();
+        // part[par] is written again two stripes later, after the next stripe's cluster barrier, which every block
+        // reaches only after these reads; fin and red are rewritten after this stripe's sweep 2 (barriers above).
 
-    if (gave_up) {
-        if (threadIdx.x == 0) atomicAdd(&status->wait_giveups, 1);
-    } else {
         XentRowOut o;
         float negML[4], rel[4];
         o.invS = 1.0f / (float)S;
@@ -423,7 +430,8 @@ xent_cluster_kernel(const __grid_constant__ CUtensorMap lmap, float *dlogits, co
                 }
             }
         }
-        // ---- sweep 2b: resident rows from shared memory: e values relative to this thread's maximum
+        // ---- sweep 2b: resident rows from shared memory (e values relative to this thread's maximum); every entry
+        // is refilled with the next stripe's element as soon as it has been read
         if (active) {
 #pragma unroll
             for (int j = 0; j < 4; j++) { o.scale[j] *= rel[j]; o.inv[j] *= rel[j]; }
@@ -431,11 +439,15 @@ xent_cluster_kernel(const __grid_constant__ CUtensorMap lmap, float *dlogits, co
             for (int q = rg; q < nres; q += R) {
                 const float4 r = res[q * XC_LG + lg];
                 const float e[4] = {r.x, r.y, r.z, r.w};
+                if (nactive) xc_cp_async16(&res[q * XC_LG + lg], logits + nbase + (size_t)(v0 + q) * S);
                 __stcs(reinterpret_cast<float4 *>(dlogits + base + (size_t)(v0 + q) * S), xent_finish(e, v0 + q, o));
             }
+        } else if (nactive) {
+            for (int q = rg; q < nres; q += R) xc_cp_async16(&res[q * XC_LG + lg], logits + nbase + (size_t)(v0 + q) * S);
         }
+        xc_cp_async_commit();
     }
-    cluster.barrier_wait();                           // peers may still be reading `part`
+    cluster.sync();                                       // peers may still be reading `part`
 }
 
 // loss_seq[b] = (sum_t loss_tok[b][t]) / S, fixed summation tree.
@@ -473,24 +485,36 @@ int ane_cuda_cross_entropy_dev(void *stream, ane_idtype idtype, int B, int V, in
     ane_cuda_status *status = ctx().status;
     const bool vec = (S % 4 == 0) && aligned16(dlogits) && aligned16(logits);
     if (vec && tuning("xent_cluster", 0) && V >= 4096 && S % XC_TW == 0) {
-        // a cluster of 8 blocks per 16-token stripe, most of the stripe resident in shared memory
+        // persistent clusters of 8 blocks per 16-token stripe, most of the stripe resident in shared memory.  In-place
+        // use (dlogits == logits) is fine: a stripe is read, prefetched and written by one cluster only.
         const int threads = tuning("xent_threads", 1024) == 512 ? 512 : 1024;
         const int sps = S / XC_TW;
         const long long nstripes = (long long)B * sps;
         const int rows_per_cta = (V + XC_CL - 1) / XC_CL;
-        int rows_res = ((rows_per_cta + XC_BOXR - 1) / XC_BOXR) * XC_BOXR;
-        const int cap = tuning("xent_boxes", threads == 512 ? 6 : 12);  // 12 boxes = 192 KB
+        const int cap = tuning("xent_boxes", threads == 512 ? 6 : 12);  // 16 KB units; 12 = 192 KB
+        int rows_res = rows_per_cta;
         if (rows_res > cap * XC_BOXR) rows_res = cap * XC_BOXR;
         const size_t smem = (size_t)rows_res * XC_TW * sizeof(float) + 128;
-        CUtensorMap lmap;
-        if (nstripes * XC_CL < 0x7fffffffLL && cap >= 0 && cap <= XC_MAXBOX - 1 &&
-            make_bcs_tensor_map(&lmap, ANE_F32, logits, B, V, S, XC_TW, XC_BOXR, 64) == ANE_CUDA_OK) {
-            void (*kern)(const CUtensorMap, float *, const float *, const void *, float *, int, int, int, int, int, float, ane_cuda_status *);
+        if (nstripes < 0x7fffffffLL && cap >= 0 && cap <= XC_MAXBOX - 1) {
+            void (*kern)(float *, const float *, const void *, float *, int, int, int, int, int, int, float, ane_cuda_status *);
             if (threads == 512) kern = idtype == ANE_ID_U16 ? xent_cluster_kernel<uint16_t, 512> : xent_cluster_kernel<int32_t, 512>;
             else kern = idtype == ANE_ID_U16 ? xent_cluster_kernel<uint16_t, 1024> : xent_cluster_kernel<int32_t, 1024>;
             ANE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            kern<<<(unsigned)(nstripes * XC_CL), threads, smem, st>>>(lmap, dlogits, logits, targets, loss_tok, V, S, sps, rows_per_cta,
-                                                                    rows_res, grad_scale, status);
+            // how many clusters can be resident at once
+            cudaLaunchConfig_t cfgq = {};
+            cfgq.gridDim = dim3(XC_CL * 64);
+            cfgq.blockDim = dim3(threads);
+            cfgq.dynamicSmemBytes = smem;
+            cudaLaunchAttribute at;
+            at.id = cudaLaunchAttributeClusterDimension;
+            at.val.clusterDim.x = XC_CL; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+            cfgq.attrs = &at;
+            cfgq.numAttrs = 1;
+            int max_clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfgq) != cudaSuccess || max_clusters < 1) { cudaGetLastError(); max_clusters = 8; }
+            int ncl = (long long)max_clusters < nstripes ? max_clusters : (int)nstripes;
+            kern<<<(unsigned)(ncl * XC_CL), threads, smem, st>>>(dlogits, logits, targets, loss_tok, V, S, sps, (int)nstripes, rows_per_cta,
+                                                                rows_res, grad_scale, status);
             xent_loss_kernel<<<B, 256, 0, st>>>(loss_seq, loss_tok, S);
             ANE_LAUNCH_OK(2);
             return ANE_CUDA_OK;
