@@ -307,6 +307,38 @@ __device__ __forceinline__ V<N> warp_rowgroup_sum(V<N> v) {
     return v;
 }
 
+// out[c] += sum over rows r of partial[r][c], in a fixed order: 32 columns x 8 row slices per block, every thread
+// walks its slice with eight independent loads in flight, the slices are added in slice order.  (One thread per
+// column walking all rows took 19 us for 444 x 1024 partials: a chain of dependent-latency loads.)
+template <int UNUSED = 0>
+__global__ void __launch_bounds__(256) column_sum_add_kernel(float *__restrict__ out, const float *__restrict__ partial, int rows, int cols) {
+    __shared__ float acc[8][32];
+    const int cl = threadIdx.x & 31, sl = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cl;
+    const int per = (rows + 7) / 8;
+    const int r0 = sl * per, r1 = r0 + per < rows ? r0 + per : rows;
+    float s = 0.0f;
+    if (c < cols) {
+        int r = r0;
+        for (; r + 8 <= r1; r += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) v[u] = partial[(size_t)(r + u) * cols + c];
+#pragma unroll
+            for (int u = 0; u < 8; u++) s += v[u];
+        }
+        for (; r < r1; r++) s += partial[(size_t)r * cols + c];
+    }
+    acc[sl][cl] = s;
+    __syncthreads();
+    if (sl == 0 && c < cols) {
+        float t = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 8; q++) t += acc[q][cl];
+        out[c] += t;
+    }
+}
+
 // A group of VEC consecutive elements held raw: one 16-byte word when VEC is the full vector
 // width of T, one element when VEC == 1 (the path for shapes that break 16-byte alignment).
 template <typename T, int VEC> struct Raw;

@@ -353,15 +353,6 @@ rmsnorm_bwd_apply_kernel(T *dx, float *__restrict__ partial, const T *dy, const 
     }
 }
 
-// dw[c] += sum over blocks, in block order.
-__global__ void dw_finalize_kernel(float *__restrict__ dw, const float *__restrict__ partial, int nblocks, int C) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
-    float s = 0.0f;
-    for (int b = 0; b < nblocks; b++) s += partial[(size_t)b * C + c];
-    dw[c] += s;
-}
-
 template <typename T, bool FUSE_RES>
 static int launch_rmsnorm_fwd(cudaStream_t st, int B, int C, int S, void *out, void *x2, const void *x, const void *f,
                               const float *w, float alpha, float eps) {
@@ -449,7 +440,7 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
             partial = static_cast<float *>(workspace((size_t)grid * C * sizeof(float)));                            \
             if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", grid, C); \
             k_<<<grid, THv, smem, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags); \
-            dw_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(dw, partial, grid, C);                              \
+            column_sum_add_kernel<><<<(C + 31) / 32, 256, 0, st>>>(dw, partial, grid, C);                              \
             ANE_LAUNCH_OK(2);                                                                                       \
             return ANE_CUDA_OK;                                                                                     \
         } while (0)
@@ -477,7 +468,7 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
             partial = static_cast<float *>(workspace((size_t)npairs * C * sizeof(float)));
             if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", npairs, C);
             k_<<<(unsigned)(2 * npairs), ST_THREADS, smem_st, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags);
-            dw_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(dw, partial, npairs, C);
+            column_sum_add_kernel<><<<(C + 31) / 32, 256, 0, st>>>(dw, partial, npairs, C);
             ANE_LAUNCH_OK(2);
             return ANE_CUDA_OK;
         }
@@ -494,7 +485,7 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
             partial = static_cast<float *>(workspace((size_t)nblk * C * sizeof(float)));
             if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", nblk, C);
             k_<<<(unsigned)nblk, ST_THREADS, smem_st, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags);
-            dw_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(dw, partial, nblk, C);
+            column_sum_add_kernel<><<<(C + 31) / 32, 256, 0, st>>>(dw, partial, nblk, C);
             ANE_LAUNCH_OK(2);
             return ANE_CUDA_OK;
         }
@@ -525,7 +516,7 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
             else
                 rmsnorm_bwd_apply_kernel<T, VEC, HAS_ADD, 2, 3><<<(unsigned)blocks, NORM_THREADS, 0, st>>>(
                     (T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, stat_rr, stat_coef, C, S, segs, row_chunks, nwarps, flags);
-            dw_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(dw, partial, (int)nseg, C);
+            column_sum_add_kernel<><<<(C + 31) / 32, 256, 0, st>>>(dw, partial, (int)nseg, C);
             ANE_LAUNCH_OK(3);
             return ANE_CUDA_OK;
         }
@@ -556,7 +547,7 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
         k<<<grid, NORM_THREADS, smem, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps,
                                             ntiles, eps, flags);
     }
-    dw_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(dw, partial, grid, C);
+    column_sum_add_kernel<><<<(C + 31) / 32, 256, 0, st>>>(dw, partial, grid, C);
     ANE_LAUNCH_OK(2);
     return ANE_CUDA_OK;
 }
@@ -649,7 +640,7 @@ static int launch_rmsnorm_bwd_static(cudaStream_t st, float *partial, int sm_cou
         rmsnorm_bwd_kernel<T, 1, LG, HAS_ADD><<<grid, NORM_THREADS, smem, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w,
                                                                                (const T *)add, C, S, tps, ntiles, eps, flags);
     }
-    dw_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(dw, partial, grid, C);
+    column_sum_add_kernel<><<<(C + 31) / 32, 256, 0, st>>>(dw, partial, grid, C);
     ANE_LAUNCH_OK(2);
     return ANE_CUDA_OK;
 }

@@ -659,14 +659,6 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
     }
 }
 
-__global__ void qk_dw_finalize_kernel(float *__restrict__ dw, const float *__restrict__ partial, int nblocks, int hd) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= hd) return;
-    float s = 0.0f;
-    for (int b = 0; b < nblocks; b++) s += partial[(size_t)b * hd + c];
-    dw[c] += s;
-}
-
 // ------------------------------------------------------------------ fused kernels, any head width
 // One thread per (sequence, head, token), scalar loads that coalesce along S.  Used for head
 // widths and alignments the register-resident kernels above do not cover; same arithmetic, so a
@@ -793,7 +785,7 @@ static int launch_qk_rope_bwd_generic(cudaStream_t st, int B, int heads, int hd,
     if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rope_qknorm_bwd: no scratch");
     qk_rope_bwd_generic_kernel<T><<<(unsigned)blocks, QKG_THREADS, 0, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, hd, S,
                                                                            total, eps, pos0, flags, fq);
-    qk_dw_finalize_kernel<<<(hd + 127) / 128, 128, 0, st>>>(dw, partial, (int)blocks, hd);
+    column_sum_add_kernel<><<<(hd + 31) / 32, 256, 0, st>>>(dw, partial, (int)blocks, hd);
     ANE_LAUNCH_OK(2);
     return ANE_CUDA_OK;
 }
@@ -929,7 +921,7 @@ static int launch_qk_bwd(cudaStream_t st, int B, int heads, int hd, int S, void 
         if (hd == 128) { if (hb == 3) ANE_QKB_TMA(4, 3); else ANE_QKB_TMA(4, 4); }
         else { if (hb == 3) ANE_QKB_TMA(2, 3); else ANE_QKB_TMA(2, 4); }
 #undef ANE_QKB_TMA
-        qk_dw_finalize_kernel<<<(hd + 127) / 128, 128, 0, st>>>(dw, partial, grid, hd);
+        column_sum_add_kernel<><<<(hd + 31) / 32, 256, 0, st>>>(dw, partial, grid, hd);
         ANE_LAUNCH_OK(2);
         return ANE_CUDA_OK;
     }
@@ -945,7 +937,7 @@ static int launch_qk_bwd(cudaStream_t st, int B, int heads, int hd, int S, void 
     if (hd == 128) ANE_QKB(4, 1);
     else ANE_QKB(2, 1);
 #undef ANE_QKB
-    qk_dw_finalize_kernel<<<(hd + 127) / 128, 128, 0, st>>>(dw, partial, grid, hd);
+    column_sum_add_kernel<><<<(hd + 31) / 32, 256, 0, st>>>(dw, partial, grid, hd);
     ANE_LAUNCH_OK(2);
     return ANE_CUDA_OK;
 }
