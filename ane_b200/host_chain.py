@@ -79,7 +79,11 @@ class HostLayerChain:
                 self.e_in_f[l].record(s_in)
         with torch.cuda.stream(s_c):
             s_c.wait_event(self.e_misc_in)
-            ch.fwd_begin()
+            ch.fwd_begin()                                  # gather + the first layer's attention norm
+            self.e_fwd_done.record(s_c)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(self.e_fwd_done)
+                self.h_out_f["xnorm"].copy_(ch.xnorm[0], **nb)
             for l in range(L):
                 s_c.wait_event(self.e_in_f[l])
                 if l >= R:
@@ -90,7 +94,10 @@ class HostLayerChain:
                     s_out.wait_event(self.e_c_f[l])
                     r = l % R
                     for k, h in self.h_out_f.items():
-                        h.copy_(getattr(ch, k)[r], **nb)
+                        if k != "xnorm":
+                            h.copy_(getattr(ch, k)[r], **nb)
+                        elif l + 1 < L:                     # layer l closes with the NEXT layer's attention norm
+                            h.copy_(ch.xnorm[(l + 1) % R], **nb)
                     self.e_out_f[l].record(s_out)
             ch.fwd_end()
             self.e_fwd_done.record(s_c)

@@ -47,6 +47,7 @@ class ChainConfig:
     rope_base: float = 1e6
     alpha: float = (2.0 * 28) ** -0.5      # train.m:188, 1/sqrt(2*NLAYERS)
     exact_norm_bwd: bool = False
+    fuse_layer_boundary: bool = True   # closing residual of a layer fused with the norm that reads it next
 
     @property
     def q_dim(self) -> int:
@@ -62,16 +63,17 @@ class ChainConfig:
 
     def bytes_per_token_layer(self) -> int:
         """Algorithmic HBM bytes per token and layer of the chain above (every tensor crosses
-        HBM once per operator): forward 2D + 2(Qd+KVd) + 4D + 3H + 3D elements, backward
+        HBM once per operator): forward 2(Qd+KVd) + 4D + 3H + 4D elements (two fused residual + norm
+        operators; the first layer's attention norm is counted with the ends), backward
         5H + 4D + 3(Qd+KVd) + 4D elements."""
         e = torch.empty((), dtype=self.dtype).element_size()
         d, h, qk = self.dim, self.hidden, self.q_dim + self.kv_dim
-        fwd = 2 * d + 2 * qk + 4 * d + 3 * h + 3 * d
+        fwd = 2 * qk + 4 * d + 3 * h + (4 * d if self.fuse_layer_boundary else 5 * d)
         bwd = 5 * h + 4 * d + 3 * qk + 4 * d
         return (fwd + bwd) * e
 
     def bytes_per_token_ends(self) -> int:
-        """Gather (ids + table row + x), final norm fwd (2D) and bwd (3D), scatter-add staging
+        """Gather (ids + table row + x), the first layer's attention norm fwd (2D), final norm bwd (3D), scatter-add staging
         (read dx once; the d_embed rows are counted per distinct id by the caller)."""
         e = torch.empty((), dtype=self.dtype).element_size()
         return 4 + 2 * self.dim * e + 2 * self.dim * e + 3 * self.dim * e + self.dim * e
@@ -209,22 +211,32 @@ class LayerChain:
         return fn()
 
     def fwd_layer(self, L):
+        """Operators of layer L.  xnorm of this layer was produced by the previous layer's closing fused
+        residual + RMSNorm (by fwd_begin for layer 0): the residual stream crosses HBM once between layers."""
         c, p = self.cfg, self.p
         r = L % self.R
         x = self.layer_in[L]
-        ops.rmsnorm(x, p.norm_w("att", L), c.eps, out=self.xnorm[r])
         ops.qknorm_rope(self.q[L], p.norm_w("q", L), c.head_dim, c.qk_eps, c.rope_base, 0, out=self.q_r[r])
         ops.qknorm_rope(self.k[L], p.norm_w("k", L), c.head_dim, c.qk_eps, c.rope_base, 0, out=self.k_r[r])
         ops.residual_rmsnorm(x, self.o_out[L], p.norm_w("ffn", L), c.alpha, c.eps, x2=self.x2[L], x2norm=self.x2norm[r])
         ops.swiglu(self.h1[L], self.h3[L], out=self.gate[r])
-        ops.residual(self.x2[L], self.ffn_out[L], c.alpha, out=self.layer_in[L + 1])
+        # x_next = x2 + alpha*ffn (train.m:497) fused with the norm that reads it next: the next layer's attention
+        # norm, or the final norm after the last layer
+        w_next = p.norm_w("att", L + 1) if L + 1 < c.layers else p.norm_w("final")
+        n_next = self.xnorm[(L + 1) % self.R] if L + 1 < c.layers else self.x_final
+        if c.fuse_layer_boundary:
+            ops.residual_rmsnorm(self.x2[L], self.ffn_out[L], w_next, c.alpha, c.eps, x2=self.layer_in[L + 1], x2norm=n_next)
+        else:
+            ops.residual(self.x2[L], self.ffn_out[L], c.alpha, out=self.layer_in[L + 1])
+            ops.rmsnorm(self.layer_in[L + 1], w_next, c.eps, out=n_next)
 
     def fwd_begin(self):
+        c, p = self.cfg, self.p
         ops.embed_lookup(self.table, self.tokens, out=self.layer_in[0])
+        ops.rmsnorm(self.layer_in[0], p.norm_w("att", 0), c.eps, out=self.xnorm[0])
 
     def fwd_end(self):
-        c, p = self.cfg, self.p
-        ops.rmsnorm(self.layer_in[c.layers], p.norm_w("final"), c.eps, out=self.x_final)
+        pass
 
     def forward(self):
         self.fwd_begin()

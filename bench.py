@@ -54,6 +54,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
+    ap.add_argument("--no-boundary-fusion", action="store_true", help="run the closing residual and the next norm as two operators")
     ap.add_argument("--cpu-seqs", type=int, default=2, help="sequences in the CPU sample")
     ap.add_argument("--e2e-seqs", type=int, default=8, help="sequences per rank and step of the host-buffer (e2e) measurement")
     return ap.parse_args()
@@ -345,7 +346,7 @@ def run_ours(args):
     lib.init(local)
     peak_gbs, peak_kind = measured_peak()
 
-    cfg = ChainConfig(layers=args.layers, alpha=(2.0 * args.layers) ** -0.5)
+    cfg = ChainConfig(layers=args.layers, alpha=(2.0 * args.layers) ** -0.5, fuse_layer_boundary=not args.no_boundary_fusion)
     lo, hi = shard_range(args.seqs, world, rank)
     my_seqs = hi - lo
     M = min(args.micro_batch, max(my_seqs, 1))
