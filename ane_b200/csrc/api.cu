@@ -152,6 +152,17 @@ int ane_cuda_set_tuning(const char *name, int value) {
     return ANE_CUDA_OK;
 }
 
+int ane_cuda_clear_tuning(const char *name) {
+    if (!name) { g_nknobs = 0; return ANE_CUDA_OK; }
+    for (int i = 0; i < g_nknobs; i++)
+        if (strcmp(g_knobs[i].name, name) == 0) {
+            g_knobs[i] = g_knobs[g_nknobs - 1];
+            g_nknobs--;
+            break;
+        }
+    return ANE_CUDA_OK;
+}
+
 const char *ane_cuda_last_error(void) { return g_err; }
 
 long long ane_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -26,19 +26,6 @@ namespace ane {
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_U = 4;  // channel rows in flight per thread and tensor
 
-// N consecutive fp32 values (16-byte aligned when N >= 4) as packed lanes.
-template <int N> __device__ __forceinline__ V<N> table_lanes_f(const float *p) {
-    V<N> v;
-#pragma unroll
-    for (int i = 0; i < N / 4; i++) {
-        const float4 q = __ldg(reinterpret_cast<const float4 *>(p) + i);
-        v.p[2 * i] = make_float2(q.x, q.y);
-        v.p[2 * i + 1] = make_float2(q.z, q.w);
-    }
-    return v;
-}
-template <> __device__ __forceinline__ V<1> table_lanes_f<1>(const float *p) { V<1> v; v.a = __ldg(p); return v; }
-
 template <typename T, int VEC, int LG, bool FUSE_RES>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_fwd_kernel(T *out, T *x2out, const T *x, const T *f,
@@ -233,126 +220,6 @@ rmsnorm_bwd_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *x,
     for (int c = threadIdx.x; c < C; c += NORM_THREADS) partial[(size_t)blockIdx.x * C + c] = dwacc[c];
 }
 
-// ------------------------------------------------------------------ split backward: statistics, then apply
-// For large C the fused backward above is held back by its block-wide barriers and by the
-// registers its second sweep needs.  Splitting it costs two extra tensor reads (6 units of
-// traffic instead of 4) but both halves stream at close to copy speed, which is faster overall:
-//   stats  one pass over x and dy: per token rrms and coef = dot * rrms^2 / C  -> stat[2][B*S]
-//   apply  element-wise: a warp owns 256 (fp32: 128) consecutive tokens of a sequence and walks
-//          over BWS_ROWS channels, four rows in flight; the per-token statistics sit in its
-//          registers.  dw[c] partials are reduced inside the warp and written per token
-//          segment; dw_finalize adds the segments in order (deterministic).
-constexpr int BWS_ROWS = 32;     // channels per warp in the apply kernel
-
-template <typename T, int VEC, int LG, int U, int MINB>
-__global__ void __launch_bounds__(NORM_THREADS, MINB)
-rmsnorm_bwd_stats_kernel(float *__restrict__ stat_rr, float *__restrict__ stat_coef, const T *__restrict__ dy,
-                         const T *__restrict__ x, const float *__restrict__ w, int C, int S, int tiles_per_seq, float eps) {
-    constexpr int R = NORM_THREADS / LG;
-    constexpr int TW = LG * VEC;
-    __shared__ __align__(16) float red[2][R][TW];
-    const int b = blockIdx.x / tiles_per_seq;
-    const int lg = threadIdx.x % LG, rg = threadIdx.x / LG;
-    const int t = (blockIdx.x % tiles_per_seq) * TW + lg * VEC;
-    const bool active = t < S;
-    const size_t base = (size_t)b * C * S + t + (size_t)rg * S;
-    const size_t step = (size_t)R * S;
-    V<VEC> ss = V<VEC>::splat(0.0f), dot = V<VEC>::splat(0.0f);
-    for (int cb = 0; cb < C; cb += R * U) {
-        Raw<T, VEC> rx[U], rd[U];
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int c = cb + u * R + rg;
-            if (active && c < C) {
-                const size_t o = base + (size_t)(cb / R + u) * step;
-                rx[u].load(x + o);        // default caching: the apply kernel reads it again soon
-                rd[u].load(dy + o);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            const int c = cb + u * R + rg;
-            if (active && c < C) {
-                const V<VEC> xv = rx[u].get(), dv = rd[u].get();
-                ss = vfma(xv, xv, ss);
-                dot = vfma_s(vmul(dv, xv), __ldg(w + c), dot);       // stories_cpu_ops.h:35-38
-            }
-        }
-    }
-    lanes_to_smem<VEC>(&red[0][rg][lg * VEC], ss);
-    lanes_to_smem<VEC>(&red[1][rg][lg * VEC], dot);
-    __syncthreads();
-    constexpr int P = NORM_THREADS / TW;
-    const float s0 = block_column_sum<R, TW, NORM_THREADS>(&red[0][0][0], threadIdx.x);
-    const float s1 = block_column_sum<R, TW, NORM_THREADS>(&red[1][0][0], threadIdx.x);
-    const int col = threadIdx.x / P;
-    const int tt = (blockIdx.x % tiles_per_seq) * TW + col;
-    if (threadIdx.x % P == 0 && tt < S) {
-        const float invd = 1.0f / (float)C;
-        const float r1 = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s0, invd), eps));
-        float r2 = r1 * r1;
-        r2 = r2 * invd;
-        stat_rr[(size_t)b * S + tt] = r1;
-        stat_coef[(size_t)b * S + tt] = s1 * r2;                     // stories_cpu_ops.h:39-41
-    }
-}
-
-template <typename T, int VEC, bool HAS_ADD, int RIF, int MINB>
-__global__ void __launch_bounds__(NORM_THREADS, MINB)
-rmsnorm_bwd_apply_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *x, const float *__restrict__ w,
-                         const T *add, const float *__restrict__ stat_rr, const float *__restrict__ stat_coef, int C, int S,
-                         int segs_per_seq, int row_chunks, long long nwarps, unsigned flags) {
-    constexpr int SEG = 32 * VEC;                 // tokens per warp
-    const bool exact = (flags & ANE_NORM_BWD_EXACT) != 0;
-    const int lane = threadIdx.x & 31;
-    const long long warp = (long long)blockIdx.x * (NORM_THREADS / 32) + (threadIdx.x >> 5);
-    if (warp >= nwarps) return;
-    const int chunk = (int)(warp % row_chunks);           // consecutive warps: same tokens, next rows
-    const long long seg_global = warp / row_chunks;       // b * segs_per_seq + seg
-    const int b = (int)(seg_global / segs_per_seq);
-    const int t = (int)(seg_global % segs_per_seq) * SEG + lane * VEC;
-    const bool active = t < S;
-    V<VEC> rr = V<VEC>::splat(0.0f), coef = V<VEC>::splat(0.0f);
-    if (active) {
-        rr = table_lanes_f<VEC>(stat_rr + (size_t)b * S + t);
-        coef = table_lanes_f<VEC>(stat_coef + (size_t)b * S + t);
-    }
-    const size_t base = (size_t)b * C * S + t;
-    const int c0 = chunk * BWS_ROWS;
-#pragma unroll 1
-    for (int cb = c0; cb < c0 + BWS_ROWS; cb += RIF) {
-        Raw<T, VEC> rx[RIF], rd[RIF], ra[RIF];
-#pragma unroll
-        for (int u = 0; u < RIF; u++) {
-            const int c = cb + u;
-            if (active && c < C) {
-                rx[u].load_stream(x + base + (size_t)c * S);
-                rd[u].load_stream(dy + base + (size_t)c * S);
-                if (HAS_ADD) ra[u].load_stream(add + base + (size_t)c * S);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < RIF; u++) {
-            const int c = cb + u;
-            float dwp = 0.0f;
-            if (active && c < C) {
-                const V<VEC> xv = rx[u].get(), dv = rd[u].get();
-                const float wc = __ldg(w + c);
-                V<VEC> o;
-                if (exact) o = vmul(vsub(vscale(dv, wc), vmul(xv, coef)), rr);
-                else o = vscale(vmul(vsub(dv, vmul(xv, coef)), rr), wc);     // stories_cpu_ops.h:43-46
-                dwp = vmul(vmul(dv, xv), rr).hsum();                          // stories_cpu_ops.h:47-50
-                if (HAS_ADD) o = vadd(o, ra[u].get());                        // train.m:590,721
-                Raw<T, VEC> ro;
-                ro.put(o);
-                ro.store_stream(dx + base + (size_t)c * S);
-            }
-            dwp = warp_sum(dwp);
-            if (lane == 0 && c < C) partial[(size_t)seg_global * C + c] = dwp;
-        }
-    }
-}
-
 template <typename T, bool FUSE_RES>
 static int launch_rmsnorm_fwd(cudaStream_t st, int B, int C, int S, void *out, void *x2, const void *x, const void *f,
                               const float *w, float alpha, float eps) {
@@ -431,27 +298,9 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
     int grid, ntiles;
     float *partial;
     if (vec) {
-#define ANE_BWD_RR(LGv, THv, NVv)                                                                                   \
-        do {                                                                                                        \
-            auto k_ = rmsnorm_bwd_rr_kernel<T, LGv, THv, NVv, HAS_ADD>;                                              \
-            const int tps_ = (S + (LGv) * VEC - 1) / ((LGv) * VEC);                                                  \
-            ntiles = B * tps_;                                                                                      \
-            grid = persistent_grid(k_, THv, smem, ntiles);                                                          \
-            partial = static_cast<float *>(workspace((size_t)grid * C * sizeof(float)));                            \
-            if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", grid, C); \
-            k_<<<grid, THv, smem, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags); \
-            column_sum_add_kernel<><<<(C + 31) / 32, 256, 0, st>>>(dw, partial, grid, C);                              \
-            ANE_LAUNCH_OK(2);                                                                                       \
-            return ANE_CUDA_OK;                                                                                     \
-        } while (0)
-#define ANE_BWD_RR_NV(LGv, THv)                                                                                     \
-        do {                                                                                                        \
-            const int nv_ = (C + (THv) / (LGv) - 1) / ((THv) / (LGv));                                               \
-            if (nv_ <= 4) ANE_BWD_RR(LGv, THv, 4);                                                                  \
-            else if (nv_ <= 8) ANE_BWD_RR(LGv, THv, 8);                                                             \
-        } while (0)
-        // Measured on B200 (C = 1024, bf16, 32-64 sequences): the block-pair kernel reaches 57-66 % of the copy
-        // rate, the two-sweep kernel 41-58 %, the split statistics/apply pair 42-57 %.
+        // Measured on B200 (C = 1024, bf16, 32-64 sequences): the block-pair kernel reaches 58-70 % of the copy rate,
+        // the two-sweep kernel below 41-58 %.  (Also tried and removed: a register-resident tile, 37-50 %; one block per
+        // strip with 32- or 64-byte rows, 37-53 %; a statistics kernel followed by an element-wise kernel, 42-57 %.)
         const int knob_b = tuning("norm_bwd", 8);
         if (knob_b == 8 && (size_t)C * 66 <= 200 * 1024 && C >= 64) {      // channel halves on a pair of blocks, 64-byte rows
             constexpr int LGs = 4;
@@ -472,61 +321,6 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
             ANE_LAUNCH_OK(2);
             return ANE_CUDA_OK;
         }
-        if ((knob_b == 6 || knob_b == 7) && (size_t)C * 132 <= 200 * 1024) {   // shared-memory-resident strips of x and dy
-            const int LGs = knob_b == 6 ? 2 : 4;                               // 32- or 64-byte rows
-            const int tps_ = (S + LGs * VEC - 1) / (LGs * VEC);
-            ntiles = B * tps_;
-            const size_t smem_st = (size_t)2 * C * LGs * 16 + (size_t)C * sizeof(float);
-            auto k_ = knob_b == 6 ? rmsnorm_bwd_st_kernel<T, 2, HAS_ADD> : rmsnorm_bwd_st_kernel<T, 4, HAS_ADD>;
-            ANE_CUDA_TRY(cudaFuncSetAttribute(k_, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_st));
-            int per_sm = (int)((200 * 1024) / (smem_st + 6 * 1024));
-            per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
-            const int nblk = ntiles < per_sm * ctx().sm_count ? ntiles : per_sm * ctx().sm_count;
-            partial = static_cast<float *>(workspace((size_t)nblk * C * sizeof(float)));
-            if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", nblk, C);
-            k_<<<(unsigned)nblk, ST_THREADS, smem_st, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags);
-            column_sum_add_kernel<><<<(C + 31) / 32, 256, 0, st>>>(dw, partial, nblk, C);
-            ANE_LAUNCH_OK(2);
-            return ANE_CUDA_OK;
-        }
-        if (knob_b == 5 && C >= 256) {            // statistics pass, then element-wise apply
-            constexpr int LGs = 8;
-            const int tps_ = (S + LGs * VEC - 1) / (LGs * VEC);
-            const int segs = (S + 32 * VEC - 1) / (32 * VEC);
-            const int row_chunks = (C + BWS_ROWS - 1) / BWS_ROWS;
-            const long long nseg = (long long)B * segs;
-            const long long nwarps = nseg * row_chunks;
-            const size_t off_coef = round_up((size_t)B * S * sizeof(float), 256);
-            const size_t off_part = 2 * off_coef;
-            float *wsf = static_cast<float *>(workspace(off_part + (size_t)nseg * C * sizeof(float)));
-            if (!wsf) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch");
-            float *stat_rr = wsf, *stat_coef = reinterpret_cast<float *>(reinterpret_cast<char *>(wsf) + off_coef);
-            partial = reinterpret_cast<float *>(reinterpret_cast<char *>(wsf) + off_part);
-            const int var = tuning("norm_bwd_var", 3);
-            if (var & 1)
-                rmsnorm_bwd_stats_kernel<T, VEC, LGs, 8, 2><<<(unsigned)(B * tps_), NORM_THREADS, 0, st>>>(
-                    stat_rr, stat_coef, (const T *)dy, (const T *)x, w, C, S, tps_, eps);
-            else
-                rmsnorm_bwd_stats_kernel<T, VEC, LGs, 4, 4><<<(unsigned)(B * tps_), NORM_THREADS, 0, st>>>(
-                    stat_rr, stat_coef, (const T *)dy, (const T *)x, w, C, S, tps_, eps);
-            const long long blocks = (nwarps + NORM_THREADS / 32 - 1) / (NORM_THREADS / 32);
-            if (var & 2)
-                rmsnorm_bwd_apply_kernel<T, VEC, HAS_ADD, 4, 2><<<(unsigned)blocks, NORM_THREADS, 0, st>>>(
-                    (T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, stat_rr, stat_coef, C, S, segs, row_chunks, nwarps, flags);
-            else
-                rmsnorm_bwd_apply_kernel<T, VEC, HAS_ADD, 2, 3><<<(unsigned)blocks, NORM_THREADS, 0, st>>>(
-                    (T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, stat_rr, stat_coef, C, S, segs, row_chunks, nwarps, flags);
-            column_sum_add_kernel<><<<(C + 31) / 32, 256, 0, st>>>(dw, partial, (int)nseg, C);
-            ANE_LAUNCH_OK(3);
-            return ANE_CUDA_OK;
-        }
-        switch (knob_b) {
-            case 2: ANE_BWD_RR_NV(4, 512); break;        // C <= 1024
-            case 3: ANE_BWD_RR_NV(8, 512); break;        // C <= 512
-            default: break;
-        }
-#undef ANE_BWD_RR_NV
-#undef ANE_BWD_RR
         constexpr int LG = 8;
         auto k = rmsnorm_bwd_kernel<T, VEC, LG, HAS_ADD>;
         const int tps = (S + LG * VEC - 1) / (LG * VEC);

@@ -8,7 +8,7 @@
 // then sweeps the resident strip twice -- reduce, then normalise -- with one vector of state per
 // thread.  Nothing is read twice from HBM or L2.
 //   forward : strip of x (TB = 64 B per row, 64 KiB for C = 1024 in bf16), 3 blocks per SM
-//   backward: strips of x and dy (TB = 32 B per row each), same footprint
+//   backward: strips of x and dy, the channels split over a pair of blocks (64 KiB per block for C = 1024)
 #pragma once
 #include "common.cuh"
 
@@ -103,110 +103,6 @@ rmsnorm_fwd_st_kernel(T *out, T *x2out, const T *x, const T *f, const float *__r
         rx.put(vscale(vmul(rx.get(), rr), __ldg(w + c)));                          // stories_cpu_ops.h:16-19
         rx.store_stream(out + base + (size_t)c * S);
     }
-}
-
-// Persistent form: block i takes tiles i, i+grid, ...; dw contributions accumulate per block in shared
-// memory and leave as partial[block][C] (added in block order afterwards).
-template <typename T, int LG, bool HAS_ADD>
-__global__ void __launch_bounds__(ST_THREADS)
-rmsnorm_bwd_st_kernel(T *dx, float *__restrict__ partial, const T *dy, const T *x, const float *__restrict__ w,
-                      const T *add, int C, int S, int tiles_per_seq, int ntiles, float eps, unsigned flags) {
-    constexpr int VEC = Elt<T>::VEC;
-    constexpr int R = ST_THREADS / LG;
-    constexpr int TW = LG * VEC;
-    extern __shared__ uint4 strip[];                 // x: [C][LG], dy: [C][LG], then dw accumulators float[C]
-    __shared__ __align__(16) float red[2][R][TW];
-    __shared__ __align__(16) float tot[2][TW];
-    uint4 *sx = strip, *sd = strip + (size_t)C * LG;
-    float *dwacc = reinterpret_cast<float *>(strip + (size_t)2 * C * LG);
-
-    const int lg = threadIdx.x % LG, rg = threadIdx.x / LG;
-    const float invd = 1.0f / (float)C;
-    const bool exact = (flags & ANE_NORM_BWD_EXACT) != 0;
-
-    for (int c = threadIdx.x; c < C; c += ST_THREADS) dwacc[c] = 0.0f;
-    __syncthreads();
-
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        const int b = tile / tiles_per_seq;
-        const int t = (tile % tiles_per_seq) * TW + lg * VEC;
-        const bool active = t < S;
-        const size_t base = (size_t)b * C * S + t;
-
-        if (active)
-            for (int c = rg; c < C; c += R) {
-                cp_async16(&sx[c * LG + lg], x + base + (size_t)c * S);
-                cp_async16(&sd[c * LG + lg], dy + base + (size_t)c * S);
-            }
-        cp_async_commit();
-        cp_async_wait_all();             // each thread reads back only what it copied itself
-
-        V<VEC> ss = V<VEC>::splat(0.0f), dot = V<VEC>::splat(0.0f);
-        if (active) {
-#pragma unroll 4
-            for (int c = rg; c < C; c += R) {
-                Raw<T, VEC> rx, rd;
-                rx.v = sx[c * LG + lg];
-                rd.v = sd[c * LG + lg];
-                const V<VEC> xv = rx.get(), dv = rd.get();
-                ss = vfma(xv, xv, ss);
-                dot = vfma_s(vmul(dv, xv), __ldg(w + c), dot);                     // stories_cpu_ops.h:35-38
-            }
-        }
-        lanes_to_smem<VEC>(&red[0][rg][lg * VEC], ss);
-        lanes_to_smem<VEC>(&red[1][rg][lg * VEC], dot);
-        __syncthreads();
-        {
-            constexpr int P = ST_THREADS / TW;
-            const float s0 = block_column_sum<R, TW, ST_THREADS>(&red[0][0][0], threadIdx.x);
-            const float s1 = block_column_sum<R, TW, ST_THREADS>(&red[1][0][0], threadIdx.x);
-            if (threadIdx.x % P == 0) {
-                const float r1 = 1.0f / sqrtf(__fadd_rn(__fmul_rn(s0, invd), eps));
-                float r2 = r1 * r1;
-                r2 = r2 * invd;
-                tot[0][threadIdx.x / P] = r1;
-                tot[1][threadIdx.x / P] = s1 * r2;                                 // stories_cpu_ops.h:39-41
-            }
-        }
-        __syncthreads();
-        const V<VEC> rr = lanes_from_smem<VEC>(&tot[0][lg * VEC]), coef = lanes_from_smem<VEC>(&tot[1][lg * VEC]);
-        constexpr int U = 4;
-        for (int cb = 0; cb < C; cb += R * U) {       // uniform trip count: the shuffles below need every lane
-            Raw<T, VEC> ra[U];
-            if (HAS_ADD) {
-#pragma unroll
-                for (int u = 0; u < U; u++) {
-                    const int c = cb + u * R + rg;
-                    if (active && c < C) ra[u].load_stream(add + base + (size_t)c * S);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                const int c = cb + u * R + rg;
-                float dwp = 0.0f;
-                if (active && c < C) {
-                    Raw<T, VEC> rx, rd;
-                    rx.v = sx[c * LG + lg];
-                    rd.v = sd[c * LG + lg];
-                    const V<VEC> xv = rx.get(), dv = rd.get();
-                    const float wc = __ldg(w + c);
-                    V<VEC> o;
-                    if (exact) o = vmul(vsub(vscale(dv, wc), vmul(xv, coef)), rr);
-                    else o = vscale(vmul(vsub(dv, vmul(xv, coef)), rr), wc);      // stories_cpu_ops.h:43-46
-                    dwp = vmul(vmul(dv, xv), rr).hsum();                           // stories_cpu_ops.h:47-50
-                    if (HAS_ADD) o = vadd(o, ra[u].get());                         // train.m:590,721
-                    Raw<T, VEC> ro;
-                    ro.put(o);
-                    ro.store_stream(dx + base + (size_t)c * S);
-                }
-#pragma unroll
-                for (int off = LG / 2; off > 0; off >>= 1) dwp += __shfl_xor_sync(0xffffffffu, dwp, off);
-                if (lg == 0 && c < C) dwacc[c] += dwp;   // row group rg is the only writer of channel c
-            }
-        }
-    }
-    __syncthreads();
-    for (int c = threadIdx.x; c < C; c += ST_THREADS) partial[(size_t)blockIdx.x * C + c] = dwacc[c];
 }
 
 // Backward on a PAIR of blocks (a thread-block cluster of two): the channels are split between the

@@ -54,6 +54,7 @@ PROTOTYPES = {
     "ane_cuda_launch_count": (C.c_longlong, []),
     "ane_cuda_reset_launch_count": (None, []),
     "ane_cuda_set_tuning": (_i, [C.c_char_p, _i]),
+    "ane_cuda_clear_tuning": (_i, [C.c_char_p]),
     "ane_cuda_alloc": (_vp, [_sz]),
     "ane_cuda_write": (_i, [_vp, _sz, _vp, _sz]),
     "ane_cuda_read": (_i, [_vp, _sz, _vp, _sz]),
@@ -159,6 +160,10 @@ def init(device: int = 0) -> None:
 
 def set_tuning(name: str, value: int) -> None:
     check(load().ane_cuda_set_tuning(name.encode(), int(value)))
+
+
+def clear_tuning(name=None) -> None:
+    check(load().ane_cuda_clear_tuning(name.encode() if name is not None else None))
 
 
 def launch_count() -> int:

@@ -92,6 +92,8 @@ void ane_cuda_reset_launch_count(void);
 /* Kernel-selection knobs for benchmarking (tile shapes; every setting computes the same result
  * up to the summation order of dw).  Unknown names are stored and ignored. */
 int ane_cuda_set_tuning(const char *name, int value);
+/* Back to the built-in choice for one knob (NULL: for all of them). */
+int ane_cuda_clear_tuning(const char *name);
 
 ANECudaBuf *ane_cuda_alloc(size_t bytes);                       /* NULL on failure */
 int ane_cuda_write(ANECudaBuf *buf, size_t offset, const void *host, size_t bytes);  /* ane_bridge_write_input */

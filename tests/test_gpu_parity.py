@@ -705,3 +705,81 @@ def test_host_layer_chain_equals_device_chain(dev):
             assert torch.equal(h.cuda(), getattr(ref, k)[0]), k
         assert torch.equal(g_host, p.g)                      # norm-weight and embedding gradients
     assert hc.h2d_bytes_per_step == 2 * 32 * 2 * (5 * (128 + 64 + 64 + 192 + 64 + 96 + 64 + 128 + 64 + 64) + 64) + 2 * 32 * 4
+
+
+# Every operator picks one kernel by default; the others stay reachable through tuning knobs (library function
+# ane_cuda_set_tuning).  Each alternate path must give the same results within the same tolerances.
+ALT_KNOBS = [
+    ("norm_fwd", 0), ("norm_fwd", 2), ("norm_fwd", 3), ("norm_fwd", 4), ("norm_fwd", 6),
+    ("norm_bwd", 0), ("norm_bwd", 8),
+    ("qk_fwd", 0), ("qk_fwd", 1), ("qk_fwd", 4), ("qk_bwd", 0), ("qk_bwd", 4),
+    ("rope_lg", 8), ("embed_tiled", 0), ("embed_rows", 0), ("xent_cluster", 1), ("xent_lg", 4),
+]
+
+
+@pytest.mark.parametrize("knob,value", ALT_KNOBS)
+def test_alternate_kernels_match_the_oracle(dev, oracle, knob, value):
+    torch = _torch()
+    from ane_b200 import lib
+    defaults = {"norm_fwd": None, "norm_bwd": None}
+    lib.set_tuning(knob, value)
+    try:
+        dt = "bf16"
+        if knob.startswith("norm"):
+            B, Cn, S = 3, 1024, 128
+            x, w, dy = gi.cfg1(seed=21, B=B, dim=Cn, seq=S)
+            f = gi.normal(gi.rng(7), (B, Cn, S))
+            xd, xr = up(x, dt)
+            fd, fr = up(f, dt)
+            dyd, dyr = up(dy, dt)
+            wd, _ = up(w)
+            assert close(down(dev.rmsnorm(xd, wd)), oracle.rmsnorm(xr, w), dt)
+            x2, x2n = dev.residual_rmsnorm(xd, fd, wd, 0.25)
+            rx2 = oracle.residual(xr, fr, 0.25)
+            assert close(down(x2), rx2, dt)
+            rx2_16 = down(up(rx2, dt)[0])                       # the norm reads the stored (rounded) sum
+            assert close(down(x2n), oracle.rmsnorm(rx2_16, w), dt)
+            dw = torch.zeros(Cn, device="cuda")
+            dx = dev.rmsnorm_bwd(dyd, xd, wd, dw, add=fd)
+            rdx, rdw = oracle.rmsnorm_bwd(dyr, xr, w)
+            assert close(down(dx), oracle.add(rdx, fr), dt)
+            assert rel_err(down(dw), rdw) <= 1e-4
+        elif knob.startswith("qk") or knob == "rope_lg":
+            B, heads, hd, S = 2, 4, 128, 256
+            q = gi.normal(gi.rng(8), (B, heads * hd, S))
+            dq = gi.normal(gi.rng(9), (B, heads * hd, S))
+            wq = (1 + 0.1 * gi.normal(gi.rng(10), (hd,))).astype(np.float32)
+            qd, qr = up(q, dt)
+            dqd, dqr = up(dq, dt)
+            wqd, _ = up(wq)
+            assert close(down(dev.qknorm_rope(qd, wqd, hd, 1e-6, 1e6, 0)), oracle.qknorm_rope(qr, wq, hd, 1e-6, 1e6), dt)
+            assert close(down(dev.rope(qd, hd, base=1e6)), oracle.rope(qr, hd, 1e6), dt)
+            dwq = torch.zeros(hd, device="cuda")
+            dx = dev.rope_qknorm_bwd(dqd, qd, wqd, dwq, hd, 1e-6, 1e6, 0)
+            rdx, rdw = oracle.rope_qknorm_bwd(dqr, qr, wq, hd, eps=1e-6, base=1e6)
+            assert close(down(dx), rdx, dt)
+            assert rel_err(down(dwq), rdw) <= 1e-4
+        elif knob.startswith("embed"):
+            V, D, B, S = 300, 256, 2, 64
+            table = gi.normal(gi.rng(11), (V, D), 0.02)
+            tok = gi.rng(12).integers(0, V, (B, S)).astype(np.int32)
+            td, tr = up(table, dt)
+            tokd = torch.from_numpy(tok).cuda()
+            x = dev.embed_lookup(td, tokd)
+            rx, _ = oracle.embed_lookup(tr, tok)
+            assert np.array_equal(down(x), rx)                  # a copy: bit-exact
+            dE = torch.zeros(V, D, device="cuda")
+            dev.embed_backward(dE, x, tokd)
+            rdE, _ = oracle.embed_backward(np.zeros((V, D), np.float32), rx, tok)
+            assert np.array_equal(down(dE), rdE)                # same additions in the same order
+        else:
+            B, V, S = 2, 8192, 128
+            logits = gi.normal(gi.rng(13), (B, V, S), 2.0)
+            tg = gi.rng(14).integers(0, V, (B, S)).astype(np.int32)
+            loss, dl = dev.cross_entropy(torch.from_numpy(logits).cuda(), torch.from_numpy(tg).cuda())
+            rloss, rdl, _ = oracle.cross_entropy(logits, tg)
+            assert rel_err(down(dl), rdl) <= TOL32
+            assert np.allclose(down(loss), rloss, rtol=1e-5, atol=1e-6)
+        assert lib.poll_status().wait_giveups == 0
+    finally:
+        lib.clear_tuning(knob)
