@@ -83,7 +83,8 @@ def close(got, ref, dt):
     return ok
 
 
-NORM_SHAPES = [(1, 768, 256), (3, 7, 5), (2, 128, 257), (1, 1, 1), (2, 1024, 64), (1, 2, 3), (5, 33, 48), (1, 300, 8)]
+NORM_SHAPES = [(1, 768, 256), (3, 7, 5), (2, 128, 257), (1, 1, 1), (2, 1024, 64), (1, 2, 3), (5, 33, 48), (1, 300, 8),
+               (2, 129, 64), (1, 3000, 32), (1, 3200, 40), (1, 64, 2048)]
 
 
 @pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
