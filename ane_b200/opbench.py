@@ -6,8 +6,12 @@ CUDA-event time of a launch.
     python -m ane_b200.opbench --op cross_entropy    # one operator (what a profiler run wraps)
     python -m ane_b200.opbench --op rmsnorm --batch 64 --iters 3 --tuning norm_fwd=0
 
-Every operator rotates through several input/output sets so that consecutive launches do not find
-their operands in the 126 MB L2 (each set is 128 MiB or more at the default batch of 32 sequences).
+Timing: CUDA events around each of 20 back-to-back launches after 5 warm-ups, median reported (best beside
+it).  Every operator rotates through four input/output sets so that consecutive launches do not find their
+operands in the 126 MB L2 (each set is 128 MiB or more at the default batch of 32 sequences).
+
+    python -m ane_b200.opbench --dim 768 --hidden 2048 --seq 256 --dtype float32 --batch 1024 \
+        --op rmsnorm --op rmsnorm_bwd --op swiglu --op swiglu_bwd --op residual      # Stories110M shapes
 """
 from __future__ import annotations
 
@@ -15,14 +19,20 @@ import argparse
 import json
 
 NOMINAL_HBM_GBS = 8000.0
-S, D, H, QD, KVD, HD, VOCAB = 2048, 1024, 3072, 2048, 1024, 128, 151936
-NSET = 3
+SEQ, DIM, HIDDEN, QD, KVD, HD, VOCAB = 2048, 1024, 3072, 2048, 1024, 128, 151936
+DEFAULT_SETS = 4
 
 
-def _cases(torch, ops, device, M):
-    """name -> (builder) ; builder() returns (fn(i), algorithmic bytes per launch, default iterations)."""
-    bf = torch.bfloat16
+def _cases(torch, ops, device, M, shape=None):
+    """name -> (builder) ; builder() returns (fn(i), algorithmic bytes per launch, default iterations).
+    shape: optional dict(dim=, hidden=, seq=, dtype=) for the norm / residual / SwiGLU rows (the reference-native
+    Stories110M shapes are dim 768, hidden 2048, seq 256, float32)."""
+    shape = shape or {}
+    S, D, H = shape.get("seq", SEQ), shape.get("dim", DIM), shape.get("hidden", HIDDEN)
+    bf = shape.get("dtype", torch.bfloat16)
+    e = torch.empty((), dtype=bf).element_size()
     T = M * S
+    NSET = shape.get("sets", DEFAULT_SETS)      # input/output sets an operator rotates through
 
     def mk(ch, dtype=bf, n=NSET, b=M):
         return [torch.randn((b, ch, S), device=device, dtype=dtype) for _ in range(n)]
@@ -35,43 +45,43 @@ def _cases(torch, ops, device, M):
 
     def rmsnorm():
         (w, _), xs, os_ = norm_w(), mk(D), mk(D)
-        return (lambda i: ops.rmsnorm(xs[i % NSET], w, out=os_[i % NSET])), 2 * D * T * 2, 12
+        return (lambda i: ops.rmsnorm(xs[i % NSET], w, out=os_[i % NSET])), 2 * D * T * e, 20
 
     def rmsnorm_bwd():
         (w, dw), xs, ys, os_ = norm_w(), mk(D), mk(D), mk(D)
-        return (lambda i: ops.rmsnorm_bwd(ys[i % NSET], xs[i % NSET], w, dw, out=os_[i % NSET])), 3 * D * T * 2, 12
+        return (lambda i: ops.rmsnorm_bwd(ys[i % NSET], xs[i % NSET], w, dw, out=os_[i % NSET])), 3 * D * T * e, 20
 
     def rmsnorm_bwd_add():
         (w, dw), xs, ys, zs, os_ = norm_w(), mk(D), mk(D), mk(D), mk(D)
-        return (lambda i: ops.rmsnorm_bwd(ys[i % NSET], xs[i % NSET], w, dw, add=zs[i % NSET], out=os_[i % NSET])), 4 * D * T * 2, 12
+        return (lambda i: ops.rmsnorm_bwd(ys[i % NSET], xs[i % NSET], w, dw, add=zs[i % NSET], out=os_[i % NSET])), 4 * D * T * e, 20
 
     def residual_rmsnorm():
         (w, _), xs, ys, os_, o2 = norm_w(), mk(D), mk(D), mk(D), mk(D)
-        return (lambda i: ops.residual_rmsnorm(xs[i % NSET], ys[i % NSET], w, 0.13, x2=os_[i % NSET], x2norm=o2[i % NSET])), 4 * D * T * 2, 12
+        return (lambda i: ops.residual_rmsnorm(xs[i % NSET], ys[i % NSET], w, 0.13, x2=os_[i % NSET], x2norm=o2[i % NSET])), 4 * D * T * e, 20
 
     def residual():
         xs, ys, os_ = mk(D), mk(D), mk(D)
-        return (lambda i: ops.residual(xs[i % NSET], ys[i % NSET], 0.13, out=os_[i % NSET])), 3 * D * T * 2, 12
+        return (lambda i: ops.residual(xs[i % NSET], ys[i % NSET], 0.13, out=os_[i % NSET])), 3 * D * T * e, 20
 
     def swiglu():
         h1, h3, g1 = mk(H), mk(H), mk(H)
-        return (lambda i: ops.swiglu(h1[i % NSET], h3[i % NSET], out=g1[i % NSET])), 3 * H * T * 2, 12
+        return (lambda i: ops.swiglu(h1[i % NSET], h3[i % NSET], out=g1[i % NSET])), 3 * H * T * e, 20
 
     def swiglu_bwd():
         h1, h3, dd, g1, g3 = mk(H), mk(H), mk(H), mk(H), mk(H)
-        return (lambda i: ops.swiglu_bwd(h1[i % NSET], h3[i % NSET], dd[i % NSET], dh1=g1[i % NSET], dh3=g3[i % NSET])), 5 * H * T * 2, 12
+        return (lambda i: ops.swiglu_bwd(h1[i % NSET], h3[i % NSET], dd[i % NSET], dh1=g1[i % NSET], dh3=g3[i % NSET])), 5 * H * T * e, 20
 
     def rope():
         q, qo = mk(QD), mk(QD)
-        return (lambda i: ops.rope(q[i % NSET], HD, base=1e6, out=qo[i % NSET])), 2 * QD * T * 2, 12
+        return (lambda i: ops.rope(q[i % NSET], HD, base=1e6, out=qo[i % NSET])), 2 * QD * T * e, 20
 
     def qknorm_rope():
         (wq, _), q, qo = head_w(), mk(QD), mk(QD)
-        return (lambda i: ops.qknorm_rope(q[i % NSET], wq, HD, out=qo[i % NSET])), 2 * QD * T * 2, 12
+        return (lambda i: ops.qknorm_rope(q[i % NSET], wq, HD, out=qo[i % NSET])), 2 * QD * T * e, 20
 
     def rope_qknorm_bwd():
         (wq, dwq), q, dq, qo = head_w(), mk(QD), mk(QD), mk(QD)
-        return (lambda i: ops.rope_qknorm_bwd(dq[i % NSET], q[i % NSET], wq, dwq, HD, out=qo[i % NSET])), 3 * QD * T * 2, 12
+        return (lambda i: ops.rope_qknorm_bwd(dq[i % NSET], q[i % NSET], wq, dwq, HD, out=qo[i % NSET])), 3 * QD * T * e, 20
 
     # embedding: batch sequences of 2048 tokens, table [151936, 1024] bf16
     def _embed_common():
@@ -83,7 +93,7 @@ def _cases(torch, ops, device, M):
 
     def embed_lookup():
         Be, table, tok, xe = _embed_common()
-        return (lambda i: ops.embed_lookup(table, tok, out=xe[i % 2])), Be * S * 4 + 2 * D * Be * S * 2, 12
+        return (lambda i: ops.embed_lookup(table, tok, out=xe[i % 2])), Be * S * 4 + 2 * D * Be * S * e, 20
 
     def embed_backward():
         Be, table, tok, xe = _embed_common()
@@ -92,7 +102,7 @@ def _cases(torch, ops, device, M):
         del table
         dE = torch.zeros(VOCAB, D, device=device)
         uniq = int(torch.unique(tok).numel())
-        return (lambda i: ops.embed_backward(dE, xe[i % 2], tok)), Be * S * 4 + D * Be * S * 2 + 2 * uniq * D * 4, 6
+        return (lambda i: ops.embed_backward(dE, xe[i % 2], tok)), Be * S * 4 + D * Be * S * e + 2 * uniq * D * 4, 10
 
     # cross-entropy: fp32 logits [batch/4][151936][2048] (10 GB at the default batch), written in place
     def cross_entropy():
@@ -116,29 +126,29 @@ def _cases(torch, ops, device, M):
 
     def adam():
         n, wv, gv, mv, vv = _flat()
-        return (lambda i: ops.adam(wv, gv, mv, vv, 1 + i, 3e-4, 0.9, 0.95, 1e-8, wd=0.1)), 28 * n, 12
+        return (lambda i: ops.adam(wv, gv, mv, vv, 1 + i, 3e-4, 0.9, 0.95, 1e-8, wd=0.1)), 28 * n, 20
 
     def grad_norm_sq():
         n, wv, gv, mv, vv = _flat()
         del wv, mv, vv
         nsq = torch.zeros(1, device=device)
-        return (lambda i: ops.grad_norm_sq(gv, 1.0, out=nsq)), 4 * n, 12
+        return (lambda i: ops.grad_norm_sq(gv, 1.0, out=nsq)), 4 * n, 20
 
     # layout helpers beside the operators (GQA 16/8 heads of 128; fp32 -> bf16 cast; compact table of a quarter of the ids)
     def gqa_tile():
         k = mk(KVD)
         o = [torch.empty((M, QD, S), dtype=bf, device=device) for _ in range(NSET)]
-        return (lambda i: ops.gqa_tile(k[i % NSET], 8, 2, out=o[i % NSET])), (KVD + QD) * T * 2, 12
+        return (lambda i: ops.gqa_tile(k[i % NSET], 8, 2, out=o[i % NSET])), (KVD + QD) * T * e, 20
 
     def gqa_reduce():
         q = mk(QD)
         o = [torch.empty((M, KVD, S), dtype=bf, device=device) for _ in range(NSET)]
-        return (lambda i: ops.gqa_reduce(q[i % NSET], 8, 2, out=o[i % NSET])), (KVD + QD) * T * 2, 12
+        return (lambda i: ops.gqa_reduce(q[i % NSET], 8, 2, out=o[i % NSET])), (KVD + QD) * T * e, 20
 
     def convert_f32_bf16():
         x = mk(D, dtype=torch.float32)
-        o = [torch.empty((M, D, S), dtype=bf, device=device) for _ in range(NSET)]
-        return (lambda i: ops.convert(x[i % NSET], bf, out=o[i % NSET])), 6 * D * T, 12
+        o = [torch.empty((M, D, S), dtype=torch.bfloat16, device=device) for _ in range(NSET)]
+        return (lambda i: ops.convert(x[i % NSET], torch.bfloat16, out=o[i % NSET])), 6 * D * T, 20
 
     def vocab_compact_embed():
         Vc = VOCAB // 4
@@ -146,7 +156,7 @@ def _cases(torch, ops, device, M):
         tok = (torch.randperm(VOCAB, device=device)[:Vc]).to(torch.int32).repeat(2)
         f2c, c2f, cnt = ops.vocab_map_build(tok, VOCAB)
         out = [torch.empty((Vc, D), device=device) for _ in range(2)]
-        return (lambda i: ops.vocab_compact_embed(full, c2f, cnt, Vc, out=out[i % 2])), 2 * Vc * D * 4 + Vc * 4, 12
+        return (lambda i: ops.vocab_compact_embed(full, c2f, cnt, Vc, out=out[i % 2])), 2 * Vc * D * 4 + Vc * 4, 20
 
     return {
         "gqa_tile": gqa_tile, "gqa_reduce": gqa_reduce, "convert_f32_bf16": convert_f32_bf16,
@@ -160,28 +170,31 @@ def _cases(torch, ops, device, M):
     }
 
 
-def time_op(torch, builder, peak_gbs, iters=None, warmup=3):
+def time_op(torch, builder, peak_gbs, iters=None, warmup=5):
+    """CUDA events around every one of `iters` back-to-back launches after `warmup` untimed ones; the reported time
+    is the median launch (the best one is given beside it)."""
     fn, nbytes, default_iters = builder()
     iters = iters or default_iters
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
+    ev[0].record()
     for i in range(iters):
         fn(i)
-    e.record()
+        ev[i + 1].record()
     torch.cuda.synchronize()
-    ms = s.elapsed_time(e) / iters
+    per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(iters))
+    ms = per[len(per) // 2]
     gbs = nbytes / ms / 1e6
-    return {"ms": round(ms, 4), "GB/s": round(gbs, 1), "frac_measured": round(gbs / peak_gbs, 3),
+    return {"ms": round(ms, 4), "ms_best": round(per[0], 4), "GB/s": round(gbs, 1), "frac_measured": round(gbs / peak_gbs, 3),
             "frac_8TBs": round(gbs / NOMINAL_HBM_GBS, 3), "bytes": nbytes}
 
 
-def per_op_table(torch, ops, device, peak_gbs, batch=32, only=None, iters=None, warmup=3):
+def per_op_table(torch, ops, device, peak_gbs, batch=32, only=None, iters=None, warmup=5, shape=None):
     """Achieved GB/s per operator on benchmark-sized bf16 tensors (algorithmic bytes / time)."""
     res = {}
-    for name, builder in _cases(torch, ops, device, batch).items():
+    for name, builder in _cases(torch, ops, device, batch, shape).items():
         if only and name not in only:
             continue
         res[name] = time_op(torch, builder, peak_gbs, iters, warmup)
@@ -193,8 +206,13 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--op", action="append", help="operator name (repeatable); default: all")
     ap.add_argument("--batch", type=int, default=32, help="sequences of 2048 tokens per launch")
+    ap.add_argument("--dim", type=int, default=None, help="channels of the norm / residual rows (default 1024)")
+    ap.add_argument("--hidden", type=int, default=None, help="channels of the SwiGLU rows (default 3072)")
+    ap.add_argument("--seq", type=int, default=None, help="tokens per sequence (default 2048)")
+    ap.add_argument("--dtype", default=None, choices=["float32", "bfloat16", "float16"])
+    ap.add_argument("--sets", type=int, default=None, help="buffer sets to rotate through (default 4; fewer for multi-GB tensors)")
     ap.add_argument("--iters", type=int, default=None)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--peak-gbs", type=float, default=None, help="roofline denominator (default: MEASURED_PEAKS.json)")
     ap.add_argument("--tuning", default="", help="comma-separated knob=value pairs")
     a = ap.parse_args(argv)
@@ -211,7 +229,10 @@ def main(argv=None):
     peak, kind = hbm_peak_gbs()
     if a.peak_gbs:
         peak, kind = a.peak_gbs, "given"
-    table = per_op_table(torch, ops, torch.device("cuda:0"), peak, a.batch, a.op, a.iters, a.warmup)
+    shape = {k: v for k, v in (("dim", a.dim), ("hidden", a.hidden), ("seq", a.seq), ("sets", a.sets)) if v}
+    if a.dtype:
+        shape["dtype"] = getattr(torch, a.dtype)
+    table = per_op_table(torch, ops, torch.device("cuda:0"), peak, a.batch, a.op, a.iters, a.warmup, shape or None)
     print(json.dumps({"batch": a.batch, "peak_gbs": peak, "peak_kind": kind, "ops": table}))
 
 

@@ -64,6 +64,7 @@ class ShardedAdam:
         self.k = kernels
         self.g_slice = torch.empty(self.slice_len, dtype=g.dtype, device=g.device) if world > 1 else None
         self.normsq = None
+        self.phase_events = None      # set to [] to collect (name, start, end) CUDA events of the next steps
 
     def _reduce_scatter(self):
         if self.world == 1:
@@ -75,8 +76,21 @@ class ShardedAdam:
             dist.reduce_scatter_tensor(self.g_slice, self.g, op=dist.ReduceOp.SUM, group=self.group)
         return self.g_slice
 
+    def _mark(self, name, fn):
+        if self.phase_events is None or not self.g.is_cuda:
+            return fn()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        r = fn()
+        e.record()
+        self.phase_events.append((name, s, e))
+        return r
+
     def step(self, t: int, gscale: float = 1.0):
-        gs = self._reduce_scatter()
+        gs = self._mark("reduce_scatter", self._reduce_scatter)
+        return self._mark("norm_clip_adam_gather", lambda: self._update(gs, t, gscale))
+
+    def _update(self, gs, t: int, gscale: float):
         normsq = self.k.grad_norm_sq(gs, gscale)
         if self.world > 1:
             dist.all_reduce(normsq, op=dist.ReduceOp.SUM, group=self.group)
@@ -91,8 +105,9 @@ class ShardedAdam:
                 self.k.adam(self.w[sl], gs[gl], self.m[sl], self.v[sl], t, self.lr, self.b1, self.b2, self.eps,
                             wd=wd, gscale=gscale, clip=factor)
         if self.world > 1:
-            dist.all_gather_into_tensor(self.w, self.w[self.lo:self.hi].clone() if dist.get_backend(self.group) == "gloo"
-                                        else self.w[self.lo:self.hi], group=self.group)
+            self._mark("all_gather", lambda: dist.all_gather_into_tensor(
+                self.w, self.w[self.lo:self.hi].clone() if dist.get_backend(self.group) == "gloo" else self.w[self.lo:self.hi],
+                group=self.group))
         return factor
 
 
