@@ -239,3 +239,25 @@ def vocab_update_full(full_embed, compact_embed, c2f, cnt, compact_max):
     V, dim = full_embed.shape
     _l.check(_l.load().ane_cuda_vocab_update_full_dev(_stream(), _p(full_embed), _p(compact_embed), _p(c2f), _p(cnt), compact_max, dim, V))
     return full_embed
+
+
+# ------------------------------------------------------------------ optimizer step over peer memory
+def _ptr_array(ptrs):
+    import ctypes as C
+    return (C.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+
+
+def p2p_reduce(g_ptrs, lo, n, g_slice, gscale=1.0, normsq=None):
+    """g_slice[:n] = sum over ranks (in rank order) of their gradient buffers at [lo, lo+n); normsq = sum (g*gscale)^2.
+    g_ptrs: device addresses of every rank's flat gradient buffer (peer-mapped)."""
+    normsq = torch.zeros(1, dtype=torch.float32, device=g_slice.device) if normsq is None else normsq
+    arr = _ptr_array(g_ptrs)
+    _l.check(_l.load().ane_cuda_p2p_reduce_dev(_stream(), len(g_ptrs), arr, lo, n, _p(g_slice), gscale, _p(normsq)))
+    return normsq
+
+
+def p2p_adam(w_ptrs, rank, lo, n, g_slice, m_slice, v_slice, t, lr, b1, b2, eps, wd=0.0, gscale=1.0, clip=None, dynamic=True):
+    """Adam on [lo, lo+n) of the flat parameters; the new weights go to every rank's buffer (w_ptrs, peer-mapped)."""
+    arr = _ptr_array(w_ptrs)
+    _l.check(_l.load().ane_cuda_p2p_adam_dev(_stream(), len(w_ptrs), rank, arr, lo, n, _p(g_slice), _p(m_slice), _p(v_slice), t, lr, b1,
+                                             b2, eps, wd, gscale, _p(clip), _l.ADAM_DYNAMIC if dynamic else _l.ADAM_STORIES))

@@ -87,7 +87,16 @@ class FlatParams:
     updates.  Gradient views into the flat buffer are handed to the operators that produce
     them (dw of the norms, d_embed of the scatter-add)."""
 
-    def __init__(self, cfg: ChainConfig, device, pad_to: int = 1):
+    @staticmethod
+    def padded_count(cfg: ChainConfig, pad_to: int = 1) -> int:
+        """Length of each flat buffer for this configuration."""
+        n = (cfg.layers * cfg.matrix_params_per_layer() + cfg.vocab * cfg.dim + cfg.layers * 2 * cfg.dim + cfg.dim
+             + cfg.layers * 2 * cfg.head_dim)
+        return (n + pad_to - 1) // pad_to * pad_to
+
+    def __init__(self, cfg: ChainConfig, device, pad_to: int = 1, wg_buffers=None):
+        """wg_buffers: optional pre-allocated (w, g) flat fp32 tensors of the padded length, e.g. peer-addressable
+        ones from ane_b200.sharded.symmetric_buffers."""
         c = cfg
         self.cfg = cfg
         self.n_matrix = c.layers * c.matrix_params_per_layer()
@@ -96,8 +105,14 @@ class FlatParams:
         self.n_norm = c.layers * 2 * c.dim + c.dim + c.layers * 2 * c.head_dim
         self.n = self.n_decay + self.n_norm
         self.n_padded = (self.n + pad_to - 1) // pad_to * pad_to
-        self.w = torch.empty(self.n_padded, dtype=torch.float32, device=device)
-        self.g = torch.empty(self.n_padded, dtype=torch.float32, device=device)
+        self.padded_length = self.n_padded
+        if wg_buffers is not None:
+            self.w, self.g = wg_buffers
+            if self.w.numel() != self.n_padded or self.g.numel() != self.n_padded:
+                raise ValueError("wg_buffers must hold padded_length elements each")
+        else:
+            self.w = torch.empty(self.n_padded, dtype=torch.float32, device=device)
+            self.g = torch.empty(self.n_padded, dtype=torch.float32, device=device)
         self.m = torch.zeros(self.n_padded, dtype=torch.float32, device=device)
         self.v = torch.zeros(self.n_padded, dtype=torch.float32, device=device)
         o = self.n_decay

@@ -49,7 +49,10 @@ class ShardedAdam:
 
     def __init__(self, w, g, m, v, n_decay: int, n_params: int, world: int = 1, rank: int = 0, group=None,
                  lr: float = 3e-4, b1: float = 0.9, b2: float = 0.95, eps: float = 1e-8, wd: float = 0.1,
-                 clip: float = 1.0, kernels=None):
+                 clip: float = 1.0, kernels=None, peer_ptrs=None):
+        """peer_ptrs = (w_ptrs, g_ptrs): device addresses of every rank's flat parameter and gradient buffer, mapped
+        into this process (see symmetric_buffers).  With them the reduce-scatter and the all-gather are not separate
+        collectives: the reduce kernel reads the peers' gradients and the Adam kernel writes the peers' parameters."""
         if w.numel() % world:
             raise ValueError("flat buffers must be padded to a multiple of the world size (see padded_length)")
         self.w, self.g, self.m, self.v = w, g, m, v
@@ -64,6 +67,8 @@ class ShardedAdam:
         self.k = kernels
         self.g_slice = torch.empty(self.slice_len, dtype=g.dtype, device=g.device) if world > 1 else None
         self.normsq = None
+        self.peer_ptrs = peer_ptrs if world > 1 else None
+        self._token = torch.zeros(1, dtype=torch.float32, device=g.device) if self.peer_ptrs else None
         self.phase_events = None      # set to [] to collect (name, start, end) CUDA events of the next steps
 
     def _reduce_scatter(self):
@@ -87,8 +92,32 @@ class ShardedAdam:
         return r
 
     def step(self, t: int, gscale: float = 1.0):
+        if self.peer_ptrs:
+            return self._mark("peer_memory_step", lambda: self._step_peer(t, gscale))
         gs = self._mark("reduce_scatter", self._reduce_scatter)
         return self._mark("norm_clip_adam_gather", lambda: self._update(gs, t, gscale))
+
+    def _rank_sync(self):
+        """Stream-ordered meeting point of all ranks: a one-element all-reduce completes on a rank only after every
+        rank has reached it on its stream, i.e. after everything each of them enqueued before it."""
+        dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.group)
+
+    def _step_peer(self, t: int, gscale: float):
+        w_ptrs, g_ptrs = self.peer_ptrs
+        self._rank_sync()                                               # every rank's gradients are complete
+        normsq = self.k.p2p_reduce(g_ptrs, self.lo, self.slice_len, self.g_slice, gscale)
+        dist.all_reduce(normsq, op=dist.ReduceOp.SUM, group=self.group)  # also: every rank has finished reading gradients
+        self.normsq = normsq
+        factor = self.k.clip_factor(normsq, self.clip)
+        for lo, hi, wd in ((0, self.n_decay, self.wd), (self.n_decay, self.n_params, 0.0)):
+            a, b = max(lo, self.lo), min(hi, self.hi)
+            if a < b:
+                sl = slice(a, b)
+                gl = slice(a - self.lo, b - self.lo)
+                self.k.p2p_adam(w_ptrs, self.rank, a, b - a, self.g_slice[gl], self.m[sl], self.v[sl], t, self.lr, self.b1, self.b2,
+                                self.eps, wd=wd, gscale=gscale, clip=factor)
+        self._rank_sync()                                               # every rank's parameter stores have landed
+        return factor
 
     def _update(self, gs, t: int, gscale: float):
         normsq = self.k.grad_norm_sq(gs, gscale)
@@ -116,3 +145,23 @@ def allreduce_scalar_sum(x: torch.Tensor, world: int, group=None) -> torch.Tenso
     if world > 1:
         dist.all_reduce(x, op=dist.ReduceOp.SUM, group=group)
     return x
+
+
+def symmetric_buffers(n: int, device, group=None):
+    """Two flat fp32 buffers of n elements (parameters, gradients) that every rank of the group can address directly,
+    and the device addresses of all ranks' copies: (w, g, (w_ptrs, g_ptrs)).  Uses torch's symmetric memory (CUDA
+    IPC over NVLink on one node).  Raises if the ranks cannot map each other's memory; callers fall back to plain
+    buffers and NCCL collectives."""
+    import torch.distributed._symmetric_memory as symm
+
+    group = group if group is not None else dist.group.WORLD
+    out, ptrs = [], []
+    for _ in range(2):
+        t = symm.empty(n, dtype=torch.float32, device=device)
+        try:
+            h = symm.rendezvous(t, group=group)
+        except TypeError:
+            h = symm.rendezvous(t, group.group_name)
+        out.append(t)
+        ptrs.append([int(p) for p in h.buffer_ptrs])
+    return out[0], out[1], (ptrs[0], ptrs[1])

@@ -54,6 +54,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
+    ap.add_argument("--no-p2p", action="store_true", help="N > 1: use NCCL reduce-scatter / all-gather instead of the peer-memory optimizer kernels")
     ap.add_argument("--no-boundary-fusion", action="store_true", help="run the closing residual and the next norm as two operators")
     ap.add_argument("--cpu-seqs", type=int, default=2, help="sequences in the CPU sample")
     ap.add_argument("--e2e-seqs", type=int, default=8, help="sequences per rank and step of the host-buffer (e2e) measurement")
@@ -400,11 +401,24 @@ def run_ours(args):
     if my_seqs % M:
         raise SystemExit(f"sequences per rank ({my_seqs}) must be a multiple of the micro-batch ({M})")
 
-    params = FlatParams(cfg, device, pad_to=world * 256)
+    peer_ptrs, exchange = None, "none (one rank)"
+    wg = None
+    if world > 1:
+        exchange = "NCCL reduce-scatter and all-gather around the Adam kernel"
+        if not args.no_p2p:
+            try:
+                from ane_b200.sharded import symmetric_buffers
+                w_s, g_s, peer_ptrs = symmetric_buffers(FlatParams.padded_count(cfg, world * 256), device)
+                wg = (w_s, g_s)
+                exchange = "peer memory: the reduce kernel reads every rank's gradients, the Adam kernel stores the new weights to every rank"
+            except Exception as exc:       # no peer mapping on this machine: the NCCL path computes the same step
+                peer_ptrs, wg = None, None
+                exchange += f" (peer mapping unavailable: {str(exc)[:120]})"
+    params = FlatParams(cfg, device, pad_to=world * 256, wg_buffers=wg)
     params.init_random()
     chain = LayerChain(cfg, M, params, device)
     opt = ShardedAdam(params.w, params.g, params.m, params.v, params.n_decay, params.n, world, rank,
-                      lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0)
+                      lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0, peer_ptrs=peer_ptrs)
     gscale = 1.0 / (10 * 256.0)       # 1/(accum_steps*loss_scale), train.m:750
     tstep = [0]
     use_graph = not args.no_graph
@@ -494,6 +508,7 @@ def run_ours(args):
         "step_frac_of_measured_peak": round(chain_bytes / world / (ms_step * 1e-3) / 1e9 / peak_gbs, 4),
         "roofline": roofline,
         "optimizer_ms_per_step": optimizer_ms,
+        "optimizer_exchange": exchange,
         "clocks": clocks,
         "gpu_launches": int(launches),
     }

@@ -784,3 +784,34 @@ def test_alternate_kernels_match_the_oracle(dev, oracle, knob, value):
         assert lib.poll_status().wait_giveups == 0
     finally:
         lib.clear_tuning(knob)
+
+
+@pytest.mark.parametrize("nranks,n,lo", [(1, 1000, 0), (2, 4099, 8), (4, 1 << 16, 1 << 14), (8, 33, 3), (3, 70001, 4)])
+def test_peer_memory_optimizer_kernels_with_emulated_ranks(dev, oracle, nranks, n, lo):
+    """ane_cuda_p2p_reduce_dev / ane_cuda_p2p_adam_dev with the ranks' buffers all on this GPU: the reduce equals the
+    rank-ordered fp32 sum, the update equals ane_cuda_adam_dev on the summed gradient bit for bit and reaches every
+    rank's parameter buffer; elements outside the slice are untouched."""
+    torch = _torch()
+    total = lo + n + 5
+    gen = torch.Generator(device="cuda").manual_seed(nranks * 1000 + n)
+    gs = [torch.randn(total, device="cuda", generator=gen) * 0.01 for _ in range(nranks)]
+    w0 = torch.randn(total, device="cuda", generator=gen) * 0.02
+    ws = [w0.clone() for _ in range(nranks)]
+    m = torch.randn(n, device="cuda", generator=gen) * 0.001
+    v = (torch.randn(n, device="cuda", generator=gen) * 0.001).abs()
+    gsl = torch.empty(n, device="cuda")
+    nsq = dev.p2p_reduce([g.data_ptr() for g in gs], lo, n, gsl, gscale=0.5)
+    want = gs[0][lo:lo + n].clone()
+    for r in range(1, nranks):
+        want = want + gs[r][lo:lo + n]                       # same order of fp32 additions
+    assert torch.equal(gsl, want)
+    ref_nsq = float(((want.double() * 0.5) ** 2).sum())
+    assert abs(float(nsq.item()) - ref_nsq) <= 1e-5 * ref_nsq
+    clip = torch.full((1,), 0.75, device="cuda")
+    wr, mr, vr = w0[lo:lo + n].clone(), m.clone(), v.clone()
+    dev.adam(wr, want, mr, vr, 3, 3e-4, 0.9, 0.95, 1e-8, wd=0.1, gscale=0.5, clip=clip)
+    dev.p2p_adam([w.data_ptr() for w in ws], nranks - 1, lo, n, gsl, m, v, 3, 3e-4, 0.9, 0.95, 1e-8, wd=0.1, gscale=0.5, clip=clip)
+    assert torch.equal(m, mr) and torch.equal(v, vr)
+    for w in ws:
+        assert torch.equal(w[lo:lo + n], wr)
+        assert torch.equal(w[:lo], w0[:lo]) and torch.equal(w[lo + n:], w0[lo + n:])

@@ -1,0 +1,63 @@
+"""Two ranks on two GPUs: the sharded optimizer step over peer memory (reduce kernel reading the other rank's
+gradients, Adam kernel storing the new weights to both ranks) gives the same parameters and moments as the same
+step through NCCL reduce-scatter / all-gather.  Skipped on a machine with fewer than two GPUs; the kernels
+themselves are covered on one GPU with emulated ranks (test_gpu_parity.py)."""
+import os
+import socket
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+    from ane_b200 import lib
+    from ane_b200.sharded import ShardedAdam, padded_length, symmetric_buffers
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    lib.init(rank)
+    n_params, n_decay = 100_003, 90_000
+    n = padded_length(n_params, world)
+    w, g, ptrs = symmetric_buffers(n, dev)
+    gen = torch.Generator(device=dev).manual_seed(7)                   # same parameters on every rank
+    w.copy_(torch.randn(n, device=dev, generator=gen) * 0.02)
+    gen_r = torch.Generator(device=dev).manual_seed(100 + rank)        # each rank its own gradients
+    g.copy_(torch.randn(n, device=dev, generator=gen_r) * 0.01)
+    g[n_params:] = 0
+    w2, g2 = w.clone(), g.clone()
+    m, v, m2, v2 = (torch.zeros(n, device=dev) for _ in range(4))
+    peer = ShardedAdam(w, g, m, v, n_decay, n_params, world, rank, peer_ptrs=ptrs)
+    nccl = ShardedAdam(w2, g2, m2, v2, n_decay, n_params, world, rank)
+    for t in (1, 2):
+        peer.step(t, 0.5)
+        nccl.step(t, 0.5)
+    torch.cuda.synchronize()
+    ok = bool(torch.equal(w, w2)) and bool(torch.equal(m[peer.lo:peer.hi], m2[peer.lo:peer.hi])) \
+        and bool(torch.equal(v[peer.lo:peer.hi], v2[peer.lo:peer.hi])) and bool(torch.equal(peer.normsq, nccl.normsq))
+    changed = bool((w != torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(7)) * 0.02)[:n_params].any())
+    with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+        f.write("ok" if ok and changed else f"mismatch ok={ok} changed={changed}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_peer_memory_step_equals_nccl_step(tmp_path):
+    import torch
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert open(tmp_path / f"rank{r}.txt").read() == "ok"
