@@ -127,8 +127,12 @@ def cpu_chain(cfg_kw, n_seqs: int, steps: int, warmup: int, threads=None):
     from oracle.oracle import Oracle, _fp, _ip
 
     orc = Oracle(fast=True)
-    if threads:
-        orc.set_num_threads(threads)
+    if not threads:      # all host cores, also under torchrun (which exports OMP_NUM_THREADS=1)
+        try:
+            threads = len(os.sched_getaffinity(0))
+        except AttributeError:
+            threads = os.cpu_count() or 1
+    orc.set_num_threads(threads)
     nthreads = orc.num_threads()
     orc.set_chunk(128)      # spread (sequence, 128-token block) pairs over the threads
     C = orc.lib
