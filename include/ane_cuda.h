@@ -189,8 +189,9 @@ int ane_cuda_rmsnorm_bwd_dev(void *stream, ane_dtype dtype, int B, int C, int S,
  *     (cudaGetSymbolAddress) -- make that first call before any stream capture;
  *   - all calls share the one array: calls that may overlap on the GPU (different streams,
  *     or other threads) race on it.  Keep them on one stream, or order them with events.
- * Results: dx is bit-identical to ane_cuda_rmsnorm_bwd_dev; dw may differ in the last bits
- * (the partials are split over at most 296 blocks, a different fixed summation order). */
+ * Results: the same operator as ane_cuda_rmsnorm_bwd_dev within fp32 rounding -- the two entry points
+ * may run different kernels, whose per-token sums and dw partials are added in different (each
+ * fixed) orders; a call with the same arguments gives the same bits every time. */
 int ane_cuda_rmsnorm_bwd_static_dev(void *stream, ane_dtype dtype, int B, int C, int S,
                                     void *dx, float *dw, const void *dy, const void *x, const float *w,
                                     const void *add, float eps, unsigned flags);
