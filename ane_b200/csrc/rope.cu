@@ -386,11 +386,11 @@ struct ItemMap {
     }
 };
 
-template <typename T, int RPT, bool ROPE, int NST>
+template <typename T, int RPT, bool ROPE, int NST, bool TILED = false>
 __global__ void __launch_bounds__(QK_THREADS)
 qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap, const float *__restrict__ w, int heads,
                   int S, int tiles_per_seq, int ntiles, float eps, ane_cuda_status *status,
-                  const float *__restrict__ cosT, const float *__restrict__ sinT) {
+                  const float *__restrict__ cosT, const float *__restrict__ sinT, int out_ratio) {
     constexpr int VEC = Elt<T>::VEC;
     constexpr int TW = QK_LG * VEC;
     constexpr int HD = RPT * QK_R;
@@ -488,18 +488,28 @@ qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap,
                     v[2 * p + 1] = vfma(a, sn[p], vmul(bb, cs[p]));
                 }
             }
-            const size_t o = (size_t)b * heads * hstep + h * hstep + (size_t)(rg * RPT) * S + t;
+            // out_ratio > 1: the result is written to the `out_ratio` query heads that share this KV head (the tiled
+            // layout of a grouped-query model, training_dynamic/io.h:330-337, as an index map instead of a copy)
+            const int n_out = TILED ? out_ratio : 1;
+            for (int r = 0; r < n_out; r++) {
+                const size_t o = TILED ? ((size_t)b * heads * out_ratio + (size_t)h * out_ratio + r) * hstep + (size_t)(rg * RPT) * S + t
+                                       : (size_t)b * heads * hstep + h * hstep + (size_t)(rg * RPT) * S + t;
 #pragma unroll
-            for (int k = 0; k < RPT; k++) {
-                Raw<T, VEC> ro;
-                ro.put(v[k]);
-                ro.store_stream(out + o + (size_t)k * S);
+                for (int k = 0; k < RPT; k++) {
+                    Raw<T, VEC> ro;
+                    ro.put(v[k]);
+                    ro.store_stream(out + o + (size_t)k * S);
+                }
             }
         }
     }
 }
 
-template <typename T, int RPT, bool ROPE, int NST>
+// GQ > 1: dy is the TILED gradient [B][heads*GQ*HD][S] of a grouped-query layout (query head h*GQ + r belongs to
+// KV head h); the GQ tiles of a head are added in fp32, in head order, and rounded once to T before anything else
+// uses them -- exactly what gqa_reduce followed by this operator computes (training_dynamic/io.h:340-351,
+// train.m:653-656), without the reduced tensor ever crossing HBM.
+template <typename T, int RPT, bool ROPE, int NST, int GQ = 1>
 __global__ void __launch_bounds__(QK_THREADS, 2)
 qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_constant__ CUtensorMap dymap,
                   const __grid_constant__ CUtensorMap xmap, const float *__restrict__ w, int heads, int S, int tiles_per_seq,
@@ -509,7 +519,7 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
     constexpr int TW = QK_LG * VEC;
     constexpr int HD = RPT * QK_R;
     constexpr uint32_t TILE_BYTES = HD * TW * sizeof(T);
-    constexpr uint32_t STAGE_BYTES = 2 * TILE_BYTES;       // x tile, then dy tile
+    constexpr uint32_t STAGE_BYTES = (1 + GQ) * TILE_BYTES;   // x tile, then the dy tile(s)
     extern __shared__ unsigned char stages_raw[];
     unsigned char *stages = stages_raw + ((128u - (smem_u32(stages_raw) & 127u)) & 127u);   // 128-byte aligned copy targets
     __shared__ __align__(8) uint64_t full[NST];
@@ -546,7 +556,9 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
         unsigned char *dst = stages + (size_t)s * STAGE_BYTES;
         mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
         tma_load_3d(dst, &xmap, (tl % tiles_per_seq) * TW, ph * HD, tl / tiles_per_seq, &full[s]);
-        tma_load_3d(dst + TILE_BYTES, &dymap, (tl % tiles_per_seq) * TW, ph * HD, tl / tiles_per_seq, &full[s]);
+#pragma unroll
+        for (int r = 0; r < GQ; r++)
+            tma_load_3d(dst + (1 + r) * TILE_BYTES, &dymap, (tl % tiles_per_seq) * TW, (ph * GQ + r) * HD, tl / tiles_per_seq, &full[s]);
         im.next(j + 1, ptl, ph);
     };
     if (threadIdx.x == 0)
@@ -573,7 +585,24 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
         }
         if (!mbar_wait_bounded(&full[s], (uint32_t)(j / NST) & 1u)) give_up = 1;
         const T *xt = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES);
-        const T *dt = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES + TILE_BYTES);
+        T *dt = reinterpret_cast<T *>(stages + (size_t)s * STAGE_BYTES + TILE_BYTES);
+        if (GQ > 1) {       // head sum into the first dy tile; a thread only ever touches its own entries of the tiles
+#pragma unroll
+            for (int k = 0; k < RPT; k++) {
+                const int e = (rg * RPT + k) * TW + lg * VEC;
+                Raw<T, VEC> a;
+                a.load(dt + e);
+                V<VEC> acc = a.get();
+#pragma unroll
+                for (int r = 1; r < GQ; r++) {
+                    Raw<T, VEC> c;
+                    c.load(dt + (size_t)r * (TILE_BYTES / sizeof(T)) + e);
+                    acc = vadd(acc, c.get());
+                }
+                a.put(acc);
+                a.store(dt + e);
+            }
+        }
         // Sweep 1 keeps nothing but the two sums; sweep 2 reads the tile again from shared memory and
         // redoes the inverse rotation (a few packed operations) -- the register file then allows two
         // blocks per SM.
@@ -790,6 +819,44 @@ static int launch_qk_rope_bwd_generic(cudaStream_t st, int B, int heads, int hd,
     return ANE_CUDA_OK;
 }
 
+// RoPE^-1 + QK-norm backward with the grouped-query head sum folded in (two-stage ring: a stage holds the x tile and
+// `ratio` dy tiles).
+template <typename T>
+static int launch_qk_bwd_gqa(cudaStream_t st, int B, int heads, int ratio, int hd, int S, void *dx, float *dw, const void *dy,
+                             const void *x, const float *w, float eps, float base, int pos0, unsigned flags, const RopeFreq &fq) {
+    constexpr int VEC = Elt<T>::VEC;
+    const float *cosT = rope_table(st, hd, S, base, pos0, fq);
+    if (!cosT) return fail(ANE_CUDA_ERR_NOMEM, "rope_qknorm_bwd_gqa: no memory for the cos/sin table");
+    const float *sinT = cosT + (size_t)S * (hd / 2);
+    const int tps = (S + QK_LG * VEC - 1) / (QK_LG * VEC);
+    const int ntiles = B * tps;
+    const ane_dtype dte = sizeof(T) == 4 ? ANE_F32 : (std::is_same<T, __half>::value ? ANE_F16 : ANE_BF16);
+    CUtensorMap xmap, dymap;
+    if (int rc = make_bcs_tensor_map(&xmap, dte, x, B, heads * hd, S, QK_LG * VEC, hd)) return rc;
+    if (int rc = make_bcs_tensor_map(&dymap, dte, dy, B, heads * ratio * hd, S, QK_LG * VEC, hd)) return rc;
+    int grid = 0;
+    float *partial = nullptr;
+#define ANE_QKB_GQA(RPTv, GQv)                                                                                       \
+    do {                                                                                                             \
+        auto k = qk_bwd_tma_kernel<T, RPTv, true, 2, GQv>;                                                            \
+        const size_t smem = (size_t)2 * (1 + GQv) * (RPTv * QK_R) * (QK_LG * VEC) * sizeof(T) + 128;                    \
+        ANE_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));               \
+        int per_sm = 0;                                                                                              \
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, QK_THREADS, smem) != cudaSuccess || per_sm < 1) per_sm = 1; \
+        grid = per_sm * ctx().sm_count;                                                                              \
+        if (grid > ntiles) grid = ntiles;                                                                            \
+        partial = static_cast<float *>(workspace((size_t)grid * hd * sizeof(float)));                                \
+        if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rope_qknorm_bwd_gqa: no scratch");                            \
+        k<<<grid, QK_THREADS, smem, st>>>((T *)dx, partial, dymap, xmap, w, heads, S, tps, ntiles, eps, flags, ctx().status, cosT, sinT); \
+    } while (0)
+    if (hd == 128) { if (ratio == 2) ANE_QKB_GQA(4, 2); else ANE_QKB_GQA(4, 4); }
+    else { if (ratio == 2) ANE_QKB_GQA(2, 2); else ANE_QKB_GQA(2, 4); }
+#undef ANE_QKB_GQA
+    column_sum_add_kernel<><<<(hd + 31) / 32, 256, 0, st>>>(dw, partial, grid, hd);
+    ANE_LAUNCH_OK(2);
+    return ANE_CUDA_OK;
+}
+
 static int fill_freq(RopeFreq &fq, int hd, float base) {
     if (hd < 2 || (hd & 1) || hd > 256) return fail(ANE_CUDA_ERR_UNSUPPORTED, "rope: head dim %d must be even and <= 256", hd);
     // freq = 1/powf(base, 2*i/hd) with the host libm                    cpu_ops.h:172
@@ -844,7 +911,7 @@ static bool qk_fast_ok(int hd, int S, const void *a, const void *b, const void *
 
 template <typename T, bool ROPE>
 static int launch_qk_fwd(cudaStream_t st, int B, int heads, int hd, int S, void *out, const void *x, const float *w,
-                         float eps, float base, int pos0, const RopeFreq &fq) {
+                         float eps, float base, int pos0, const RopeFreq &fq, int out_ratio = 1) {
     constexpr int VEC = Elt<T>::VEC;
     const float *cosT = nullptr, *sinT = nullptr;
     if (ROPE) {
@@ -854,7 +921,7 @@ static int launch_qk_fwd(cudaStream_t st, int B, int heads, int hd, int S, void 
     }
     const int tps = (S + QK_LG * VEC - 1) / (QK_LG * VEC);
     const unsigned grid = (unsigned)(B * tps);
-    const int hb = tuning("qk_fwd", 3);
+    const int hb = out_ratio > 1 ? 3 : tuning("qk_fwd", 3);       // the tiled output exists in the TMA kernel only
     if (hb >= 3) {       // TMA-fed ring of hb stages
         CUtensorMap xmap;
         if (int rc = make_bcs_tensor_map(&xmap, sizeof(T) == 4 ? ANE_F32 : (std::is_same<T, __half>::value ? ANE_F16 : ANE_BF16), x, B,
@@ -862,14 +929,14 @@ static int launch_qk_fwd(cudaStream_t st, int B, int heads, int hd, int S, void 
         const int ntiles = B * tps;
 #define ANE_QKF_TMA(RPTv, NSTv)                                                                                      \
         do {                                                                                                         \
-            auto k = qk_fwd_tma_kernel<T, RPTv, ROPE, NSTv>;                                                          \
+            auto k = out_ratio > 1 ? qk_fwd_tma_kernel<T, RPTv, ROPE, NSTv, true> : qk_fwd_tma_kernel<T, RPTv, ROPE, NSTv, false>; \
             const size_t smem = (size_t)NSTv * (RPTv * QK_R) * (QK_LG * VEC) * sizeof(T) + 128;                             \
             ANE_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));           \
             int per_sm = 0;                                                                                          \
             if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, QK_THREADS, smem) != cudaSuccess || per_sm < 1) per_sm = 1; \
             int g = per_sm * ctx().sm_count;                                                                         \
             if (g > ntiles) g = ntiles;                                                                              \
-            k<<<g, QK_THREADS, smem, st>>>((T *)out, xmap, w, heads, S, tps, ntiles, eps, ctx().status, cosT, sinT);   \
+            k<<<g, QK_THREADS, smem, st>>>((T *)out, xmap, w, heads, S, tps, ntiles, eps, ctx().status, cosT, sinT, out_ratio); \
         } while (0)
         if (hd == 128) { if (hb == 3) ANE_QKF_TMA(4, 3); else if (hb == 4) ANE_QKF_TMA(4, 4); else ANE_QKF_TMA(4, 6); }
         else { if (hb == 3) ANE_QKF_TMA(2, 3); else if (hb == 4) ANE_QKF_TMA(2, 4); else ANE_QKF_TMA(2, 6); }
@@ -1010,6 +1077,42 @@ int ane_cuda_qknorm_rope_dev(void *stream, ane_dtype dtype, int B, int heads, in
     // other head widths and unaligned shapes
     ANE_DISPATCH_DTYPE(dtype, T, return (launch_qk_rope_fwd_generic<T>(st, B, heads, hd, S, out, x, w, eps, pos0, fq)));
     return ANE_CUDA_OK;
+}
+
+int ane_cuda_qknorm_rope_tiled_dev(void *stream, ane_dtype dtype, int B, int kv_heads, int ratio, int hd, int S, void *out_tiled,
+                                   const void *x, const float *w, float eps, float base, int pos0) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(out_tiled && x && w, "%s: null pointer", __func__);
+    ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
+    ANE_REQUIRE(ratio >= 1 && ratio <= 64, "%s: bad ratio %d", __func__, ratio);
+    if (int rc = check_qk(__func__, B, kv_heads, hd, S)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    RopeFreq fq;
+    if (int rc = fill_freq(fq, hd, base)) return rc;
+    ANE_DISPATCH_DTYPE(dtype, T,
+        if (qk_fast_ok<T, true>(hd, S, out_tiled, x, nullptr))
+            return (launch_qk_fwd<T, true>(st, B, kv_heads, hd, S, out_tiled, x, w, eps, base, pos0, fq, ratio)));
+    return fail(ANE_CUDA_ERR_UNSUPPORTED, "%s: the tiled output covers head widths 64 and 128 and 16-byte aligned rows; use "
+                "ane_cuda_qknorm_rope_dev followed by ane_cuda_gqa_tile_dev for other shapes", __func__);
+}
+
+int ane_cuda_rope_qknorm_bwd_gqa_dev(void *stream, ane_dtype dtype, int B, int kv_heads, int ratio, int hd, int S, void *dx, float *dw,
+                                     const void *dy_tiled, const void *x, const float *w, float eps, float base, int pos0,
+                                     unsigned flags) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(dx && dw && dy_tiled && x && w, "%s: null pointer", __func__);
+    ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
+    ANE_REQUIRE(flags == ANE_NORM_BWD_REFERENCE || flags == ANE_NORM_BWD_EXACT, "%s: bad flags %u", __func__, flags);
+    if (int rc = check_qk(__func__, B, kv_heads, hd, S)) return rc;
+    if (ratio == 1) return ane_cuda_rope_qknorm_bwd_dev(stream, dtype, B, kv_heads, hd, S, dx, dw, dy_tiled, x, w, eps, base, pos0, flags);
+    cudaStream_t st = (cudaStream_t)stream;
+    RopeFreq fq;
+    if (int rc = fill_freq(fq, hd, base)) return rc;
+    ANE_DISPATCH_DTYPE(dtype, T,
+        if ((ratio == 2 || ratio == 4) && qk_fast_ok<T, true>(hd, S, dx, dy_tiled, x))
+            return (launch_qk_bwd_gqa<T>(st, B, kv_heads, ratio, hd, S, dx, dw, dy_tiled, x, w, eps, base, pos0, flags, fq)));
+    return fail(ANE_CUDA_ERR_UNSUPPORTED, "%s: the fused form covers ratios 2 and 4, head widths 64 and 128 and 16-byte aligned rows; "
+                "use ane_cuda_gqa_reduce_dev followed by ane_cuda_rope_qknorm_bwd_dev for other shapes", __func__);
 }
 
 int ane_cuda_rope_qknorm_bwd_dev(void *stream, ane_dtype dtype, int B, int heads, int hd, int S, void *dx, float *dw,

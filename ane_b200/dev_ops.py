@@ -261,3 +261,22 @@ def p2p_adam(w_ptrs, rank, lo, n, g_slice, m_slice, v_slice, t, lr, b1, b2, eps,
     arr = _ptr_array(w_ptrs)
     _l.check(_l.load().ane_cuda_p2p_adam_dev(_stream(), len(w_ptrs), rank, arr, lo, n, _p(g_slice), _p(m_slice), _p(v_slice), t, lr, b1,
                                              b2, eps, wd, gscale, _p(clip), _l.ADAM_DYNAMIC if dynamic else _l.ADAM_STORIES))
+
+
+def rope_qknorm_bwd_gqa(dy_tiled, x, w, dw, hd, ratio, eps=1e-6, base=1e6, pos0=0, exact=False, out=None):
+    """RoPE^-1 + QK-norm backward of the K side; dy_tiled [B][kv_heads*ratio*hd][S] is summed over each KV head's
+    `ratio` query heads inside the kernel (gqa_reduce folded in)."""
+    out = torch.empty_like(x) if out is None else out
+    B, Cn, S = _bcs(x)
+    _l.check(_l.load().ane_cuda_rope_qknorm_bwd_gqa_dev(_stream(), _dt(x), B, Cn // hd, ratio, hd, S, _p(out), _p(dw), _p(dy_tiled),
+                                                        _p(x), _p(w), eps, base, pos0,
+                                                        _l.NORM_BWD_EXACT if exact else _l.NORM_BWD_REFERENCE))
+    return out
+
+
+def qknorm_rope_tiled(x, w, hd, ratio, eps=1e-6, base=1e6, pos0=0, out=None):
+    """QK-norm + RoPE of K [B][kv_heads*hd][S] written into the tiled layout [B][kv_heads*ratio*hd][S]."""
+    B, Cn, S = _bcs(x)
+    out = torch.empty((B, Cn * ratio, S), dtype=x.dtype, device=x.device) if out is None else out
+    _l.check(_l.load().ane_cuda_qknorm_rope_tiled_dev(_stream(), _dt(x), B, Cn // hd, ratio, hd, S, _p(out), _p(x), _p(w), eps, base, pos0))
+    return out

@@ -109,6 +109,8 @@ PROTOTYPES = {
     "ane_cuda_grad_norm_sq_dev": (_i, [_vp, _sz, _vp, _f, _vp]),
     "ane_cuda_clip_factor_dev": (_i, [_vp, _vp, _i, _f, _vp]),
     # layout helpers
+    "ane_cuda_qknorm_rope_tiled_dev": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _f, _f, _i]),
+    "ane_cuda_rope_qknorm_bwd_gqa_dev": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _u]),
     "ane_cuda_gqa_tile_dev": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "ane_cuda_gqa_reduce_dev": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "ane_cuda_convert_dev": (_i, [_vp, _i, _i, _sz, _vp, _vp]),

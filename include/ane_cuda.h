@@ -258,6 +258,21 @@ int ane_cuda_clip_factor_dev(void *stream, const float *normsq_dev, int n_terms,
  * times (query head kv*ratio + r reads KV head kv).       training_dynamic/io.h:330-337 (gqa_tile_kv) */
 int ane_cuda_gqa_tile_dev(void *stream, ane_dtype dtype, int B, int kv_heads, int ratio, int hd, int S,
                           void *out, const void *in);
+/* QK-norm + RoPE of the K side written straight into the tiled (query-head) layout [B][kv_heads*ratio*hd][S]: every KV
+ * head's result goes to its `ratio` query heads -- ane_cuda_qknorm_rope_dev followed by ane_cuda_gqa_tile_dev, bit for
+ * bit, without the untiled tensor crossing HBM.  Head widths 64 and 128, 16-byte aligned rows (else
+ * ANE_CUDA_ERR_UNSUPPORTED).                                              training_dynamic/train.m:620-621, io.h:330-337 */
+int ane_cuda_qknorm_rope_tiled_dev(void *stream, ane_dtype dtype, int B, int kv_heads, int ratio, int hd, int S, void *out_tiled,
+                                   const void *x, const float *w, float eps, float base, int pos0);
+/* RoPE^-1 + QK-norm backward of the K side with the head sum folded in: dy_tiled is the gradient in the tiled
+ * (query-head) layout [B][kv_heads*ratio*hd][S] that SDPA backward produces; the `ratio` heads of each KV head are
+ * added in fp32 in head order and rounded once to the storage type, then the operator runs as
+ * ane_cuda_rope_qknorm_bwd_dev -- the result equals ane_cuda_gqa_reduce_dev followed by that call bit for bit, and
+ * the reduced tensor never crosses HBM.  Ratios 2 and 4 (1 forwards to the plain call), head widths 64 and 128,
+ * 16-byte aligned rows; other shapes return ANE_CUDA_ERR_UNSUPPORTED.   training_dynamic/train.m:653-656, io.h:340-351 */
+int ane_cuda_rope_qknorm_bwd_gqa_dev(void *stream, ane_dtype dtype, int B, int kv_heads, int ratio, int hd, int S, void *dx,
+                                     float *dw, const void *dy_tiled, const void *x, const float *w, float eps, float base,
+                                     int pos0, unsigned flags);
 /* GQA head sum: in [B][kv_heads*ratio*hd][S] -> out [B][kv_heads*hd][S], out = 0 + in[r=0] + in[r=1] + ...
  * in head order (fp32 adds, one rounding on store).        training_dynamic/io.h:340-351 (gqa_reduce_kv) */
 int ane_cuda_gqa_reduce_dev(void *stream, ane_dtype dtype, int B, int kv_heads, int ratio, int hd, int S,

@@ -166,3 +166,49 @@ def test_vocab_compaction_matches_oracle(orc, case):
     # compact-vocabulary round trip: gather, change, write back, gather again
     assert torch.equal(ops.vocab_compact_embed(u, c2f, cnt, cv), comp_d)
     assert lib.poll_status().oor_ids == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32", "float16"])
+@pytest.mark.parametrize("case", [(2, 8, 2, 128, 256), (1, 2, 4, 128, 192), (3, 4, 2, 64, 128), (1, 1, 4, 64, 64)])
+def test_head_sum_folded_into_k_backward(orc, dtype, case):
+    """ane_cuda_rope_qknorm_bwd_gqa_dev equals gqa_reduce followed by rope_qknorm_bwd bit for bit (dx and dw), and the
+    unfused pair equals the oracle's gqa_reduce + rope_qknorm_bwd within the storage type's tolerance."""
+    torch = _cuda()
+    from ane_b200 import dev_ops as ops
+    B, kv, ratio, hd, S = case
+    tdt = getattr(torch, dtype)
+    rng = np.random.default_rng(31)
+    x = torch.from_numpy(rng.standard_normal((B, kv * hd, S)).astype(np.float32)).to(tdt).cuda()
+    dyt = torch.from_numpy(rng.standard_normal((B, kv * ratio * hd, S)).astype(np.float32)).to(tdt).cuda()
+    w = torch.from_numpy((1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)).cuda()
+    dw_a, dw_b = torch.zeros(hd, device="cuda"), torch.zeros(hd, device="cuda")
+    fused = ops.rope_qknorm_bwd_gqa(dyt, x, w, dw_a, hd, ratio)
+    dk = ops.gqa_reduce(dyt, kv, ratio)
+    plain = ops.rope_qknorm_bwd(dk, x, w, dw_b, hd)
+    assert torch.equal(fused, plain)
+    assert torch.equal(dw_a, dw_b)
+    # and the pair against the oracle
+    rdk = torch.from_numpy(orc.gqa_reduce(dyt.float().cpu().numpy(), kv, ratio)).to(tdt).float().numpy()
+    rdx, rdw = orc.rope_qknorm_bwd(rdk, x.float().cpu().numpy(), w.cpu().numpy(), hd, eps=1e-6, base=1e6)
+    got = fused.float().cpu().numpy()
+    scale = np.abs(rdx).max()
+    tol = 1e-5 if dtype == "float32" else (2.0 ** -8 if dtype == "bfloat16" else 2.0 ** -11)
+    assert np.abs(got - rdx).max() <= tol * scale
+    assert np.abs(dw_a.cpu().numpy() - rdw).max() <= (1e-5 if dtype == "float32" else 1e-4) * np.abs(rdw).max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("case", [(2, 8, 2, 128, 256), (1, 2, 4, 128, 192), (3, 4, 3, 64, 128)])
+def test_k_forward_written_into_the_tiled_layout(dtype, case):
+    """ane_cuda_qknorm_rope_tiled_dev equals qknorm_rope followed by gqa_tile bit for bit."""
+    torch = _cuda()
+    from ane_b200 import dev_ops as ops
+    B, kv, ratio, hd, S = case
+    tdt = getattr(torch, dtype)
+    rng = np.random.default_rng(41)
+    x = torch.from_numpy(rng.standard_normal((B, kv * hd, S)).astype(np.float32)).to(tdt).cuda()
+    w = torch.from_numpy((1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)).cuda()
+    fused = ops.qknorm_rope_tiled(x, w, hd, ratio)
+    assert torch.equal(fused, ops.gqa_tile(ops.qknorm_rope(x, w, hd), kv, ratio))
