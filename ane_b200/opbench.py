@@ -145,6 +145,15 @@ def _cases(torch, ops, device, M, shape=None):
         o = [torch.empty((M, KVD, S), dtype=bf, device=device) for _ in range(NSET)]
         return (lambda i: ops.gqa_reduce(q[i % NSET], 8, 2, out=o[i % NSET])), (KVD + QD) * T * e, 20
 
+    def qknorm_rope_tiled():
+        (wq, _), k = head_w(), mk(KVD)
+        o = [torch.empty((M, QD, S), dtype=bf, device=device) for _ in range(NSET)]
+        return (lambda i: ops.qknorm_rope_tiled(k[i % NSET], wq, HD, 2, out=o[i % NSET])), (KVD + QD) * T * e, 20
+
+    def rope_qknorm_bwd_gqa():
+        (wq, dwq), k, dyt, o = head_w(), mk(KVD), mk(QD), mk(KVD)
+        return (lambda i: ops.rope_qknorm_bwd_gqa(dyt[i % NSET], k[i % NSET], wq, dwq, HD, 2, out=o[i % NSET])), (QD + 2 * KVD) * T * e, 20
+
     def convert_f32_bf16():
         x = mk(D, dtype=torch.float32)
         o = [torch.empty((M, D, S), dtype=torch.bfloat16, device=device) for _ in range(NSET)]
@@ -159,7 +168,8 @@ def _cases(torch, ops, device, M, shape=None):
         return (lambda i: ops.vocab_compact_embed(full, c2f, cnt, Vc, out=out[i % 2])), 2 * Vc * D * 4 + Vc * 4, 20
 
     return {
-        "gqa_tile": gqa_tile, "gqa_reduce": gqa_reduce, "convert_f32_bf16": convert_f32_bf16,
+        "gqa_tile": gqa_tile, "gqa_reduce": gqa_reduce, "qknorm_rope_tiled(K)": qknorm_rope_tiled,
+        "rope_qknorm_bwd_gqa(K)": rope_qknorm_bwd_gqa, "convert_f32_bf16": convert_f32_bf16,
         "vocab_compact_embed": vocab_compact_embed,
         "rmsnorm": rmsnorm, "rmsnorm_bwd": rmsnorm_bwd, "rmsnorm_bwd_add": rmsnorm_bwd_add,
         "residual_rmsnorm": residual_rmsnorm, "residual": residual, "swiglu": swiglu, "swiglu_bwd": swiglu_bwd,
