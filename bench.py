@@ -246,7 +246,8 @@ def workload_config(args, world):
     return {
         "workload": "configs[4]: Qwen3-0.6B non-matmul layer chain (28 layers, dim 1024, hidden 3072, GQA 16/8, "
                     "head_dim 128, bf16 activations) + Adam on 596M fp32 params",
-        "sequences": args.seqs, "seq_len": 2048, "layers": args.layers, "micro_batch_per_gpu": args.micro_batch,
+        "sequences": args.seqs, "seq_len": 2048, "layers": args.layers,
+        "micro_batch_per_gpu": min(args.micro_batch, max(1, args.seqs // world)),
         "parallelism": f"dp{world} (sequences sharded, ZeRO-1 Adam)",
         "launch": "host launches" if getattr(args, "no_graph", False) else "CUDA graph replay per micro-batch (the first micro-batch of the first timed step runs eagerly, with events around the dominant kernel)",
         "l2_policy": f"inputs larger than L2: every operator reads per-layer buffers ({4 * min(args.micro_batch, max(1, args.seqs // world))}-"
