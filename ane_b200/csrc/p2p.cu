@@ -142,7 +142,7 @@ using namespace ane;
 extern "C" {
 
 int ane_cuda_p2p_reduce_dev(void *stream, int nranks, const float *const *g_ranks, size_t lo, size_t n, float *g_slice, float gscale,
-                            float *normsq_dev) {
+                            float *normsq_dev, float *scratch) {
     ANE_REQUIRE_INIT();
     ANE_REQUIRE(g_ranks && g_slice && normsq_dev, "%s: null pointer", __func__);
     ANE_REQUIRE(nranks >= 1 && nranks <= P2P_MAX_RANKS, "%s: 1..%d ranks (got %d)", __func__, P2P_MAX_RANKS, nranks);
@@ -152,7 +152,9 @@ int ane_cuda_p2p_reduce_dev(void *stream, int nranks, const float *const *g_rank
     size_t blocks = (n + (size_t)P2P_THREADS * 16 - 1) / ((size_t)P2P_THREADS * 16);
     if (blocks < 1) blocks = 1;
     if (blocks > P2P_MAX_BLOCKS) blocks = P2P_MAX_BLOCKS;
-    float *partial = static_cast<float *>(workspace(P2P_MAX_BLOCKS * sizeof(float)));
+    // block partials: the caller's scratch (needed when this call runs on a stream beside other operators of the
+    // library, which share the library-owned range) or the library-owned range
+    float *partial = scratch ? scratch : static_cast<float *>(workspace(P2P_MAX_BLOCKS * sizeof(float)));
     if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "%s: no scratch", __func__);
     cudaStream_t st = (cudaStream_t)stream;
     p2p_reduce_kernel<<<(unsigned)blocks, P2P_THREADS, 0, st>>>(g_slice, partial, g, nranks, lo, n, gscale);

@@ -120,7 +120,7 @@ PROTOTYPES = {
     "ane_cuda_vocab_scatter_grads_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "ane_cuda_vocab_update_full_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     # optimizer step over peer memory
-    "ane_cuda_p2p_reduce_dev": (_i, [_vp, _i, _vp, _sz, _sz, _vp, _f, _vp]),
+    "ane_cuda_p2p_reduce_dev": (_i, [_vp, _i, _vp, _sz, _sz, _vp, _f, _vp, _vp]),
     "ane_cuda_p2p_adam_dev": (_i, [_vp, _i, _i, _vp, _sz, _sz, _vp, _vp, _vp, _i, _f, _f, _f, _f, _f, _f, _vp, _u]),
     # checkpoints
     "ane_cuda_ckpt_read_header": (_i, [C.c_char_p, _vp]),

@@ -49,10 +49,13 @@ class ShardedAdam:
 
     def __init__(self, w, g, m, v, n_decay: int, n_params: int, world: int = 1, rank: int = 0, group=None,
                  lr: float = 3e-4, b1: float = 0.9, b2: float = 0.95, eps: float = 1e-8, wd: float = 0.1,
-                 clip: float = 1.0, kernels=None, peer_ptrs=None):
+                 clip: float = 1.0, kernels=None, peer_ptrs=None, n_early: int = 0):
         """peer_ptrs = (w_ptrs, g_ptrs): device addresses of every rank's flat parameter and gradient buffer, mapped
         into this process (see symmetric_buffers).  With them the reduce-scatter and the all-gather are not separate
-        collectives: the reduce kernel reads the peers' gradients and the Adam kernel writes the peers' parameters."""
+        collectives: the reduce kernel reads the peers' gradients and the Adam kernel writes the peers' parameters.
+        n_early: gradients [0, n_early) are complete when begin_step() is called (the caller's matmul gradients, as
+        opposed to the embedding and norm-weight gradients the operator chain produces during the step); in peer mode
+        their part of the reduce then runs on a side stream beside the chain."""
         if w.numel() % world:
             raise ValueError("flat buffers must be padded to a multiple of the world size (see padded_length)")
         self.w, self.g, self.m, self.v = w, g, m, v
@@ -69,6 +72,13 @@ class ShardedAdam:
         self.normsq = None
         self.peer_ptrs = peer_ptrs if world > 1 else None
         self._token = torch.zeros(1, dtype=torch.float32, device=g.device) if self.peer_ptrs else None
+        self.n_early = n_early if self.peer_ptrs else 0
+        self._early = None            # (event, end of the range already reduced) of the step in flight
+        if self.peer_ptrs:
+            self._side = torch.cuda.Stream(device=g.device)
+            self._normsq2 = torch.zeros(2, dtype=torch.float32, device=g.device)
+            self._token2 = torch.zeros(1, dtype=torch.float32, device=g.device)
+            self._scratch = torch.zeros(1184, dtype=torch.float32, device=g.device)   # block partials of the side-stream reduce
         self.phase_events = None      # set to [] to collect (name, start, end) CUDA events of the next steps
 
     def _reduce_scatter(self):
@@ -102,13 +112,42 @@ class ShardedAdam:
         rank has reached it on its stream, i.e. after everything each of them enqueued before it."""
         dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.group)
 
+    def begin_step(self, gscale: float = 1.0):
+        """Peer mode with n_early > 0: start reducing the part of this rank's slice whose gradients are already complete,
+        on a side stream, so that it overlaps the operator chain.  Every rank must call it (it contains a collective)."""
+        if not self.peer_ptrs or self.n_early <= 0:
+            return
+        w_ptrs, g_ptrs = self.peer_ptrs
+        a, b = self.lo, min(self.hi, self.n_early)
+        cur = torch.cuda.current_stream()
+        self._side.wait_stream(cur)
+        with torch.cuda.stream(self._side):
+            dist.all_reduce(self._token2, op=dist.ReduceOp.SUM, group=self.group)      # all ranks' early gradients are in place
+            self._normsq2.zero_()
+            if a < b:
+                self.k.p2p_reduce(g_ptrs, a, b - a, self.g_slice[:b - a], gscale, normsq=self._normsq2[0:1], scratch=self._scratch)
+            ev = torch.cuda.Event()
+            ev.record(self._side)
+        self._early = (ev, max(a, b), gscale)
+
     def _step_peer(self, t: int, gscale: float):
         w_ptrs, g_ptrs = self.peer_ptrs
+        start = self.lo
+        if self._early is not None:
+            ev, start, gs0 = self._early
+            if gs0 != gscale:
+                raise ValueError("begin_step and step must use the same gscale")
+            torch.cuda.current_stream().wait_event(ev)
+            self._early = None
+        else:
+            self._normsq2.zero_()
         self._rank_sync()                                               # every rank's gradients are complete
-        normsq = self.k.p2p_reduce(g_ptrs, self.lo, self.slice_len, self.g_slice, gscale)
-        dist.all_reduce(normsq, op=dist.ReduceOp.SUM, group=self.group)  # also: every rank has finished reading gradients
+        if start < self.hi:
+            self.k.p2p_reduce(g_ptrs, start, self.hi - start, self.g_slice[start - self.lo:], gscale, normsq=self._normsq2[1:2])
+        dist.all_reduce(self._normsq2, op=dist.ReduceOp.SUM, group=self.group)  # also: every rank has finished reading gradients
+        normsq = self._normsq2.sum().reshape(1)
         self.normsq = normsq
-        factor = self.k.clip_factor(normsq, self.clip)
+        factor = self.k.clip_factor(self._normsq2, self.clip)
         for lo, hi, wd in ((0, self.n_decay, self.wd), (self.n_decay, self.n_params, 0.0)):
             a, b = max(lo, self.lo), min(hi, self.hi)
             if a < b:

@@ -423,7 +423,7 @@ def run_ours(args):
     params.init_random()
     chain = LayerChain(cfg, M, params, device)
     opt = ShardedAdam(params.w, params.g, params.m, params.v, params.n_decay, params.n, world, rank,
-                      lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0, peer_ptrs=peer_ptrs)
+                      lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0, peer_ptrs=peer_ptrs, n_early=params.n_matrix)
     gscale = 1.0 / (10 * 256.0)       # 1/(accum_steps*loss_scale), train.m:750
     tstep = [0]
     use_graph = not args.no_graph
@@ -434,6 +434,7 @@ def run_ours(args):
 
     def step():
         params.zero_produced_grads()
+        opt.begin_step(gscale)       # the matmul gradients are complete: their share of the exchange overlaps the chain
         for mb in range(n_micro):
             if use_graph and not (mb == 0 and chain.timed_op is not None):
                 chain.replay()

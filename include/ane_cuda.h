@@ -309,7 +309,9 @@ int ane_cuda_vocab_update_full_dev(void *stream, float *full_embed, const float 
  * single-device program; the arithmetic is the reference's (train.m:770-869, cpu_ops.h:56-64).
  * reduce: g_slice[i] = sum over ranks r = 0..nranks-1 (in that order) of g_ranks[r][lo + i], i < n -- the
  *         reduce-scatter, read from the peers' memory -- and *normsq_dev = sum_i (g_slice[i]*gscale)^2 in a fixed
- *         order (the caller all-reduces this scalar over the ranks for the clipping norm).
+ *         order (the caller all-reduces this scalar over the ranks for the clipping norm).  scratch: NULL, or 1184
+ *         floats of device memory for the block partials -- required when the call runs on a stream of its own
+ *         beside other operators of this library (they share the library-owned scratch range).
  * adam:   Adam on the slice (arguments as ane_cuda_adam_dev; g_slice, m_slice, v_slice start at the slice) with the
  *         new weights stored to position lo of EVERY rank's buffer w_ranks[r] -- the all-gather.
  * g_ranks / w_ranks are host arrays of nranks (<= 8) device pointers.  The kernels never wait for another rank:
@@ -317,7 +319,7 @@ int ane_cuda_vocab_update_full_dev(void *stream, float *full_embed, const float 
  * overwritten, and "all adam kernels complete" before parameters are read, across the ranks (any collective on
  * the same stream does). */
 int ane_cuda_p2p_reduce_dev(void *stream, int nranks, const float *const *g_ranks, size_t lo, size_t n, float *g_slice,
-                            float gscale, float *normsq_dev);
+                            float gscale, float *normsq_dev, float *scratch);
 int ane_cuda_p2p_adam_dev(void *stream, int nranks, int self, float *const *w_ranks, size_t lo, size_t n, const float *g_slice,
                           float *m_slice, float *v_slice, int t, float lr, float b1, float b2, float eps, float wd, float gscale,
                           const float *clip_dev, unsigned flags);

@@ -36,15 +36,26 @@ def _worker(rank, world, port, out_dir):
     g.copy_(torch.randn(n, device=dev, generator=gen_r) * 0.01)
     g[n_params:] = 0
     w2, g2 = w.clone(), g.clone()
-    m, v, m2, v2 = (torch.zeros(n, device=dev) for _ in range(4))
+    w3, g3, ptrs3 = symmetric_buffers(n, dev)
+    w3.copy_(w)
+    g3.copy_(g)
+    m, v, m2, v2, m3, v3 = (torch.zeros(n, device=dev) for _ in range(6))
     peer = ShardedAdam(w, g, m, v, n_decay, n_params, world, rank, peer_ptrs=ptrs)
     nccl = ShardedAdam(w2, g2, m2, v2, n_decay, n_params, world, rank)
+    early = ShardedAdam(w3, g3, m3, v3, n_decay, n_params, world, rank, peer_ptrs=ptrs3, n_early=70_001)   # part of the reduce ahead of time
     for t in (1, 2):
+        early.begin_step(0.5)
         peer.step(t, 0.5)
         nccl.step(t, 0.5)
+        early.step(t, 0.5)
     torch.cuda.synchronize()
     ok = bool(torch.equal(w, w2)) and bool(torch.equal(m[peer.lo:peer.hi], m2[peer.lo:peer.hi])) \
-        and bool(torch.equal(v[peer.lo:peer.hi], v2[peer.lo:peer.hi])) and bool(torch.equal(peer.normsq, nccl.normsq))
+        and bool(torch.equal(v[peer.lo:peer.hi], v2[peer.lo:peer.hi])) and bool(torch.equal(peer.normsq, nccl.normsq)) \
+        and bool(torch.allclose(early.normsq, nccl.normsq, rtol=1e-6)) \
+        and bool(torch.allclose(w3, w2, rtol=1e-5, atol=1e-8)) \
+        and bool(torch.allclose(m3[peer.lo:peer.hi], m2[peer.lo:peer.hi], rtol=1e-5, atol=1e-10))
+    # (the early form adds the squared norm as two partial sums, so its clip factor, and with it the update, may differ
+    # from the one-pass forms in the last bit)
     changed = bool((w != torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(7)) * 0.02)[:n_params].any())
     with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
         f.write("ok" if ok and changed else f"mismatch ok={ok} changed={changed}")
