@@ -167,9 +167,9 @@ xent_kernel(float *dlogits, const float *logits, const void *__restrict__ target
 // flight, so the second sweep always comes from HBM again (3 bytes moved per 2 needed).
 // Here a thread-block CLUSTER of XC_CL blocks owns a 16-token stripe (64-byte rows); block r of the
 // cluster takes vocabulary rows [r*rows_per_cta, (r+1)*rows_per_cta):
-//   1. one thread asks the copy engine (TMA) for the first `rows_res` rows of the slice, 256-row
-//      boxes, each signalling its own mbarrier -- up to 192 KB per SM in flight with no register
-//      staging; the rows that do not fit (if any) stream through registers meanwhile;
+//   1. the first `rows_res` rows of the slice are copied into shared memory with asynchronous 16-byte
+//      copies (up to 192 KB per SM in flight, no register staging), every entry by the thread that
+//      will use it; the rows that do not fit (if any) stream through registers meanwhile;
 //   2. online (max, sum) per token over the slice; warp shuffles, then shared memory, give the
 //      block's pair; the cluster exchanges the XC_CL pairs through distributed shared memory
 //      (hardware cluster barrier -- no flags in global memory, no cooperative launch);
@@ -179,8 +179,8 @@ xent_kernel(float *dlogits, const float *logits, const void *__restrict__ target
 constexpr int XC_CL = 8;               // blocks per cluster (portable maximum)
 constexpr int XC_LG = 4;               // 16-byte lanes per row: 16 tokens, 64-byte rows
 constexpr int XC_TW = XC_LG * 4;
-constexpr int XC_BOXR = 256;           // rows per copy-engine box (16 KB)
-constexpr int XC_MAXBOX = 13;
+constexpr int XC_UNIT = 256;           // resident rows are budgeted in units of 256 rows (16 KB)
+constexpr int XC_MAXUNITS = 12;        // 192 KB per block
 constexpr int XC_U = 4;
 
 // running (max, sum) of four tokens; ml = max * log2(e)
@@ -493,9 +493,9 @@ int ane_cuda_cross_entropy_dev(void *stream, ane_idtype idtype, int B, int V, in
         const int rows_per_cta = (V + XC_CL - 1) / XC_CL;
         const int cap = tuning("xent_boxes", threads == 512 ? 6 : 12);  // 16 KB units; 12 = 192 KB
         int rows_res = rows_per_cta;
-        if (rows_res > cap * XC_BOXR) rows_res = cap * XC_BOXR;
+        if (rows_res > cap * XC_UNIT) rows_res = cap * XC_UNIT;
         const size_t smem = (size_t)rows_res * XC_TW * sizeof(float) + 128;
-        if (nstripes < 0x7fffffffLL && cap >= 0 && cap <= XC_MAXBOX - 1) {
+        if (nstripes < 0x7fffffffLL && cap >= 0 && cap <= XC_MAXUNITS) {
             void (*kern)(float *, const float *, const void *, float *, int, int, int, int, int, int, float, ane_cuda_status *);
             if (threads == 512) kern = idtype == ANE_ID_U16 ? xent_cluster_kernel<uint16_t, 512> : xent_cluster_kernel<int32_t, 512>;
             else kern = idtype == ANE_ID_U16 ? xent_cluster_kernel<uint16_t, 1024> : xent_cluster_kernel<int32_t, 1024>;
