@@ -289,6 +289,38 @@ static int persistent_grid(KernelT kernel, int threads, size_t dyn_smem, int nti
     return (int)g;
 }
 
+// The cluster forms of the backward: CL blocks share the channels of one token tile (norm_st.cuh).
+template <typename T, bool HAS_ADD, int LGs, int CL, int NBUF>
+static int launch_rmsnorm_bwd_cluster(cudaStream_t st, int B, int C, int S, void *dx, float *dw, const void *dy, const void *x,
+                                      const float *w, const void *add, float eps, unsigned flags) {
+    constexpr int VEC = Elt<T>::VEC;
+    const int tps_ = (S + LGs * VEC - 1) / (LGs * VEC);
+    const int ntiles = B * tps_;
+    const int part = (C + CL - 1) / CL;
+    const size_t smem_st = (size_t)2 * NBUF * part * LGs * 16 + (size_t)part * sizeof(float);
+    auto k_ = rmsnorm_bwd_cluster_kernel<T, LGs, HAS_ADD, CL, NBUF>;
+    ANE_CUDA_TRY(cudaFuncSetAttribute(k_, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_st));
+    static int max_clusters = 0;               // co-resident clusters of this instantiation at the last smem size
+    static size_t max_clusters_smem = 0;
+    if (max_clusters == 0 || max_clusters_smem != smem_st) {
+        cudaLaunchConfig_t q = {};
+        q.gridDim = dim3(CL * ctx().sm_count * 4, 1, 1);
+        q.blockDim = dim3(ST_THREADS, 1, 1);
+        q.dynamicSmemBytes = smem_st;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, k_, &q) != cudaSuccess || n < 1) { cudaGetLastError(); n = ctx().sm_count / CL; }
+        max_clusters = n;
+        max_clusters_smem = smem_st;
+    }
+    const int ngroups = max_clusters < ntiles ? max_clusters : ntiles;
+    float *partial = static_cast<float *>(workspace((size_t)ngroups * C * sizeof(float)));
+    if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", ngroups, C);
+    k_<<<(unsigned)(CL * ngroups), ST_THREADS, smem_st, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags);
+    column_sum_add_kernel<><<<(C + 31) / 32, 256, 0, st>>>(dw, partial, ngroups, C);
+    ANE_LAUNCH_OK(2);
+    return ANE_CUDA_OK;
+}
+
 template <typename T, bool HAS_ADD>
 static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, float *dw, const void *dy, const void *x,
                               const float *w, const void *add, float eps, unsigned flags) {
@@ -298,11 +330,25 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
     int grid, ntiles;
     float *partial;
     if (vec) {
-        // Measured on B200 (C = 1024, bf16, 32-64 sequences): the block-pair kernel reaches 58-70 % of the copy rate,
-        // the two-sweep kernel below 41-58 %.  (Also tried and removed: a register-resident tile, 37-50 %; one block per
-        // strip with 32- or 64-byte rows, 37-53 %; a statistics kernel followed by an element-wise kernel, 42-57 %.)
-        const int knob_b = tuning("norm_bwd", 8);
-        if (knob_b == 8 && (size_t)C * 66 <= 200 * 1024 && C >= 64) {      // channel halves on a pair of blocks, 64-byte rows
+        // Measured on B200, fraction of the copy rate (bf16 C = 1024 at 32 / 64 sequences; fp32 C = 768 x 256 at 1024 sequences):
+        //   pair of blocks, 64-byte rows (8)              0.65 / 0.72, with add 0.60 / 0.64; fp32 0.53, with add 0.62
+        //   cluster of four, 128-byte rows (10)           0.64 / 0.70, with add 0.68 / 0.73; fp32 0.65, with add 0.72
+        //   cluster of four, 64-byte rows, two strips (9) 0.55 / 0.58, with add 0.53 / 0.54; fp32 0.63, with add 0.64
+        //   cluster of eight, 256-byte rows (11)          0.50 / 0.54, with add 0.59 / 0.62; fp32 0.67, with add 0.77
+        //   two-sweep kernel below (0)                    0.41 - 0.58
+        // The width of a row segment decides: the same kernel with more warps, fewer instructions, the next tile always in
+        // flight or the rows to add prefetched runs at the same speed, wider rows run faster until the cluster gets too
+        // large to place.  (Also tried and removed: a register-resident tile, 0.37-0.50; one block per strip with 32- or
+        // 64-byte rows, 0.37-0.53; a statistics kernel followed by an element-wise kernel, 0.42-0.57.)
+        const int knob_b = tuning("norm_bwd", (HAS_ADD || sizeof(T) == 4) ? 10 : 8);
+        if (knob_b == 11 && C >= 512 && (size_t)C * 66 <= 200 * 1024)           // channel eighths on a cluster of eight, 256-byte rows
+            return launch_rmsnorm_bwd_cluster<T, HAS_ADD, 16, 8, 1>(st, B, C, S, dx, dw, dy, x, w, add, eps, flags);
+        if ((knob_b == 9 || knob_b == 10) && C >= 256 && (size_t)C * 66 <= 200 * 1024) {
+            // channel quarters on a cluster of four: 64-byte rows with double-buffered strips (9), or 128-byte rows (10)
+            if (knob_b == 9) return launch_rmsnorm_bwd_cluster<T, HAS_ADD, 4, 4, 2>(st, B, C, S, dx, dw, dy, x, w, add, eps, flags);
+            return launch_rmsnorm_bwd_cluster<T, HAS_ADD, 8, 4, 1>(st, B, C, S, dx, dw, dy, x, w, add, eps, flags);
+        }
+        if ((knob_b >= 8) && (size_t)C * 66 <= 200 * 1024 && C >= 64) {      // channel halves on a pair of blocks, 64-byte rows
             constexpr int LGs = 4;
             const int tps_ = (S + LGs * VEC - 1) / (LGs * VEC);
             ntiles = B * tps_;

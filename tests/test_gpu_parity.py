@@ -136,6 +136,45 @@ def test_rmsnorm_bwd_fused_add_and_determinism(dev, oracle, dt):
     assert torch.equal(dx1, dx2) and torch.equal(dw1, dw2)              # bit-stable run to run
 
 
+RING_SHAPES = [(1, 768, 256), (2, 1024, 64), (1, 3000, 32), (1, 3200, 40), (3, 257, 72), (2, 1024, 2048 + 8), (40, 1024, 512)]
+
+
+@pytest.mark.parametrize("knob", [9, 10, 11])
+@pytest.mark.parametrize("with_add", [False, True])
+@pytest.mark.parametrize("exact", [False, True])
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("shape", RING_SHAPES)
+def test_rmsnorm_bwd_cluster_of_four_kernels(dev, oracle, shape, dt, exact, with_add, knob):
+    """The backward kernels on clusters of four blocks (tuning knob norm_bwd = 9: 64-byte rows, double-buffered
+    strips; 10: 128-byte rows): ragged channel quarters (C = 257, 3000), ragged token tiles, more tiles than
+    resident clusters (several rounds), and the same bits from two runs."""
+    torch = _torch()
+    from ane_b200 import lib
+    B, Cn, S = shape
+    x, w, dy = gi.cfg1(seed=15, B=B, dim=Cn, seq=S)
+    add = gi.normal(gi.rng(16), (B, Cn, S)) if with_add else None
+    xd, xr = up(x, dt)
+    dyd, dyr = up(dy, dt)
+    wd, _ = up(w)
+    ad, ar = up(add, dt) if with_add else (None, None)
+    dw0 = gi.normal(gi.rng(5), (Cn,), 0.1)
+    rdx, rdw = oracle.rmsnorm_bwd(dyr, xr, w, dw=dw0, eps=1e-5, exact=exact)
+    if with_add:
+        rdx = oracle.add(rdx, ar)
+    lib.set_tuning("norm_bwd", knob)
+    try:
+        outs = []
+        for _ in range(2):
+            dwd, _ = up(dw0)
+            dx = dev.rmsnorm_bwd(dyd, xd, wd, dwd, eps=1e-5, exact=exact, add=ad)
+            outs.append((dx, dwd))
+        assert close(down(outs[0][0]), rdx, dt)
+        assert rel_err(down(outs[0][1]), rdw) <= (TOL32 if dt == "f32" else 1e-4)
+        assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    finally:
+        lib.clear_tuning("norm_bwd")
+
+
 def test_rmsnorm_reference_fixtures_on_gpu(dev, golden):
     """The reference tests' own inputs (test_rmsnorm_bwd.m:26-33, test_classifier.m:25-27)
     against the committed outputs of the reference functions."""
@@ -712,7 +751,7 @@ def test_host_layer_chain_equals_device_chain(dev):
 # ane_cuda_set_tuning).  Each alternate path must give the same results within the same tolerances.
 ALT_KNOBS = [
     ("norm_fwd", 0), ("norm_fwd", 2), ("norm_fwd", 3), ("norm_fwd", 4), ("norm_fwd", 6),
-    ("norm_bwd", 0), ("norm_bwd", 8),
+    ("norm_bwd", 0), ("norm_bwd", 8), ("norm_bwd", 9), ("norm_bwd", 10),
     ("qk_fwd", 0), ("qk_fwd", 1), ("qk_fwd", 4), ("qk_bwd", 0), ("qk_bwd", 4),
     ("rope_lg", 8), ("embed_tiled", 0), ("embed_rows", 0), ("xent_cluster", 1), ("xent_lg", 4),
 ]
