@@ -31,20 +31,27 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 
-template <typename ID, int VEC, int LG>
+// CL > 1: the kernel is launched in clusters of CL blocks that share a stripe; block r of a cluster sweeps the
+// vocabulary rows [r * rows_per_block, (r + 1) * rows_per_block) and the CL (max, sum) pairs per token cross through
+// distributed shared memory once, between the sweeps.  It keeps every SM busy when there are few stripes.
+template <typename ID, int VEC, int LG, int CL>
 __global__ void __launch_bounds__(XE_THREADS)
 xent_kernel(float *dlogits, const float *logits, const void *__restrict__ targets, float *__restrict__ loss_tok,
-            int V, int S, int tiles_per_seq, float grad_scale, ane_cuda_status *status) {
+            int V, int S, int tiles_per_seq, int rows_per_block, float grad_scale, ane_cuda_status *status) {
     constexpr int R = XE_THREADS / LG;
     constexpr int TW = LG * VEC;
     __shared__ float red_m[R][TW];
     __shared__ float red_s[R][TW];
     __shared__ float tot_m[TW];
     __shared__ float tot_is[TW];
+    __shared__ float xpart[2][TW];       // CL > 1: this block's (max, sum) per token, read by the other blocks of the cluster
 
-    const int b = blockIdx.x / tiles_per_seq;
+    const int stripe = blockIdx.x / CL, crank = blockIdx.x % CL;      // clusters are consecutive blocks
+    const int v0 = CL > 1 ? crank * rows_per_block : 0;
+    const int v1 = CL > 1 ? (v0 + rows_per_block < V ? v0 + rows_per_block : V) : V;
+    const int b = stripe / tiles_per_seq;
     const int lg = threadIdx.x % LG, rg = threadIdx.x / LG;
-    const int t = (blockIdx.x % tiles_per_seq) * TW + lg * VEC;
+    const int t = (stripe % tiles_per_seq) * TW + lg * VEC;
     const bool active = t < S;
     const size_t base = (size_t)b * V * S + t;
 
@@ -52,13 +59,13 @@ xent_kernel(float *dlogits, const float *logits, const void *__restrict__ target
     float m[VEC], s[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; j++) { m[j] = -INFINITY; s[j] = 0.0f; }
-    for (int vb = 0; vb < V; vb += R * XE_U) {
+    for (int vb = v0; vb < v1; vb += R * XE_U) {
         Raw<float, VEC> r[XE_U];
         bool ok[XE_U];
 #pragma unroll
         for (int u = 0; u < XE_U; u++) {
             const int v = vb + u * R + rg;
-            ok[u] = active && v < V;
+            ok[u] = active && v < v1;
             if (ok[u]) r[u].load(logits + base + (size_t)v * S);
         }
         float l[XE_U][VEC];
@@ -96,8 +103,34 @@ xent_kernel(float *dlogits, const float *logits, const void *__restrict__ target
             const float mq = red_m[q][threadIdx.x];
             if (mq > -INFINITY) sum += red_s[q][threadIdx.x] * expf(mq - M);
         }
-        tot_m[threadIdx.x] = M;
-        tot_is[threadIdx.x] = 1.0f / sum;                    // inv_sum, stories_cpu_ops.h:91-92
+        if (CL == 1) {
+            tot_m[threadIdx.x] = M;
+            tot_is[threadIdx.x] = 1.0f / sum;                // inv_sum, stories_cpu_ops.h:91-92
+        } else {
+            xpart[0][threadIdx.x] = M;
+            xpart[1][threadIdx.x] = sum;
+        }
+    }
+    if constexpr (CL > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();                                      // every block's pair is published (also a block barrier)
+        if (threadIdx.x < TW) {                              // the same merge, in block order, in every block
+            float pm[CL], ps[CL];
+            float M = -INFINITY;
+#pragma unroll
+            for (int q = 0; q < CL; q++) {
+                const float *px = cluster.map_shared_rank(&xpart[0][0], (unsigned)q);
+                pm[q] = px[threadIdx.x];
+                ps[q] = px[TW + threadIdx.x];
+                M = fmaxf(M, pm[q]);
+            }
+            float sum = 0.0f;
+#pragma unroll
+            for (int q = 0; q < CL; q++)
+                if (pm[q] > -INFINITY) sum += ps[q] * expf(pm[q] - M);
+            tot_m[threadIdx.x] = M;
+            tot_is[threadIdx.x] = 1.0f / sum;
+        }
     }
     __syncthreads();
 
@@ -112,7 +145,7 @@ xent_kernel(float *dlogits, const float *logits, const void *__restrict__ target
         if (active) {
             const int id = (int)reinterpret_cast<const ID *>(targets)[(size_t)b * S + t + j];
             if (id >= 0 && id < V) tgt[j] = id;
-            else if (rg == 0) {                                // one thread per token reports it
+            else if (rg == 0 && crank == 0) {                  // one thread per token reports it
                 atomicAdd(&status->oor_ids, 1);
                 loss_tok[(size_t)b * S + t + j] = 0.0f;        // no loss term (stories_cpu_ops.h:98)
             }
@@ -124,13 +157,13 @@ xent_kernel(float *dlogits, const float *logits, const void *__restrict__ target
     }
 
     // sweep 2: p = exp(l - M) * inv_sum ; target row: loss and -1 ; then *1/S (and grad_scale)
-    for (int vb = 0; vb < V; vb += R * XE_U) {
+    for (int vb = v0; vb < v1; vb += R * XE_U) {
         Raw<float, VEC> r[XE_U];
         bool ok[XE_U];
 #pragma unroll
         for (int u = 0; u < XE_U; u++) {
             const int v = vb + u * R + rg;
-            ok[u] = active && v < V;
+            ok[u] = active && v < v1;
             if (ok[u]) r[u].load_stream(logits + base + (size_t)v * S);
         }
 #pragma unroll
@@ -159,6 +192,7 @@ xent_kernel(float *dlogits, const float *logits, const void *__restrict__ target
             }
         }
     }
+    if constexpr (CL > 1) cg::this_cluster().sync();         // a peer may still be reading xpart
 }
 
 // ------------------------------------------------------------------ cluster kernel
@@ -470,6 +504,45 @@ __global__ void __launch_bounds__(256) xent_loss_kernel(float *__restrict__ loss
 
 using namespace ane;
 
+// One block per stripe of LG * VEC tokens, or -- when that leaves SMs idle -- a cluster of CL blocks per stripe.
+template <typename ID, int VEC, int LG, int CL>
+static int launch_xent_cl(cudaStream_t st, unsigned nstripes, int V, int S, int tps, float *dlogits, const float *logits,
+                          const void *targets, float *loss_tok, float grad_scale, ane_cuda_status *status) {
+    const int rows_per_block = (V + CL - 1) / CL;
+    if (CL == 1) {
+        xent_kernel<ID, VEC, LG, CL><<<nstripes, XE_THREADS, 0, st>>>(dlogits, logits, targets, loss_tok, V, S, tps, rows_per_block, grad_scale, status);
+        return ANE_CUDA_OK;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(nstripes * CL, 1, 1);
+    cfg.blockDim = dim3(XE_THREADS, 1, 1);
+    cfg.stream = st;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = CL; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    ANE_CUDA_TRY(cudaLaunchKernelEx(&cfg, xent_kernel<ID, VEC, LG, CL>, dlogits, logits, targets, loss_tok, V, S, tps, rows_per_block, grad_scale, status));
+    return ANE_CUDA_OK;
+}
+
+template <int VEC, int LG>
+static int launch_xent_stripes(cudaStream_t st, ane_idtype idtype, int B, int V, int S, float *dlogits, const float *logits,
+                               const void *targets, float *loss_tok, float grad_scale, ane_cuda_status *status, int cl) {
+    const int tps = (S + LG * VEC - 1) / (LG * VEC);
+    const unsigned n = (unsigned)(B * tps);
+#define ANE_XENT_CL(CLV)                                                                                                              \
+    return idtype == ANE_ID_U16 ? launch_xent_cl<uint16_t, VEC, LG, CLV>(st, n, V, S, tps, dlogits, logits, targets, loss_tok, grad_scale, status) \
+                                : launch_xent_cl<int32_t, VEC, LG, CLV>(st, n, V, S, tps, dlogits, logits, targets, loss_tok, grad_scale, status)
+    if constexpr (VEC == 4) {
+        if (cl == 8) { ANE_XENT_CL(8); }
+        if (cl == 4) { ANE_XENT_CL(4); }
+        if (cl == 2) { ANE_XENT_CL(2); }
+    }
+    ANE_XENT_CL(1);
+#undef ANE_XENT_CL
+}
+
 extern "C" {
 
 int ane_cuda_cross_entropy_dev(void *stream, ane_idtype idtype, int B, int V, int S, float *dlogits, const float *logits,
@@ -520,27 +593,21 @@ int ane_cuda_cross_entropy_dev(void *stream, ane_idtype idtype, int B, int V, in
             return ANE_CUDA_OK;
         }
     }
-    // 32-token stripes (128-byte rows) unless that leaves fewer than four blocks per SM: then 16-token stripes
-    const int lg_auto = (long long)B * ((S + 31) / 32) < 4LL * ctx().sm_count ? 4 : 8;
-    if (vec && tuning("xent_lg", lg_auto) == 4) {
-        constexpr int LG = 4, VEC = 4;
-        const int tps = (S + LG * VEC - 1) / (LG * VEC);
-        const unsigned grid = (unsigned)(B * tps);
-        if (idtype == ANE_ID_U16) xent_kernel<uint16_t, VEC, LG><<<grid, XE_THREADS, 0, st>>>(dlogits, logits, targets, loss_tok, V, S, tps, grad_scale, status);
-        else xent_kernel<int32_t, VEC, LG><<<grid, XE_THREADS, 0, st>>>(dlogits, logits, targets, loss_tok, V, S, tps, grad_scale, status);
-    } else if (vec) {
-        constexpr int LG = 8, VEC = 4;
-        const int tps = (S + LG * VEC - 1) / (LG * VEC);
-        const unsigned grid = (unsigned)(B * tps);
-        if (idtype == ANE_ID_U16) xent_kernel<uint16_t, VEC, LG><<<grid, XE_THREADS, 0, st>>>(dlogits, logits, targets, loss_tok, V, S, tps, grad_scale, status);
-        else xent_kernel<int32_t, VEC, LG><<<grid, XE_THREADS, 0, st>>>(dlogits, logits, targets, loss_tok, V, S, tps, grad_scale, status);
-    } else {
-        constexpr int LG = 32, VEC = 1;
-        const int tps = (S + LG - 1) / LG;
-        const unsigned grid = (unsigned)(B * tps);
-        if (idtype == ANE_ID_U16) xent_kernel<uint16_t, VEC, LG><<<grid, XE_THREADS, 0, st>>>(dlogits, logits, targets, loss_tok, V, S, tps, grad_scale, status);
-        else xent_kernel<int32_t, VEC, LG><<<grid, XE_THREADS, 0, st>>>(dlogits, logits, targets, loss_tok, V, S, tps, grad_scale, status);
-    }
+    // Stripes of 64 tokens (256-byte rows: measured 0.64 of the copy rate against 0.57 with 128-byte rows and 0.53 with
+    // 64-byte rows); when that gives fewer than four blocks per SM, clusters of 2, 4 or 8 blocks share a stripe's vocabulary.
+    const int lg_knob = tuning("xent_lg", S >= 64 ? 16 : 8);
+    const int lg_eff = !vec ? 32 : (lg_knob == 4 || lg_knob == 16 || lg_knob == 32) ? lg_knob : 8;
+    const long long nstripes_ = (long long)B * ((S + lg_eff * (vec ? 4 : 1) - 1) / (lg_eff * (vec ? 4 : 1)));
+    int cl_auto = 1;
+    while (cl_auto < 8 && nstripes_ * cl_auto < 4LL * ctx().sm_count && V / (2 * cl_auto) >= 2048) cl_auto *= 2;
+    const int cl = vec ? tuning("xent_split", cl_auto) : 1;
+    int rc;
+    if (!vec) rc = launch_xent_stripes<1, 32>(st, idtype, B, V, S, dlogits, logits, targets, loss_tok, grad_scale, status, 1);
+    else if (lg_eff == 4) rc = launch_xent_stripes<4, 4>(st, idtype, B, V, S, dlogits, logits, targets, loss_tok, grad_scale, status, cl);
+    else if (lg_eff == 16) rc = launch_xent_stripes<4, 16>(st, idtype, B, V, S, dlogits, logits, targets, loss_tok, grad_scale, status, cl);
+    else if (lg_eff == 32) rc = launch_xent_stripes<4, 32>(st, idtype, B, V, S, dlogits, logits, targets, loss_tok, grad_scale, status, cl);
+    else rc = launch_xent_stripes<4, 8>(st, idtype, B, V, S, dlogits, logits, targets, loss_tok, grad_scale, status, cl);
+    if (rc != ANE_CUDA_OK) return rc;
     xent_loss_kernel<<<B, 256, 0, st>>>(loss_seq, loss_tok, S);
     ANE_LAUNCH_OK(2);
     return ANE_CUDA_OK;
