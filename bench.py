@@ -55,6 +55,7 @@ def parse_args():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     ap.add_argument("--no-p2p", action="store_true", help="N > 1: use NCCL reduce-scatter / all-gather instead of the peer-memory optimizer kernels")
+    ap.add_argument("--early-reduce", action="store_true", help="N > 1, peer memory: reduce the matmul gradients on a side stream beside the chain instead of at the end of the step (measured slower: the chain is HBM-bound)")
     ap.add_argument("--no-boundary-fusion", action="store_true", help="run the closing residual and the next norm as two operators")
     ap.add_argument("--cpu-seqs", type=int, default=2, help="sequences in the CPU sample")
     ap.add_argument("--e2e-seqs", type=int, default=8, help="sequences per rank and step of the host-buffer (e2e) measurement")
@@ -423,7 +424,7 @@ def run_ours(args):
     params.init_random()
     chain = LayerChain(cfg, M, params, device)
     opt = ShardedAdam(params.w, params.g, params.m, params.v, params.n_decay, params.n, world, rank,
-                      lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0, peer_ptrs=peer_ptrs, n_early=params.n_matrix)
+                      lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0, peer_ptrs=peer_ptrs, n_early=params.n_matrix if args.early_reduce else 0)
     gscale = 1.0 / (10 * 256.0)       # 1/(accum_steps*loss_scale), train.m:750
     tstep = [0]
     use_graph = not args.no_graph
@@ -434,7 +435,7 @@ def run_ours(args):
 
     def step():
         params.zero_produced_grads()
-        opt.begin_step(gscale)       # the matmul gradients are complete: their share of the exchange overlaps the chain
+        opt.begin_step(gscale)       # --early-reduce: the matmul gradients are complete, their share of the exchange overlaps the chain
         for mb in range(n_micro):
             if use_graph and not (mb == 0 and chain.timed_op is not None):
                 chain.replay()
