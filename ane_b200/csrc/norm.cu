@@ -334,13 +334,15 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
         //   pair of blocks, 64-byte rows (8)              0.65 / 0.72, with add 0.60 / 0.64; fp32 0.53, with add 0.62
         //   cluster of four, 128-byte rows (10)           0.64 / 0.70, with add 0.68 / 0.73; fp32 0.65, with add 0.72
         //   cluster of four, 64-byte rows, two strips (9) 0.55 / 0.58, with add 0.53 / 0.54; fp32 0.63, with add 0.64
-        //   cluster of eight, 256-byte rows (11)          0.50 / 0.54, with add 0.59 / 0.62; fp32 0.67, with add 0.77
+        //   cluster of eight, 256-byte rows (11)          0.50 / 0.54, with add 0.59 / 0.62; fp32 0.68, with add 0.77
         //   two-sweep kernel below (0)                    0.41 - 0.58
         // The width of a row segment decides: the same kernel with more warps, fewer instructions, the next tile always in
         // flight or the rows to add prefetched runs at the same speed, wider rows run faster until the cluster gets too
         // large to place.  (Also tried and removed: a register-resident tile, 0.37-0.50; one block per strip with 32- or
         // 64-byte rows, 0.37-0.53; a statistics kernel followed by an element-wise kernel, 0.42-0.57.)
-        const int knob_b = tuning("norm_bwd", (HAS_ADD || sizeof(T) == 4) ? 10 : 8);
+        // fp32 over many tiles gains another 3-6 % from 256-byte rows (C = 768 and 1024, 256 sequences and more)
+        const bool wide_f32 = sizeof(T) == 4 && C >= 512 && (long long)B * ((S + 63) / 64) >= 256;
+        const int knob_b = tuning("norm_bwd", wide_f32 ? 11 : (HAS_ADD || sizeof(T) == 4) ? 10 : 8);
         if (knob_b == 11 && C >= 512 && (size_t)C * 66 <= 200 * 1024)           // channel eighths on a cluster of eight, 256-byte rows
             return launch_rmsnorm_bwd_cluster<T, HAS_ADD, 16, 8, 1>(st, B, C, S, dx, dw, dy, x, w, add, eps, flags);
         if ((knob_b == 9 || knob_b == 10) && C >= 256 && (size_t)C * 66 <= 200 * 1024) {
