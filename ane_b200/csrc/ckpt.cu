@@ -12,6 +12,17 @@
 // Device layout ("weight order"): the weights in file order with the moments taken out --
 //   [layer 0: Wq Wk Wv Wo W1 W2 W3 rms_att rms_ffn] ... [layer L-1: ...] rms_final embed
 // -- in three parallel buffers w, m, v of ane_cuda_ckpt_param_count() floats each.
+//
+// Device layout ("optimizer order", the *_flat entry points): what a flat optimizer wants -- everything that takes
+// weight decay first, the norm weights (no decay, train.m:837-869) after it:
+//   [layer 0: Wq Wk Wv Wo W1 W2 W3] ... [layer L-1: ...] embed | rms_att[0..L-1] rms_ffn[0..L-1] rms_final | (caller's extras)
+// The first ane_cuda_ckpt_flat_decay_count() floats are the decayed range; floats beyond param_count (for example
+// per-head QK-norm weights, which the reference's files do not store) are left untouched by a load and are not
+// written by a save.
+//
+// llama2.c weight files (train_large.m:13-56): a 7-int header, then embed, rms_att[all layers], wq[all], wk[all],
+// wv[all], wo[all], rms_ffn[all], w1[all], w2[all], w3[all], rms_final (then RoPE tables and, when vocab_size < 0, a
+// separate classifier, neither of which the reference reads).
 #include "common.cuh"
 
 #include <stdio.h>
@@ -57,32 +68,46 @@ static int read_header(FILE *f, ane_ckpt_header *h) {
     return ANE_CUDA_OK;
 }
 
+enum Layout { WEIGHT_ORDER = 0, OPTIMIZER_ORDER = 1 };
+enum Tensor { T_WQ = 0, T_WK, T_WV, T_WO, T_W1, T_W2, T_W3, T_RMS_ATT, T_RMS_FFN, T_RMS_FINAL, T_EMBED };
+
+// Offset (in floats) of tensor `t` of layer `L` in a device buffer of the given layout.
+static size_t tensor_offset(const ane_ckpt_header &h, Layout layout, int t, int L) {
+    size_t sz[9];
+    layer_extents(h, sz);
+    size_t per_layer = 0, matrices = 0;
+    for (int i = 0; i < 9; i++) { per_layer += sz[i]; if (i < 7) matrices += sz[i]; }
+    const size_t nl = (size_t)h.n_layers, d = (size_t)h.dim, e = (size_t)h.vocab_size * h.dim;
+    size_t within = 0;
+    if (t < 9) for (int i = 0; i < t; i++) within += sz[i];
+    if (layout == WEIGHT_ORDER) {
+        if (t < 9) return (size_t)L * per_layer + within;
+        return nl * per_layer + (t == T_EMBED ? d : 0);
+    }
+    if (t < 7) return (size_t)L * matrices + within;
+    if (t == T_EMBED) return nl * matrices;
+    const size_t norms = nl * matrices + e;
+    if (t == T_RMS_ATT) return norms + (size_t)L * d;
+    if (t == T_RMS_FFN) return norms + nl * d + (size_t)L * d;
+    return norms + 2 * nl * d;                                                           // rms_final
+}
+
 // One pass over the file's tensors in file order.  io(dev_buffer_index 0/1/2 = w/m/v, offset in floats, count) moves
 // `count` floats between the file position and the device range.
 template <class IO>
-static int walk(const ane_ckpt_header &h, IO io) {
+static int walk(const ane_ckpt_header &h, Layout layout, IO io) {
     size_t sz[9];
     layer_extents(h, sz);
-    size_t off = 0;
     for (int L = 0; L < h.n_layers; L++) {
-        size_t o = off;
-        for (int i = 0; i < 9; i++) { if (int rc = io(0, o, sz[i])) return rc; o += sz[i]; }
-        o = off;
+        for (int i = 0; i < 9; i++) if (int rc = io(0, tensor_offset(h, layout, i, L), sz[i])) return rc;
         for (int i = 0; i < 9; i++) {
-            if (int rc = io(1, o, sz[i])) return rc;
-            if (int rc = io(2, o, sz[i])) return rc;
-            o += sz[i];
+            if (int rc = io(1, tensor_offset(h, layout, i, L), sz[i])) return rc;
+            if (int rc = io(2, tensor_offset(h, layout, i, L), sz[i])) return rc;
         }
-        off = o;
     }
     const size_t d = (size_t)h.dim, e = (size_t)h.vocab_size * h.dim;
-    if (int rc = io(0, off, d)) return rc;
-    if (int rc = io(1, off, d)) return rc;
-    if (int rc = io(2, off, d)) return rc;
-    off += d;
-    if (int rc = io(0, off, e)) return rc;
-    if (int rc = io(1, off, e)) return rc;
-    if (int rc = io(2, off, e)) return rc;
+    for (int which = 0; which < 3; which++) if (int rc = io(which, tensor_offset(h, layout, T_RMS_FINAL, 0), d)) return rc;
+    for (int which = 0; which < 3; which++) if (int rc = io(which, tensor_offset(h, layout, T_EMBED, 0), e)) return rc;
     return ANE_CUDA_OK;
 }
 
@@ -105,19 +130,20 @@ int ane_cuda_ckpt_read_header(const char *path, ane_ckpt_header *hdr) {
 
 size_t ane_cuda_ckpt_param_count(const ane_ckpt_header *hdr) { return hdr ? param_count(*hdr) : 0; }
 
-int ane_cuda_ckpt_load(const char *path, ane_ckpt_header *hdr, float *w_dev, float *m_dev, float *v_dev, size_t n_floats) {
+static int ckpt_load(Layout layout, const char *path, ane_ckpt_header *hdr, float *w_dev, float *m_dev, float *v_dev,
+                     size_t n_floats) {
     ANE_REQUIRE_INIT();
     ANE_REQUIRE(path && hdr && w_dev, "%s: null pointer", __func__);
     ANE_REQUIRE((m_dev == nullptr) == (v_dev == nullptr), "%s: give both moment buffers or neither", __func__);
     FILE *f = fopen(path, "rb");
     if (!f) return fail(ANE_CUDA_ERR_INVALID, "%s: cannot open %s", __func__, path);
     int rc = read_header(f, hdr);
-    if (rc == ANE_CUDA_OK && param_count(*hdr) != n_floats)
+    if (rc == ANE_CUDA_OK && (layout == WEIGHT_ORDER ? param_count(*hdr) != n_floats : param_count(*hdr) > n_floats))
         rc = fail(ANE_CUDA_ERR_INVALID, "%s: the file holds %zu parameters, the buffers %zu", __func__, param_count(*hdr), n_floats);
     if (rc != ANE_CUDA_OK) { fclose(f); return rc; }
     std::vector<float> stage(CKPT_CHUNK);
     float *dst[3] = {w_dev, m_dev, v_dev};
-    rc = walk(*hdr, [&](int which, size_t off, size_t count) -> int {
+    rc = walk(*hdr, layout, [&](int which, size_t off, size_t count) -> int {
         if (!dst[which]) return fseek(f, (long)(count * sizeof(float)), SEEK_CUR) == 0 ? ANE_CUDA_OK
                                                                                         : fail(ANE_CUDA_ERR_INVALID, "%s: seek failed", __func__);
         for (size_t done = 0; done < count; done += CKPT_CHUNK) {
@@ -131,20 +157,20 @@ int ane_cuda_ckpt_load(const char *path, ane_ckpt_header *hdr, float *w_dev, flo
     return rc;
 }
 
-int ane_cuda_ckpt_save(const char *path, const ane_ckpt_header *hdr, const float *w_dev, const float *m_dev, const float *v_dev,
-                       size_t n_floats) {
+static int ckpt_save(Layout layout, const char *path, const ane_ckpt_header *hdr, const float *w_dev, const float *m_dev,
+                     const float *v_dev, size_t n_floats) {
     ANE_REQUIRE_INIT();
     ANE_REQUIRE(path && hdr && w_dev && m_dev && v_dev, "%s: null pointer", __func__);
     ANE_REQUIRE(hdr->magic == CKPT_MAGIC && (hdr->version == 2 || hdr->version == 4), "%s: bad header", __func__);
-    ANE_REQUIRE(param_count(*hdr) == n_floats && n_floats > 0, "%s: the header describes %zu parameters, the buffers %zu", __func__,
-                param_count(*hdr), n_floats);
+    ANE_REQUIRE(param_count(*hdr) > 0 && (layout == WEIGHT_ORDER ? param_count(*hdr) == n_floats : param_count(*hdr) <= n_floats),
+                "%s: the header describes %zu parameters, the buffers %zu", __func__, param_count(*hdr), n_floats);
     FILE *f = fopen(path, "wb");
     if (!f) return fail(ANE_CUDA_ERR_INVALID, "%s: cannot create %s", __func__, path);
     int rc = fwrite(hdr, sizeof(*hdr), 1, f) == 1 ? ANE_CUDA_OK : fail(ANE_CUDA_ERR_INVALID, "%s: write failed", __func__);
     std::vector<float> stage(CKPT_CHUNK);
     const float *src[3] = {w_dev, m_dev, v_dev};
     if (rc == ANE_CUDA_OK)
-        rc = walk(*hdr, [&](int which, size_t off, size_t count) -> int {
+        rc = walk(*hdr, layout, [&](int which, size_t off, size_t count) -> int {
             for (size_t done = 0; done < count; done += CKPT_CHUNK) {
                 const size_t n = count - done < CKPT_CHUNK ? count - done : CKPT_CHUNK;
                 ANE_CUDA_TRY(cudaMemcpy(stage.data(), src[which] + off + done, n * sizeof(float), cudaMemcpyDeviceToHost));
@@ -153,6 +179,107 @@ int ane_cuda_ckpt_save(const char *path, const ane_ckpt_header *hdr, const float
             return ANE_CUDA_OK;
         });
     if (fclose(f) != 0 && rc == ANE_CUDA_OK) rc = fail(ANE_CUDA_ERR_INVALID, "%s: close failed", __func__);
+    return rc;
+}
+
+int ane_cuda_ckpt_load(const char *path, ane_ckpt_header *hdr, float *w_dev, float *m_dev, float *v_dev, size_t n_floats) {
+    return ckpt_load(WEIGHT_ORDER, path, hdr, w_dev, m_dev, v_dev, n_floats);
+}
+int ane_cuda_ckpt_save(const char *path, const ane_ckpt_header *hdr, const float *w_dev, const float *m_dev, const float *v_dev,
+                       size_t n_floats) {
+    return ckpt_save(WEIGHT_ORDER, path, hdr, w_dev, m_dev, v_dev, n_floats);
+}
+int ane_cuda_ckpt_load_flat(const char *path, ane_ckpt_header *hdr, float *w_dev, float *m_dev, float *v_dev, size_t n_floats) {
+    return ckpt_load(OPTIMIZER_ORDER, path, hdr, w_dev, m_dev, v_dev, n_floats);
+}
+int ane_cuda_ckpt_save_flat(const char *path, const ane_ckpt_header *hdr, const float *w_dev, const float *m_dev, const float *v_dev,
+                            size_t n_floats) {
+    return ckpt_save(OPTIMIZER_ORDER, path, hdr, w_dev, m_dev, v_dev, n_floats);
+}
+
+size_t ane_cuda_ckpt_flat_decay_count(const ane_ckpt_header *hdr) {
+    if (!hdr || param_count(*hdr) == 0) return 0;
+    return tensor_offset(*hdr, OPTIMIZER_ORDER, T_RMS_ATT, 0);
+}
+
+int ane_cuda_ckpt_tensor_offset(const ane_ckpt_header *hdr, int flat, int tensor, int layer, size_t *offset, size_t *count) {
+    ANE_REQUIRE(hdr && offset && count, "%s: null pointer", __func__);
+    ANE_REQUIRE(param_count(*hdr) > 0, "%s: bad header", __func__);
+    ANE_REQUIRE(tensor >= 0 && tensor <= T_EMBED && layer >= 0 && layer < hdr->n_layers, "%s: no tensor %d in layer %d", __func__, tensor, layer);
+    size_t sz[9];
+    layer_extents(*hdr, sz);
+    *offset = tensor_offset(*hdr, flat ? OPTIMIZER_ORDER : WEIGHT_ORDER, tensor, tensor < 9 ? layer : 0);
+    *count = tensor < 9 ? sz[tensor] : tensor == T_RMS_FINAL ? (size_t)hdr->dim : (size_t)hdr->vocab_size * hdr->dim;
+    return ANE_CUDA_OK;
+}
+
+// ------------------------------------------------------------------ llama2.c weight files (train_large.m:13-56)
+int ane_cuda_llama2c_read_config(const char *path, ane_llama2c_config *cfg) {
+    ANE_REQUIRE(path && cfg, "%s: null pointer", __func__);
+    FILE *f = fopen(path, "rb");
+    if (!f) return fail(ANE_CUDA_ERR_INVALID, "%s: cannot open %s", __func__, path);
+    const size_t got = fread(cfg, sizeof(*cfg), 1, f);
+    fclose(f);
+    if (got != 1) return fail(ANE_CUDA_ERR_INVALID, "%s: %s is shorter than its 28-byte header", __func__, path);
+    if (cfg->dim < 1 || cfg->hidden_dim < 1 || cfg->n_layers < 1 || cfg->n_heads < 1 || cfg->n_kv_heads < 1 || cfg->vocab_size == 0 ||
+        cfg->dim % cfg->n_heads != 0 || cfg->n_heads % cfg->n_kv_heads != 0)
+        return fail(ANE_CUDA_ERR_INVALID, "%s: inconsistent dimensions in the header of %s", __func__, path);
+    return ANE_CUDA_OK;
+}
+
+int ane_cuda_llama2c_to_header(const ane_llama2c_config *cfg, ane_ckpt_header *hdr) {
+    ANE_REQUIRE(cfg && hdr, "%s: null pointer", __func__);
+    memset(hdr, 0, sizeof(*hdr));
+    const bool gqa = cfg->n_kv_heads != cfg->n_heads;
+    hdr->magic = CKPT_MAGIC;
+    hdr->version = gqa ? 4 : 2;       // the square-attention files of train_large.m are version 2, grouped-query ones version 4
+    hdr->n_layers = cfg->n_layers;
+    hdr->vocab_size = cfg->vocab_size < 0 ? -cfg->vocab_size : cfg->vocab_size;      // sign = shared classifier (train_large.m:25-26)
+    hdr->dim = cfg->dim;
+    hdr->hidden_dim = cfg->hidden_dim;
+    hdr->n_heads = cfg->n_heads;
+    hdr->seq_len = cfg->seq_len;
+    if (gqa) {
+        hdr->head_dim = cfg->dim / cfg->n_heads;
+        hdr->kv_heads = cfg->n_kv_heads;
+        hdr->q_dim = cfg->dim;
+    }
+    return param_count(*hdr) ? ANE_CUDA_OK : fail(ANE_CUDA_ERR_INVALID, "%s: inconsistent dimensions", __func__);
+}
+
+int ane_cuda_llama2c_load(const char *path, const ane_llama2c_config *expect, ane_ckpt_header *hdr, float *w_dev, size_t n_floats, int flat) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(path && hdr && w_dev, "%s: null pointer", __func__);
+    ane_llama2c_config cfg;
+    if (int rc = ane_cuda_llama2c_read_config(path, &cfg)) return rc;
+    if (expect && (cfg.dim != expect->dim || cfg.hidden_dim != expect->hidden_dim || cfg.n_layers != expect->n_layers))
+        return fail(ANE_CUDA_ERR_INVALID, "%s: config mismatch: the file has dim=%d hidden=%d layers=%d, expected dim=%d hidden=%d layers=%d",
+                    __func__, cfg.dim, cfg.hidden_dim, cfg.n_layers, expect->dim, expect->hidden_dim, expect->n_layers);
+    if (int rc = ane_cuda_llama2c_to_header(&cfg, hdr)) return rc;
+    const Layout layout = flat ? OPTIMIZER_ORDER : WEIGHT_ORDER;
+    if (flat ? param_count(*hdr) > n_floats : param_count(*hdr) != n_floats)
+        return fail(ANE_CUDA_ERR_INVALID, "%s: the file holds %zu parameters, the buffer %zu", __func__, param_count(*hdr), n_floats);
+    FILE *f = fopen(path, "rb");
+    if (!f) return fail(ANE_CUDA_ERR_INVALID, "%s: cannot open %s", __func__, path);
+    if (fseek(f, (long)sizeof(cfg), SEEK_SET) != 0) { fclose(f); return fail(ANE_CUDA_ERR_INVALID, "%s: seek failed", __func__); }
+    size_t sz[9];
+    layer_extents(*hdr, sz);
+    std::vector<float> stage(CKPT_CHUNK);
+    auto read_to = [&](size_t off, size_t count) -> int {
+        for (size_t done = 0; done < count; done += CKPT_CHUNK) {
+            const size_t n = count - done < CKPT_CHUNK ? count - done : CKPT_CHUNK;
+            if (fread(stage.data(), sizeof(float), n, f) != n) return fail(ANE_CUDA_ERR_INVALID, "%s: %s is truncated", __func__, path);
+            ANE_CUDA_TRY(cudaMemcpy(w_dev + off + done, stage.data(), n * sizeof(float), cudaMemcpyHostToDevice));
+        }
+        return ANE_CUDA_OK;
+    };
+    // file order: embed, then each kind of tensor for all layers
+    static const int order[9] = {T_RMS_ATT, T_WQ, T_WK, T_WV, T_WO, T_RMS_FFN, T_W1, T_W2, T_W3};
+    int rc = read_to(tensor_offset(*hdr, layout, T_EMBED, 0), (size_t)hdr->vocab_size * hdr->dim);
+    for (int k = 0; k < 9 && rc == ANE_CUDA_OK; k++)
+        for (int L = 0; L < hdr->n_layers && rc == ANE_CUDA_OK; L++) rc = read_to(tensor_offset(*hdr, layout, order[k], L), sz[order[k]]);
+    if (rc == ANE_CUDA_OK) rc = read_to(tensor_offset(*hdr, layout, T_RMS_FINAL, 0), (size_t)hdr->dim);
+    fclose(f);
     return rc;
 }
 

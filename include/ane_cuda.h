@@ -186,7 +186,10 @@ int ane_cuda_rmsnorm_bwd_dev(void *stream, ane_dtype dtype, int B, int C, int S,
  *   - it does not need ane_cuda_init(), and calls no cudaMalloc / cudaFree or any allocating
  *     library routine; the caller passes inputs and outputs on the CURRENT device;
  *   - the first call on each device looks up the array's device address
- *     (cudaGetSymbolAddress) -- make that first call before any stream capture;
+ *     (cudaGetSymbolAddress) -- make that first call before any stream capture, and make it at
+ *     start-up, BEFORE a framework takes the rest of the device for its pool: with CUDA's lazy
+ *     module loading the library image that contains the array is placed in device memory when
+ *     one of its kernels is first used, so that first call may itself need 2.3 MiB of free memory;
  *   - all calls share the one array: calls that may overlap on the GPU (different streams,
  *     or other threads) race on it.  Keep them on one stream, or order them with events.
  * Results: the same operator as ane_cuda_rmsnorm_bwd_dev within fp32 rounding -- the two entry points

@@ -312,6 +312,77 @@ def reference_available() -> bool:
     return all(os.path.exists(os.path.join(HERE, "_ref", n)) for n in ("libref_stories.so", "libref_dynamic.so"))
 
 
+def reference_inline_available() -> bool:
+    return os.path.exists(os.path.join(HERE, "_ref", "libref_inline.so"))
+
+
+class LayerGradPtrs(C.Structure):
+    """Field order of the LayerGrads stand-in in ref_inline_exports.c.in."""
+    _fields_ = [(n, _f32p) for n in ("Wq", "Wk", "Wv", "Wo", "W1", "W2", "W3", "rms_att", "rms_ffn")]
+
+
+class ReferenceInline:
+    """The reference's INLINE operator blocks (statements of training_dynamic/train.m's main()) and the plain-C
+    helpers of training/forward.h, compiled by line range into oracle/_ref/libref_inline.so."""
+
+    def __init__(self):
+        if not reference_inline_available():
+            raise FileNotFoundError("oracle/_ref/libref_inline.so is not built (run oracle/build_oracle.py where the reference is)")
+        L = self.lib = C.CDLL(os.path.join(HERE, "_ref", "libref_inline.so"))
+        L.ref_inline_residual.argtypes = [_f32p, _f32p, _f32p, C.c_float, C.c_int, C.c_int]
+        L.ref_inline_swiglu_bwd.argtypes = [_f32p] * 7 + [C.c_int, C.c_int]
+        L.ref_inline_grad_scale_norm_clip.argtypes = [C.POINTER(LayerGradPtrs), C.c_int, _f32p, _f32p] + [C.c_size_t] * 7 + \
+            [C.c_int, C.c_int, C.c_float, C.c_float, _f32p]
+        L.ref_inline_grad_scale_norm_clip.restype = C.c_float
+        L.ref_inline_cpu_rope.argtypes = [_f32p, _f32p, C.c_int, C.c_int, C.c_int]
+        L.ref_inline_silu.argtypes = [C.c_float]
+        L.ref_inline_silu.restype = C.c_float
+        L.ref_inline_swiglu.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int]
+
+    def residual(self, x, f, alpha):
+        """train.m:460 on one [DIM, SEQ] pair (flat: the statement treats both as SEQ*DIM elements)."""
+        out = np.empty_like(x)
+        self.lib.ref_inline_residual(_fp(out), _fp(x), _fp(f), alpha, x.shape[-1], x.size // x.shape[-1])
+        return out
+
+    def swiglu_bwd(self, h1, h3, dsilu):
+        """train.m:538-554 on [HIDDEN, SEQ] arrays -> (dh1, dh3)."""
+        dh1, dh3, t1, t2 = (np.empty_like(h1) for _ in range(4))
+        self.lib.ref_inline_swiglu_bwd(_fp(dh1), _fp(dh3), _fp(h1), _fp(h3), _fp(dsilu), _fp(t1), _fp(t2), h1.shape[0], h1.shape[1])
+        return dh1, dh3
+
+    def swiglu(self, h1, h3):
+        """forward.h:149-151 (element-wise, so the row-major statement applies to any layout)."""
+        out = np.empty_like(h1)
+        self.lib.ref_inline_swiglu(_fp(out), _fp(h1), _fp(h3), 1, h1.size)
+        return out
+
+    def rope_channel_first(self, x, hd):
+        """forward.h:55-70 (row-major [S][heads*hd], base 10000) applied to a channel-first [C, S] array."""
+        Cn, S = x.shape
+        q = np.ascontiguousarray(x.T).copy()
+        k = q.copy()
+        self.lib.ref_inline_cpu_rope(_fp(q), _fp(k), S, Cn // hd, hd)
+        assert np.array_equal(q, k)
+        return np.ascontiguousarray(q.T)
+
+    def grad_scale_norm_clip(self, layers, grms_final, gembed, gsc, grad_clip):
+        """train.m:754-767,770-788,809-825.  layers: list of dicts with the nine LayerGrads fields (Wq..W3 flat fp32 of
+        equal per-field sizes across layers, rms_att / rms_ffn of DIM elements); every array is scaled / clipped in
+        place.  Returns (grad_norm, grad_norm_sq)."""
+        n = len(layers)
+        arr = (LayerGradPtrs * n)()
+        for i, lay in enumerate(layers):
+            for name, _ in LayerGradPtrs._fields_:
+                setattr(arr[i], name, _fp(lay[name]))
+        sizes = [layers[0][k].size for k in ("Wq", "Wk", "Wv", "Wo", "W1", "W2", "W3")]
+        dim = grms_final.size
+        nsq = np.zeros(1, np.float32)
+        norm = self.lib.ref_inline_grad_scale_norm_clip(arr, n, _fp(grms_final), _fp(gembed), *sizes, dim, gembed.size // dim,
+                                                        gsc, grad_clip, _fp(nsq))
+        return float(norm), float(nsq[0])
+
+
 class Reference:
     """The reference's own functions (single sequence, uint16 ids, reference signatures)."""
 

@@ -156,6 +156,26 @@ def adam_inputs(seed: int = 1234, n: int = 1 << 16):
 
 
 # ---------------------------------------------------------------- bf16 helpers (numpy has no bf16)
+GRAD_POST_GSC = float(np.float32(1.0) / np.float32(10 * 256.0))      # 1/(accum_steps*loss_scale), train.m:750
+GRAD_POST_FIELDS = ("Wq", "Wk", "Wv", "Wo", "W1", "W2", "W3", "rms_att", "rms_ffn")
+
+
+def grad_post_inputs(seed: int = 1234, n_layers: int = 3, dim: int = 48, q_dim: int = 64, kv_dim: int = 32, hidden: int = 80,
+                     vocab: int = 96):
+    """Unscaled gradients of a small model in the reference's per-tensor arrangement (LayerGrads of
+    training_dynamic/config.h, grms_final, gembed): large enough that the clip at 1.0 triggers after the scale."""
+    r = rng(seed + 5)
+    sizes = {"Wq": q_dim * dim, "Wk": kv_dim * dim, "Wv": kv_dim * dim, "Wo": dim * q_dim, "W1": hidden * dim,
+             "W2": dim * hidden, "W3": hidden * dim, "rms_att": dim, "rms_ffn": dim}
+    layers = [{k: normal(r, (sizes[k],), 60.0) for k in GRAD_POST_FIELDS} for _ in range(n_layers)]
+    return layers, normal(r, (dim,), 60.0), normal(r, (vocab * dim,), 60.0)
+
+
+def grad_post_flat(layers, grms_final, gembed) -> np.ndarray:
+    """All tensors of grad_post_inputs as one flat array, in the order the reference's norm loop visits them."""
+    return np.concatenate([lay[k] for lay in layers for k in GRAD_POST_FIELDS] + [grms_final, gembed]).astype(np.float32)
+
+
 def to_bf16_bits(a: np.ndarray) -> np.ndarray:
     """fp32 -> bf16 bit pattern (uint16), round-to-nearest-even; NaN stays NaN."""
     u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)

@@ -24,7 +24,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 
 from oracle import build_oracle  # noqa: E402
-from oracle.oracle import Reference  # noqa: E402
+from oracle.oracle import Reference, ReferenceInline  # noqa: E402
 from tests.golden import gen_inputs as gi  # noqa: E402
 
 OUT = os.path.join(HERE, "golden.npz")
@@ -116,6 +116,24 @@ def main() -> int:
     g["vocab_cv"] = np.int64(cv)
     g["vocab_c2f_head"] = c2f[:64].copy()
     g["vocab_f2c_sum"] = np.int64(f2c.astype(np.int64).sum())
+
+    # 9. the inline operator blocks of training_dynamic/train.m and the helpers of training/forward.h
+    rin = ReferenceInline()
+    h1, h3, d, x, f = (a[0] for a in gi.cfg2())
+    dh1, dh3 = rin.swiglu_bwd(h1, h3, d)                                   # train.m:538-554
+    sample(g, "inline_swiglu_bwd_dh1", dh1, 53)
+    sample(g, "inline_swiglu_bwd_dh3", dh3, 53)
+    sample(g, "inline_swiglu", rin.swiglu(h1, h3), 53)                    # forward.h:101,149-151
+    for name, alpha in (("a25", np.float32(24.0 ** -0.25)), ("a50", np.float32(1.0) / np.sqrt(np.float32(24.0)))):
+        sample(g, f"inline_residual_{name}", rin.residual(x, f, alpha), 53)  # train.m:460 (alpha of train.m:188 is a50)
+    q = gi.cfg3()[0][0]
+    sample(g, "inline_rope_hd128", rin.rope_channel_first(q, 128), 53)    # forward.h:55-70
+    sample(g, "inline_rope_hd64", rin.rope_channel_first(np.ascontiguousarray(q[:768]), 64), 53)
+    layers, fin, emb = gi.grad_post_inputs()
+    norm, nsq = rin.grad_scale_norm_clip(layers, fin, emb, gi.GRAD_POST_GSC, 1.0)   # train.m:754-767,770-788,809-825
+    g["inline_grad_norm"] = np.float32(norm)
+    g["inline_grad_norm_sq"] = np.float32(nsq)
+    sample(g, "inline_grad_flat", gi.grad_post_flat(layers, fin, emb), 7)
 
     np.savez_compressed(OUT, **g)
     print(f"wrote {OUT}: {os.path.getsize(OUT)/1024:.1f} KiB, {len(g)} arrays")

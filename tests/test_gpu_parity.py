@@ -136,18 +136,21 @@ def test_rmsnorm_bwd_fused_add_and_determinism(dev, oracle, dt):
     assert torch.equal(dx1, dx2) and torch.equal(dw1, dw2)              # bit-stable run to run
 
 
-RING_SHAPES = [(1, 768, 256), (2, 1024, 64), (1, 3000, 32), (1, 3200, 40), (3, 257, 72), (2, 1024, 2048 + 8), (40, 1024, 512)]
+RING_SHAPES = [(1, 768, 256), (2, 1024, 64), (1, 3000, 32), (1, 3200, 40), (3, 257, 72), (2, 1024, 2048 + 8), (40, 1024, 512),
+               (150, 256, 512)]
 
 
-@pytest.mark.parametrize("knob", [9, 10, 11])
+@pytest.mark.parametrize("knob", [0, 8, 9, 10, 11])
 @pytest.mark.parametrize("with_add", [False, True])
 @pytest.mark.parametrize("exact", [False, True])
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
 @pytest.mark.parametrize("shape", RING_SHAPES)
 def test_rmsnorm_bwd_cluster_of_four_kernels(dev, oracle, shape, dt, exact, with_add, knob):
-    """The backward kernels on clusters of four blocks (tuning knob norm_bwd = 9: 64-byte rows, double-buffered
-    strips; 10: 128-byte rows): ragged channel quarters (C = 257, 3000), ragged token tiles, more tiles than
-    resident clusters (several rounds), and the same bits from two runs."""
+    """Every persistent form of the backward (tuning knob norm_bwd = 0: two sweeps per tile, the second from L2;
+    8: pair of blocks; 9: cluster of four, 64-byte rows, double-buffered strips; 10: cluster of four, 128-byte rows;
+    11: cluster of eight): ragged channel parts (C = 257, 3000), ragged token tiles, more tiles than resident
+    blocks, pairs or clusters (the last two shapes: 320 to 2400 tiles, so every block steps through several
+    rounds and the last round is ragged), and the same bits from two runs."""
     torch = _torch()
     from ane_b200 import lib
     B, Cn, S = shape
@@ -217,6 +220,38 @@ def test_residual_alpha_of_the_reference(dev, oracle):
     for alpha in (float(np.float32(1.0) / np.sqrt(np.float32(24.0))), 1.0):
         got = down(dev.residual(up(x)[0], up(f)[0], alpha))
         assert np.array_equal(got, oracle.residual(x, f, alpha))
+
+
+def test_inline_reference_blocks_golden_on_gpu(dev, golden):
+    """The reference's own inline statements (training_dynamic/train.m:460 residual, :538-554 SwiGLU backward,
+    :754-825 gradient scale / norm / clip; training/forward.h:55-70 RoPE forward, :101,149-151 SwiGLU gate), compiled
+    where the reference is and committed as golden vectors, against the device operators."""
+    torch = _torch()
+
+    def sampled(t, name):
+        return down(t).reshape(-1)[::int(golden[name + "_stride"])]
+
+    h1, h3, d, x, f = (a[0] for a in gi.cfg2())
+    g1, g3 = dev.swiglu_bwd(up(h1)[0], up(h3)[0], up(d)[0])
+    assert rel_err(sampled(g1, "inline_swiglu_bwd_dh1"), golden["inline_swiglu_bwd_dh1"]) <= TOL32
+    assert rel_err(sampled(g3, "inline_swiglu_bwd_dh3"), golden["inline_swiglu_bwd_dh3"]) <= TOL32
+    assert rel_err(sampled(dev.swiglu(up(h1)[0], up(h3)[0]), "inline_swiglu"), golden["inline_swiglu"]) <= TOL32
+    for name, alpha in (("a25", np.float32(24.0 ** -0.25)), ("a50", np.float32(1.0) / np.sqrt(np.float32(24.0)))):
+        got = dev.residual(up(x)[0], up(f)[0], float(alpha))
+        assert np.array_equal(sampled(got, f"inline_residual_{name}"), golden[f"inline_residual_{name}"])
+    q = gi.cfg3()[0][0]
+    for name, arr, hd in (("inline_rope_hd128", q, 128), ("inline_rope_hd64", np.ascontiguousarray(q[:768]), 64)):
+        assert rel_err(sampled(dev.rope(up(arr)[0], hd, base=10000.0), name), golden[name]) <= TOL32
+    # scale / norm / clip: the library folds the scale and the clip factor into Adam; here the same factors are applied
+    # with the scale operator so that the gradient itself can be compared
+    layers, fin, emb = gi.grad_post_inputs()
+    flat = torch.from_numpy(gi.grad_post_flat(layers, fin, emb)).cuda()
+    nsq = dev.grad_norm_sq(flat, gi.GRAD_POST_GSC)
+    assert abs(float(nsq[0]) - float(golden["inline_grad_norm_sq"])) <= TOL32 * float(golden["inline_grad_norm_sq"])
+    cf = dev.clip_factor(nsq, 1.0)
+    assert float(cf[0]) < 1.0
+    got = dev.scale(dev.scale(flat, gi.GRAD_POST_GSC), float(cf[0]))
+    assert rel_err(sampled(got, "inline_grad_flat"), golden["inline_grad_flat"]) <= TOL32
 
 
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
@@ -294,6 +329,57 @@ def test_qknorm_and_fusions_bwd(dev, oracle, B, heads, hd, S, dt, exact):
     dx = down(dev.rope_qknorm_bwd(dyd, xd, wd, dw, hd, 1e-6, 1e6, 3, exact=exact))
     rdx, rdw = oracle.rope_qknorm_bwd(dyr, xr, w, hd, eps=1e-6, base=1e6, pos0=3, exact=exact)
     assert close(dx, rdx, dt) and rel_err(down(dw), rdw) <= dwtol
+
+
+# More (token tile, head) items than the persistent grid of the TMA kernels holds (296 blocks over 64-token
+# tiles): 320 tiles = one full round and 24 left-over tiles shared out head by head, 608 tiles = two rounds and
+# 16 left over, 1216 tiles of 8 heads, and a 64-wide head shape; S = 2048 with base 1e6 is the Qwen3 attention
+# prep as configured (positions to 2047, where one ulp of a frequency already moves the angle by 1e-4).
+QK_ROUNDS = [(10, 16, 128, 2048), (19, 8, 128, 2048), (5, 16, 128, 2048 + 64 + 8), (12, 12, 64, 2048), (38, 2, 128, 2048)]
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("B,heads,hd,S", QK_ROUNDS)
+def test_qk_kernels_over_several_rounds_fwd(dev, oracle, B, heads, hd, S, dt):
+    from ane_b200 import lib
+    r = gi.rng(53)
+    x = gi.normal(r, (B, heads * hd, S))
+    w = gi.normal(r, (hd,), 0.02, 1.0)
+    xd, xr = up(x, dt)
+    wd, _ = up(w)
+    lib.poll_status(reset=True)
+    assert close(down(dev.qknorm(xd, wd, hd, 1e-6)), oracle.qknorm(xr, w, hd, 1e-6), dt)
+    assert close(down(dev.qknorm_rope(xd, wd, hd, 1e-6, 1e6, 0)), oracle.qknorm_rope(xr, w, hd, 1e-6, 1e6, 0), dt)
+    assert close(down(dev.rope(xd, hd, base=1e6)), oracle.rope(xr, hd, base=1e6), dt)
+    assert lib.poll_status().wait_giveups == 0
+
+
+@pytest.mark.parametrize("exact", [False, True])
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("B,heads,hd,S", QK_ROUNDS)
+def test_qk_kernels_over_several_rounds_bwd(dev, oracle, B, heads, hd, S, dt, exact):
+    torch = _torch()
+    from ane_b200 import lib
+    r = gi.rng(54)
+    x = gi.normal(r, (B, heads * hd, S))
+    dy = gi.normal(r, (B, heads * hd, S))
+    w = gi.normal(r, (hd,), 0.02, 1.0)
+    (xd, xr), (dyd, dyr) = up(x, dt), up(dy, dt)
+    wd, _ = up(w)
+    dwtol = TOL32 if dt == "f32" else 1e-4
+    lib.poll_status(reset=True)
+    dw = torch.zeros(hd, device="cuda")
+    dx = down(dev.qknorm_bwd(dyd, xd, wd, dw, hd, 1e-6, exact=exact))
+    rdx, rdw = oracle.qknorm_bwd(dyr, xr, w, hd, eps=1e-6, exact=exact)
+    assert close(dx, rdx, dt) and rel_err(down(dw), rdw) <= dwtol
+    outs = []
+    for _ in range(2):
+        dw = torch.zeros(hd, device="cuda")
+        outs.append((dev.rope_qknorm_bwd(dyd, xd, wd, dw, hd, 1e-6, 1e6, 0, exact=exact), dw))
+    rdx, rdw = oracle.rope_qknorm_bwd(dyr, xr, w, hd, eps=1e-6, base=1e6, pos0=0, exact=exact)
+    assert close(down(outs[0][0]), rdx, dt) and rel_err(down(outs[0][1]), rdw) <= dwtol
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])     # bit-stable run to run
+    assert lib.poll_status().wait_giveups == 0
 
 
 @pytest.mark.parametrize("dt", ["f32", "bf16"])

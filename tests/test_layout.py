@@ -212,3 +212,46 @@ def test_k_forward_written_into_the_tiled_layout(dtype, case):
     w = torch.from_numpy((1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)).cuda()
     fused = ops.qknorm_rope_tiled(x, w, hd, ratio)
     assert torch.equal(fused, ops.gqa_tile(ops.qknorm_rope(x, w, hd), kv, ratio))
+
+
+# More (token tile, KV head) items than the persistent grid of the TMA kernels holds (296 blocks over 64-token tiles):
+# every block steps through several full rounds and the ragged last round is shared out head by head.
+GQA_ROUNDS = [(10, 8, 2, 128, 2048), (19, 4, 4, 128, 2048), (21, 2, 2, 128, 1024 + 72)]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("case", GQA_ROUNDS)
+def test_gqa_fused_k_side_over_several_rounds_against_the_oracle(orc, dtype, case):
+    """ane_cuda_qknorm_rope_tiled_dev and ane_cuda_rope_qknorm_bwd_gqa_dev at Qwen3's sequence length (base 1e6,
+    positions to 2047) with 320 to 608 token tiles, each against the oracle's own sequence of operators
+    (qknorm_rope then gqa_tile; gqa_reduce then rope_qknorm_bwd), in both forms of the norm backward."""
+    torch = _cuda()
+    from ane_b200 import dev_ops as ops
+    from ane_b200 import lib
+    B, kv, ratio, hd, S = case
+    tdt = getattr(torch, dtype)
+    rng = np.random.default_rng(43)
+    x = torch.from_numpy(rng.standard_normal((B, kv * hd, S)).astype(np.float32)).to(tdt).cuda()
+    dyt = torch.from_numpy(rng.standard_normal((B, kv * ratio * hd, S)).astype(np.float32)).to(tdt).cuda()
+    w_np = (1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)
+    w = torch.from_numpy(w_np).cuda()
+    xr = x.float().cpu().numpy()
+    tol = 1e-5 if dtype == "float32" else 2.0 ** -8
+    lib.poll_status(reset=True)
+
+    fwd = ops.qknorm_rope_tiled(x, w, hd, ratio).float().cpu().numpy()
+    want = orc.gqa_tile(orc.qknorm_rope(xr, w_np, hd, 1e-6, 1e6, 0), kv, ratio)
+    assert np.abs(fwd - want).max() <= tol * np.abs(want).max()
+    if dtype != "float32":
+        l2 = np.sqrt(((fwd - want).astype(np.float64) ** 2).sum() / (want.astype(np.float64) ** 2).sum())
+        assert l2 <= 2e-3
+
+    rdk = torch.from_numpy(orc.gqa_reduce(dyt.float().cpu().numpy(), kv, ratio)).to(tdt).float().numpy()
+    for exact in (False, True):
+        dw = torch.zeros(hd, device="cuda")
+        got = ops.rope_qknorm_bwd_gqa(dyt, x, w, dw, hd, ratio, exact=exact).float().cpu().numpy()
+        rdx, rdw = orc.rope_qknorm_bwd(rdk, xr, w_np, hd, eps=1e-6, base=1e6, exact=exact)
+        assert np.abs(got - rdx).max() <= tol * np.abs(rdx).max()
+        assert np.abs(dw.cpu().numpy() - rdw).max() <= (1e-5 if dtype == "float32" else 1e-4) * np.abs(rdw).max()
+    assert lib.poll_status().wait_giveups == 0

@@ -240,3 +240,85 @@ def test_live_reference_ce_out_of_range_quirk(oracle):
     assert abs(loss[0] - rl) <= TOL * abs(rl)
     assert rel_err(dl, rdl) <= TOL
     assert abs(dl[:, 2].sum() - 1.0) < 1e-4
+
+
+# ------------------------------------------------------------------ the reference's inline blocks, compiled by line range
+def _grad_post_by_oracle(oracle):
+    """Scale, norm and clip the way the library folds them: norm of the scaled gradient, one clip factor, g*gsc*factor."""
+    layers, fin, emb = gi.grad_post_inputs()
+    flat = gi.grad_post_flat(layers, fin, emb)
+    nsq = oracle.grad_norm_sq(flat, gi.GRAD_POST_GSC)
+    cf = oracle.clip_factor(np.float32(nsq), 1.0)
+    return (flat * np.float32(gi.GRAD_POST_GSC)) * np.float32(cf), nsq, cf
+
+
+def test_inline_blocks_golden(golden, oracle):
+    """SwiGLU fwd / bwd, the DeepNet residual, RoPE forward and the gradient scale / norm / clip chain against the
+    committed outputs of the reference's own statements (training_dynamic/train.m:460,538-554,754-825,
+    training/forward.h:55-70,101,149-151)."""
+    h1, h3, d, x, f = (a[0] for a in gi.cfg2())
+    dh1, dh3 = oracle.swiglu_bwd(h1, h3, d)
+    for name, got in (("inline_swiglu_bwd_dh1", dh1), ("inline_swiglu_bwd_dh3", dh3), ("inline_swiglu", oracle.swiglu(h1, h3))):
+        assert rel_err(got.reshape(-1)[::int(golden[name + "_stride"])], golden[name]) <= TOL
+    for name, alpha in (("a25", np.float32(24.0 ** -0.25)), ("a50", np.float32(1.0) / np.sqrt(np.float32(24.0)))):
+        got = oracle.residual(x, f, alpha)
+        assert np.array_equal(got.reshape(-1)[::int(golden[f"inline_residual_{name}_stride"])], golden[f"inline_residual_{name}"])
+    q = gi.cfg3()[0][0]
+    for name, arr, hd in (("inline_rope_hd128", q, 128), ("inline_rope_hd64", np.ascontiguousarray(q[:768]), 64)):
+        got = oracle.rope(arr, hd, base=10000.0)
+        assert rel_err(got.reshape(-1)[::int(golden[name + "_stride"])], golden[name]) <= TOL
+    flat, nsq, cf = _grad_post_by_oracle(oracle)
+    assert cf < 1.0                                                       # the clip branch ran
+    assert abs(np.sqrt(nsq) - float(golden["inline_grad_norm"])) <= TOL * float(golden["inline_grad_norm"])
+    assert rel_err(flat[::int(golden["inline_grad_flat_stride"])], golden["inline_grad_flat"]) <= TOL
+
+
+def _reference_inline():
+    from oracle.oracle import ReferenceInline, reference_inline_available
+    if not reference_inline_available():
+        pytest.skip("oracle/_ref/libref_inline.so not built on this box")
+    return ReferenceInline()
+
+
+def test_live_reference_swiglu(oracle):
+    """train.m:538-554 (13 vDSP passes) and forward.h:101,149-151 compiled, on other seeds and a ragged size."""
+    ref = _reference_inline()
+    for seed, hidden, seq in ((7, 2048, 256), (8, 33, 5)):
+        h1, h3, d, _, _ = (a[0] for a in gi.cfg2(seed=seed, hidden=hidden, seq=seq))
+        dh1, dh3 = oracle.swiglu_bwd(h1, h3, d)
+        rdh1, rdh3 = ref.swiglu_bwd(h1, h3, d)
+        assert rel_err(dh1, rdh1) <= TOL and rel_err(dh3, rdh3) <= TOL
+        assert rel_err(oracle.swiglu(h1, h3), ref.swiglu(h1, h3)) <= TOL
+
+
+def test_live_reference_residual(oracle):
+    """train.m:460 compiled: x + alpha*f, bit for bit, for the alpha of train.m:188, the benchmark's and 1."""
+    ref = _reference_inline()
+    _, _, _, x, f = (a[0] for a in gi.cfg2(seed=9))
+    for alpha in (np.float32(1.0) / np.sqrt(np.float32(24.0)), np.float32(24.0 ** -0.25), np.float32(1.0)):
+        assert np.array_equal(oracle.residual(x, f, alpha), ref.residual(x, f, alpha))
+
+
+def test_live_reference_rope_forward(oracle):
+    """forward.h:55-70 compiled (row-major, base 10000) against the channel-first restatement."""
+    ref = _reference_inline()
+    q = gi.cfg3(seed=10)[0][0]
+    assert rel_err(oracle.rope(q, 128, base=10000.0), ref.rope_channel_first(q, 128)) <= TOL
+    q64 = np.ascontiguousarray(q[:768, :100])
+    assert rel_err(oracle.rope(q64, 64, base=10000.0), ref.rope_channel_first(q64, 64)) <= TOL
+
+
+def test_live_reference_grad_scale_norm_clip(oracle):
+    """train.m:754-767 (scale), :770-788 (norm), :809-825 (clip) compiled, against the folded form the library uses
+    (norm of the scaled gradient, then g * gscale * factor inside Adam); with and without the clip triggering."""
+    ref = _reference_inline()
+    for clip in (1.0, 1e9, 0.0):
+        layers, fin, emb = gi.grad_post_inputs(seed=77)
+        flat0 = gi.grad_post_flat(layers, fin, emb)
+        norm, nsq = ref.grad_scale_norm_clip(layers, fin, emb, gi.GRAD_POST_GSC, clip)
+        want_nsq = oracle.grad_norm_sq(flat0, gi.GRAD_POST_GSC)
+        assert abs(nsq - want_nsq) <= TOL * want_nsq
+        cf = oracle.clip_factor(np.float32(want_nsq), clip)
+        assert (cf < 1.0) == (clip == 1.0)
+        want = (flat0 * np.float32(gi.GRAD_POST_GSC)) * np.float32(cf)
+        assert rel_err(gi.grad_post_flat(layers, fin, emb), want) <= TOL

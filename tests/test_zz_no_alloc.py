@@ -84,6 +84,57 @@ def test_static_scratch_matches_regular_entry_point(dtype, with_add):
     assert float((dws - dwr).abs().max()) <= 1e-4 * float(dwr.abs().max())
 
 
+# (B, C, S, dtype, fused add): 320 and 1280 token tiles against at most 296 blocks (every block walks several
+# tiles and the shared array is used row by row up to its cap), a ragged fp32 shape that takes the scalar
+# path (S not a multiple of the vector width), odd channel counts, and the largest channel count the array holds.
+ORACLE_CASES = [(40, 1024, 512, "bfloat16", True), (40, 1024, 512, "float32", False), (3, 100, 33, "float32", False),
+                (2, 333, 40, "bfloat16", True), (5, 2047, 96, "float32", True), (2, 2048, 72, "bfloat16", False)]
+
+
+@pytest.mark.parametrize("exact", [False, True])
+@pytest.mark.parametrize("B,C,S,dtype,with_add", ORACLE_CASES)
+def test_static_scratch_matches_the_cpu_oracle_and_allocates_nothing(oracle, B, C, S, dtype, with_add, exact):
+    """dx and dw of the allocation-free entry point against the CPU oracle (the tolerances of test_gpu_parity),
+    and the property the entry point exists for: across the call, neither the free device memory nor the
+    library's cudaMalloc-grown scratch range changes."""
+    import torch
+    from ane_b200 import lib
+    from tests.test_gpu_parity import close
+    assert torch.cuda.is_available(), "needs a CUDA device"
+    torch.cuda.set_device(0)
+    L = lib.load()
+    tdt = getattr(torch, dtype)
+    dt, short = {"float32": (lib.F32, "f32"), "bfloat16": (lib.BF16, "bf16")}[dtype]
+    rng = np.random.default_rng(C * 7 + S)
+    mk = lambda *sh: torch.from_numpy(rng.standard_normal(sh).astype(np.float32)).cuda().to(tdt)
+    x, dy = mk(B, C, S), mk(B, C, S)
+    add = mk(B, C, S) if with_add else None
+    w_np = (1 + 0.02 * rng.standard_normal(C)).astype(np.float32)
+    dw0 = (0.1 * rng.standard_normal(C)).astype(np.float32)
+    w = torch.from_numpy(w_np).cuda()
+    flags = lib.NORM_BWD_EXACT if exact else lib.NORM_BWD_REFERENCE
+
+    def run():
+        dx = torch.empty_like(x)
+        dw = torch.from_numpy(dw0).cuda()
+        torch.cuda.synchronize()
+        free0, ws0 = torch.cuda.mem_get_info()[0], L.ane_cuda_workspace_bytes()
+        rc = _call(L, L.ane_cuda_rmsnorm_bwd_static_dev, dt, B, C, S, dx, dw, dy, x, w, add, flags)
+        assert rc == lib.OK, L.ane_cuda_last_error()
+        torch.cuda.synchronize()
+        return dx, dw, free0 - torch.cuda.mem_get_info()[0], L.ane_cuda_workspace_bytes() - ws0
+
+    run()                                   # the first call on a device resolves the array's address
+    dx, dw, free_delta, ws_delta = run()
+    assert free_delta == 0 and ws_delta == 0
+    rdx, rdw = oracle.rmsnorm_bwd(dy.float().cpu().numpy(), x.float().cpu().numpy(), w_np, dw=dw0, eps=1e-5, exact=exact)
+    if with_add:
+        rdx = oracle.add(rdx, add.float().cpu().numpy())
+    assert close(dx.float().cpu().numpy(), rdx, short)
+    err = float(np.abs(dw.cpu().numpy() - rdw).max()) / float(np.abs(rdw).max())
+    assert err <= (1e-5 if dtype == "float32" else 1e-4)
+
+
 def test_static_scratch_rejects_sizes_beyond_its_array():
     import torch
     from ane_b200 import lib
