@@ -4,6 +4,8 @@
 // the overwrite / accumulate behaviour of training/stories_cpu_ops.h and
 // training/training_dynamic/cpu_ops.h.
 #include "common.cuh"
+
+#include <vector>
 #include "tma.cuh"
 
 #include <atomic>
@@ -82,21 +84,41 @@ int tuning(const char *name, int dflt) {
     return dflt;
 }
 
+static std::vector<void *> g_retired;      // device ranges replaced by larger ones; freed at shutdown
+static bool g_frozen = false;
+
+bool frozen() { return g_frozen; }
+void retire_device_range(void *p) { if (p) g_retired.push_back(p); }
+
+cudaError_t dev_malloc(void **p, size_t bytes) {
+    for (int i = 0; i < g_nknobs; i++)
+        if (strcmp(g_knobs[i].name, "fail_alloc") == 0 && g_knobs[i].value > 0) {
+            g_knobs[i].value--;
+            *p = nullptr;
+            return cudaErrorMemoryAllocation;
+        }
+    const cudaError_t e = cudaMalloc(p, bytes);
+    if (e != cudaSuccess) cudaGetLastError();
+    return e;
+}
+
 void *workspace(size_t bytes) {
     Context &c = g_ctx;
     if (bytes <= c.ws_bytes && c.ws) return c.ws;
-    // Grow: cudaFree waits for all work on the device, so kernels still using the old range finish first.
-    if (c.ws) { cudaFree(c.ws); c.ws = nullptr; c.ws_bytes = 0; }
+    if (g_frozen) return nullptr;       // the caller reports "no scratch"; ane_cuda_reserve_workspace before freezing avoids it
+    // Grow into a NEW range.  The old one stays allocated until shutdown: kernels already enqueued and CUDA graphs already
+    // captured keep a valid address (each launch fully rewrites the part of the scratch it reads, so an old and a new
+    // range never have to agree).
     const size_t want = round_up(bytes + bytes / 4, (size_t)1 << 20);
     void *p = nullptr;
-    if (cudaMalloc(&p, want) != cudaSuccess) {
-        cudaGetLastError();
-        if (cudaMalloc(&p, round_up(bytes, 256)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-        c.ws_bytes = round_up(bytes, 256);
-    } else {
-        c.ws_bytes = want;
+    size_t got = want;
+    if (dev_malloc(&p, want) != cudaSuccess) {
+        got = round_up(bytes, 256);
+        if (dev_malloc(&p, got) != cudaSuccess) return nullptr;
     }
+    retire_device_range(c.ws);
     c.ws = p;
+    c.ws_bytes = got;
     return p;
 }
 
@@ -115,9 +137,9 @@ static int stage_reserve(Stage &s, size_t total) {
     Context &c = g_ctx;
     total += 4096;
     if (total > c.stage_bytes) {
-        if (c.stage) { cudaFree(c.stage); c.stage = nullptr; c.stage_bytes = 0; }
+        if (c.stage) { cudaFree(c.stage); c.stage = nullptr; c.stage_bytes = 0; }      // host-buffer calls are synchronous: nothing refers to it
         void *p = nullptr;
-        if (cudaMalloc(&p, total) != cudaSuccess) { cudaGetLastError(); return fail(ANE_CUDA_ERR_NOMEM, "staging: cudaMalloc(%zu) failed", total); }
+        if (dev_malloc(&p, total) != cudaSuccess) return fail(ANE_CUDA_ERR_NOMEM, "staging: cudaMalloc(%zu) failed", total);
         c.stage = p;
         c.stage_bytes = total;
     }
@@ -207,6 +229,9 @@ void ane_cuda_shutdown(void) {
     rope_tables_release();
     embed_side_release();
     if (c.ws) cudaFree(c.ws);
+    for (void *p : g_retired) cudaFree(p);
+    g_retired.clear();
+    g_frozen = false;
     if (c.stage) cudaFree(c.stage);
     if (c.status) cudaFree(c.status);
     if (c.pinned) cudaFreeHost(c.pinned);
@@ -217,7 +242,7 @@ ANECudaBuf *ane_cuda_alloc(size_t bytes) {
     if (!g_ctx.inited) { fail(ANE_CUDA_ERR_NOT_INIT, "ane_cuda_alloc: call ane_cuda_init first"); return nullptr; }
     if (bytes == 0) { fail(ANE_CUDA_ERR_INVALID, "ane_cuda_alloc: zero bytes"); return nullptr; }
     void *p = nullptr;
-    if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); fail(ANE_CUDA_ERR_NOMEM, "ane_cuda_alloc: cudaMalloc(%zu) failed", bytes); return nullptr; }
+    if (dev_malloc(&p, bytes) != cudaSuccess) { fail(ANE_CUDA_ERR_NOMEM, "ane_cuda_alloc: cudaMalloc(%zu) failed", bytes); return nullptr; }
     ANECudaBuf *b = new ANECudaBuf{p, bytes};
     return b;
 }
@@ -262,6 +287,13 @@ int ane_cuda_sync(void *stream) {
     return ANE_CUDA_OK;
 }
 
+int ane_cuda_zero_dev(void *stream, void *dev, size_t bytes) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(dev || bytes == 0, "%s: null pointer", __func__);
+    if (bytes) ANE_CUDA_TRY(cudaMemsetAsync(dev, 0, bytes, (cudaStream_t)stream));
+    return ANE_CUDA_OK;
+}
+
 int ane_cuda_poll_status(ane_cuda_status *out, int reset) {
     ANE_REQUIRE_INIT();
     ANE_REQUIRE(out, "%s: null pointer", __func__);
@@ -272,6 +304,30 @@ int ane_cuda_poll_status(ane_cuda_status *out, int reset) {
 }
 
 size_t ane_cuda_workspace_bytes(void) { return g_ctx.ws_bytes; }
+
+int ane_cuda_reserve_workspace(size_t bytes) {
+    ANE_REQUIRE_INIT();
+    if (bytes == 0) return ANE_CUDA_OK;
+    if (!workspace(bytes))
+        return fail(g_frozen ? ANE_CUDA_ERR_UNSUPPORTED : ANE_CUDA_ERR_NOMEM, "%s: cannot provide %zu bytes of scratch%s", __func__, bytes,
+                    g_frozen ? " (the library is frozen)" : "");
+    return ANE_CUDA_OK;
+}
+
+int ane_cuda_freeze(int on) {
+    ANE_REQUIRE_INIT();
+    g_frozen = on != 0;
+    return ANE_CUDA_OK;
+}
+
+int ane_cuda_release_caches(void) {
+    ANE_REQUIRE_INIT();
+    ANE_CUDA_TRY(cudaDeviceSynchronize());
+    rope_tables_release();
+    for (void *p : g_retired) cudaFree(p);
+    g_retired.clear();
+    return ANE_CUDA_OK;
+}
 
 }  // extern "C"
 

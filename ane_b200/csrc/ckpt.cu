@@ -140,6 +140,14 @@ static int ckpt_load(Layout layout, const char *path, ane_ckpt_header *hdr, floa
     int rc = read_header(f, hdr);
     if (rc == ANE_CUDA_OK && (layout == WEIGHT_ORDER ? param_count(*hdr) != n_floats : param_count(*hdr) > n_floats))
         rc = fail(ANE_CUDA_ERR_INVALID, "%s: the file holds %zu parameters, the buffers %zu", __func__, param_count(*hdr), n_floats);
+    if (rc == ANE_CUDA_OK) {      // the whole body must be there, also the parts a weights-only load skips over
+        const long body = (long)sizeof(*hdr);
+        if (fseek(f, 0, SEEK_END) != 0 || ftell(f) < 0 || (size_t)ftell(f) < sizeof(*hdr) + 3 * sizeof(float) * param_count(*hdr))
+            rc = fail(ANE_CUDA_ERR_INVALID, "%s: %s is truncated (%ld bytes, the header promises %zu)", __func__, path, ftell(f),
+                      sizeof(*hdr) + 3 * sizeof(float) * param_count(*hdr));
+        else if (fseek(f, body, SEEK_SET) != 0)
+            rc = fail(ANE_CUDA_ERR_INVALID, "%s: seek failed", __func__);
+    }
     if (rc != ANE_CUDA_OK) { fclose(f); return rc; }
     std::vector<float> stage(CKPT_CHUNK);
     float *dst[3] = {w_dev, m_dev, v_dev};

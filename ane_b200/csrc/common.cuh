@@ -27,8 +27,16 @@ struct Context {
 Context &ctx();
 int fail(int code, const char *fmt, ...);
 void note_launch(int n = 1);
-// Returns a device scratch range of at least `bytes` (256-byte aligned) or nullptr.
+// Returns a device scratch range of at least `bytes` (256-byte aligned) or nullptr.  A range that was handed out is never
+// freed or moved before ane_cuda_shutdown: when the scratch has to grow, a new range is allocated and the old one is kept
+// (a captured CUDA graph may hold its address).  After ane_cuda_freeze(1) a request that would grow fails instead.
 void *workspace(size_t bytes);
+// cudaMalloc behind the library's allocation-failure hook (tuning knob "fail_alloc" = number of coming allocations that
+// fail as if the device were out of memory; host-side fault injection for the error paths).
+cudaError_t dev_malloc(void **p, size_t bytes);
+// Keeps a device range alive until ane_cuda_shutdown (ranges that were replaced but may still be referenced).
+void retire_device_range(void *p);
+bool frozen();
 // Kernel-selection knobs (ane_cuda_set_tuning); `dflt` when the knob was never set.
 int tuning(const char *name, int dflt);
 // Frees the cached RoPE cos/sin tables (rope.cu).

@@ -36,40 +36,89 @@ __global__ void rope_table_kernel(float *__restrict__ cosT, float *__restrict__ 
     sinT[idx] = sinf(theta);
 }
 
-struct RopeTable { int hd, S, pos0; float base; float *dev; size_t bytes; unsigned long long stamp; };
-static RopeTable g_tables[4] = {};
-static unsigned long long g_table_clock = 0;
+// A table that was handed out is never freed, moved or refilled with other contents before ane_cuda_shutdown (or
+// ane_cuda_release_caches): a kernel already enqueued or a CUDA graph already captured may hold its address.
+struct RopeTable { int hd, S, pos0; float base; float *dev; cudaEvent_t filled; cudaStream_t filled_on; };
+constexpr int ROPE_MAX_TABLES = 64;
+static RopeTable g_tables[ROPE_MAX_TABLES] = {};
+static int g_ntables = 0;
 
 void rope_tables_release() {
-    for (auto &t : g_tables) { if (t.dev) cudaFree(t.dev); t = RopeTable(); }
+    for (int i = 0; i < g_ntables; i++) {
+        if (g_tables[i].dev) cudaFree(g_tables[i].dev);
+        if (g_tables[i].filled) cudaEventDestroy(g_tables[i].filled);
+        g_tables[i] = RopeTable();
+    }
+    g_ntables = 0;
 }
 
-// Returns cos table (sin table follows at + S*hd/2 floats) or nullptr on failure.
-static const float *rope_table(cudaStream_t st, int hd, int S, float base, int pos0, const RopeFreq &fq) {
-    RopeTable *slot = &g_tables[0];
-    for (auto &t : g_tables) {
-        if (t.dev && t.hd == hd && t.S == S && t.pos0 == pos0 && t.base == base) { t.stamp = ++g_table_clock; return t.dev; }
-        if (t.stamp < slot->stamp) slot = &t;
+// Returns the cos table (the sin table follows at + S*hd/2 floats), or nullptr with *rc set.
+static const float *rope_table(cudaStream_t st, int hd, int S, float base, int pos0, const RopeFreq &fq, int *rc, const char *who) {
+    for (int i = 0; i < g_ntables; i++) {
+        RopeTable &t = g_tables[i];
+        if (t.hd == hd && t.S == S && t.pos0 == pos0 && t.base == base) {
+            // filled on another stream: order this stream after the fill unless it is known to be complete.  Not while
+            // this stream is being captured: a table used in a capture was filled by an eager call before it, and the
+            // capture's own start already comes after the caller's synchronisation with that call.
+            if (t.filled_on != st) {
+                cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+                if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) cudaGetLastError();
+                if (cap == cudaStreamCaptureStatusNone && cudaEventQuery(t.filled) != cudaSuccess) {
+                    cudaGetLastError();
+                    cudaStreamWaitEvent(st, t.filled, 0);
+                }
+            }
+            return t.dev;
+        }
     }
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) cudaGetLastError();
+    if (cap != cudaStreamCaptureStatusNone) {
+        *rc = fail(ANE_CUDA_ERR_UNSUPPORTED, "%s: no cos/sin table for (head width %d, S %d, base %g, first position %d) yet and the stream is "
+                   "being captured; run the operator once with these arguments before capturing", who, hd, S, (double)base, pos0);
+        return nullptr;
+    }
+    if (frozen()) {
+        *rc = fail(ANE_CUDA_ERR_UNSUPPORTED, "%s: no cos/sin table for (head width %d, S %d, base %g, first position %d) and the library is "
+                   "frozen (ane_cuda_freeze)", who, hd, S, (double)base, pos0);
+        return nullptr;
+    }
+    if (g_ntables == ROPE_MAX_TABLES) {
+        *rc = fail(ANE_CUDA_ERR_UNSUPPORTED, "%s: %d distinct cos/sin tables are cached; call ane_cuda_release_caches() once no enqueued work "
+                   "or captured graph uses them", who, ROPE_MAX_TABLES);
+        return nullptr;
+    }
+    RopeTable &t = g_tables[g_ntables];
     const size_t n = (size_t)S * (hd / 2);
-    const size_t bytes = 2 * n * sizeof(float);
-    if (slot->dev && slot->bytes < bytes) { cudaFree(slot->dev); slot->dev = nullptr; }
-    if (!slot->dev) {
-        if (cudaMalloc(reinterpret_cast<void **>(&slot->dev), bytes) != cudaSuccess) { cudaGetLastError(); slot->dev = nullptr; return nullptr; }
-        slot->bytes = bytes;
+    float *dev = nullptr;
+    if (dev_malloc(reinterpret_cast<void **>(&dev), 2 * n * sizeof(float)) != cudaSuccess) {
+        *rc = fail(ANE_CUDA_ERR_NOMEM, "%s: no memory for the cos/sin table", who);
+        return nullptr;
     }
-    slot->hd = hd; slot->S = S; slot->pos0 = pos0; slot->base = base; slot->stamp = ++g_table_clock;
-    rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(slot->dev, slot->dev + n, S, hd / 2, pos0, fq);
+    cudaEvent_t ev = nullptr;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(dev);
+        *rc = fail(ANE_CUDA_ERR_CUDA, "%s: cudaEventCreate failed", who);
+        return nullptr;
+    }
+    rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(dev, dev + n, S, hd / 2, pos0, fq);
+    cudaEventRecord(ev, st);
     note_launch(1);
-    return slot->dev;
+    t = RopeTable{hd, S, pos0, base, dev, ev, st};
+    g_ntables++;
+    return dev;
 }
 
 // ------------------------------------------------------------------ stand-alone RoPE
 // One thread: one pair index i, VEC tokens, all heads.   cpu_ops.h:168-184 / forward.h:55-70
+// cos / sin come from the cached table when there is one (cosT != nullptr; vector path only), else from the same
+// cosf / sinf expressions evaluated here -- the same bits either way.
+template <int N> __device__ __forceinline__ V<N> table_lanes(const float *p);
 template <typename T, int VEC, int LG>
 __global__ void __launch_bounds__(QK_THREADS)
 rope_kernel(T *out, const T *x, int heads, int hd, int S, int tiles_per_seq, int pos0, bool inverse,
-            const __grid_constant__ RopeFreq freq) {
+            const __grid_constant__ RopeFreq freq, const float *__restrict__ cosT, const float *__restrict__ sinT) {
     constexpr int R = QK_THREADS / LG;
     constexpr int TW = LG * VEC;
     const int b = blockIdx.x / tiles_per_seq;
@@ -81,12 +130,26 @@ rope_kernel(T *out, const T *x, int heads, int hd, int S, int tiles_per_seq, int
     const size_t hstep = (size_t)hd * S;
     for (int i = blockIdx.y * R + rg; i < hd / 2; i += gridDim.y * R) {
         V<VEC> cs, sn;
-        const float fr = freq.f[i];
+        bool from_table = false;
+        if constexpr (VEC >= 4) {
+            if (cosT) {
+                cs = table_lanes<VEC>(cosT + (size_t)i * S + t);
+                sn = table_lanes<VEC>(sinT + (size_t)i * S + t);
+                if (inverse) {
 #pragma unroll
-        for (int j = 0; j < VEC; j++) {
-            const float theta = (float)(pos0 + t + j) * fr;
-            cs.set(j, cosf(theta));
-            sn.set(j, inverse ? -sinf(theta) : sinf(theta));
+                    for (int q = 0; q < VEC / 2; q++) sn.p[q] = make_float2(-sn.p[q].x, -sn.p[q].y);
+                }
+                from_table = true;
+            }
+        }
+        if (!from_table) {
+            const float fr = freq.f[i];
+#pragma unroll
+            for (int j = 0; j < VEC; j++) {
+                const float theta = (float)(pos0 + t + j) * fr;
+                cs.set(j, cosf(theta));
+                sn.set(j, inverse ? -sinf(theta) : sinf(theta));
+            }
         }
         const size_t o0 = base + (size_t)(2 * i) * S;
         int h = 0;
@@ -825,8 +888,9 @@ template <typename T>
 static int launch_qk_bwd_gqa(cudaStream_t st, int B, int heads, int ratio, int hd, int S, void *dx, float *dw, const void *dy,
                              const void *x, const float *w, float eps, float base, int pos0, unsigned flags, const RopeFreq &fq) {
     constexpr int VEC = Elt<T>::VEC;
-    const float *cosT = rope_table(st, hd, S, base, pos0, fq);
-    if (!cosT) return fail(ANE_CUDA_ERR_NOMEM, "rope_qknorm_bwd_gqa: no memory for the cos/sin table");
+    int trc = ANE_CUDA_OK;
+    const float *cosT = rope_table(st, hd, S, base, pos0, fq, &trc, "rope_qknorm_bwd_gqa");
+    if (!cosT) return trc;
     const float *sinT = cosT + (size_t)S * (hd / 2);
     const int tps = (S + QK_LG * VEC - 1) / (QK_LG * VEC);
     const int ntiles = B * tps;
@@ -866,16 +930,21 @@ static int fill_freq(RopeFreq &fq, int hd, float base) {
 }
 
 template <typename T>
-static int launch_rope(cudaStream_t st, int B, int heads, int hd, int S, void *out, const void *x, int pos0, bool inverse,
+static int launch_rope(cudaStream_t st, int B, int heads, int hd, int S, void *out, const void *x, float base, int pos0, bool inverse,
                        const RopeFreq &fq) {
     constexpr int VEC = Elt<T>::VEC;
     const bool vec = (S % VEC == 0) && aligned16(out) && aligned16(x);
     if (vec) {
+        // the cached table when it exists or can be made now; a miss while the stream is being captured, or after
+        // ane_cuda_freeze, falls back to the in-kernel evaluation (same bits) instead of failing
+        int trc = ANE_CUDA_OK;
+        const float *cosT = tuning("rope_table", 1) ? rope_table(st, hd, S, base, pos0, fq, &trc, "rope") : nullptr;
+        const float *sinT = cosT ? cosT + (size_t)S * (hd / 2) : nullptr;
 #define ANE_ROPE_LG(LGv)                                                                                             \
         do {                                                                                                         \
             const int tps_ = (S + (LGv) * VEC - 1) / ((LGv) * VEC);                                                   \
             dim3 grid_((unsigned)(B * tps_), (unsigned)((hd / 2 + (QK_THREADS / (LGv)) - 1) / (QK_THREADS / (LGv)))); \
-            rope_kernel<T, VEC, LGv><<<grid_, QK_THREADS, 0, st>>>((T *)out, (const T *)x, heads, hd, S, tps_, pos0, inverse, fq); \
+            rope_kernel<T, VEC, LGv><<<grid_, QK_THREADS, 0, st>>>((T *)out, (const T *)x, heads, hd, S, tps_, pos0, inverse, fq, cosT, sinT); \
         } while (0)
         switch (tuning("rope_lg", 16)) {
             case 32: ANE_ROPE_LG(32); break;
@@ -887,7 +956,7 @@ static int launch_rope(cudaStream_t st, int B, int heads, int hd, int S, void *o
         constexpr int LG = 32;
         const int tps = (S + LG - 1) / LG;
         dim3 grid((unsigned)(B * tps), (unsigned)((hd / 2 + (QK_THREADS / LG) - 1) / (QK_THREADS / LG)));
-        rope_kernel<T, 1, LG><<<grid, QK_THREADS, 0, st>>>((T *)out, (const T *)x, heads, hd, S, tps, pos0, inverse, fq);
+        rope_kernel<T, 1, LG><<<grid, QK_THREADS, 0, st>>>((T *)out, (const T *)x, heads, hd, S, tps, pos0, inverse, fq, nullptr, nullptr);
     }
     ANE_LAUNCH_OK(1);
     return ANE_CUDA_OK;
@@ -915,8 +984,9 @@ static int launch_qk_fwd(cudaStream_t st, int B, int heads, int hd, int S, void 
     constexpr int VEC = Elt<T>::VEC;
     const float *cosT = nullptr, *sinT = nullptr;
     if (ROPE) {
-        cosT = rope_table(st, hd, S, base, pos0, fq);
-        if (!cosT) return fail(ANE_CUDA_ERR_NOMEM, "qknorm_rope: no memory for the cos/sin table");
+        int trc = ANE_CUDA_OK;
+        cosT = rope_table(st, hd, S, base, pos0, fq, &trc, "qknorm_rope");
+        if (!cosT) return trc;
         sinT = cosT + (size_t)S * (hd / 2);
     }
     const int tps = (S + QK_LG * VEC - 1) / (QK_LG * VEC);
@@ -958,8 +1028,9 @@ static int launch_qk_bwd(cudaStream_t st, int B, int heads, int hd, int S, void 
     constexpr int VEC = Elt<T>::VEC;
     const float *cosT = nullptr, *sinT = nullptr;
     if (ROPE) {
-        cosT = rope_table(st, hd, S, base, pos0, fq);
-        if (!cosT) return fail(ANE_CUDA_ERR_NOMEM, "rope_qknorm_bwd: no memory for the cos/sin table");
+        int trc = ANE_CUDA_OK;
+        cosT = rope_table(st, hd, S, base, pos0, fq, &trc, "rope_qknorm_bwd");
+        if (!cosT) return trc;
         sinT = cosT + (size_t)S * (hd / 2);
     }
     const int tps = (S + QK_LG * VEC - 1) / (QK_LG * VEC);
@@ -1032,7 +1103,7 @@ int ane_cuda_rope_dev(void *stream, ane_dtype dtype, int B, int C, int S, int hd
     ANE_REQUIRE(flags == ANE_ROPE_FORWARD || flags == ANE_ROPE_INVERSE, "%s: bad flags %u", __func__, flags);
     RopeFreq fq;
     if (int rc = fill_freq(fq, hd, base)) return rc;
-    ANE_DISPATCH_DTYPE(dtype, T, return (launch_rope<T>((cudaStream_t)stream, B, C / hd, hd, S, out, x, pos0, flags == ANE_ROPE_INVERSE, fq)));
+    ANE_DISPATCH_DTYPE(dtype, T, return (launch_rope<T>((cudaStream_t)stream, B, C / hd, hd, S, out, x, base, pos0, flags == ANE_ROPE_INVERSE, fq)));
     return ANE_CUDA_OK;
 }
 

@@ -156,7 +156,9 @@ class FlatParams:
 
     def zero_produced_grads(self):
         """Clear the gradients this library's operators accumulate into (train.m:874-877)."""
-        self.g[self.n_matrix:self.n].zero_()
+        from . import lib as _l
+        part = self.g[self.n_matrix:self.n]
+        _l.check(_l.load().ane_cuda_zero_dev(torch.cuda.current_stream().cuda_stream, part.data_ptr(), part.numel() * 4))
 
 
 class LayerChain:

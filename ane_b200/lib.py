@@ -64,8 +64,12 @@ PROTOTYPES = {
     "ane_cuda_host_alloc": (_vp, [_sz]),
     "ane_cuda_host_free": (None, [_vp]),
     "ane_cuda_sync": (_i, [_vp]),
+    "ane_cuda_zero_dev": (_i, [_vp, _vp, _sz]),
     "ane_cuda_poll_status": (_i, [C.POINTER(Status), _i]),
     "ane_cuda_workspace_bytes": (_sz, []),
+    "ane_cuda_reserve_workspace": (_i, [_sz]),
+    "ane_cuda_freeze": (_i, [_i]),
+    "ane_cuda_release_caches": (_i, []),
     # host-pointer drop-ins
     "ane_cuda_rmsnorm": (_i, [_fp, _fp, _fp, _i, _i]),
     "ane_cuda_rmsnorm_bwd": (_i, [_fp, _fp, _fp, _fp, _fp, _i, _i]),
@@ -127,6 +131,13 @@ PROTOTYPES = {
     "ane_cuda_ckpt_param_count": (_sz, [_vp]),
     "ane_cuda_ckpt_load": (_i, [C.c_char_p, _vp, _vp, _vp, _vp, _sz]),
     "ane_cuda_ckpt_save": (_i, [C.c_char_p, _vp, _vp, _vp, _vp, _sz]),
+    "ane_cuda_ckpt_load_flat": (_i, [C.c_char_p, _vp, _vp, _vp, _vp, _sz]),
+    "ane_cuda_ckpt_save_flat": (_i, [C.c_char_p, _vp, _vp, _vp, _vp, _sz]),
+    "ane_cuda_ckpt_flat_decay_count": (_sz, [_vp]),
+    "ane_cuda_ckpt_tensor_offset": (_i, [_vp, _i, _i, _i, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    "ane_cuda_llama2c_read_config": (_i, [C.c_char_p, _vp]),
+    "ane_cuda_llama2c_to_header": (_i, [_vp, _vp]),
+    "ane_cuda_llama2c_load": (_i, [C.c_char_p, _vp, _vp, _vp, _sz, _i]),
 }
 
 _lib = None

@@ -83,6 +83,15 @@ def _cases(torch, ops, device, M, shape=None):
         (wq, dwq), q, dq, qo = head_w(), mk(QD), mk(QD), mk(QD)
         return (lambda i: ops.rope_qknorm_bwd(dq[i % NSET], q[i % NSET], wq, dwq, HD, out=qo[i % NSET])), 3 * QD * T * e, 20
 
+    # the K side of the attention prep on its own (8 KV heads of 128): half the bytes of the Q side per launch
+    def qknorm_rope_k():
+        (wq, _), k, ko = head_w(), mk(KVD, n=2 * NSET), mk(KVD, n=2 * NSET)
+        return (lambda i: ops.qknorm_rope(k[i % (2 * NSET)], wq, HD, out=ko[i % (2 * NSET)])), 2 * KVD * T * e, 20
+
+    def rope_qknorm_bwd_k():
+        (wq, dwq), k, dk, ko = head_w(), mk(KVD, n=2 * NSET), mk(KVD, n=2 * NSET), mk(KVD, n=2 * NSET)
+        return (lambda i: ops.rope_qknorm_bwd(dk[i % (2 * NSET)], k[i % (2 * NSET)], wq, dwq, HD, out=ko[i % (2 * NSET)])), 3 * KVD * T * e, 20
+
     # embedding: batch sequences of 2048 tokens, table [151936, 1024] bf16
     def _embed_common():
         Be = M
@@ -174,6 +183,7 @@ def _cases(torch, ops, device, M, shape=None):
         "rmsnorm": rmsnorm, "rmsnorm_bwd": rmsnorm_bwd, "rmsnorm_bwd_add": rmsnorm_bwd_add,
         "residual_rmsnorm": residual_rmsnorm, "residual": residual, "swiglu": swiglu, "swiglu_bwd": swiglu_bwd,
         "rope": rope, "qknorm_rope(Q)": qknorm_rope, "rope_qknorm_bwd(Q)": rope_qknorm_bwd,
+        "qknorm_rope(K)": qknorm_rope_k, "rope_qknorm_bwd(K)": rope_qknorm_bwd_k,
         "embed_lookup": embed_lookup, "embed_backward": embed_backward,
         "cross_entropy": cross_entropy, "cross_entropy_compact": cross_entropy_compact,
         "adam": adam, "grad_norm_sq": grad_norm_sq,
@@ -210,6 +220,26 @@ def per_op_table(torch, ops, device, peak_gbs, batch=32, only=None, iters=None, 
         res[name] = time_op(torch, builder, peak_gbs, iters, warmup)
         torch.cuda.empty_cache()
     return res
+
+
+REFERENCE_SHAPE_OPS = ("rmsnorm", "rmsnorm_bwd", "rmsnorm_bwd_add", "residual_rmsnorm", "residual", "swiglu", "swiglu_bwd")
+
+
+def reference_shape_table(torch, ops, device, peak_gbs, batches=(1, 64, 1024, 4096)):
+    """The norm / residual / SwiGLU rows at the reference's own shapes (Stories110M: fp32, DIM 768, HIDDEN 2048, SEQ 256;
+    stories_config.h), batched over B sequences.  B = 1 is one reference call: everything fits in L2, so the row is a
+    latency (its GB/s is not an HBM figure); at B = 1024 and 4096 a tensor is 0.8-8.6 GB and fewer buffer sets are
+    rotated (every launch still reads data last touched gigabytes earlier)."""
+    out = {}
+    for B in batches:
+        sets = 4 if B <= 64 else 2 if B <= 1024 else 1
+        shape = dict(dim=768, hidden=2048, seq=256, dtype=torch.float32, sets=sets)
+        rows = per_op_table(torch, ops, device, peak_gbs, batch=B, only=REFERENCE_SHAPE_OPS, iters=10 if B >= 1024 else 20, shape=shape)
+        if B == 1:
+            rows = {k: {"latency_us": round(v["ms"] * 1e3, 2), "latency_us_best": round(v["ms_best"] * 1e3, 2), "bytes": v["bytes"]}
+                    for k, v in rows.items()}
+        out[f"B={B}"] = rows
+    return out
 
 
 def main(argv=None):

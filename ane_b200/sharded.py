@@ -143,21 +143,27 @@ class ShardedAdam:
             self._early = None
         else:
             self._normsq2.zero_()
-        self._rank_sync()                                               # every rank's gradients are complete
+        self._mark("peer.sync_gradients_complete", self._rank_sync)     # every rank's gradients are complete
         if start < self.hi:
-            self.k.p2p_reduce(g_ptrs, start, self.hi - start, self.g_slice[start - self.lo:], gscale, normsq=self._normsq2[1:2])
-        dist.all_reduce(self._normsq2, op=dist.ReduceOp.SUM, group=self.group)  # also: every rank has finished reading gradients
+            self._mark("peer.reduce", lambda: self.k.p2p_reduce(g_ptrs, start, self.hi - start, self.g_slice[start - self.lo:], gscale,
+                                                                  normsq=self._normsq2[1:2]))
+        # the squared norm; also: every rank has finished reading gradients
+        self._mark("peer.allreduce_norm", lambda: dist.all_reduce(self._normsq2, op=dist.ReduceOp.SUM, group=self.group))
         normsq = self._normsq2.sum().reshape(1)
         self.normsq = normsq
         factor = self.k.clip_factor(self._normsq2, self.clip)
-        for lo, hi, wd in ((0, self.n_decay, self.wd), (self.n_decay, self.n_params, 0.0)):
-            a, b = max(lo, self.lo), min(hi, self.hi)
-            if a < b:
-                sl = slice(a, b)
-                gl = slice(a - self.lo, b - self.lo)
-                self.k.p2p_adam(w_ptrs, self.rank, a, b - a, self.g_slice[gl], self.m[sl], self.v[sl], t, self.lr, self.b1, self.b2,
-                                self.eps, wd=wd, gscale=gscale, clip=factor)
-        self._rank_sync()                                               # every rank's parameter stores have landed
+
+        def update():
+            for lo, hi, wd in ((0, self.n_decay, self.wd), (self.n_decay, self.n_params, 0.0)):
+                a, b = max(lo, self.lo), min(hi, self.hi)
+                if a < b:
+                    sl = slice(a, b)
+                    gl = slice(a - self.lo, b - self.lo)
+                    self.k.p2p_adam(w_ptrs, self.rank, a, b - a, self.g_slice[gl], self.m[sl], self.v[sl], t, self.lr, self.b1, self.b2,
+                                    self.eps, wd=wd, gscale=gscale, clip=factor)
+
+        self._mark("peer.adam_store_all", update)
+        self._mark("peer.sync_parameters_landed", self._rank_sync)      # every rank's parameter stores have landed
         return factor
 
     def _update(self, gs, t: int, gscale: float):

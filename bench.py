@@ -236,6 +236,9 @@ def run_reference(args):
         "ms_per_step": r["ms_per_step_extrapolated"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, args.gpus),
+        "extrapolated": True, "sample_ms": round(r["sample_ms"], 1),
+        "note": "ms_per_step and value are EXTRAPOLATED from a bounded sample (see cpu_baseline.sample): the timed work per step "
+                "is sample_ms, scaled linearly in sequences and parameters to the full step",
         "cpu_baseline": {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]},
         "e2e": {"value": r["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -375,6 +378,51 @@ def cpu_reference_ops():
     t = best_of(lambda: ref.adam_update(wv, gv, mv, vv, 1, 3e-4, 0.9, 0.999, 1e-8), 2)
     out["adam 24.6M params"] = {"ms": round(t * 1e3, 2), "GB/s": round(28 * n / t / 1e9, 2)}
     return {"threads": 1, "kind": "reference", "build": "gcc -O3 -march=native, Accelerate calls through a portable C stand-in", "ops": out}
+
+
+def cross_rank_checks(torch, dist, params, opt, t_last, gscale, world, rank, peer_mode):
+    """Outside the timed region, world > 1: (a) every rank ends the timed steps with the same parameters -- a 64-bit sum
+    of the parameter bits, MIN and MAX over the ranks; (b) one more optimizer step from the same state through both
+    forms of the exchange (peer memory, then NCCL reduce-scatter / all-gather on restored buffers) and the largest
+    difference between the two results relative to the largest parameter.  NCCL adds the ranks' gradients in its own
+    order, the peer kernels in rank order: equal bits on two ranks, fp32 rounding beyond."""
+    from ane_b200.sharded import ShardedAdam
+
+    def checksum():
+        c = params.w[:params.n].view(torch.int32).to(torch.int64).sum().reshape(1)
+        lo, hi = c.clone(), c.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        return int(lo[0]) == int(hi[0])
+
+    out = {"params_equal_across_ranks": checksum()}
+    if not peer_mode:
+        return out
+    w0, m0, v0 = params.w.clone(), params.m.clone(), params.v.clone()
+    opt.step(t_last + 1, gscale)
+    torch.cuda.synchronize()
+    dist.barrier()
+    w_peer = params.w.clone()
+    out["params_equal_across_ranks_after_peer_step"] = checksum()
+    dist.barrier()
+    params.w.copy_(w0)
+    params.m.copy_(m0)
+    params.v.copy_(v0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    nccl = ShardedAdam(params.w, params.g, params.m, params.v, params.n_decay, params.n, world, rank,
+                       lr=opt.lr, b1=opt.b1, b2=opt.b2, eps=opt.eps, wd=opt.wd, clip=opt.clip)
+    nccl.step(t_last + 1, gscale)
+    torch.cuda.synchronize()
+    dist.barrier()
+    diff = (params.w[:params.n] - w_peer[:params.n]).abs().max() / w_peer[:params.n].abs().max()
+    moved = (w_peer[:params.n] - w0[:params.n]).abs().max() / w0[:params.n].abs().max()
+    d = torch.stack([diff, -moved]).float()
+    dist.all_reduce(d, op=dist.ReduceOp.MAX)
+    out["optimizer_forms_max_rel_diff"] = float(d[0])
+    out["optimizer_step_moved_params_rel"] = float(-d[1])
+    out["params_equal_across_ranks_after_nccl_step"] = checksum()
+    return out
 
 
 # ------------------------------------------------------------------------------------- main (ours)
@@ -520,11 +568,15 @@ def run_ours(args):
         "gpu_launches": int(launches),
     }
 
+    line["ms_per_step_x_sm_mhz"] = round(ms_step * clocks["sm_mhz"], 1) if clocks.get("sm_mhz") else None
     del chain
     torch.cuda.empty_cache()
+    if world > 1:
+        line.update(cross_rank_checks(torch, dist, params, opt, tstep[0], gscale, world, rank, peer_ptrs is not None))
     if not args.no_ops and rank == 0 and world == 1:
-        from ane_b200.opbench import per_op_table
+        from ane_b200.opbench import per_op_table, reference_shape_table
         line["ops"] = per_op_table(torch, ops, device, peak_gbs, batch=32)
+        line["ops_reference_shapes_f32"] = reference_shape_table(torch, ops, device, peak_gbs)
     if world > 1:
         dist.barrier()
 

@@ -105,10 +105,28 @@ void ane_cuda_free(ANECudaBuf *buf);                            /* ane_bridge_fr
 void *ane_cuda_host_alloc(size_t bytes);
 void ane_cuda_host_free(void *p);
 int ane_cuda_sync(void *stream);
+/* Clears `bytes` bytes of device memory on the stream (the memset of the accumulated gradients, train.m:874-877). */
+int ane_cuda_zero_dev(void *stream, void *dev, size_t bytes);
 /* Copy the device status words to *out and optionally clear them. */
 int ane_cuda_poll_status(ane_cuda_status *out, int reset);
 /* Bytes of library-owned scratch currently held on the device (grow-only cache). */
 size_t ane_cuda_workspace_bytes(void);
+/* Library-owned device memory and CUDA graphs.  Operators keep two kinds of device memory between calls: the scratch
+ * range (dw partials, sort buffers, per-token losses) and cached RoPE cos/sin tables, one per (head width, S, base,
+ * first position), at most 64.  The rule: an address that an operator has used is never freed, moved or refilled with
+ * other contents before ane_cuda_shutdown / ane_cuda_release_caches -- when the scratch must grow, a new range is
+ * allocated and the old one is kept -- so work already enqueued and graphs already captured stay valid whatever is
+ * called later.  What a capture needs must exist BEFORE the capture: run every operator once with the arguments to be
+ * captured (or call ane_cuda_reserve_workspace), because an allocation inside a capture is refused
+ * (ANE_CUDA_ERR_NOMEM for scratch, ANE_CUDA_ERR_UNSUPPORTED for a missing RoPE table; ane_cuda_rope_dev alone falls
+ * back to evaluating cos/sin in the kernel).  ane_cuda_freeze(1) turns every later growth or new table into that
+ * same refusal, outside captures too: a loop that must not allocate calls it after warm-up; ane_cuda_freeze(0) lifts it.
+ * A table filled on one stream and used on another is ordered by an event. */
+int ane_cuda_reserve_workspace(size_t bytes);
+int ane_cuda_freeze(int on);
+/* Frees the cached RoPE tables and the scratch ranges that were replaced by larger ones, after a device-wide
+ * synchronisation.  Only when no captured graph that used them will be launched again. */
+int ane_cuda_release_caches(void);
 
 /* =====================================================================================
  * 2. Host-buffer entry points
@@ -351,6 +369,40 @@ int ane_cuda_ckpt_load(const char *path, ane_ckpt_header *hdr, float *w_dev, flo
 /* Device -> file, byte-identical to what the reference's save_checkpoint writes for the same values. */
 int ane_cuda_ckpt_save(const char *path, const ane_ckpt_header *hdr, const float *w_dev, const float *m_dev,
                        const float *v_dev, size_t n_floats);
+/* The same files to and from "optimizer order", the arrangement a flat optimizer wants: everything that takes weight
+ * decay first, the norm weights (no decay, train.m:837-869) after it --
+ *   [layer 0: Wq Wk Wv Wo W1 W2 W3] ... [layer L-1: ...] embed | rms_att[all layers] rms_ffn[all layers] rms_final | extras
+ * so that Adam is two range updates: [0, ane_cuda_ckpt_flat_decay_count) with decay, the rest without.  n_floats may
+ * exceed the file's parameter count: floats past it (for example per-head QK-norm weights, which the reference's
+ * files do not hold) are not touched by a load and not written by a save -- after loading a file into a model that
+ * has them, initialise them yourself (1 for weights, 0 for moments); saving drops them. */
+int ane_cuda_ckpt_load_flat(const char *path, ane_ckpt_header *hdr, float *w_dev, float *m_dev, float *v_dev, size_t n_floats);
+int ane_cuda_ckpt_save_flat(const char *path, const ane_ckpt_header *hdr, const float *w_dev, const float *m_dev,
+                            const float *v_dev, size_t n_floats);
+size_t ane_cuda_ckpt_flat_decay_count(const ane_ckpt_header *hdr);
+/* Where one tensor lies in either arrangement (flat = 0: weight order, 1: optimizer order).  tensor: 0..6 = Wq Wk Wv Wo
+ * W1 W2 W3, 7 = rms_att, 8 = rms_ffn (each per layer), 9 = rms_final, 10 = embed.  No GPU needed. */
+enum { ANE_T_WQ = 0, ANE_T_WK, ANE_T_WV, ANE_T_WO, ANE_T_W1, ANE_T_W2, ANE_T_W3, ANE_T_RMS_ATT, ANE_T_RMS_FFN, ANE_T_RMS_FINAL, ANE_T_EMBED };
+int ane_cuda_ckpt_tensor_offset(const ane_ckpt_header *hdr, int flat, int tensor, int layer, size_t *offset, size_t *count);
+
+/* ---- llama2.c weight files: the pretrained-weights loader of training/train_large.m:13-56 (load_pretrained).
+ * Header of seven ints (stories_config.h:108-110), then embed, rms_att[all layers], wq[all], wk[all], wv[all], wo[all],
+ * rms_ffn[all], w1[all], w2[all], w3[all], rms_final; a negative vocab_size marks an unshared classifier, which -- like
+ * the reference -- this loader does not read.  Wk and Wv are dim * (dim * n_kv_heads / n_heads) each (equal to the
+ * reference's dim * dim when n_kv_heads == n_heads, the only case it handles). */
+typedef struct {
+    int dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len;
+} ane_llama2c_config;
+/* Reads and validates the 28-byte header only (no GPU needed). */
+int ane_cuda_llama2c_read_config(const char *path, ane_llama2c_config *cfg);
+/* The checkpoint header describing the same model (version 2 for square attention, 4 for grouped-query; step counters
+ * zero), i.e. what ane_cuda_ckpt_save needs to write these weights as a reference checkpoint. */
+int ane_cuda_llama2c_to_header(const ane_llama2c_config *cfg, ane_ckpt_header *hdr);
+/* File -> device weights in weight order (flat = 0) or optimizer order (flat = 1); *hdr receives the header above.
+ * expect may be NULL; otherwise dim, hidden_dim and n_layers must equal the file's ("Config mismatch",
+ * train_large.m:20-23).  A file shorter than its header promises is refused (ANE_CUDA_ERR_INVALID). */
+int ane_cuda_llama2c_load(const char *path, const ane_llama2c_config *expect, ane_ckpt_header *hdr, float *w_dev,
+                          size_t n_floats, int flat);
 
 #ifdef __cplusplus
 }

@@ -46,3 +46,32 @@ def weight_order(layers, rms_final, embed, which):
     """flat array of the w (which=0), m (1) or v (2) parts in weight order"""
     parts = [t[which].ravel() for tensors in layers for t in tensors] + [rms_final[which].ravel(), embed[which].ravel()]
     return np.concatenate(parts).astype(np.float32)
+
+
+LLAMA2C_FMT = "<7i"                   # stories_config.h:108-110
+
+
+def write_llama2c(path, dim, hidden, n_layers, n_heads, n_kv_heads, vocab, seq_len, layers, rms_final, embed, shared=True,
+                  trailing=b""):
+    """A llama2.c weight file in the order load_pretrained reads it (training/train_large.m:28-50): header, embed, then
+    rms_att, wq, wk, wv, wo, rms_ffn, w1, w2, w3 each for all layers, rms_final.  layers: per layer the nine weight
+    arrays in CHECKPOINT order (Wq Wk Wv Wo W1 W2 W3 rms_att rms_ffn).  A negative vocab_size in the header marks an
+    unshared classifier (train_large.m:25-26); `trailing` stands for what follows rms_final in real files."""
+    order = [7, 0, 1, 2, 3, 8, 4, 5, 6]
+    with open(path, "wb") as f:
+        f.write(struct.pack(LLAMA2C_FMT, dim, hidden, n_layers, n_heads, n_kv_heads, vocab if shared else -vocab, seq_len))
+        f.write(np.ascontiguousarray(embed, np.float32).tobytes())
+        for k in order:
+            for tensors in layers:
+                f.write(np.ascontiguousarray(tensors[k], np.float32).tobytes())
+        f.write(np.ascontiguousarray(rms_final, np.float32).tobytes())
+        f.write(trailing)
+
+
+def optimizer_order(layers, rms_final, embed, which):
+    """flat array of the w (which=0), m (1) or v (2) parts in optimizer order:
+    [per-layer matrices | embed | rms_att[all] | rms_ffn[all] | rms_final]"""
+    parts = [t[which].ravel() for tensors in layers for t in tensors[:7]] + [embed[which].ravel()]
+    parts += [tensors[7][which].ravel() for tensors in layers] + [tensors[8][which].ravel() for tensors in layers]
+    parts.append(rms_final[which].ravel())
+    return np.concatenate(parts).astype(np.float32)

@@ -1,0 +1,185 @@
+"""Library-owned device memory against captured CUDA graphs, and host-injected allocation failures.
+
+The operators keep a scratch range and cached RoPE cos/sin tables between calls.  A CUDA graph bakes their
+addresses in, so the library never frees, moves or refills an address it has handed out: these tests capture a
+graph, then make the library grow its scratch and fill more tables than the old four-slot cache held, replay the
+graph and compare with the eager result.  Failure paths are driven from the host (a refused allocation through the
+"fail_alloc" hook, a frozen library); nothing here faults or hangs the GPU.
+"""
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    import torch
+    from ane_b200 import dev_ops, lib
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    lib.init(0)
+    return dev_ops
+
+
+def _inputs(torch, B, heads, hd, S, C):
+    g = torch.Generator(device="cuda").manual_seed(11)
+    q = torch.randn(B, heads * hd, S, device="cuda", generator=g).to(torch.bfloat16)
+    dq = torch.randn(B, heads * hd, S, device="cuda", generator=g).to(torch.bfloat16)
+    wq = 1 + 0.02 * torch.randn(hd, device="cuda", generator=g)
+    x = torch.randn(B, C, S, device="cuda", generator=g).to(torch.bfloat16)
+    dy = torch.randn(B, C, S, device="cuda", generator=g).to(torch.bfloat16)
+    w = 1 + 0.02 * torch.randn(C, device="cuda", generator=g)
+    return q, dq, wq, x, dy, w
+
+
+def test_replay_after_cache_growth_matches_eager(dev):
+    import torch
+    from ane_b200 import lib
+    B, heads, hd, S, C = 2, 4, 128, 256, 512
+    q, dq, wq, x, dy, w = _inputs(torch, B, heads, hd, S, C)
+    out = {k: torch.empty_like(q) for k in ("qr", "dqo", "r")}
+    dx = torch.empty_like(x)
+    dwq, dw = torch.zeros(hd, device="cuda"), torch.zeros(C, device="cuda")
+
+    def chain():
+        dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, 0, out=out["qr"])
+        dev.rope(q, hd, base=1e6, pos0=0, out=out["r"])
+        dev.rope_qknorm_bwd(dq, q, wq, dwq, hd, 1e-6, 1e6, 0, out=out["dqo"])
+        dev.rmsnorm_bwd(dy, x, w, dw, out=dx)
+
+    chain()                                               # everything a capture needs exists before it
+    torch.cuda.synchronize()
+    want = {k: v.clone() for k, v in out.items()}
+    want_dx, want_dw, want_dwq = dx.clone(), dw.clone(), dwq.clone()
+    s = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(graph, stream=s):
+            chain()
+    ws_before = lib.load().ane_cuda_workspace_bytes()
+
+    # later eager calls: six more table keys (the graph's table must survive) and a scratch need far above the present one
+    for pos0 in range(1, 7):
+        dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, pos0)
+    big = torch.randn(300, 2048, 64, device="cuda").to(torch.bfloat16)
+    dev.rmsnorm_bwd(big, big, torch.ones(2048, device="cuda"), torch.zeros(2048, device="cuda"))
+    lib.check(lib.load().ane_cuda_reserve_workspace(ws_before * 4 + (64 << 20)))
+    assert lib.load().ane_cuda_workspace_bytes() > ws_before
+    torch.cuda.synchronize()
+
+    for t in out.values():
+        t.zero_()
+    dx.zero_()
+    dw.zero_()
+    dwq.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    for k in out:
+        assert torch.equal(out[k], want[k]), k
+    assert torch.equal(dx, want_dx)
+    # a capture does not execute: one replay onto zeroed accumulators equals the one eager run
+    assert torch.equal(dw, want_dw) and torch.equal(dwq, want_dwq)
+    assert lib.poll_status().wait_giveups == 0
+
+
+def test_missing_table_inside_a_capture_is_refused_not_baked_in(dev):
+    import torch
+    from ane_b200 import lib
+    B, heads, hd, S, C = 1, 2, 128, 128, 256
+    q, dq, wq, x, dy, w = _inputs(torch, B, heads, hd, S, C)
+    dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, 0)
+    want_rope = dev.rope(q, hd, base=1e6, pos0=977)       # eager: fills the table for first position 977
+    lib.check(lib.load().ane_cuda_release_caches())       # and drop it again
+    want_fused = None
+    s = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    got_rope = torch.empty_like(q)
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(graph, stream=s):
+            with pytest.raises(lib.AneCudaError) as err:
+                dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, 977)            # no table for this key yet
+            assert err.value.code == lib.ERR_UNSUPPORTED
+            dev.rope(q, hd, base=1e6, pos0=977, out=got_rope)        # the stand-alone RoPE evaluates cos/sin in the kernel instead
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(got_rope, want_rope)                          # the same bits as with the table
+    want_fused = dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, 977)          # outside the capture the table is made
+    assert bool(torch.isfinite(want_fused.float()).all())
+
+
+def test_frozen_library_refuses_to_grow(dev):
+    import torch
+    from ane_b200 import lib
+    L = lib.load()
+    B, heads, hd, S, C = 1, 2, 128, 64, 256
+    q, dq, wq, x, dy, w = _inputs(torch, B, heads, hd, S, C)
+    dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, 0)
+    lib.check(L.ane_cuda_freeze(1))
+    try:
+        dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, 0)                               # known key: fine
+        with pytest.raises(lib.AneCudaError) as err:
+            dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, 12345)                       # new key
+        assert err.value.code == lib.ERR_UNSUPPORTED and "frozen" in str(err.value)
+        assert L.ane_cuda_reserve_workspace(L.ane_cuda_workspace_bytes() + (32 << 20)) == lib.ERR_UNSUPPORTED
+        ws = L.ane_cuda_workspace_bytes()
+        Sx = 1024
+        Bx = (ws // 4 + (1 << 20)) // Sx + 1                                   # more per-token losses than the scratch holds
+        logits = torch.zeros(Bx, 2, Sx, device="cuda")
+        tg = torch.zeros(Bx, Sx, device="cuda", dtype=torch.int32)
+        with pytest.raises(lib.AneCudaError) as err:
+            dev.cross_entropy(logits, tg)
+        assert err.value.code == lib.ERR_NOMEM
+        assert L.ane_cuda_workspace_bytes() == ws
+    finally:
+        lib.check(L.ane_cuda_freeze(0))
+    dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, 12345)                               # allowed again
+    loss, _ = dev.cross_entropy(logits, tg)                                    # and the scratch grows
+    assert L.ane_cuda_workspace_bytes() > ws
+    assert abs(float(loss[0]) - 0.6931472) < 1e-5                              # log 2 per token
+
+
+def test_refused_allocations_come_back_as_error_codes(dev, oracle):
+    """The allocation hook makes the next device allocations fail as if the GPU were out of memory: every entry point
+    that allocates returns ANE_CUDA_ERR_NOMEM, nothing is launched on a null pointer, and the same call works afterwards."""
+    import numpy as np
+    import torch
+    from ane_b200 import lib
+    from tests.conftest import rel_err
+    L = lib.load()
+    lib.set_tuning("fail_alloc", 1)
+    assert not L.ane_cuda_alloc(1 << 20)
+    assert b"cudaMalloc" in L.ane_cuda_last_error()
+    buf = L.ane_cuda_alloc(1 << 20)
+    assert buf
+    L.ane_cuda_free(buf)
+    # a cos/sin table that cannot be allocated
+    B, heads, hd, S, C = 1, 2, 128, 64, 256
+    q, dq, wq, x, dy, w = _inputs(torch, B, heads, hd, S, C)
+    lib.set_tuning("fail_alloc", 1)
+    with pytest.raises(lib.AneCudaError) as err:
+        dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, 4242)
+    assert err.value.code == lib.ERR_NOMEM
+    got = dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, 4242)
+    want = oracle.qknorm_rope(q.float().cpu().numpy(), wq.cpu().numpy(), hd, 1e-6, 1e6, 4242)
+    assert rel_err(got.float().cpu().numpy(), want) <= 2.0 ** -8
+    # scratch growth that fails twice (the larger and the exact request)
+    ws = L.ane_cuda_workspace_bytes()
+    lib.set_tuning("fail_alloc", 2)
+    assert L.ane_cuda_reserve_workspace(ws + (16 << 20)) == lib.ERR_NOMEM
+    assert L.ane_cuda_workspace_bytes() == ws
+    assert L.ane_cuda_reserve_workspace(ws + (16 << 20)) == lib.OK
+    # a host-pointer drop-in whose device staging cannot be allocated (a fresh library state: nothing staged yet)
+    from ane_b200 import cpu_ops
+    torch.cuda.synchronize()
+    L.ane_cuda_shutdown()
+    lib.init(0)
+    xs = np.random.default_rng(0).standard_normal((1024, 256)).astype(np.float32)
+    out = np.empty_like(xs)
+    lib.set_tuning("fail_alloc", 1)
+    try:
+        with pytest.raises(lib.AneCudaError) as err:
+            cpu_ops.rmsnorm(out, xs, np.ones(1024, np.float32), 1024, 256)
+        assert err.value.code == lib.ERR_NOMEM
+    finally:
+        lib.clear_tuning("fail_alloc")
+    cpu_ops.rmsnorm(out, xs, np.ones(1024, np.float32), 1024, 256)
+    assert rel_err(out, oracle.rmsnorm(xs, np.ones(1024, np.float32))) <= 1e-5
