@@ -417,7 +417,8 @@ __device__ __forceinline__ int eb_dest(const void *tokens, const int *count, siz
 template <typename T, int ESZ, typename ID>
 __global__ void __launch_bounds__(ER_THREADS)
 eb_stage_rows_kernel(void *__restrict__ stagev, float *__restrict__ d_embed, const void *__restrict__ dxv,
-                     const void *__restrict__ tokens, const int *__restrict__ count, int vocab, int D, int S, int tiles_per_seq) {
+                     const void *__restrict__ tokens, const int *__restrict__ count, int vocab, int D, int S, int tiles_per_seq,
+                     const int *__restrict__ seg_start, const int *__restrict__ arr_of_pos, int *__restrict__ seg_pos) {
     constexpr int TPW = ESZ == 2 ? 2 : 1;
     constexpr int TOK = ER_WC * TPW;
     __shared__ uint32_t tile[ER_DC * ER_STRIDE];
@@ -430,7 +431,10 @@ eb_stage_rows_kernel(void *__restrict__ stagev, float *__restrict__ d_embed, con
 
     if (threadIdx.x < TOK) {
         const int t = t0 + threadIdx.x;
-        dst[threadIdx.x] = t < S ? eb_dest<ID>(tokens, count, (size_t)b * S + t, vocab) : EB_SKIP;
+        const int dsel = t < S ? eb_dest<ID>(tokens, count, (size_t)b * S + t, vocab) : EB_SKIP;
+        dst[threadIdx.x] = dsel;
+        // the sort-free form: a repeated position is filed in its id's segment, at its arrival number
+        if (seg_pos && dsel >= 0 && blockIdx.y == 0) seg_pos[seg_start[load_id<ID>(tokens, (size_t)dsel)] + arr_of_pos[dsel]] = dsel;
     }
     constexpr int VPR = ER_WC / 4;                       // 16-byte vectors per tile row
     for (int item = threadIdx.x; item < dcount * VPR; item += ER_THREADS) {
@@ -574,6 +578,167 @@ eb_reduce_runs_kernel(float *__restrict__ d_embed, const void *__restrict__ stag
     }
 }
 
+// ---------------------------------------------------------------- scatter-add without a sort
+// The sort above exists only to put the positions of a repeated id into increasing order.  Repeated ids are few and
+// their runs short (uniform ids over a 152 k vocabulary: 10 k runs of 2.2 positions on average in 65 k tokens), so
+// here the order is made where it is needed instead:
+//   eb_count_arrival   count[id]++ gives every position its arrival number within its id (any order);
+//   eb_segments        every id that occurs twice or more gets a segment of count[id] slots in a position list and an
+//                      entry in the list of runs (one atomic per block, not per id);
+//   eb_stage_rows      the staging kernel above; on its way it files each repeated position in its id's segment;
+//   eb_reduce_segments a warp per (run, 256-channel piece) sorts the run's positions -- up to 32 in registers, up to 256 by
+//                      counting ranks, longer runs by walking the token array in order -- and adds the staging rows onto
+//                      the d_embed row in increasing position order: the reference's additions in the reference's order.
+constexpr int EB_INLINE_MAX = 32;      // positions of a run sorted in registers
+constexpr int EB_RANK_MAX = 256;       // longer runs: ranked by counting up to here, found by a walk over the tokens beyond
+struct EbLists {
+    int *count;        // [vocab]  occurrences per id
+    int *seg_start;    // [vocab]  first slot of an id's segment (ids with count >= 2)
+    int *arr_of_pos;   // [n]      arrival number of a position within its id
+    int *seg_pos;      // [n]      positions, grouped by id, in arrival order
+    int4 *run_info;    // [n / 2]  (id, count, first slot, 0) of every id with count >= 2
+    int *cursor;       // [0] slots handed out, [1] runs
+};
+
+template <typename ID>
+__global__ void eb_count_arrival_kernel(EbLists L, const void *__restrict__ tokens, int n, int vocab, ane_cuda_status *status) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int id = load_id<ID>(tokens, i);
+    if (id < 0 || id >= vocab) atomicAdd(&status->oor_ids, 1);
+    else L.arr_of_pos[i] = atomicAdd(&L.count[id], 1);
+}
+
+constexpr int SEG_THREADS = 1024;
+__global__ void __launch_bounds__(SEG_THREADS) eb_segments_kernel(EbLists L, int vocab) {
+    __shared__ int wsum[2][SEG_THREADS / 32];
+    __shared__ int base[2];
+    const int id = blockIdx.x * SEG_THREADS + threadIdx.x;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int c = id < vocab ? L.count[id] : 0;
+    const int slots = c >= 2 ? c : 0, isrun = c >= 2 ? 1 : 0;
+    int ps = slots, pr = isrun;                          // inclusive scans over the warp
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int a = __shfl_up_sync(0xffffffffu, ps, o), r = __shfl_up_sync(0xffffffffu, pr, o);
+        if (lane >= o) { ps += a; pr += r; }
+    }
+    if (lane == 31) { wsum[0][w] = ps; wsum[1][w] = pr; }
+    __syncthreads();
+    if (w == 0) {
+        int a = wsum[0][lane], r = wsum[1][lane];        // SEG_THREADS / 32 == 32 warps
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int a2 = __shfl_up_sync(0xffffffffu, a, o), r2 = __shfl_up_sync(0xffffffffu, r, o);
+            if (lane >= o) { a += a2; r += r2; }
+        }
+        if (lane == 31) { base[0] = a ? atomicAdd(&L.cursor[0], a) : 0; base[1] = r ? atomicAdd(&L.cursor[1], r) : 0; }
+        wsum[0][lane] = a - wsum[0][lane];               // exclusive offsets of the warps
+        wsum[1][lane] = r - wsum[1][lane];
+    }
+    __syncthreads();
+    if (isrun) {
+        L.seg_start[id] = base[0] + wsum[0][w] + ps - slots;
+        L.run_info[base[1] + wsum[1][w] + pr - 1] = make_int4(id, c, base[0] + wsum[0][w] + ps - slots, 0);
+    }
+}
+
+// cnt (<= 32) staging row pieces, lane u holding the position of the u-th, added onto acc in that order
+template <typename T, int ESZ, int NJ>
+__device__ __forceinline__ void eb_add_rows_in_order(float4 (&acc)[NJ], const char *stage, int D, int d0, int dcount, int lane,
+                                                     int mypos, int cnt) {
+    for (int u = 0; u < cnt; u += 2) {                   // two rows in flight; added in order
+        const size_t row0 = (size_t)__shfl_sync(0xffffffffu, mypos, u) * D;
+        const size_t row1 = (size_t)__shfl_sync(0xffffffffu, mypos, (u + 1) & 31) * D;
+        const bool two = u + 1 < cnt;
+        uint4 v0[NJ], v1[NJ];
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            const int d = (j * 32 + lane) * 4;
+            if (d < dcount) {
+                v0[j] = rr_load<ESZ>(stage + (row0 + d0 + d) * ESZ);
+                if (two) v1[j] = rr_load<ESZ>(stage + (row1 + d0 + d) * ESZ);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            const int d = (j * 32 + lane) * 4;
+            if (d < dcount) {
+                rr_add<T, ESZ>(acc[j], v0[j]);
+                if (two) rr_add<T, ESZ>(acc[j], v1[j]);
+            }
+        }
+    }
+}
+
+constexpr int RS_THREADS = 256, RS_J = 2, RS_CH = 128 * RS_J;     // a warp item covers RS_CH channels of a run
+#ifndef ANE_RS_MINB
+#define ANE_RS_MINB 4
+#endif
+template <typename T, int ESZ, typename ID>
+__global__ void __launch_bounds__(RS_THREADS, ANE_RS_MINB)
+eb_reduce_segments_kernel(float *__restrict__ d_embed, const void *__restrict__ stagev, const void *__restrict__ tokens, EbLists L,
+                          int n, int D) {
+    __shared__ int sorted[RS_THREADS / 32][EB_RANK_MAX];
+    const char *stage = static_cast<const char *>(stagev);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int nruns = L.cursor[1];
+    const int pieces = (D + RS_CH - 1) / RS_CH;
+    const long long nitems = (long long)nruns * pieces;
+    for (long long item = (long long)blockIdx.x * (RS_THREADS / 32) + w; item < nitems; item += (long long)gridDim.x * (RS_THREADS / 32)) {
+        const int4 info = L.run_info[item / pieces];
+        const int key = info.x, cnt = info.y, s = info.z;
+        const int d0 = (int)(item % pieces) * RS_CH;
+        const int dcount = D - d0 < RS_CH ? D - d0 : RS_CH;
+        float *erow = d_embed + (size_t)key * D + d0;
+        float4 acc[RS_J];
+#pragma unroll
+        for (int j = 0; j < RS_J; j++) {                 // the d_embed row piece: in flight while the positions are sorted
+            const int d = (j * 32 + lane) * 4;
+            if (d < dcount) acc[j] = *reinterpret_cast<const float4 *>(erow + d);
+        }
+        if (cnt <= EB_INLINE_MAX) {
+            const int mine = lane < cnt ? L.seg_pos[s + lane] : 0x7fffffff;
+            int rank = 0;
+            for (int j = 0; j < cnt; j++) rank += __shfl_sync(0xffffffffu, mine, j) < mine;
+            if (lane < cnt) sorted[w][rank] = mine;
+            __syncwarp();
+            const int mypos = lane < cnt ? sorted[w][lane] : 0;
+            __syncwarp();
+            eb_add_rows_in_order<T, ESZ, RS_J>(acc, stage, D, d0, dcount, lane, mypos, cnt);
+        } else if (cnt <= EB_RANK_MAX) {
+            for (int i = lane; i < cnt; i += 32) {
+                const int p = L.seg_pos[s + i];
+                int rank = 0;
+                for (int j = 0; j < cnt; j++) rank += L.seg_pos[s + j] < p;
+                sorted[w][rank] = p;
+            }
+            __syncwarp();
+            for (int q0 = 0; q0 < cnt; q0 += 32) {
+                const int c = cnt - q0 < 32 ? cnt - q0 : 32;
+                const int mypos = lane < c ? sorted[w][q0 + lane] : 0;
+                eb_add_rows_in_order<T, ESZ, RS_J>(acc, stage, D, d0, dcount, lane, mypos, c);
+            }
+            __syncwarp();
+        } else {
+            for (int q0 = 0; q0 < n; q0 += 32) {
+                const int idx = q0 + lane;
+                const bool same = idx < n && load_id<ID>(tokens, idx) == key;
+                const unsigned m = __ballot_sync(0xffffffffu, same);
+                if (m == 0) continue;
+                const int c = __popc(m);
+                const int mypos = lane < c ? q0 + (int)__fns(m, 0, lane + 1) : 0;
+                eb_add_rows_in_order<T, ESZ, RS_J>(acc, stage, D, d0, dcount, lane, mypos, c);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < RS_J; j++) {
+            const int d = (j * 32 + lane) * 4;
+            if (d < dcount) *reinterpret_cast<float4 *>(erow + d) = acc[j];
+        }
+    }
+}
+
 // Side stream for the sort (created on first use, destroyed at shutdown).
 struct EmbedSide { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; bool ok = false; };
 static EmbedSide g_side;
@@ -680,10 +845,55 @@ int ane_cuda_embed_backward_dev(void *stream, ane_dtype dtype, ane_idtype idtype
     const size_t esz = dtype_size(dtype);
     const bool u16 = idtype == ANE_ID_U16;
 
+    const bool tiled = tuning("embed_tiled", 1) && aligned16(dx) && aligned16(d_embed) && S % (16 / (int)esz) == 0 && D % 4 == 0;
+    const size_t ints = round_up((size_t)n * sizeof(int), 256);
+    const int pb = (n + 255) / 256;
+    if (tiled && !tuning("embed_sort", 0)) {
+        // no sort: arrival numbers -> segments and run list -> staging kernel (files the repeated positions) -> ordered adds per run
+        const size_t o_cursor = 0;                                                           // 64 ints
+        const size_t o_count = 256;
+        const size_t o_zero_end = o_count + round_up((size_t)vocab * sizeof(int), 256);      // everything up to here starts at zero
+        const size_t o_seg = o_zero_end;
+        const size_t o_arr = o_seg + round_up((size_t)vocab * sizeof(int), 256);
+        const size_t o_pos = o_arr + ints;
+        const size_t o_run = o_pos + ints;
+        const size_t o_stage2 = o_run + round_up(((size_t)n / 2 + 1) * sizeof(int4), 256);
+        const size_t total2 = o_stage2 + round_up((size_t)n * D * esz, 256);
+        char *ws2 = static_cast<char *>(workspace(total2));
+        if (!ws2) return fail(ANE_CUDA_ERR_NOMEM, "%s: no scratch (%zu bytes)", __func__, total2);
+        EbLists L;
+        L.cursor = (int *)(ws2 + o_cursor);
+        L.count = (int *)(ws2 + o_count);
+        L.seg_start = (int *)(ws2 + o_seg);
+        L.arr_of_pos = (int *)(ws2 + o_arr);
+        L.seg_pos = (int *)(ws2 + o_pos);
+        L.run_info = (int4 *)(ws2 + o_run);
+        void *stage2 = ws2 + o_stage2;
+        ANE_CUDA_TRY(cudaMemsetAsync(ws2, 0, o_zero_end, st));
+        if (u16) eb_count_arrival_kernel<uint16_t><<<pb, 256, 0, st>>>(L, tokens, n, vocab, ctx().status);
+        else eb_count_arrival_kernel<int32_t><<<pb, 256, 0, st>>>(L, tokens, n, vocab, ctx().status);
+        eb_segments_kernel<<<(vocab + SEG_THREADS - 1) / SEG_THREADS, SEG_THREADS, 0, st>>>(L, vocab);
+        const int TOKr = ER_WC * (esz == 2 ? 2 : 1);
+        const int tps = (S + TOKr - 1) / TOKr;
+        dim3 grid((unsigned)(B * tps), (unsigned)((D + ER_DC - 1) / ER_DC));
+        const int rblocks = 8 * ctx().sm_count;
+#define ANE_EB_SCATTER(Tv, ESZv, IDv)                                                                                                  \
+        do {                                                                                                                          \
+            eb_stage_rows_kernel<Tv, ESZv, IDv><<<grid, ER_THREADS, 0, st>>>(stage2, d_embed, dx, tokens, L.count, vocab, D, S, tps,  \
+                                                                             L.seg_start, L.arr_of_pos, L.seg_pos);                   \
+            eb_reduce_segments_kernel<Tv, ESZv, IDv><<<rblocks, RS_THREADS, 0, st>>>(d_embed, stage2, tokens, L, n, D);                \
+        } while (0)
+        if (dtype == ANE_F32) { if (u16) ANE_EB_SCATTER(float, 4, uint16_t); else ANE_EB_SCATTER(float, 4, int32_t); }
+        else if (dtype == ANE_BF16) { if (u16) ANE_EB_SCATTER(__nv_bfloat16, 2, uint16_t); else ANE_EB_SCATTER(__nv_bfloat16, 2, int32_t); }
+        else { if (u16) ANE_EB_SCATTER(__half, 2, uint16_t); else ANE_EB_SCATTER(__half, 2, int32_t); }
+#undef ANE_EB_SCATTER
+        ANE_LAUNCH_OK(4);
+        return ANE_CUDA_OK;
+    }
+
     size_t cub_bytes = 0;
     cub::DoubleBuffer<int> kb(nullptr, nullptr), vb(nullptr, nullptr);
     ANE_CUDA_TRY(cub::DeviceRadixSort::SortPairs(nullptr, cub_bytes, kb, vb, n, 0, sort_bits(vocab), st));
-    const size_t ints = round_up((size_t)n * sizeof(int), 256);
     const size_t off_k0 = 0, off_k1 = ints, off_v0 = 2 * ints, off_v1 = 3 * ints, off_aux = 4 * ints;   // aux: rank_of_pos or run_start
     const size_t off_cnt = 5 * ints;                                                                   // run_count, then count[vocab]
     const size_t off_cub = off_cnt + round_up(((size_t)vocab + 64) * sizeof(int), 256);
@@ -696,9 +906,7 @@ int ane_cuda_embed_backward_dev(void *stream, ane_dtype dtype, ane_idtype idtype
     void *stage = ws + off_stage;
     kb = cub::DoubleBuffer<int>(k0, k1);
     vb = cub::DoubleBuffer<int>(v0, v1);
-    const int pb = (n + 255) / 256;
 
-    const bool tiled = tuning("embed_tiled", 1) && aligned16(dx) && aligned16(d_embed) && S % (16 / (int)esz) == 0 && D % 4 == 0;
     if (tiled) {
         EmbedSide *side = embed_side();
         if (!side) return fail(ANE_CUDA_ERR_CUDA, "%s: cannot create the side stream", __func__);
@@ -721,8 +929,8 @@ int ane_cuda_embed_backward_dev(void *stream, ane_dtype dtype, ane_idtype idtype
         const int rblocks = ((n + 1) / 2 + RR_THREADS / 32 - 1) / (RR_THREADS / 32);   // a run has two positions or more
 #define ANE_EB_ROWS(Tv, ESZv)                                                                                                         \
         do {                                                                                                                          \
-            if (u16) eb_stage_rows_kernel<Tv, ESZv, uint16_t><<<grid, ER_THREADS, 0, st>>>(stage, d_embed, dx, tokens, count, vocab, D, S, tps); \
-            else eb_stage_rows_kernel<Tv, ESZv, int32_t><<<grid, ER_THREADS, 0, st>>>(stage, d_embed, dx, tokens, count, vocab, D, S, tps);      \
+            if (u16) eb_stage_rows_kernel<Tv, ESZv, uint16_t><<<grid, ER_THREADS, 0, st>>>(stage, d_embed, dx, tokens, count, vocab, D, S, tps, nullptr, nullptr, nullptr); \
+            else eb_stage_rows_kernel<Tv, ESZv, int32_t><<<grid, ER_THREADS, 0, st>>>(stage, d_embed, dx, tokens, count, vocab, D, S, tps, nullptr, nullptr, nullptr);      \
             ANE_CUDA_TRY(cudaStreamWaitEvent(st, side->join, 0));                                                                     \
             eb_reduce_runs_kernel<Tv, ESZv><<<rblocks, RR_THREADS, 0, st>>>(d_embed, stage, kb.Current(), vb.Current(), run_start, run_count, n, D); \
         } while (0)

@@ -421,10 +421,12 @@ def test_embed_lookup_out_of_range(dev, oracle):
 
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
 @pytest.mark.parametrize("B,D,S,V,dup", [(1, 768, 256, 32000, 10), (2, 1024, 64, 151936, 0), (3, 5, 7, 11, 0),
-                                         (2, 96, 130, 50, 0), (1, 64, 300, 1000, 300)])
+                                         (2, 96, 130, 50, 0), (1, 64, 300, 1000, 300), (2, 256, 512, 5000, 100), (3, 1024, 256, 400, 40),
+                                         (2, 1536, 64, 30, 0)])
 def test_embed_backward_bit_exact_and_deterministic(dev, oracle, B, D, S, V, dup, dt):
     """fp32 additions happen in the reference's order (increasing (b, t) per row), so the result
-    equals the sequential CPU sum bit for bit."""
+    equals the sequential CPU sum bit for bit.  The cases cover every way a run's positions get ordered: runs of
+    2-32 positions (sorted in registers), up to 256 (ranked by counting), beyond (a walk over the token array)."""
     torch = _torch()
     r = gi.rng(63)
     tok = r.integers(0, V, size=(B, S)).astype(np.int32)
@@ -442,6 +444,29 @@ def test_embed_backward_bit_exact_and_deterministic(dev, oracle, B, D, S, V, dup
         outs.append(dE)
     assert torch.equal(outs[0], outs[1])
     assert np.array_equal(down(outs[0]), want)
+
+
+@pytest.mark.parametrize("sorted_path", [0, 1])
+def test_embed_backward_skewed_ids(dev, oracle, sorted_path):
+    """Ids drawn from a heavy-tailed distribution (a few ids take thousands of positions, most occur once or never), as
+    token streams of real text are: still the sequential sum, bit for bit, through both forms of the scatter-add."""
+    torch = _torch()
+    from ane_b200 import lib
+    r = gi.rng(65)
+    B, D, S, V = 8, 512, 1024, 20000
+    tok = np.minimum((r.pareto(0.9, size=(B, S)) * 3).astype(np.int64), V - 1).astype(np.int32)
+    assert np.bincount(tok.reshape(-1)).max() > 300
+    dx = gi.normal(r, (B, D, S))
+    dE0 = gi.normal(r, (V, D), 0.01)
+    dxd, dxr = up(dx, "bf16")
+    want, _ = oracle.embed_backward(dE0, dxr, tok)
+    lib.set_tuning("embed_sort", sorted_path)
+    try:
+        dE = torch.from_numpy(dE0).cuda()
+        dev.embed_backward(dE, dxd, torch.from_numpy(tok).cuda())
+        assert np.array_equal(down(dE), want)
+    finally:
+        lib.clear_tuning("embed_sort")
 
 
 def test_embed_backward_skips_out_of_range(dev, oracle):
@@ -839,7 +864,7 @@ ALT_KNOBS = [
     ("norm_fwd", 0), ("norm_fwd", 2), ("norm_fwd", 3), ("norm_fwd", 4), ("norm_fwd", 6),
     ("norm_bwd", 0), ("norm_bwd", 8), ("norm_bwd", 9), ("norm_bwd", 10),
     ("qk_fwd", 0), ("qk_fwd", 1), ("qk_fwd", 4), ("qk_bwd", 0), ("qk_bwd", 4),
-    ("rope_lg", 8), ("embed_tiled", 0), ("embed_rows", 0), ("xent_cluster", 1), ("xent_lg", 4), ("xent_lg", 8), ("xent_lg", 32), ("xent_split", 1), ("xent_split", 2), ("xent_split", 8),
+    ("rope_lg", 8), ("rope_table", 0), ("embed_tiled", 0), ("embed_rows", 0), ("embed_sort", 1), ("xent_cluster", 1), ("xent_lg", 4), ("xent_lg", 8), ("xent_lg", 32), ("xent_split", 1), ("xent_split", 2), ("xent_split", 8),
 ]
 
 
