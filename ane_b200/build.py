@@ -73,7 +73,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     objs = [os.path.join(OBJ, os.path.basename(s)[:-3] + ".o") for s in srcs]
     if todo or _stale(LIB, objs):
         # hidden visibility + explicit export of the C ABI
-        cmd = [_nvcc(), *ARCH, "-shared", "-o", LIB, *objs, "-Xlinker", "--no-undefined"]
+        cmd = [_nvcc(), *ARCH, "-shared", "-o", LIB, *objs, "-ldl", "-Xlinker", "--no-undefined"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

@@ -225,6 +225,7 @@ void ane_cuda_shutdown(void) {
     Context &c = g_ctx;
     if (!c.inited) return;
     cudaDeviceSynchronize();
+    ane_cuda_comm_destroy();
     pipe_destroy();
     rope_tables_release();
     embed_side_release();

@@ -126,6 +126,17 @@ PROTOTYPES = {
     # optimizer step over peer memory
     "ane_cuda_p2p_reduce_dev": (_i, [_vp, _i, _vp, _sz, _sz, _vp, _f, _vp, _vp]),
     "ane_cuda_p2p_adam_dev": (_i, [_vp, _i, _i, _vp, _sz, _sz, _vp, _vp, _vp, _i, _f, _f, _f, _f, _f, _f, _vp, _u]),
+    # multi-GPU group
+    "ane_cuda_comm_unique_id": (_i, [_vp]),
+    "ane_cuda_comm_init": (_i, [_i, _i, _vp, C.c_double]),
+    "ane_cuda_comm_size": (_i, []),
+    "ane_cuda_comm_rank": (_i, []),
+    "ane_cuda_comm_destroy": (_i, []),
+    "ane_cuda_comm_wait": (_i, [_vp, C.c_double]),
+    "ane_cuda_allreduce_f32": (_i, [_vp, _vp, _sz]),
+    "ane_cuda_comm_map_peers": (_i, [_vp, _vp, _sz]),
+    "ane_cuda_comm_unmap_peers": (_i, []),
+    "ane_cuda_sharded_adam_step": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _i, _f, _f, _f, _f, _f, _f, _f, _u, _vp]),
     # checkpoints
     "ane_cuda_ckpt_read_header": (_i, [C.c_char_p, _vp]),
     "ane_cuda_ckpt_param_count": (_sz, [_vp]),

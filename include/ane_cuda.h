@@ -345,6 +345,42 @@ int ane_cuda_p2p_adam_dev(void *stream, int nranks, int self, float *const *w_ra
                           float *m_slice, float *v_slice, int t, float lr, float b1, float b2, float eps, float wd, float gscale,
                           const float *clip_dev, unsigned flags);
 
+/* ---- the multi-GPU group: one process per GPU, NCCL (loaded at run time) as the transport -----------------------
+ * The reference is a single-process program; its optimizer step is the scale / norm / clip of
+ * training_dynamic/train.m:750-825 followed by the per-tensor Adam loop of :837-869.  Style of these calls:
+ * bridge/ane_bridge.h:20-68 (int status, explicit create / destroy).
+ *   unique_id  rank 0 makes the 128-byte id and hands it to the other ranks by any means (a file, MPI, a socket).
+ *   init       joins the group on the CURRENT device (after ane_cuda_init).  timeout_s bounds this call and becomes the
+ *              default for the waits below; a rank that never joins ends it with ANE_CUDA_ERR_TIMEOUT, and the
+ *              half-made communicator is aborted.
+ *   allreduce  sum over the ranks, in place, on the stream (the scalar loss of a data-parallel step).
+ *   wait       host-side wait for the stream with a deadline (timeout_s < 0: the default): polls the stream and the
+ *              communicator; on a timeout or a communicator error the communicator is ABORTED (so that a collective
+ *              kernel waiting for a missing rank ends) and an error code is returned.  The group must then be rebuilt.
+ *   map_peers  optional, collective, blocking: exchanges CUDA IPC handles of the flat parameter and gradient buffers
+ *              so that the sharded step below runs on this library's peer-memory kernels instead of NCCL's
+ *              reduce-scatter / all-gather.  ANE_CUDA_ERR_UNSUPPORTED where the ranks cannot map each other.
+ *   sharded_adam_step   the whole optimizer step over flat fp32 buffers of n_padded floats (a multiple of the rank
+ *              count): reduce-scatter of g, squared norm of (g * gscale), one clip factor for all ranks
+ *              (clip <= 0: none), Adam on this rank's slice with weight decay on [0, n_decay) and none on
+ *              [n_decay, n_params), all-gather of w.  Asynchronous on the stream; normsq_out (device, may be NULL)
+ *              receives the squared norm.  Every rank must call it with the same arguments.  With one rank it is
+ *              the plain local step. */
+#define ANE_CUDA_COMM_ID_BYTES 128
+#define ANE_CUDA_MAX_RANKS 8
+int ane_cuda_comm_unique_id(void *id_out);
+int ane_cuda_comm_init(int nranks, int rank, const void *id, double timeout_s);
+int ane_cuda_comm_size(void);
+int ane_cuda_comm_rank(void);
+int ane_cuda_comm_destroy(void);
+int ane_cuda_comm_wait(void *stream, double timeout_s);
+int ane_cuda_allreduce_f32(void *stream, float *buf, size_t n);
+int ane_cuda_comm_map_peers(float *w, float *g, size_t n_floats);
+int ane_cuda_comm_unmap_peers(void);
+int ane_cuda_sharded_adam_step(void *stream, float *w, float *g, float *m, float *v, size_t n_padded, size_t n_decay,
+                               size_t n_params, int t, float lr, float b1, float b2, float eps, float wd, float gscale,
+                               float clip, unsigned flags, float *normsq_out);
+
 /* ---- checkpoints of the reference's training loops ("BLZT" files) ------------------------------------
  * Header as written by save_checkpoint: version 2 (training/stories_config.h:95-104, train_large.m:109-145;
  * the last three ints are padding) and version 4 (training_dynamic/config.h:78-86, train.m:104-138). */
