@@ -137,3 +137,69 @@ class HostLayerChain:
     def synchronize(self):
         for s in (self.s_in, self.s_c, self.s_out):
             s.synchronize()
+
+
+class CHostLayerChain:
+    """The same step through the C ABI's chain object (ane_cuda_chain_create / _step / _sync, csrc/chain.cu): what a C
+    caller of the library uses.  Host buffers, tokens and parameters are taken from a HostLayerChain `like` (same bytes
+    in, so the same bytes must come out); only the device buffers, streams and the launch sequence are the library's."""
+
+    def __init__(self, like: HostLayerChain, params: FlatParams):
+        import ctypes as C
+
+        from . import lib as _l
+
+        self._l, self._C = _l, C
+        c = like.cfg
+        self.cfg, self.B, self.like = c, like.B, like
+        L = c.layers
+
+        class Config(C.Structure):
+            _fields_ = [(n, C.c_int) for n in ("layers", "dim", "hidden", "heads", "kv_heads", "head_dim", "seq", "vocab", "dtype")] + \
+                       [(n, C.c_float) for n in ("alpha", "eps", "qk_eps", "rope_base")] + [("norm_bwd_flags", C.c_uint), ("rotate", C.c_int)]
+
+        class Params(C.Structure):
+            _fields_ = [(n, C.c_void_p) for n in ("att_w", "ffn_w", "final_w", "q_w", "k_w", "att_g", "ffn_g", "final_g", "q_g", "k_g",
+                                                  "table", "embed_g")]
+
+        io_names = ("q", "k", "o_out", "h1", "h3", "ffn_out", "xnorm", "q_r", "k_r", "x2norm", "gate", "dsilu", "dx_ffn", "dq_in", "dk_in",
+                    "dx_attn", "dh1", "dh3", "dq", "dk")
+
+        class HostIO(C.Structure):
+            _fields_ = [(n, C.POINTER(C.c_void_p)) for n in io_names] + [("dy_cls", C.c_void_p), ("x_final", C.c_void_p), ("tokens", C.c_void_p)]
+
+        dt = {torch.float32: _l.F32, torch.bfloat16: _l.BF16, torch.float16: _l.F16}[c.dtype]
+        cfg = Config(c.layers, c.dim, c.hidden, c.heads, c.kv_heads, c.head_dim, c.seq, c.vocab, dt, c.alpha, c.eps, c.qk_eps, c.rope_base,
+                     _l.NORM_BWD_EXACT if c.exact_norm_bwd else _l.NORM_BWD_REFERENCE, like.chain.R)
+        p = params
+        ptr = lambda which, grad: p.norm_w(which, 0, grad=grad).data_ptr()
+        par = Params(ptr("att", False), ptr("ffn", False), ptr("final", False), ptr("q", False), ptr("k", False),
+                     ptr("att", True), ptr("ffn", True), ptr("final", True), ptr("q", True), ptr("k", True),
+                     like.chain.table.data_ptr(), p.embed(grad=True).data_ptr())
+        self._keep = (cfg, par)
+        self.handle = _l.load().ane_cuda_chain_create(C.byref(cfg), like.B, C.byref(par))
+        if not self.handle:
+            raise _l.AneCudaError(-1, _l.load().ane_cuda_last_error().decode())
+        hosts = {**like.h_in_f, **like.h_out_f, **like.h_in_b, **like.h_out_b}
+        self._tables = {n: (C.c_void_p * L)(*([hosts[n].data_ptr()] * L)) for n in io_names}        # one host buffer per kind, all layers
+        self.io = HostIO(*[C.cast(self._tables[n], C.POINTER(C.c_void_p)) for n in io_names], like.h_dy_cls.data_ptr(),
+                         like.h_x_final.data_ptr(), like.h_tokens.data_ptr())
+        self.h2d_bytes_per_step = int(_l.load().ane_cuda_chain_h2d_bytes(self.handle))
+        self.d2h_bytes_per_step = int(_l.load().ane_cuda_chain_d2h_bytes(self.handle))
+
+    def step(self):
+        self._l.check(self._l.load().ane_cuda_chain_step(self.handle, self._C.byref(self.io)))
+
+    def synchronize(self):
+        self._l.check(self._l.load().ane_cuda_chain_sync(self.handle))
+
+    def close(self):
+        if self.handle:
+            self._l.load().ane_cuda_chain_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -126,6 +126,14 @@ PROTOTYPES = {
     # optimizer step over peer memory
     "ane_cuda_p2p_reduce_dev": (_i, [_vp, _i, _vp, _sz, _sz, _vp, _f, _vp, _vp]),
     "ane_cuda_p2p_adam_dev": (_i, [_vp, _i, _i, _vp, _sz, _sz, _vp, _vp, _vp, _i, _f, _f, _f, _f, _f, _f, _vp, _u]),
+    # operator chain with host buffers
+    "ane_cuda_chain_create": (_vp, [_vp, _i, _vp]),
+    "ane_cuda_chain_step": (_i, [_vp, _vp]),
+    "ane_cuda_chain_sync": (_i, [_vp]),
+    "ane_cuda_chain_compute_stream": (_vp, [_vp]),
+    "ane_cuda_chain_h2d_bytes": (_sz, [_vp]),
+    "ane_cuda_chain_d2h_bytes": (_sz, [_vp]),
+    "ane_cuda_chain_destroy": (None, [_vp]),
     # multi-GPU group
     "ane_cuda_comm_unique_id": (_i, [_vp]),
     "ane_cuda_comm_init": (_i, [_i, _i, _vp, C.c_double]),

@@ -263,20 +263,30 @@ def workload_config(args, world):
 def e2e_chain(torch, cfg, params, device, n_seqs, steps, warmup):
     """The chain with host buffers on the contraction side (ane_b200.host_chain.HostLayerChain): every tensor a matmul
     or SDPA produces or consumes crosses PCIe inside the timed region, from / to page-locked host memory."""
-    from ane_b200.host_chain import HostLayerChain
+    from ane_b200.host_chain import CHostLayerChain, HostLayerChain
+
+    def timed(chain):
+        for _ in range(warmup):
+            chain.step()
+        chain.synchronize()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            chain.step()
+        chain.synchronize()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / steps
 
     hc = HostLayerChain(cfg, n_seqs, params, device)
-    for _ in range(warmup):
-        hc.step()
-    hc.synchronize()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        hc.step()
-    hc.synchronize()
-    torch.cuda.synchronize()
-    dt = (time.perf_counter() - t0) / steps
-    return n_seqs * cfg.seq / dt, hc.h2d_bytes_per_step, hc.d2h_bytes_per_step, dt
+    dt_py = timed(hc)
+    # the headline: the same step through the C ABI's chain object (ane_cuda_chain_step), from the same host buffers
+    del hc.chain.q, hc.chain.k, hc.chain.h1, hc.chain.h3, hc.chain.o_out, hc.chain.ffn_out, hc.chain.layer_in, hc.chain.x2
+    torch.cuda.empty_cache()
+    cc = CHostLayerChain(hc, params)
+    dt = timed(cc)
+    h2d, d2h = cc.h2d_bytes_per_step, cc.d2h_bytes_per_step
+    cc.close()
+    return n_seqs * cfg.seq / dt, h2d, d2h, dt, n_seqs * cfg.seq / dt_py
 
 
 def e2e_per_op(torch, cfg, n_seqs, steps, warmup):
@@ -582,14 +592,16 @@ def run_ours(args):
 
     if not args.no_e2e:
         e2e_seqs = args.e2e_seqs
-        tps, h2d, d2h, dt = e2e_chain(torch, cfg, params, device, e2e_seqs, steps=2, warmup=1)
-        t = torch.tensor([tps], device=device)
+        tps, h2d, d2h, dt, tps_py = e2e_chain(torch, cfg, params, device, e2e_seqs, steps=2, warmup=1)
+        t = torch.tensor([tps, tps_py], device=device)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.SUM)
         line["e2e"] = {"value": round(float(t[0]), 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                       "note": f"HostLayerChain.step(): {e2e_seqs} sequences x 2048 tokens per rank and step ({dt*1e3:.0f} ms); every "
-                               "contraction-side tensor of every layer is copied from / to page-locked host memory inside the timed "
-                               f"region ({(h2d + d2h) / dt / 1e9:.1f} GB/s over PCIe, both directions); PCIe-bound"}
+                       "python_chain_value": round(float(t[1]), 1),
+                       "note": f"ane_cuda_chain_step (the C ABI's chain object): {e2e_seqs} sequences x 2048 tokens per rank and step "
+                               f"({dt*1e3:.0f} ms); every contraction-side tensor of every layer is copied from / to page-locked host "
+                               f"memory inside the timed region ({(h2d + d2h) / dt / 1e9:.1f} GB/s over PCIe, both directions); "
+                               "PCIe-bound.  python_chain_value: the same step driven by ane_b200.host_chain.HostLayerChain over torch streams"}
         torch.cuda.empty_cache()
         if rank == 0 and world == 1 and not args.no_ops:
             tps2, h2d2, d2h2, dt2 = e2e_per_op(torch, cfg, 4, steps=1, warmup=1)

@@ -345,6 +345,52 @@ int ane_cuda_p2p_adam_dev(void *stream, int nranks, int self, float *const *w_ra
                           float *m_slice, float *v_slice, int t, float lr, float b1, float b2, float eps, float wd, float gscale,
                           const float *clip_dev, unsigned flags);
 
+/* ---- the operator chain of one micro-batch with host buffers on the contraction side ---------------------------
+ * The arrangement of the reference's loop (training_dynamic/train.m:428-482 forward, :527-720 backward): the
+ * contractions run elsewhere and hand their results over in HOST memory, the operators between them run here.
+ * One ane_cuda_chain_step uploads, per layer, what the contractions produced (q, k, attention output, h1, h3, FFN
+ * output; dsilu, dx_ffn, dq, dk, dx_attn), runs the operators in the reference's order and downloads what the next
+ * contraction consumes (xnorm, rotated q and k, x2norm, gate; dh1, dh3, dq, dk), on three streams so that copies
+ * and operators of neighbouring layers overlap -- which one blocking ane_cuda_*_host call per operator cannot do.
+ * The residual stream, x2 and the running gradient stay on the device; the norm-weight and embedding gradients
+ * are accumulated into the caller's device buffers.  Page-locked host buffers (ane_cuda_host_alloc) are needed
+ * for the overlap.  All tensors are [n_seqs][channels][seq] of `dtype`; every table below holds `layers` pointers
+ * (the same pointer may be given for several layers). */
+typedef struct {
+    int layers, dim, hidden, heads, kv_heads, head_dim, seq, vocab;
+    ane_dtype dtype;
+    float alpha, eps, qk_eps, rope_base;
+    unsigned norm_bwd_flags;         /* ANE_NORM_BWD_REFERENCE or ANE_NORM_BWD_EXACT */
+    int rotate;                      /* device buffer sets the contraction-side tensors rotate through (>= 1; 4 is a good value) */
+} ane_chain_config;
+typedef struct {                     /* device pointers the caller owns */
+    const float *att_w, *ffn_w;      /* [layers][dim] */
+    const float *final_w;            /* [dim] */
+    const float *q_w, *k_w;          /* [layers][head_dim] */
+    float *att_g, *ffn_g, *final_g, *q_g, *k_g;   /* gradients of the above, accumulated into */
+    const void *table;               /* [vocab][dim] of dtype */
+    float *embed_g;                  /* [vocab][dim] fp32, accumulated into */
+} ane_chain_params;
+typedef struct {
+    const void *const *q, *const *k, *const *o_out, *const *h1, *const *h3, *const *ffn_out;     /* forward, host -> device */
+    void *const *xnorm, *const *q_r, *const *k_r, *const *x2norm, *const *gate;                  /* forward, device -> host */
+    const void *const *dsilu, *const *dx_ffn, *const *dq_in, *const *dk_in, *const *dx_attn;     /* backward, host -> device */
+    void *const *dh1, *const *dh3, *const *dq, *const *dk;                                       /* backward, device -> host */
+    const void *dy_cls;              /* [n_seqs][dim][seq]: gradient entering the final norm */
+    void *x_final;                   /* [n_seqs][dim][seq]: output of the final norm */
+    const int32_t *tokens;           /* [n_seqs][seq] */
+} ane_chain_host_io;
+typedef struct ANECudaChain ANECudaChain;
+ANECudaChain *ane_cuda_chain_create(const ane_chain_config *cfg, int n_seqs, const ane_chain_params *params);   /* NULL on failure */
+/* Enqueues one forward + backward pass; returns before the work is done.  The host buffers must stay valid and
+ * unchanged until ane_cuda_chain_sync (or the next step's completion). */
+int ane_cuda_chain_step(ANECudaChain *chain, const ane_chain_host_io *io);
+int ane_cuda_chain_sync(ANECudaChain *chain);
+void *ane_cuda_chain_compute_stream(ANECudaChain *chain);       /* the stream the operators run on (to order an optimizer step after it) */
+size_t ane_cuda_chain_h2d_bytes(const ANECudaChain *chain);     /* bytes one step copies host -> device */
+size_t ane_cuda_chain_d2h_bytes(const ANECudaChain *chain);     /* and device -> host */
+void ane_cuda_chain_destroy(ANECudaChain *chain);
+
 /* ---- the multi-GPU group: one process per GPU, NCCL (loaded at run time) as the transport -----------------------
  * The reference is a single-process program; its optimizer step is the scale / norm / clip of
  * training_dynamic/train.m:750-825 followed by the per-tensor Adam loop of :837-869.  Style of these calls:

@@ -858,6 +858,46 @@ def test_host_layer_chain_equals_device_chain(dev):
     assert hc.h2d_bytes_per_step == 2 * 32 * 2 * (5 * (128 + 64 + 64 + 192 + 64 + 96 + 64 + 128 + 64 + 64) + 64) + 2 * 32 * 4
 
 
+def test_c_chain_object_equals_python_host_chain(dev):
+    """ane_cuda_chain_step (the chain object a C caller uses, csrc/chain.cu) hands back the same bytes as
+    HostLayerChain.step() from the same host buffers: every downloaded tensor and every accumulated gradient, over two
+    consecutive steps; a null host table is an argument error."""
+    torch = _torch()
+    import ctypes as C
+    from ane_b200 import lib
+    from ane_b200.host_chain import CHostLayerChain, HostLayerChain
+    from ane_b200.layer_chain import ChainConfig, FlatParams
+    cfg = ChainConfig(layers=6, dim=64, hidden=96, heads=2, kv_heads=1, head_dim=64, seq=64, vocab=50,
+                      dtype=torch.bfloat16, alpha=0.5, rope_base=1e4)
+    p = FlatParams(cfg, "cuda")
+    p.init_random(seed=3)
+    hc = HostLayerChain(cfg, 3, p, "cuda", rotate=2)
+    cc = CHostLayerChain(hc, p)
+    outs = {**hc.h_out_f, **hc.h_out_b, "x_final": hc.h_x_final}
+    assert cc.h2d_bytes_per_step == hc.h2d_bytes_per_step and cc.d2h_bytes_per_step == hc.d2h_bytes_per_step
+    for _ in range(2):
+        p.zero_produced_grads()
+        hc.step()
+        hc.synchronize()
+        torch.cuda.synchronize()
+        want = {k: v.clone() for k, v in outs.items()}
+        want_g = p.g.clone()
+        for v in outs.values():
+            v.zero_()
+        p.zero_produced_grads()
+        torch.cuda.synchronize()
+        cc.step()
+        cc.synchronize()
+        torch.cuda.synchronize()
+        for k, v in outs.items():
+            assert torch.equal(v, want[k]), k
+        assert torch.equal(p.g, want_g)
+    bad = type(cc.io).from_buffer_copy(cc.io)
+    bad.gate = C.POINTER(C.c_void_p)()
+    assert lib.load().ane_cuda_chain_step(cc.handle, C.byref(bad)) == lib.ERR_INVALID
+    cc.close()
+
+
 # Every operator picks one kernel by default; the others stay reachable through tuning knobs (library function
 # ane_cuda_set_tuning).  Each alternate path must give the same results within the same tolerances.
 ALT_KNOBS = [
