@@ -453,7 +453,7 @@ template <typename T, int RPT, bool ROPE, int NST, bool TILED = false>
 __global__ void __launch_bounds__(QK_THREADS)
 qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap, const float *__restrict__ w, int heads,
                   int S, int tiles_per_seq, int ntiles, float eps, ane_cuda_status *status,
-                  const float *__restrict__ cosT, const float *__restrict__ sinT, int out_ratio) {
+                  const float *__restrict__ cosT, const float *__restrict__ sinT, int out_ratio, RingTest test) {
     constexpr int VEC = Elt<T>::VEC;
     constexpr int TW = QK_LG * VEC;
     constexpr int HD = RPT * QK_R;
@@ -486,12 +486,21 @@ qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap,
     int ptl, ph, ctl, ch;                // producer (thread 0) and consumer positions
     im.first(ctl, ch);
     im.first(ptl, ph);
+    int issued = 0;                      // thread 0: items whose copies have been started
     auto issue = [&](int j) {
         const int tl = ptl;
         const int s = j % NST;
         mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-        tma_load_3d(stages + (size_t)s * STAGE_BYTES, &xmap, (tl % tiles_per_seq) * TW, ph * HD, tl / tiles_per_seq, &full[s]);
+        if (j != test.skip_item)
+            tma_load_3d(stages + (size_t)s * STAGE_BYTES, &xmap, (tl % tiles_per_seq) * TW, ph * HD, tl / tiles_per_seq, &full[s]);
         im.next(j + 1, ptl, ph);
+        issued = j + 1;
+    };
+    // After a give-up nothing may still be in flight into this block's shared memory when it exits: thread 0 waits
+    // (bounded) for every later item whose copy was started.
+    auto drain = [&](int j) {
+        for (int jj = j + 1; jj < issued; jj++)
+            if (jj != test.skip_item) mbar_wait_bounded(&full[jj % NST], (uint32_t)(jj / NST) & 1u, test.wait_limit);
     };
     if (threadIdx.x == 0)
         for (int j = 0; j < NST && j < n_items; j++) issue(j);
@@ -515,7 +524,7 @@ qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap,
                 sn[p] = table_lanes<VEC>(sinT + (size_t)(rg * (RPT / 2) + p) * S + t);
             }
         }
-        if (!mbar_wait_bounded(&full[s], (uint32_t)(j / NST) & 1u)) give_up = 1;
+        if (!mbar_wait_bounded(&full[s], (uint32_t)(j / NST) & 1u, test.wait_limit)) atomicExch(&give_up, 1);
         const T *tile = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES);
         Raw<T, VEC> r[RPT];
         V<VEC> ss = V<VEC>::splat(0.0f);
@@ -527,8 +536,8 @@ qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap,
         }
         lanes_to_smem<VEC>(&red[buf][rg][lg * VEC], ss);
         __syncthreads();                                   // every thread has its part of stage s in registers
-        if (give_up) {
-            if (threadIdx.x == 0) atomicAdd(&status->wait_giveups, 1);
+        if (*(volatile int *)&give_up) {
+            if (threadIdx.x == 0) { atomicAdd(&status->wait_giveups, 1); drain(j); }
             return;
         }
         if (threadIdx.x == 0 && j + NST < n_items) { fence_proxy_async(); issue(j + NST); }
@@ -577,7 +586,7 @@ __global__ void __launch_bounds__(QK_THREADS, 2)
 qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_constant__ CUtensorMap dymap,
                   const __grid_constant__ CUtensorMap xmap, const float *__restrict__ w, int heads, int S, int tiles_per_seq,
                   int ntiles, float eps, unsigned flags, ane_cuda_status *status,
-                  const float *__restrict__ cosT, const float *__restrict__ sinT) {
+                  const float *__restrict__ cosT, const float *__restrict__ sinT, RingTest test) {
     constexpr int VEC = Elt<T>::VEC;
     constexpr int TW = QK_LG * VEC;
     constexpr int HD = RPT * QK_R;
@@ -613,16 +622,26 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
     int ptl, ph, ctl, ch;                // producer (thread 0) and consumer positions
     im.first(ctl, ch);
     im.first(ptl, ph);
+    int issued = 0;                      // thread 0: items whose copies have been started
     auto issue = [&](int j) {
         const int tl = ptl;
         const int s = j % NST;
         unsigned char *dst = stages + (size_t)s * STAGE_BYTES;
         mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-        tma_load_3d(dst, &xmap, (tl % tiles_per_seq) * TW, ph * HD, tl / tiles_per_seq, &full[s]);
+        if (j != test.skip_item) {
+            tma_load_3d(dst, &xmap, (tl % tiles_per_seq) * TW, ph * HD, tl / tiles_per_seq, &full[s]);
 #pragma unroll
-        for (int r = 0; r < GQ; r++)
-            tma_load_3d(dst + (1 + r) * TILE_BYTES, &dymap, (tl % tiles_per_seq) * TW, (ph * GQ + r) * HD, tl / tiles_per_seq, &full[s]);
+            for (int r = 0; r < GQ; r++)
+                tma_load_3d(dst + (1 + r) * TILE_BYTES, &dymap, (tl % tiles_per_seq) * TW, (ph * GQ + r) * HD, tl / tiles_per_seq, &full[s]);
+        }
         im.next(j + 1, ptl, ph);
+        issued = j + 1;
+    };
+    // After a give-up nothing may still be in flight into this block's shared memory when it exits: thread 0 waits
+    // (bounded) for every later item whose copies were started.
+    auto drain = [&](int j) {
+        for (int jj = j + 1; jj < issued; jj++)
+            if (jj != test.skip_item) mbar_wait_bounded(&full[jj % NST], (uint32_t)(jj / NST) & 1u, test.wait_limit);
     };
     if (threadIdx.x == 0)
         for (int j = 0; j < NST && j < n_items; j++) issue(j);
@@ -646,7 +665,7 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
                 sn[p] = table_lanes<VEC>(sinT + (size_t)(rg * (RPT / 2) + p) * S + t);
             }
         }
-        if (!mbar_wait_bounded(&full[s], (uint32_t)(j / NST) & 1u)) give_up = 1;
+        if (!mbar_wait_bounded(&full[s], (uint32_t)(j / NST) & 1u, test.wait_limit)) atomicExch(&give_up, 1);
         const T *xt = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES);
         T *dt = reinterpret_cast<T *>(stages + (size_t)s * STAGE_BYTES + TILE_BYTES);
         if (GQ > 1) {       // head sum into the first dy tile; a thread only ever touches its own entries of the tiles
@@ -702,8 +721,8 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
             lanes_to_smem<VEC>(&red[buf][1][threadIdx.x >> 5][lg * VEC], dot);
         }
         __syncthreads();                                   // every thread has left sweep 2 of item j-1
-        if (give_up) {
-            if (threadIdx.x == 0) atomicAdd(&status->wait_giveups, 1);
+        if (*(volatile int *)&give_up) {
+            if (threadIdx.x == 0) { atomicAdd(&status->wait_giveups, 1); drain(j); }
             break;
         }
         if (threadIdx.x == 0 && j >= 1 && j - 1 + NST < n_items) { fence_proxy_async(); issue(j - 1 + NST); }   // refill the stage of item j-1
@@ -882,6 +901,14 @@ static int launch_qk_rope_bwd_generic(cudaStream_t st, int B, int heads, int hd,
     return ANE_CUDA_OK;
 }
 
+static RingTest ring_test() {
+    RingTest t;
+    t.skip_item = tuning("qk_test_skip_item", -1);
+    const int lim = tuning("qk_wait_limit", 0);
+    t.wait_limit = lim > 0 ? (uint32_t)lim : MBAR_WAIT_LIMIT;
+    return t;
+}
+
 // RoPE^-1 + QK-norm backward with the grouped-query head sum folded in (two-stage ring: a stage holds the x tile and
 // `ratio` dy tiles).
 template <typename T>
@@ -911,7 +938,7 @@ static int launch_qk_bwd_gqa(cudaStream_t st, int B, int heads, int ratio, int h
         if (grid > ntiles) grid = ntiles;                                                                            \
         partial = static_cast<float *>(workspace((size_t)grid * hd * sizeof(float)));                                \
         if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rope_qknorm_bwd_gqa: no scratch");                            \
-        k<<<grid, QK_THREADS, smem, st>>>((T *)dx, partial, dymap, xmap, w, heads, S, tps, ntiles, eps, flags, ctx().status, cosT, sinT); \
+        k<<<grid, QK_THREADS, smem, st>>>((T *)dx, partial, dymap, xmap, w, heads, S, tps, ntiles, eps, flags, ctx().status, cosT, sinT, ring_test()); \
     } while (0)
     if (hd == 128) { if (ratio == 2) ANE_QKB_GQA(4, 2); else ANE_QKB_GQA(4, 4); }
     else { if (ratio == 2) ANE_QKB_GQA(2, 2); else ANE_QKB_GQA(2, 4); }
@@ -1006,7 +1033,7 @@ static int launch_qk_fwd(cudaStream_t st, int B, int heads, int hd, int S, void 
             if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, QK_THREADS, smem) != cudaSuccess || per_sm < 1) per_sm = 1; \
             int g = per_sm * ctx().sm_count;                                                                         \
             if (g > ntiles) g = ntiles;                                                                              \
-            k<<<g, QK_THREADS, smem, st>>>((T *)out, xmap, w, heads, S, tps, ntiles, eps, ctx().status, cosT, sinT, out_ratio); \
+            k<<<g, QK_THREADS, smem, st>>>((T *)out, xmap, w, heads, S, tps, ntiles, eps, ctx().status, cosT, sinT, out_ratio, ring_test()); \
         } while (0)
         if (hd == 128) { if (hb == 3) ANE_QKF_TMA(4, 3); else if (hb == 4) ANE_QKF_TMA(4, 4); else ANE_QKF_TMA(4, 6); }
         else { if (hb == 3) ANE_QKF_TMA(2, 3); else if (hb == 4) ANE_QKF_TMA(2, 4); else ANE_QKF_TMA(2, 6); }
@@ -1054,7 +1081,7 @@ static int launch_qk_bwd(cudaStream_t st, int B, int heads, int hd, int S, void 
             if (grid > ntiles) grid = ntiles;                                                                        \
             partial = static_cast<float *>(workspace((size_t)grid * hd * sizeof(float)));                            \
             if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "qknorm_bwd: no scratch");                                 \
-            k<<<grid, QK_THREADS, smem, st>>>((T *)dx, partial, dymap, xmap, w, heads, S, tps, ntiles, eps, flags, ctx().status, cosT, sinT); \
+            k<<<grid, QK_THREADS, smem, st>>>((T *)dx, partial, dymap, xmap, w, heads, S, tps, ntiles, eps, flags, ctx().status, cosT, sinT, ring_test()); \
         } while (0)
         if (hd == 128) { if (hb == 3) ANE_QKB_TMA(4, 3); else ANE_QKB_TMA(4, 4); }
         else { if (hb == 3) ANE_QKB_TMA(2, 3); else ANE_QKB_TMA(2, 4); }

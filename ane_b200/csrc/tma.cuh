@@ -53,8 +53,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // limit below is far beyond any legitimate copy latency (several milliseconds at least) and still
 // finite.  Returns false when it gave up.
 constexpr uint32_t MBAR_WAIT_LIMIT = 1u << 20;
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
-    for (uint32_t i = 0; i < MBAR_WAIT_LIMIT; i++)
+// Test hook of the ring kernels (tuning knobs "qk_test_skip_item", "qk_wait_limit"): the producer arms the barrier of
+// one work item but issues no copy for it, so that the consumer's bounded wait runs out -- the give-up path can be
+// exercised without any fault.  skip_item < 0: off.
+struct RingTest { int skip_item; uint32_t wait_limit; };
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint32_t limit = MBAR_WAIT_LIMIT) {
+    for (uint32_t i = 0; i < limit; i++)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }

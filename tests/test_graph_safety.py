@@ -183,3 +183,41 @@ def test_refused_allocations_come_back_as_error_codes(dev, oracle):
         lib.clear_tuning("fail_alloc")
     cpu_ops.rmsnorm(out, xs, np.ones(1024, np.float32), 1024, 256)
     assert rel_err(out, oracle.rmsnorm(xs, np.ones(1024, np.float32))) <= 1e-5
+
+
+@pytest.mark.parametrize("which", ["fwd", "bwd"])
+def test_ring_kernel_gives_up_cleanly_when_a_copy_never_arrives(dev, oracle, which):
+    """The bounded waits of the TMA ring kernels, made to run out on purpose and harmlessly: a test hook lets the
+    producer arm the barrier of one work item without starting its copy, with a short wait limit.  The call returns,
+    the give-up is counted in the status words, nothing faults, and the next ordinary call is correct."""
+    import numpy as np
+    import torch
+    from ane_b200 import lib
+    from tests.conftest import rel_err
+    B, heads, hd, S = 2, 4, 128, 256
+    q, dq, wq, *_ = _inputs(torch, B, heads, hd, S, 256)
+    dw = torch.zeros(hd, device="cuda")
+    dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, 0)                     # table exists, scratch sized
+    dev.rope_qknorm_bwd(dq, q, wq, dw, hd, 1e-6, 1e6, 0)
+    torch.cuda.synchronize()
+    lib.poll_status(reset=True)
+    lib.set_tuning("qk_test_skip_item", 1)
+    lib.set_tuning("qk_wait_limit", 64)
+    try:
+        if which == "fwd":
+            dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, 0)
+        else:
+            dev.rope_qknorm_bwd(dq, q, wq, torch.zeros(hd, device="cuda"), hd, 1e-6, 1e6, 0)
+        torch.cuda.synchronize()
+    finally:
+        lib.clear_tuning("qk_test_skip_item")
+        lib.clear_tuning("qk_wait_limit")
+    assert lib.poll_status(reset=True).wait_giveups > 0
+    qn, wn = q.float().cpu().numpy(), wq.cpu().numpy()
+    got = dev.qknorm_rope(q, wq, hd, 1e-6, 1e6, 0)
+    assert rel_err(got.float().cpu().numpy(), oracle.qknorm_rope(qn, wn, hd, 1e-6, 1e6, 0)) <= 2.0 ** -8
+    dw = torch.zeros(hd, device="cuda")
+    dx = dev.rope_qknorm_bwd(dq, q, wq, dw, hd, 1e-6, 1e6, 0)
+    rdx, rdw = oracle.rope_qknorm_bwd(dq.float().cpu().numpy(), qn, wn, hd, eps=1e-6, base=1e6, pos0=0)
+    assert rel_err(dx.float().cpu().numpy(), rdx) <= 2.0 ** -8 and rel_err(dw.cpu().numpy(), rdw) <= 1e-4
+    assert lib.poll_status().wait_giveups == 0
