@@ -295,6 +295,13 @@ int ane_cuda_zero_dev(void *stream, void *dev, size_t bytes) {
     return ANE_CUDA_OK;
 }
 
+int ane_cuda_copy_dev(void *stream, void *dst, const void *src, size_t bytes) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE((dst && src) || bytes == 0, "%s: null pointer", __func__);
+    if (bytes) ANE_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, (cudaStream_t)stream));
+    return ANE_CUDA_OK;
+}
+
 int ane_cuda_poll_status(ane_cuda_status *out, int reset) {
     ANE_REQUIRE_INIT();
     ANE_REQUIRE(out, "%s: null pointer", __func__);

@@ -143,6 +143,11 @@ extern "C" {
 
 int ane_cuda_p2p_reduce_dev(void *stream, int nranks, const float *const *g_ranks, size_t lo, size_t n, float *g_slice, float gscale,
                             float *normsq_dev, float *scratch) {
+    return ane_cuda_p2p_reduce_limited_dev(stream, nranks, g_ranks, lo, n, g_slice, gscale, normsq_dev, scratch, 0);
+}
+
+int ane_cuda_p2p_reduce_limited_dev(void *stream, int nranks, const float *const *g_ranks, size_t lo, size_t n, float *g_slice, float gscale,
+                                    float *normsq_dev, float *scratch, int max_blocks) {
     ANE_REQUIRE_INIT();
     ANE_REQUIRE(g_ranks && g_slice && normsq_dev, "%s: null pointer", __func__);
     ANE_REQUIRE(nranks >= 1 && nranks <= P2P_MAX_RANKS, "%s: 1..%d ranks (got %d)", __func__, P2P_MAX_RANKS, nranks);
@@ -152,6 +157,7 @@ int ane_cuda_p2p_reduce_dev(void *stream, int nranks, const float *const *g_rank
     size_t blocks = (n + (size_t)P2P_THREADS * 16 - 1) / ((size_t)P2P_THREADS * 16);
     if (blocks < 1) blocks = 1;
     if (blocks > P2P_MAX_BLOCKS) blocks = P2P_MAX_BLOCKS;
+    if (max_blocks > 0 && blocks > (size_t)max_blocks) blocks = (size_t)max_blocks;      // a background reduce beside other kernels
     // block partials: the caller's scratch (needed when this call runs on a stream beside other operators of the
     // library, which share the library-owned range) or the library-owned range
     float *partial = scratch ? scratch : static_cast<float *>(workspace(P2P_MAX_BLOCKS * sizeof(float)));

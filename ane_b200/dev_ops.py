@@ -247,14 +247,16 @@ def _ptr_array(ptrs):
     return (C.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
 
 
-def p2p_reduce(g_ptrs, lo, n, g_slice, gscale=1.0, normsq=None, scratch=None):
+def p2p_reduce(g_ptrs, lo, n, g_slice, gscale=1.0, normsq=None, scratch=None, max_blocks=0):
     """g_slice[:n] = sum over ranks (in rank order) of their gradient buffers at [lo, lo+n); normsq = sum (g*gscale)^2.
-    g_ptrs: device addresses of every rank's flat gradient buffer (peer-mapped)."""
+    g_ptrs: device addresses of every rank's flat gradient buffer (peer-mapped).  max_blocks > 0 limits the grid (a
+    background reduce on a side stream)."""
     normsq = torch.zeros(1, dtype=torch.float32, device=g_slice.device) if normsq is None else normsq
     arr = _ptr_array(g_ptrs)
     if scratch is not None and scratch.numel() < 1184:
         raise ValueError("scratch must hold 1184 floats")
-    _l.check(_l.load().ane_cuda_p2p_reduce_dev(_stream(), len(g_ptrs), arr, lo, n, _p(g_slice), gscale, _p(normsq), _p(scratch)))
+    _l.check(_l.load().ane_cuda_p2p_reduce_limited_dev(_stream(), len(g_ptrs), arr, lo, n, _p(g_slice), gscale, _p(normsq), _p(scratch),
+                                                       int(max_blocks)))
     return normsq
 
 

@@ -321,3 +321,40 @@ class LayerChain:
     def launches_per_microbatch(self) -> int:
         """Kernels of this library launched by forward() + backward() (counted during capture())."""
         return getattr(self, "launches_measured", 0)
+
+    # ------------------------------------------------------------------ backward in segments (gradient exchange beside it)
+    def layer_groups(self, n_groups: int):
+        """The layers split into n_groups contiguous groups, in the order the backward pass finishes them:
+        [(hi, lo), ...] with hi >= lo, first the top layers."""
+        L = self.cfg.layers
+        n_groups = max(1, min(n_groups, L))
+        edges = [round(i * L / n_groups) for i in range(n_groups + 1)]
+        return [(edges[i + 1] - 1, edges[i]) for i in range(n_groups - 1, -1, -1)]
+
+    def run_segment(self, groups, i):
+        """Segment i of a micro-batch launched from the host: segment 0 is the forward pass, the final norm's backward and
+        the backward of the first (top) group of layers; the last segment ends with the embedding scatter-add."""
+        if i == 0:
+            self.forward()
+            self.bwd_begin()
+        hi, lo = groups[i]
+        for L in range(hi, lo - 1, -1):
+            self.bwd_layer(L)
+        if i == len(groups) - 1:
+            self.bwd_end()
+
+    def capture_segments(self, n_groups: int):
+        """The same micro-batch as capture(), recorded as one CUDA graph per group of layers of the backward pass, so that
+        the caller can start exchanging a group's weight gradients (on another stream) as soon as the group is done --
+        what a data-parallel loop does while the rest of the backward pass runs.  capture() must have run before (it sizes the
+        library's scratch)."""
+        groups = self.layer_groups(n_groups)
+        torch.cuda.synchronize()
+        graphs = []
+        for i in range(len(groups)):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.run_segment(groups, i)
+            graphs.append(g)
+        self.segment_groups, self.segment_graphs = groups, graphs
+        return groups

@@ -65,6 +65,7 @@ PROTOTYPES = {
     "ane_cuda_host_free": (None, [_vp]),
     "ane_cuda_sync": (_i, [_vp]),
     "ane_cuda_zero_dev": (_i, [_vp, _vp, _sz]),
+    "ane_cuda_copy_dev": (_i, [_vp, _vp, _vp, _sz]),
     "ane_cuda_poll_status": (_i, [C.POINTER(Status), _i]),
     "ane_cuda_workspace_bytes": (_sz, []),
     "ane_cuda_reserve_workspace": (_i, [_sz]),
@@ -125,6 +126,7 @@ PROTOTYPES = {
     "ane_cuda_vocab_update_full_dev": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     # optimizer step over peer memory
     "ane_cuda_p2p_reduce_dev": (_i, [_vp, _i, _vp, _sz, _sz, _vp, _f, _vp, _vp]),
+    "ane_cuda_p2p_reduce_limited_dev": (_i, [_vp, _i, _vp, _sz, _sz, _vp, _f, _vp, _vp, _i]),
     "ane_cuda_p2p_adam_dev": (_i, [_vp, _i, _i, _vp, _sz, _sz, _vp, _vp, _vp, _i, _f, _f, _f, _f, _f, _f, _vp, _u]),
     # operator chain with host buffers
     "ane_cuda_chain_create": (_vp, [_vp, _i, _vp]),

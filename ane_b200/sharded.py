@@ -187,11 +187,169 @@ class ShardedAdam:
         return factor
 
 
+class RegionShardedAdam:
+    """The peer-memory optimizer step with the gradient exchange spread over the backward pass.
+
+    The flat parameter space is cut into REGIONS at `boundaries` (for the layer chain: groups of layers in the order the
+    backward pass finishes them, then the embedding and norm weights), and every rank owns the same fraction of EVERY
+    region instead of one contiguous slice.  As soon as a rank's backward pass has finished a group of layers, the rank
+    PUSHES its gradients of that region to their owners: one copy per peer into the owner's staging buffer, issued on a
+    side stream and carried out by the copy engines over NVLink -- no SM is taken from the operator chain (whose
+    persistent kernels assume they have the GPU to themselves: a reduce KERNEL resident beside them, even on 32 blocks,
+    was measured to slow the chain by more than it saved), and no rank waits for another during the chain.  At the end of
+    the step one rank sync says that every push has landed; the owner then adds the staged copies and its own gradients
+    in rank order from LOCAL memory (HBM speed instead of NVLink speed), pulls only the regions that were never pushed
+    (the last layer group, embedding, norm weights) through the peer-reading reduce kernel, and goes on as ShardedAdam's
+    peer form does: norm, clip factor, Adam with the stores to every rank.  Per element the arithmetic is the same as
+    there; the squared norm is summed region by region, so the clip factor can differ in the last bit."""
+
+    def __init__(self, w, g, m, v, n_decay: int, n_params: int, world: int, rank: int, peer_ptrs, boundaries, group=None,
+                 lr: float = 3e-4, b1: float = 0.9, b2: float = 0.95, eps: float = 1e-8, wd: float = 0.1, clip: float = 1.0,
+                 kernels=None, staging=None):
+        """staging = (tensor, ptrs): a peer-addressable fp32 buffer of staging_floats(...) elements on every rank and the
+        device addresses of all ranks' copies (symmetric_buffer); None: nothing can be pushed, every region is pulled."""
+        if world < 2 or peer_ptrs is None:
+            raise ValueError("RegionShardedAdam needs two or more ranks with peer-mapped buffers")
+        b = list(boundaries)
+        if b[0] != 0 or b[-1] != w.numel() or any(y <= x for x, y in zip(b, b[1:])):
+            raise ValueError("boundaries must rise from 0 to the length of the flat buffers")
+        if any((y - x) % (world * 4) for x, y in zip(b, b[1:])):
+            raise ValueError("every region must split into `world` parts of a multiple of four floats")
+        self.w, self.g, self.m, self.v = w, g, m, v
+        self.n_decay, self.n_params = n_decay, n_params
+        self.world, self.rank, self.group = world, rank, group
+        self.lr, self.b1, self.b2, self.eps, self.wd, self.clip = lr, b1, b2, eps, wd, clip
+        self.peer_ptrs = peer_ptrs
+        self.bounds = b
+        self.part_len = [(y - x) // world for x, y in zip(b, b[1:])]
+        self.parts = self.partition(b, world, rank)
+        self.offsets = [0]
+        for n in self.part_len:
+            self.offsets.append(self.offsets[-1] + n)
+        if kernels is None:
+            from . import dev_ops as kernels  # noqa: WPS433
+        self.k = kernels
+        dev = g.device
+        self.g_slice = torch.empty(self.offsets[-1], dtype=g.dtype, device=dev)
+        self._normsq = torch.zeros(len(self.parts), dtype=torch.float32, device=dev)
+        self._token = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._side = torch.cuda.Stream(device=dev)
+        self._events, self._pushed = [], set()
+        self.staging = staging
+        if staging is not None and staging[0].numel() < self.staging_floats(b, world):
+            raise ValueError("the staging buffer is too small for these regions")
+        self.normsq = None
+        self.phase_events = None
+        self.lo, self.hi = self.parts[0]          # for callers that only report a range
+
+    _mark = ShardedAdam._mark
+
+    @staticmethod
+    def partition(boundaries, world: int, rank: int):
+        """The ranges rank `rank` owns: part `rank` of `world` equal parts of every region."""
+        return [(x + rank * ((y - x) // world), x + (rank + 1) * ((y - x) // world)) for x, y in zip(boundaries, boundaries[1:])]
+
+    @staticmethod
+    def staging_floats(boundaries, world: int) -> int:
+        """Floats of staging every rank needs: one slot per peer, each holding this rank's part of every region."""
+        return (world - 1) * sum((y - x) // world for x, y in zip(boundaries, boundaries[1:]))
+
+    def owned_ranges(self):
+        return list(self.parts)
+
+    def begin_step(self, gscale: float = 1.0):
+        self._events, self._pushed = [], set()
+
+    def _slot(self, src: int, owner: int) -> int:
+        """Slot of rank `src` in rank `owner`'s staging buffer."""
+        return src if src < owner else src - 1
+
+    def push_region(self, i: int, after: "torch.cuda.Event"):
+        """This rank's gradients of region i are complete on its compute stream (`after` = an event recorded there): copy
+        each peer's part of the region into that peer's staging buffer, on the side stream."""
+        if self.staging is None:
+            raise ValueError("no staging buffer was given")
+        from . import lib as _l
+        L = _l.load()
+        _, st_ptrs = self.staging
+        x, n = self.bounds[i], self.part_len[i]
+        g_base = self.g.data_ptr()
+        with torch.cuda.stream(self._side):
+            self._side.wait_event(after)
+            sid = self._side.cuda_stream
+            for owner in range(self.world):
+                if owner == self.rank:
+                    continue
+                dst = st_ptrs[owner] + 4 * (self._slot(self.rank, owner) * self.offsets[-1] + self.offsets[i])
+                _l.check(L.ane_cuda_copy_dev(sid, dst, g_base + 4 * (x + owner * n), 4 * n))
+            ev = torch.cuda.Event()
+            ev.record(self._side)
+        self._events.append(ev)
+        self._pushed.add(i)
+
+    reduce_region = push_region
+
+    def step(self, t: int, gscale: float = 1.0):
+        return self._mark("peer_memory_step", lambda: self._step(t, gscale))
+
+    def _step(self, t: int, gscale: float):
+        w_ptrs, g_ptrs = self.peer_ptrs
+        cur = torch.cuda.current_stream()
+        for ev in self._events:
+            cur.wait_event(ev)
+        # every rank's gradients are complete and every push has landed
+        self._mark("peer.sync_gradients_complete", lambda: dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.group))
+
+        def reduce_all():
+            for i, (a, e) in enumerate(self.parts):
+                gs = self.g_slice[self.offsets[i]:self.offsets[i + 1]]
+                if i in self._pushed:      # the peers' copies are in this rank's staging buffer: a local sum, in rank order
+                    mine = self.staging[0].data_ptr()
+                    ptrs = [self.g.data_ptr() if r == self.rank
+                            else mine + 4 * (self._slot(r, self.rank) * self.offsets[-1] + self.offsets[i] - a) for r in range(self.world)]
+                    self.k.p2p_reduce(ptrs, a, e - a, gs, gscale, normsq=self._normsq[i:i + 1])
+                else:
+                    self.k.p2p_reduce(g_ptrs, a, e - a, gs, gscale, normsq=self._normsq[i:i + 1])
+
+        self._mark("peer.reduce", reduce_all)
+        self._mark("peer.allreduce_norm", lambda: dist.all_reduce(self._normsq, op=dist.ReduceOp.SUM, group=self.group))
+        self.normsq = self._normsq.sum().reshape(1)
+        factor = self.k.clip_factor(self._normsq, self.clip)
+
+        def update():
+            for i, (pa, pe) in enumerate(self.parts):
+                for lo, hi, wd in ((0, self.n_decay, self.wd), (self.n_decay, self.n_params, 0.0)):
+                    a, b = max(lo, pa), min(hi, pe)
+                    if a < b:
+                        off = self.offsets[i] + (a - pa)
+                        self.k.p2p_adam(w_ptrs, self.rank, a, b - a, self.g_slice[off:off + (b - a)], self.m[a:b], self.v[a:b], t, self.lr,
+                                        self.b1, self.b2, self.eps, wd=wd, gscale=gscale, clip=factor)
+
+        self._mark("peer.adam_store_all", update)
+        self._mark("peer.sync_parameters_landed", lambda: dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.group))
+        self._events, self._pushed = [], set()
+        return factor
+
+
 def allreduce_scalar_sum(x: torch.Tensor, world: int, group=None) -> torch.Tensor:
     """Sum of a small tensor over the ranks (the loss all-reduce of a data-parallel step)."""
     if world > 1:
         dist.all_reduce(x, op=dist.ReduceOp.SUM, group=group)
     return x
+
+
+def symmetric_buffer(n: int, device, group=None):
+    """One flat fp32 buffer of n elements that every rank of the group can address, and the device addresses of all
+    ranks' copies: (tensor, ptrs)."""
+    import torch.distributed._symmetric_memory as symm
+
+    group = group if group is not None else dist.group.WORLD
+    t = symm.empty(n, dtype=torch.float32, device=device)
+    try:
+        h = symm.rendezvous(t, group=group)
+    except TypeError:
+        h = symm.rendezvous(t, group.group_name)
+    return t, [int(p) for p in h.buffer_ptrs]
 
 
 def symmetric_buffers(n: int, device, group=None):

@@ -57,6 +57,7 @@ def parse_args():
     ap.add_argument("--no-p2p", action="store_true", help="N > 1: use NCCL reduce-scatter / all-gather instead of the peer-memory optimizer kernels")
     ap.add_argument("--early-reduce", action="store_true", help="N > 1, peer memory: reduce the matmul gradients on a side stream beside the chain instead of at the end of the step (measured slower: the chain is HBM-bound)")
     ap.add_argument("--no-boundary-fusion", action="store_true", help="run the closing residual and the next norm as two operators")
+    ap.add_argument("--overlap-groups", type=int, default=7, help="N > 1, peer memory: the backward pass of a step's last micro-batch runs as this many groups of layers, and each group's gradients are reduced on a side stream while the next groups run (0 or 1: reduce everything at the end of the step)")
     ap.add_argument("--cpu-seqs", type=int, default=2, help="sequences in the CPU sample")
     ap.add_argument("--e2e-seqs", type=int, default=8, help="sequences per rank and step of the host-buffer (e2e) measurement")
     return ap.parse_args()
@@ -392,10 +393,11 @@ def cpu_reference_ops():
 
 def cross_rank_checks(torch, dist, params, opt, t_last, gscale, world, rank, peer_mode):
     """Outside the timed region, world > 1: (a) every rank ends the timed steps with the same parameters -- a 64-bit sum
-    of the parameter bits, MIN and MAX over the ranks; (b) one more optimizer step from the same state through both
-    forms of the exchange (peer memory, then NCCL reduce-scatter / all-gather on restored buffers) and the largest
-    difference between the two results relative to the largest parameter.  NCCL adds the ranks' gradients in its own
-    order, the peer kernels in rank order: equal bits on two ranks, fp32 rounding beyond."""
+    of the parameter bits, MIN and MAX over the ranks; (b) one optimizer step from the same parameters and gradients, with
+    cleared moments (the two forms keep the moments of different ranges on a rank), through both forms of the exchange
+    (peer memory, then NCCL reduce-scatter / all-gather on restored buffers) and the largest difference between the two
+    results relative to the largest parameter.  NCCL adds the ranks' gradients in its own order, the peer kernels in rank
+    order, and the squared norm is summed over different partitions: fp32 rounding apart, the same step."""
     from ane_b200.sharded import ShardedAdam
 
     def checksum():
@@ -408,21 +410,26 @@ def cross_rank_checks(torch, dist, params, opt, t_last, gscale, world, rank, pee
     out = {"params_equal_across_ranks": checksum()}
     if not peer_mode:
         return out
-    w0, m0, v0 = params.w.clone(), params.m.clone(), params.v.clone()
-    opt.step(t_last + 1, gscale)
+    w0 = params.w.clone()
+    params.m.zero_()
+    params.v.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    opt.begin_step(gscale)
+    opt.step(1, gscale)
     torch.cuda.synchronize()
     dist.barrier()
     w_peer = params.w.clone()
     out["params_equal_across_ranks_after_peer_step"] = checksum()
     dist.barrier()
     params.w.copy_(w0)
-    params.m.copy_(m0)
-    params.v.copy_(v0)
+    params.m.zero_()
+    params.v.zero_()
     torch.cuda.synchronize()
     dist.barrier()
     nccl = ShardedAdam(params.w, params.g, params.m, params.v, params.n_decay, params.n, world, rank,
                        lr=opt.lr, b1=opt.b1, b2=opt.b2, eps=opt.eps, wd=opt.wd, clip=opt.clip)
-    nccl.step(t_last + 1, gscale)
+    nccl.step(1, gscale)
     torch.cuda.synchronize()
     dist.barrier()
     diff = (params.w[:params.n] - w_peer[:params.n]).abs().max() / w_peer[:params.n].abs().max()
@@ -443,7 +450,7 @@ def run_ours(args):
     from ane_b200 import dev_ops as ops
     from ane_b200 import lib
     from ane_b200.layer_chain import ChainConfig, FlatParams, LayerChain
-    from ane_b200.sharded import ShardedAdam, padded_length, shard_range
+    from ane_b200.sharded import RegionShardedAdam, ShardedAdam, padded_length, shard_range
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -490,15 +497,43 @@ def run_ours(args):
         chain.capture()
     per_mb = chain.launches_per_microbatch()
     graph_launches = [0]
+    # The gradient exchange beside the backward pass: a layer's weight gradients are final once the step's last micro-batch
+    # has run that layer's backward operators (in a full loop the dW contractions sit there), so the reduce of a finished
+    # group of layers can run while the remaining groups are computed.  Every rank owns a share of every group.
+    groups, region_of_group = None, None
+    if world > 1 and peer_ptrs is not None and args.overlap_groups > 1 and not args.early_reduce:
+        groups = chain.capture_segments(args.overlap_groups) if use_graph else chain.layer_groups(args.overlap_groups)
+        per_layer = cfg.matrix_params_per_layer()
+        edges = sorted({lo_ * per_layer for _, lo_ in groups} | {params.n_matrix, params.n_padded})
+        region_of_group = [edges.index(lo_ * per_layer) for _, lo_ in groups]
+        from ane_b200.sharded import symmetric_buffer
+        opt = RegionShardedAdam(params.w, params.g, params.m, params.v, params.n_decay, params.n, world, rank, peer_ptrs, edges,
+                                lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0,
+                                staging=symmetric_buffer(RegionShardedAdam.staging_floats(edges, world), device))
+        exchange += (f"; every rank owns a share of every layer group, and the gradients of {len(groups) - 1} of {len(groups)} groups are pushed to "
+                     "their owners by the copy engines (side stream) while the rest of the backward pass runs")
 
     def step():
         params.zero_produced_grads()
-        opt.begin_step(gscale)       # --early-reduce: the matmul gradients are complete, their share of the exchange overlaps the chain
+        opt.begin_step(gscale)
         for mb in range(n_micro):
-            if use_graph and not (mb == 0 and chain.timed_op is not None):
+            eager = not use_graph or (mb == 0 and chain.timed_op is not None)   # the first micro-batch of a timed step runs eagerly, with events around the dominant kernel
+            if groups is not None and mb == n_micro - 1:
+                for i in range(len(groups)):
+                    if eager:
+                        chain.run_segment(groups, i)
+                    else:
+                        chain.segment_graphs[i].replay()
+                    if i + 1 < len(groups):
+                        ev = torch.cuda.Event()
+                        ev.record()
+                        opt.reduce_region(region_of_group[i], ev)
+                if not eager:
+                    graph_launches[0] += per_mb
+            elif not eager:
                 chain.replay()
                 graph_launches[0] += per_mb
-            else:       # the first micro-batch of a timed step runs eagerly, with events around the dominant kernel
+            else:
                 chain.forward()
                 chain.backward()
         tstep[0] += 1

@@ -107,6 +107,9 @@ void ane_cuda_host_free(void *p);
 int ane_cuda_sync(void *stream);
 /* Clears `bytes` bytes of device memory on the stream (the memset of the accumulated gradients, train.m:874-877). */
 int ane_cuda_zero_dev(void *stream, void *dev, size_t bytes);
+/* Copy between device ranges on the stream; either side may be another GPU's memory mapped into this process (the copy
+ * engines move it over NVLink, no SM is used -- what the gradient push of the data-parallel step relies on). */
+int ane_cuda_copy_dev(void *stream, void *dst, const void *src, size_t bytes);
 /* Copy the device status words to *out and optionally clear them. */
 int ane_cuda_poll_status(ane_cuda_status *out, int reset);
 /* Bytes of library-owned scratch currently held on the device (grow-only cache). */
@@ -341,6 +344,10 @@ int ane_cuda_vocab_update_full_dev(void *stream, float *full_embed, const float 
  * the same stream does). */
 int ane_cuda_p2p_reduce_dev(void *stream, int nranks, const float *const *g_ranks, size_t lo, size_t n, float *g_slice,
                             float gscale, float *normsq_dev, float *scratch);
+/* The same reduce on at most max_blocks thread blocks (0: no limit): for a reduce that runs on a side stream beside the
+ * operator chain and must leave the SMs to it.  The block count is part of the (fixed) summation order of normsq. */
+int ane_cuda_p2p_reduce_limited_dev(void *stream, int nranks, const float *const *g_ranks, size_t lo, size_t n, float *g_slice,
+                                    float gscale, float *normsq_dev, float *scratch, int max_blocks);
 int ane_cuda_p2p_adam_dev(void *stream, int nranks, int self, float *const *w_ranks, size_t lo, size_t n, const float *g_slice,
                           float *m_slice, float *v_slice, int t, float lr, float b1, float b2, float eps, float wd, float gscale,
                           const float *clip_dev, unsigned flags);

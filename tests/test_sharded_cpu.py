@@ -106,3 +106,23 @@ def test_sharded_adam_matches_single_process(world):
         assert abs(fr - factor) <= 1e-6
         assert np.max(np.abs(wr - w)) <= 1e-6 * np.max(np.abs(w))
     assert np.array_equal(out[0][0], out[1][0])          # every rank ends with the same parameters
+
+
+def test_region_ownership_covers_the_flat_space_exactly_once():
+    """RegionShardedAdam's ownership: the parts of all ranks tile every region without gap or overlap, every rank owns the
+    same number of elements, and the staging buffer holds one slot per peer."""
+    from ane_b200.sharded import RegionShardedAdam
+    bounds = [0, 4096, 4096 + 8 * 1000, 20000 + 8 * 13, 65536]
+    for world in (2, 4, 8):
+        seen = [0] * bounds[-1]
+        sizes = []
+        for rank in range(world):
+            parts = RegionShardedAdam.partition(bounds, world, rank)
+            assert len(parts) == len(bounds) - 1
+            sizes.append(sum(e - a for a, e in parts))
+            for (a, e), lo, hi in zip(parts, bounds, bounds[1:]):
+                assert lo <= a < e <= hi
+                for i in range(a, e):
+                    seen[i] += 1
+        assert all(c == 1 for c in seen) and len(set(sizes)) == 1
+        assert RegionShardedAdam.staging_floats(bounds, world) == (world - 1) * sizes[0]

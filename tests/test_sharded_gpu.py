@@ -16,11 +16,19 @@ def _free_port():
         return s.getsockname()[1]
 
 
+def m2_full(m_local, opt, dist, dev, n):
+    """The first moments of all ranks' slices of a one-slice optimizer, gathered (each rank only updates its own slice)."""
+    import torch
+    out = torch.empty(n, device=dev)
+    dist.all_gather_into_tensor(out, m_local[opt.lo:opt.hi].contiguous())
+    return out
+
+
 def _worker(rank, world, port, out_dir):
     import torch
     import torch.distributed as dist
     from ane_b200 import lib
-    from ane_b200.sharded import ShardedAdam, padded_length, symmetric_buffers
+    from ane_b200.sharded import RegionShardedAdam, ShardedAdam, padded_length, symmetric_buffer, symmetric_buffers
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -39,6 +47,13 @@ def _worker(rank, world, port, out_dir):
     w3, g3, ptrs3 = symmetric_buffers(n, dev)
     w3.copy_(w)
     g3.copy_(g)
+    w4, g4, ptrs4 = symmetric_buffers(n, dev)
+    w4.copy_(w)
+    g4.copy_(g)
+    m4, v4 = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    bounds = [0, 40_000, 80_000, n]
+    regions = RegionShardedAdam(w4, g4, m4, v4, n_decay, n_params, world, rank, ptrs4, bounds,
+                                staging=symmetric_buffer(RegionShardedAdam.staging_floats(bounds, world), dev))
     m, v, m2, v2, m3, v3 = (torch.zeros(n, device=dev) for _ in range(6))
     peer = ShardedAdam(w, g, m, v, n_decay, n_params, world, rank, peer_ptrs=ptrs)
     nccl = ShardedAdam(w2, g2, m2, v2, n_decay, n_params, world, rank)
@@ -48,7 +63,19 @@ def _worker(rank, world, port, out_dir):
         peer.step(t, 0.5)
         nccl.step(t, 0.5)
         early.step(t, 0.5)
+        # every rank owns a part of every region; two of the three regions are pushed to their owners "during the step"
+        regions.begin_step(0.5)
+        for i in (1, 0):
+            ev = torch.cuda.Event()
+            ev.record()
+            regions.reduce_region(i, ev)
+        regions.step(t, 0.5)
     torch.cuda.synchronize()
+    own = torch.zeros(n, dtype=torch.bool, device=dev)
+    for a, e in regions.owned_ranges():
+        own[a:e] = True
+    ok_regions = bool(torch.allclose(regions.normsq, nccl.normsq, rtol=1e-6)) and bool(torch.allclose(w4, w2, rtol=1e-5, atol=1e-8)) \
+        and bool(torch.allclose(m4[own], m2_full(m2, nccl, dist, dev, n)[own], rtol=1e-5, atol=1e-10)) and int(own.sum()) == n // world
     ok = bool(torch.equal(w, w2)) and bool(torch.equal(m[peer.lo:peer.hi], m2[peer.lo:peer.hi])) \
         and bool(torch.equal(v[peer.lo:peer.hi], v2[peer.lo:peer.hi])) and bool(torch.equal(peer.normsq, nccl.normsq)) \
         and bool(torch.allclose(early.normsq, nccl.normsq, rtol=1e-6)) \
@@ -58,7 +85,7 @@ def _worker(rank, world, port, out_dir):
     # from the one-pass forms in the last bit)
     changed = bool((w != torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(7)) * 0.02)[:n_params].any())
     with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
-        f.write("ok" if ok and changed else f"mismatch ok={ok} changed={changed}")
+        f.write("ok" if ok and changed and ok_regions else f"mismatch ok={ok} changed={changed} regions={ok_regions}")
     dist.barrier()
     dist.destroy_process_group()
 
