@@ -127,6 +127,13 @@ def _cases(torch, ops, device, M, shape=None):
         tg = torch.randint(0, Vc, (M, S), device=device, dtype=torch.int32)
         return (lambda i: ops.cross_entropy(logits, tg, dlogits=logits)), 2 * Vc * M * S * 4, 3
 
+    # the compact vocabulary of the reference's own run (training/README.md: 9.2 k of 32 k ids in use)
+    def cross_entropy_9200():
+        Vc = 9200
+        sets = [torch.randn((M, Vc, S), device=device) for _ in range(2)]
+        tg = torch.randint(0, Vc, (M, S), device=device, dtype=torch.int32)
+        return (lambda i: ops.cross_entropy(sets[i % 2], tg, dlogits=sets[i % 2])), 2 * Vc * M * S * 4, 6
+
     def _flat():
         n = 2 * M << 20
         wv, gv, mv, vv = (torch.randn(n, device=device) * 0.01 for _ in range(4))
@@ -185,7 +192,7 @@ def _cases(torch, ops, device, M, shape=None):
         "rope": rope, "qknorm_rope(Q)": qknorm_rope, "rope_qknorm_bwd(Q)": rope_qknorm_bwd,
         "qknorm_rope(K)": qknorm_rope_k, "rope_qknorm_bwd(K)": rope_qknorm_bwd_k,
         "embed_lookup": embed_lookup, "embed_backward": embed_backward,
-        "cross_entropy": cross_entropy, "cross_entropy_compact": cross_entropy_compact,
+        "cross_entropy": cross_entropy, "cross_entropy_compact": cross_entropy_compact, "cross_entropy_9200": cross_entropy_9200,
         "adam": adam, "grad_norm_sq": grad_norm_sq,
     }
 

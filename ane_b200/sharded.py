@@ -109,6 +109,9 @@ class ShardedAdam:
         gs = self._mark("reduce_scatter", self._reduce_scatter)
         return self._mark("norm_clip_adam_gather", lambda: self._update(gs, t, gscale))
 
+    def flush(self):
+        """Nothing is deferred in this form."""
+
     def _rank_sync(self):
         """Stream-ordered meeting point of all ranks: a one-element all-reduce completes on a rank only after every
         rank has reached it on its stream, i.e. after everything each of them enqueued before it."""
@@ -205,9 +208,16 @@ class RegionShardedAdam:
 
     def __init__(self, w, g, m, v, n_decay: int, n_params: int, world: int, rank: int, peer_ptrs, boundaries, group=None,
                  lr: float = 3e-4, b1: float = 0.9, b2: float = 0.95, eps: float = 1e-8, wd: float = 0.1, clip: float = 1.0,
-                 kernels=None, staging=None):
+                 kernels=None, staging=None, deferred_broadcast: bool = False):
         """staging = (tensor, ptrs): a peer-addressable fp32 buffer of staging_floats(...) elements on every rank and the
-        device addresses of all ranks' copies (symmetric_buffer); None: nothing can be pushed, every region is pulled."""
+        device addresses of all ranks' copies (symmetric_buffer); None: nothing can be pushed, every region is pulled.
+        deferred_broadcast: Adam writes the new weights of the owned parts to LOCAL memory only and the copy engines carry
+        them to the peers afterwards: the range without weight decay (the norm weights, which the operator chain reads from
+        its first kernel on) at once, confirmed by the closing rank sync; everything else (matrices, embedding table: read by
+        the contractions, layer by layer, not by this library) on the side stream, beside the next step's operator chain,
+        confirmed by the NEXT step's first rank sync -- or by flush().  A full training loop would issue these copies in
+        layer order and let each layer's contraction wait for its own event; here nothing consumes them before the next
+        optimizer step."""
         if world < 2 or peer_ptrs is None:
             raise ValueError("RegionShardedAdam needs two or more ranks with peer-mapped buffers")
         b = list(boundaries)
@@ -235,6 +245,8 @@ class RegionShardedAdam:
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
         self._side = torch.cuda.Stream(device=dev)
         self._events, self._pushed = [], set()
+        self.deferred_broadcast = deferred_broadcast
+        self._bcast_done = None
         self.staging = staging
         if staging is not None and staging[0].numel() < self.staging_floats(b, world):
             raise ValueError("the staging buffer is too small for these regions")
@@ -297,6 +309,9 @@ class RegionShardedAdam:
         cur = torch.cuda.current_stream()
         for ev in self._events:
             cur.wait_event(ev)
+        if self._bcast_done is not None:        # this rank's weight copies of the last step: landed before the sync below says so
+            cur.wait_event(self._bcast_done)
+            self._bcast_done = None
         # every rank's gradients are complete and every push has landed
         self._mark("peer.sync_gradients_complete", lambda: dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.group))
 
@@ -316,19 +331,53 @@ class RegionShardedAdam:
         self.normsq = self._normsq.sum().reshape(1)
         factor = self.k.clip_factor(self._normsq, self.clip)
 
+        deferred = self.deferred_broadcast
+        later = []                               # (a, b) ranges whose copies to the peers run beside the next step
+
         def update():
+            targets, me = ([self.w.data_ptr()], 0) if deferred else (w_ptrs, self.rank)
             for i, (pa, pe) in enumerate(self.parts):
                 for lo, hi, wd in ((0, self.n_decay, self.wd), (self.n_decay, self.n_params, 0.0)):
                     a, b = max(lo, pa), min(hi, pe)
                     if a < b:
                         off = self.offsets[i] + (a - pa)
-                        self.k.p2p_adam(w_ptrs, self.rank, a, b - a, self.g_slice[off:off + (b - a)], self.m[a:b], self.v[a:b], t, self.lr,
+                        self.k.p2p_adam(targets, me, a, b - a, self.g_slice[off:off + (b - a)], self.m[a:b], self.v[a:b], t, self.lr,
                                         self.b1, self.b2, self.eps, wd=wd, gscale=gscale, clip=factor)
+                        if deferred:
+                            if wd == 0.0:
+                                self._copy_to_peers(cur, a, b)       # norm weights: needed by the next step's first operator
+                            else:
+                                later.append((a, b))
 
-        self._mark("peer.adam_store_all", update)
+        self._mark("peer.adam_store_all" if not deferred else "peer.adam_local_and_norm_weights", update)
+        if later:
+            done = torch.cuda.Event()
+            done.record(cur)
+            with torch.cuda.stream(self._side):
+                self._side.wait_event(done)
+                for a, b in later:
+                    self._copy_to_peers(self._side, a, b)
+                self._bcast_done = torch.cuda.Event()
+                self._bcast_done.record(self._side)
         self._mark("peer.sync_parameters_landed", lambda: dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.group))
         self._events, self._pushed = [], set()
         return factor
+
+    def _copy_to_peers(self, stream, a: int, b: int):
+        from . import lib as _l
+        L = _l.load()
+        w_ptrs, _ = self.peer_ptrs
+        src = self.w.data_ptr() + 4 * a
+        for r in range(self.world):
+            if r != self.rank:
+                _l.check(L.ane_cuda_copy_dev(stream.cuda_stream, w_ptrs[r] + 4 * a, src, 4 * (b - a)))
+
+    def flush(self):
+        """Ends with every rank's deferred weight copies landed everywhere (a rank sync on the current stream)."""
+        if self._bcast_done is not None:
+            torch.cuda.current_stream().wait_event(self._bcast_done)
+            self._bcast_done = None
+            dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.group)
 
 
 def allreduce_scalar_sum(x: torch.Tensor, world: int, group=None) -> torch.Tensor:

@@ -13,10 +13,14 @@
  * Parity pins: oracle rmsnorm / rmsnorm_bwd / cross-entropy / Adam / embed / RoPE-bwd are
  * checked against the reference's own functions compiled from source (oracle/_ref) and
  * against the seeded fixtures of training/test_rmsnorm_bwd.m:26-33 and
- * training/test_classifier.m:25-27,132-134 (tests/golden).  The ops with no compilable
- * reference function (SwiGLU fwd/bwd, RoPE fwd, residual, QK-norm, grad post-processing)
- * restate the cited lines; the reference ships no test or vector for them, so for those
- * "parity unpinned" applies: parity means agreement with this restatement.
+ * training/test_classifier.m:25-27,132-134 (tests/golden).  SwiGLU fwd/bwd, RoPE fwd, the
+ * residual and the gradient scale / norm / clip are statements inside the reference's
+ * Objective-C main file or functions of a header that includes Objective-C: they are checked
+ * against those very lines, extracted by line range and compiled behind the Accelerate
+ * stand-in (ref_inline_exports.c.in -> oracle/_ref/libref_inline.so), live and through golden
+ * vectors.  "Parity unpinned" remains for the per-head QK-norm (the reference has none: it is
+ * rmsnorm over the channels of one head, checked against the pinned rmsnorm head by head) and
+ * for the GQA / cast / pack helpers (their reference header is Objective-C over IOSurface).
  */
 #include <math.h>
 #include <stdint.h>

@@ -126,3 +126,54 @@ def test_region_ownership_covers_the_flat_space_exactly_once():
                     seen[i] += 1
         assert all(c == 1 for c in seen) and len(set(sizes)) == 1
         assert RegionShardedAdam.staging_floats(bounds, world) == (world - 1) * sizes[0]
+
+
+def _rank_that_leaves(rank, world, port, out):
+    """Rank 1 leaves the job between two steps (nothing of it is in flight); rank 0 learns of it when its next collective
+    fails within the process group's short timeout, and reports instead of hanging."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    w, grads, m, v = _inputs(world)
+    L = padded_length(N, world, 16)
+
+    def padded(a):
+        t = torch.zeros(L)
+        t[:N] = torch.from_numpy(a)
+        return t
+
+    opt = ShardedAdam(padded(w), padded(grads[rank]), padded(m), padded(v), N_DECAY, N, world, rank,
+                      lr=3e-4, b2=0.95, wd=0.1, clip=1.0, kernels=OracleKernels())
+    opt.step(1, gscale=1.0 / 64)
+    w_after_1 = opt.w[:N].numpy().copy()
+    dist.barrier()
+    if rank == 1:
+        out[1] = "left after step 1"
+        os._exit(0)                      # the rank is gone: no destroy_process_group, no goodbye
+    t0 = time.time()
+    try:
+        opt.step(2, gscale=1.0 / 64)
+        out[0] = "no error"
+    except Exception as exc:             # gloo reports the closed connection or the timeout
+        out[0] = ("detected", time.time() - t0, type(exc).__name__, bool(np.array_equal(opt.w[:N].numpy()[opt.lo:min(opt.hi, N)],
+                                                                                   w_after_1[opt.lo:min(opt.hi, N)])))
+    os._exit(0)                          # the group is broken; leave without the collective shutdown
+
+
+def test_a_rank_that_leaves_between_steps_is_detected_not_waited_for():
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_that_leaves, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert not p.is_alive(), "a rank hung"
+    assert out[1] == "left after step 1"
+    assert out[0][0] == "detected", out[0]
+    assert out[0][1] < 60.0               # within the group's timeout, not forever
+    assert out[0][3]                      # the failed step did not half-update this rank's own slice

@@ -54,6 +54,12 @@ def _worker(rank, world, port, out_dir):
     bounds = [0, 40_000, 80_000, n]
     regions = RegionShardedAdam(w4, g4, m4, v4, n_decay, n_params, world, rank, ptrs4, bounds,
                                 staging=symmetric_buffer(RegionShardedAdam.staging_floats(bounds, world), dev))
+    w5, g5, ptrs5 = symmetric_buffers(n, dev)
+    w5.copy_(w)
+    g5.copy_(g)
+    m5, v5 = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    deferred = RegionShardedAdam(w5, g5, m5, v5, n_decay, n_params, world, rank, ptrs5, bounds, deferred_broadcast=True,
+                                 staging=symmetric_buffer(RegionShardedAdam.staging_floats(bounds, world), dev))
     m, v, m2, v2, m3, v3 = (torch.zeros(n, device=dev) for _ in range(6))
     peer = ShardedAdam(w, g, m, v, n_decay, n_params, world, rank, peer_ptrs=ptrs)
     nccl = ShardedAdam(w2, g2, m2, v2, n_decay, n_params, world, rank)
@@ -70,12 +76,25 @@ def _worker(rank, world, port, out_dir):
             ev.record()
             regions.reduce_region(i, ev)
         regions.step(t, 0.5)
+        # the same with the weights leaving through the copy engines after a local Adam; the norm weights (no decay) must be
+        # everywhere when step() is over, the rest after the next step's first sync or flush()
+        deferred.begin_step(0.5)
+        ev = torch.cuda.Event()
+        ev.record()
+        deferred.push_region(0, ev)
+        deferred.step(t, 0.5)
+        torch.cuda.synchronize()
+        dist.barrier()
+        norms_there = bool(torch.equal(w5[n_decay:n_params], w4[n_decay:n_params]))
+    deferred.flush()
     torch.cuda.synchronize()
+    dist.barrier()
     own = torch.zeros(n, dtype=torch.bool, device=dev)
     for a, e in regions.owned_ranges():
         own[a:e] = True
     ok_regions = bool(torch.allclose(regions.normsq, nccl.normsq, rtol=1e-6)) and bool(torch.allclose(w4, w2, rtol=1e-5, atol=1e-8)) \
-        and bool(torch.allclose(m4[own], m2_full(m2, nccl, dist, dev, n)[own], rtol=1e-5, atol=1e-10)) and int(own.sum()) == n // world
+        and bool(torch.allclose(m4[own], m2_full(m2, nccl, dist, dev, n)[own], rtol=1e-5, atol=1e-10)) and int(own.sum()) == n // world \
+        and norms_there and bool(torch.equal(w5, w4))
     ok = bool(torch.equal(w, w2)) and bool(torch.equal(m[peer.lo:peer.hi], m2[peer.lo:peer.hi])) \
         and bool(torch.equal(v[peer.lo:peer.hi], v2[peer.lo:peer.hi])) and bool(torch.equal(peer.normsq, nccl.normsq)) \
         and bool(torch.allclose(early.normsq, nccl.normsq, rtol=1e-6)) \
