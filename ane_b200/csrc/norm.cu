@@ -345,6 +345,8 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
         const int knob_b = tuning("norm_bwd", wide_f32 ? 11 : (HAS_ADD || sizeof(T) == 4) ? 10 : 8);
         if (knob_b == 11 && C >= 512 && (size_t)C * 66 <= 200 * 1024)           // channel eighths on a cluster of eight, 256-byte rows
             return launch_rmsnorm_bwd_cluster<T, HAS_ADD, 16, 8, 1>(st, B, C, S, dx, dw, dy, x, w, add, eps, flags);
+        if (knob_b == 12 && C >= 512 && (size_t)C * 66 <= 200 * 1024)           // channel eighths, 128-byte rows, two strip pairs: the next tile always in flight
+            return launch_rmsnorm_bwd_cluster<T, HAS_ADD, 8, 8, 2>(st, B, C, S, dx, dw, dy, x, w, add, eps, flags);
         if ((knob_b == 9 || knob_b == 10) && C >= 256 && (size_t)C * 66 <= 200 * 1024) {
             // channel quarters on a cluster of four: 64-byte rows with double-buffered strips (9), or 128-byte rows (10)
             if (knob_b == 9) return launch_rmsnorm_bwd_cluster<T, HAS_ADD, 4, 4, 2>(st, B, C, S, dx, dw, dy, x, w, add, eps, flags);

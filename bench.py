@@ -648,6 +648,33 @@ def run_ours(args):
     }
 
     line["ms_per_step_x_sm_mhz"] = round(ms_step * clocks["sm_mhz"], 1) if clocks.get("sm_mhz") else None
+    if world == 1 and not args.no_ops and use_graph:
+        # the same step with the classifier loss after every micro-batch, at the compacted vocabulary (a quarter of the 151,936
+        # ids: training_dynamic/cpu_ops.h:96-148 compacts to the ids in use): fp32 logits [M][37984][2048], softmax-CE forward + backward in place
+        Vc = cfg.vocab // 4
+        logits = torch.randn((M, Vc, cfg.seq), device=device)
+        targets = torch.randint(0, Vc, (M, cfg.seq), device=device, dtype=torch.int32)
+
+        def step_with_loss():
+            params.zero_produced_grads()
+            for _ in range(n_micro):
+                chain.replay()
+                ops.cross_entropy(logits, targets, dlogits=logits)
+            tstep[0] += 1
+            opt.step(tstep[0], gscale)
+
+        step_with_loss()
+        torch.cuda.synchronize()
+        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0.record()
+        for _ in range(2):
+            step_with_loss()
+        l1.record()
+        torch.cuda.synchronize()
+        ms_l = l0.elapsed_time(l1) / 2
+        line["chain_plus_loss"] = {"value": round(tokens / (ms_l * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(ms_l, 3),
+                                   "loss": f"softmax cross-entropy forward + backward over a compact vocabulary of {Vc} ids, fp32 logits, after every micro-batch"}
+        del logits, targets
     del chain
     torch.cuda.empty_cache()
     if world > 1:

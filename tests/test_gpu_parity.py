@@ -140,7 +140,7 @@ RING_SHAPES = [(1, 768, 256), (2, 1024, 64), (1, 3000, 32), (1, 3200, 40), (3, 2
                (150, 256, 512)]
 
 
-@pytest.mark.parametrize("knob", [0, 8, 9, 10, 11])
+@pytest.mark.parametrize("knob", [0, 8, 9, 10, 11, 12])
 @pytest.mark.parametrize("with_add", [False, True])
 @pytest.mark.parametrize("exact", [False, True])
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
@@ -148,7 +148,7 @@ RING_SHAPES = [(1, 768, 256), (2, 1024, 64), (1, 3000, 32), (1, 3200, 40), (3, 2
 def test_rmsnorm_bwd_cluster_of_four_kernels(dev, oracle, shape, dt, exact, with_add, knob):
     """Every persistent form of the backward (tuning knob norm_bwd = 0: two sweeps per tile, the second from L2;
     8: pair of blocks; 9: cluster of four, 64-byte rows, double-buffered strips; 10: cluster of four, 128-byte rows;
-    11: cluster of eight): ragged channel parts (C = 257, 3000), ragged token tiles, more tiles than resident
+    11: cluster of eight, 256-byte rows; 12: cluster of eight, 128-byte rows, double-buffered strips): ragged channel parts (C = 257, 3000), ragged token tiles, more tiles than resident
     blocks, pairs or clusters (the last two shapes: 320 to 2400 tiles, so every block steps through several
     rounds and the last round is ragged), and the same bits from two runs."""
     torch = _torch()
@@ -902,7 +902,7 @@ def test_c_chain_object_equals_python_host_chain(dev):
 # ane_cuda_set_tuning).  Each alternate path must give the same results within the same tolerances.
 ALT_KNOBS = [
     ("norm_fwd", 0), ("norm_fwd", 2), ("norm_fwd", 3), ("norm_fwd", 4), ("norm_fwd", 6),
-    ("norm_bwd", 0), ("norm_bwd", 8), ("norm_bwd", 9), ("norm_bwd", 10),
+    ("norm_bwd", 0), ("norm_bwd", 8), ("norm_bwd", 9), ("norm_bwd", 10), ("norm_bwd", 11), ("norm_bwd", 12),
     ("qk_fwd", 0), ("qk_fwd", 1), ("qk_fwd", 4), ("qk_bwd", 0), ("qk_bwd", 4),
     ("rope_lg", 8), ("rope_table", 0), ("embed_tiled", 0), ("embed_rows", 0), ("embed_sort", 1), ("xent_cluster", 1), ("xent_lg", 4), ("xent_lg", 8), ("xent_lg", 32), ("xent_split", 1), ("xent_split", 2), ("xent_split", 8),
 ]

@@ -76,7 +76,7 @@ def test_norm_operators_stay_inside_their_outputs(dev, shape, dt):
     G.check("rmsnorm")
     dev.residual_rmsnorm(x, f, w, 0.25, x2=G.new(shape, tdt), x2norm=G.new(shape, tdt))
     G.check("residual_rmsnorm")
-    for knob in (None, 0, 8, 9, 10, 11):
+    for knob in (None, 0, 8, 9, 10, 11, 12):
         if knob is not None:
             lib.set_tuning("norm_bwd", knob)
         try:
