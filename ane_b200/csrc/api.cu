@@ -84,6 +84,30 @@ int tuning(const char *name, int dflt) {
     return dflt;
 }
 
+bool check_extents_on() { return tuning("check_extents", 0) != 0; }
+
+int check_extent(const char *fn, const char *what, const void *p, size_t bytes) {
+    typedef CUresult (*RangeFn)(CUdeviceptr *, size_t *, CUdeviceptr);
+    static RangeFn range = nullptr;
+    if (!range) {
+        cudaDriverEntryPointQueryResult qr;
+        void *f = nullptr;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &f, cudaEnableDefault, &qr) != cudaSuccess || !f) {
+            cudaGetLastError();
+            return ANE_CUDA_OK;          // cannot check on this driver: do not block the call
+        }
+        range = reinterpret_cast<RangeFn>(f);
+    }
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (range(&base, &size, (CUdeviceptr)p) != CUDA_SUCCESS)
+        return fail(ANE_CUDA_ERR_INVALID, "%s: %s = %p is not inside a device allocation", fn, what, p);
+    const size_t off = (size_t)((CUdeviceptr)p - base);
+    if (bytes > size - off)
+        return fail(ANE_CUDA_ERR_INVALID, "%s: %s needs %zu bytes but its allocation has only %zu left from that address", fn, what, bytes, size - off);
+    return ANE_CUDA_OK;
+}
+
 static std::vector<void *> g_retired;      // device ranges replaced by larger ones; freed at shutdown
 static bool g_frozen = false;
 

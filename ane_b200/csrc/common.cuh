@@ -37,6 +37,17 @@ cudaError_t dev_malloc(void **p, size_t bytes);
 // Keeps a device range alive until ane_cuda_shutdown (ranges that were replaced but may still be referenced).
 void retire_device_range(void *p);
 bool frozen();
+// Debug mode (tuning knob "check_extents" = 1, e.g. ANE_CUDA_TUNING=check_extents=1): before an operator is launched,
+// every device range it is about to touch is checked against the allocation that holds the pointer (the driver knows the
+// extent of every allocation).  A buffer that is too small for the given shape comes back as ANE_CUDA_ERR_INVALID with the
+// argument's name instead of a stray write.  Off by default: one driver call per pointer.
+int check_extent(const char *fn, const char *what, const void *p, size_t bytes);
+bool check_extents_on();
+#define ANE_CHECK_EXTENT(ptr, bytes)                                                                                      \
+    do {                                                                                                                  \
+        if (::ane::check_extents_on() && (ptr))                                                                           \
+            if (int rc__ = ::ane::check_extent(__func__, #ptr, (ptr), (bytes))) return rc__;                              \
+    } while (0)
 // Kernel-selection knobs (ane_cuda_set_tuning); `dflt` when the knob was never set.
 int tuning(const char *name, int dflt);
 // Frees the cached RoPE cos/sin tables (rope.cu).

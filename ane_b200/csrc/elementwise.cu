@@ -223,6 +223,7 @@ int ane_cuda_residual_dev(void *stream, ane_dtype dtype, size_t n, void *out, co
     ANE_REQUIRE_INIT();
     ANE_REQUIRE(out && x && f, "%s: null pointer", __func__);
     if (n == 0) return ANE_CUDA_OK;
+    ANE_CHECK_EXTENT(out, n * dtype_size(dtype)); ANE_CHECK_EXTENT(x, n * dtype_size(dtype)); ANE_CHECK_EXTENT(f, n * dtype_size(dtype));
     EwPtrs<2, 1> p{{x, f}, {out}};
     ANE_DISPATCH_DTYPE(dtype, T, return (launch_ew<T, 2, 1>((cudaStream_t)stream, p, n, ResidualOp{alpha})));
     return ANE_CUDA_OK;
@@ -232,6 +233,7 @@ int ane_cuda_scale_dev(void *stream, ane_dtype dtype, size_t n, void *out, const
     ANE_REQUIRE_INIT();
     ANE_REQUIRE(out && x, "%s: null pointer", __func__);
     if (n == 0) return ANE_CUDA_OK;
+    ANE_CHECK_EXTENT(out, n * dtype_size(dtype)); ANE_CHECK_EXTENT(x, n * dtype_size(dtype));
     EwPtrs<1, 1> p{{x}, {out}};
     ANE_DISPATCH_DTYPE(dtype, T, return (launch_ew<T, 1, 1>((cudaStream_t)stream, p, n, ScaleOp{alpha})));
     return ANE_CUDA_OK;
@@ -241,6 +243,7 @@ int ane_cuda_swiglu_dev(void *stream, ane_dtype dtype, size_t n, void *out, cons
     ANE_REQUIRE_INIT();
     ANE_REQUIRE(out && h1 && h3, "%s: null pointer", __func__);
     if (n == 0) return ANE_CUDA_OK;
+    ANE_CHECK_EXTENT(out, n * dtype_size(dtype)); ANE_CHECK_EXTENT(h1, n * dtype_size(dtype)); ANE_CHECK_EXTENT(h3, n * dtype_size(dtype));
     EwPtrs<2, 1> p{{h1, h3}, {out}};
     ANE_DISPATCH_DTYPE(dtype, T, return (launch_ew<T, 2, 1>((cudaStream_t)stream, p, n, SwigluOp{})));
     return ANE_CUDA_OK;
@@ -251,6 +254,8 @@ int ane_cuda_swiglu_bwd_dev(void *stream, ane_dtype dtype, size_t n, void *dh1, 
     ANE_REQUIRE_INIT();
     ANE_REQUIRE(dh1 && dh3 && h1 && h3 && dsilu, "%s: null pointer", __func__);
     if (n == 0) return ANE_CUDA_OK;
+    ANE_CHECK_EXTENT(dh1, n * dtype_size(dtype)); ANE_CHECK_EXTENT(dh3, n * dtype_size(dtype)); ANE_CHECK_EXTENT(h1, n * dtype_size(dtype));
+    ANE_CHECK_EXTENT(h3, n * dtype_size(dtype)); ANE_CHECK_EXTENT(dsilu, n * dtype_size(dtype));
     EwPtrs<3, 2> p{{h1, h3, dsilu}, {dh1, dh3}};
     ANE_DISPATCH_DTYPE(dtype, T, return (launch_ew<T, 3, 2>((cudaStream_t)stream, p, n, SwigluBwdOp{})));
     return ANE_CUDA_OK;
@@ -263,6 +268,7 @@ int ane_cuda_adam_dev(void *stream, size_t n, float *w, const float *g, float *m
     ANE_REQUIRE(t >= 1, "%s: step t must be >= 1 (got %d)", __func__, t);
     ANE_REQUIRE(flags == ANE_ADAM_STORIES || flags == ANE_ADAM_DYNAMIC, "%s: bad flags %u", __func__, flags);
     if (n == 0) return ANE_CUDA_OK;
+    ANE_CHECK_EXTENT(w, n * 4); ANE_CHECK_EXTENT(g, n * 4); ANE_CHECK_EXTENT(m, n * 4); ANE_CHECK_EXTENT(v, n * 4);
     AdamOp op;
     op.b1 = b1; op.b2 = b2;
     op.omb1 = 1 - b1; op.omb2 = 1 - b2;

@@ -782,6 +782,8 @@ int ane_cuda_embed_lookup_dev(void *stream, ane_dtype dtype, ane_idtype idtype, 
     ANE_REQUIRE(idtype == ANE_ID_U16 || idtype == ANE_ID_I32, "%s: bad id type", __func__);
     ANE_REQUIRE(B >= 1 && D >= 1 && S >= 1 && vocab >= 1, "%s: bad shape B=%d D=%d S=%d vocab=%d", __func__, B, D, S, vocab);
     ANE_REQUIRE(flags == ANE_OOR_SKIP || flags == ANE_OOR_ZERO, "%s: bad flags %u", __func__, flags);
+    ANE_CHECK_EXTENT(x, (size_t)B * D * S * dtype_size(dtype)); ANE_CHECK_EXTENT(table, (size_t)vocab * D * dtype_size(dtype));
+    ANE_CHECK_EXTENT(tokens, (size_t)B * S * (idtype == ANE_ID_U16 ? 2 : 4));
     cudaStream_t st = (cudaStream_t)stream;
     const bool zero = flags == ANE_OOR_ZERO;
     ane_cuda_status *status = ctx().status;
@@ -840,6 +842,8 @@ int ane_cuda_embed_backward_dev(void *stream, ane_dtype dtype, ane_idtype idtype
     ANE_REQUIRE(idtype == ANE_ID_U16 || idtype == ANE_ID_I32, "%s: bad id type", __func__);
     ANE_REQUIRE(B >= 1 && D >= 1 && S >= 1 && vocab >= 1, "%s: bad shape B=%d D=%d S=%d vocab=%d", __func__, B, D, S, vocab);
     ANE_REQUIRE((long long)B * S < 0x7fffffffLL, "%s: too many tokens", __func__);
+    ANE_CHECK_EXTENT(d_embed, (size_t)vocab * D * 4); ANE_CHECK_EXTENT(dx, (size_t)B * D * S * dtype_size(dtype));
+    ANE_CHECK_EXTENT(tokens, (size_t)B * S * (idtype == ANE_ID_U16 ? 2 : 4));
     cudaStream_t st = (cudaStream_t)stream;
     const int n = B * S;
     const size_t esz = dtype_size(dtype);

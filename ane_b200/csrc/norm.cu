@@ -501,6 +501,7 @@ int ane_cuda_rmsnorm_dev(void *stream, ane_dtype dtype, int B, int C, int S, voi
     ANE_REQUIRE(out && x && w, "%s: null pointer", __func__);
     ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
     if (int rc = check_bcs(__func__, B, C, S)) return rc;
+    ANE_CHECK_EXTENT(out, (size_t)B * C * S * dtype_size(dtype)); ANE_CHECK_EXTENT(x, (size_t)B * C * S * dtype_size(dtype)); ANE_CHECK_EXTENT(w, (size_t)C * 4);
     return rmsnorm_fwd_any((cudaStream_t)stream, dtype, B, C, S, out, x, w, eps);
 }
 
@@ -511,6 +512,10 @@ int ane_cuda_residual_rmsnorm_dev(void *stream, ane_dtype dtype, int B, int C, i
     ANE_REQUIRE(x2 != x2norm, "%s: x2 and x2norm must be different buffers", __func__);
     ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
     if (int rc = check_bcs(__func__, B, C, S)) return rc;
+    {
+        const size_t nb = (size_t)B * C * S * dtype_size(dtype);
+        ANE_CHECK_EXTENT(x2, nb); ANE_CHECK_EXTENT(x2norm, nb); ANE_CHECK_EXTENT(x, nb); ANE_CHECK_EXTENT(f, nb); ANE_CHECK_EXTENT(w, (size_t)C * 4);
+    }
     ANE_DISPATCH_DTYPE(dtype, T, return (launch_rmsnorm_fwd<T, true>((cudaStream_t)stream, B, C, S, x2norm, x2, x, f, w, alpha, eps)));
     return ANE_CUDA_OK;
 }
@@ -522,6 +527,11 @@ int ane_cuda_rmsnorm_bwd_dev(void *stream, ane_dtype dtype, int B, int C, int S,
     ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
     ANE_REQUIRE(flags == ANE_NORM_BWD_REFERENCE || flags == ANE_NORM_BWD_EXACT, "%s: bad flags %u", __func__, flags);
     if (int rc = check_bcs(__func__, B, C, S)) return rc;
+    {
+        const size_t nb = (size_t)B * C * S * dtype_size(dtype);
+        ANE_CHECK_EXTENT(dx, nb); ANE_CHECK_EXTENT(dy, nb); ANE_CHECK_EXTENT(x, nb); ANE_CHECK_EXTENT(add, nb);
+        ANE_CHECK_EXTENT(w, (size_t)C * 4); ANE_CHECK_EXTENT(dw, (size_t)C * 4);
+    }
     return rmsnorm_bwd_any((cudaStream_t)stream, dtype, B, C, S, dx, dw, dy, x, w, add, eps, flags);
 }
 

@@ -1128,6 +1128,7 @@ int ane_cuda_rope_dev(void *stream, ane_dtype dtype, int B, int C, int S, int hd
     ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
     ANE_REQUIRE(B >= 1 && C >= 1 && S >= 1 && hd >= 2 && C % hd == 0, "%s: bad shape B=%d C=%d S=%d hd=%d", __func__, B, C, S, hd);
     ANE_REQUIRE(flags == ANE_ROPE_FORWARD || flags == ANE_ROPE_INVERSE, "%s: bad flags %u", __func__, flags);
+    ANE_CHECK_EXTENT(out, (size_t)B * C * S * dtype_size(dtype)); ANE_CHECK_EXTENT(x, (size_t)B * C * S * dtype_size(dtype));
     RopeFreq fq;
     if (int rc = fill_freq(fq, hd, base)) return rc;
     ANE_DISPATCH_DTYPE(dtype, T, return (launch_rope<T>((cudaStream_t)stream, B, C / hd, hd, S, out, x, base, pos0, flags == ANE_ROPE_INVERSE, fq)));
@@ -1141,6 +1142,11 @@ int ane_cuda_qknorm_dev(void *stream, ane_dtype dtype, int B, int heads, int hd,
     ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
     if (int rc = check_qk(__func__, B, heads, hd, S)) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+    {
+        const size_t nb = (size_t)B * heads * hd * S * dtype_size(dtype);
+        ANE_CHECK_EXTENT(out, nb); ANE_CHECK_EXTENT(x, nb);
+        ANE_CHECK_EXTENT(w, (size_t)hd * 4);
+    }
     RopeFreq fq = {};
     ANE_DISPATCH_DTYPE(dtype, T,
         if (qk_fast_ok<T, false>(hd, S, out, x, nullptr)) return (launch_qk_fwd<T, false>(st, B, heads, hd, S, out, x, w, eps, 0.0f, 0, fq)));
@@ -1155,6 +1161,11 @@ int ane_cuda_qknorm_bwd_dev(void *stream, ane_dtype dtype, int B, int heads, int
     ANE_REQUIRE(flags == ANE_NORM_BWD_REFERENCE || flags == ANE_NORM_BWD_EXACT, "%s: bad flags %u", __func__, flags);
     if (int rc = check_qk(__func__, B, heads, hd, S)) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+    {
+        const size_t nb = (size_t)B * heads * hd * S * dtype_size(dtype);
+        ANE_CHECK_EXTENT(dx, nb); ANE_CHECK_EXTENT(dy, nb); ANE_CHECK_EXTENT(x, nb);
+        ANE_CHECK_EXTENT(w, (size_t)hd * 4); ANE_CHECK_EXTENT(dw, (size_t)hd * 4);
+    }
     RopeFreq fq = {};
     ANE_DISPATCH_DTYPE(dtype, T,
         if (qk_fast_ok<T, false>(hd, S, dx, dy, x)) return (launch_qk_bwd<T, false>(st, B, heads, hd, S, dx, dw, dy, x, w, eps, 0.0f, 0, flags, fq)));
@@ -1168,6 +1179,11 @@ int ane_cuda_qknorm_rope_dev(void *stream, ane_dtype dtype, int B, int heads, in
     ANE_REQUIRE(dtype_ok(dtype), "%s: bad dtype", __func__);
     if (int rc = check_qk(__func__, B, heads, hd, S)) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+    {
+        const size_t nb = (size_t)B * heads * hd * S * dtype_size(dtype);
+        ANE_CHECK_EXTENT(out, nb); ANE_CHECK_EXTENT(x, nb);
+        ANE_CHECK_EXTENT(w, (size_t)hd * 4);
+    }
     RopeFreq fq;
     if (int rc = fill_freq(fq, hd, base)) return rc;
     ANE_DISPATCH_DTYPE(dtype, T,
@@ -1222,6 +1238,11 @@ int ane_cuda_rope_qknorm_bwd_dev(void *stream, ane_dtype dtype, int B, int heads
     ANE_REQUIRE(flags == ANE_NORM_BWD_REFERENCE || flags == ANE_NORM_BWD_EXACT, "%s: bad flags %u", __func__, flags);
     if (int rc = check_qk(__func__, B, heads, hd, S)) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+    {
+        const size_t nb = (size_t)B * heads * hd * S * dtype_size(dtype);
+        ANE_CHECK_EXTENT(dx, nb); ANE_CHECK_EXTENT(dy, nb); ANE_CHECK_EXTENT(x, nb);
+        ANE_CHECK_EXTENT(w, (size_t)hd * 4); ANE_CHECK_EXTENT(dw, (size_t)hd * 4);
+    }
     RopeFreq fq;
     if (int rc = fill_freq(fq, hd, base)) return rc;
     ANE_DISPATCH_DTYPE(dtype, T,

@@ -552,6 +552,8 @@ int ane_cuda_cross_entropy_dev(void *stream, ane_idtype idtype, int B, int V, in
     ANE_REQUIRE(idtype == ANE_ID_U16 || idtype == ANE_ID_I32, "%s: bad id type", __func__);
     ANE_REQUIRE(B >= 1 && V >= 1 && S >= 1, "%s: bad shape B=%d V=%d S=%d", __func__, B, V, S);
     ANE_REQUIRE((long long)B * S < 0x7fffffffLL, "%s: too many tokens", __func__);
+    ANE_CHECK_EXTENT(dlogits, (size_t)B * V * S * 4); ANE_CHECK_EXTENT(logits, (size_t)B * V * S * 4);
+    ANE_CHECK_EXTENT(targets, (size_t)B * S * (idtype == ANE_ID_U16 ? 2 : 4)); ANE_CHECK_EXTENT(loss_seq, (size_t)B * 4);
     cudaStream_t st = (cudaStream_t)stream;
     float *loss_tok = static_cast<float *>(workspace((size_t)B * S * sizeof(float)));
     if (!loss_tok) return fail(ANE_CUDA_ERR_NOMEM, "%s: no scratch", __func__);

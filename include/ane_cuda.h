@@ -94,6 +94,10 @@ void ane_cuda_reset_launch_count(void);
 int ane_cuda_set_tuning(const char *name, int value);
 /* Back to the built-in choice for one knob (NULL: for all of them). */
 int ane_cuda_clear_tuning(const char *name);
+/* One knob is a debugging aid rather than a kernel choice: "check_extents" = 1 makes every device-resident operator check,
+ * before it launches anything, that each device range it will touch lies inside the allocation that holds the pointer
+ * (the driver knows every allocation's extent); a buffer too small for the given shape returns ANE_CUDA_ERR_INVALID with
+ * the argument's name.  One driver call per pointer, so it is off by default. */
 
 ANECudaBuf *ane_cuda_alloc(size_t bytes);                       /* NULL on failure */
 int ane_cuda_write(ANECudaBuf *buf, size_t offset, const void *host, size_t bytes);  /* ane_bridge_write_input */

@@ -221,3 +221,45 @@ def test_ring_kernel_gives_up_cleanly_when_a_copy_never_arrives(dev, oracle, whi
     rdx, rdw = oracle.rope_qknorm_bwd(dq.float().cpu().numpy(), qn, wn, hd, eps=1e-6, base=1e6, pos0=0)
     assert rel_err(dx.float().cpu().numpy(), rdx) <= 2.0 ** -8 and rel_err(dw.cpu().numpy(), rdw) <= 1e-4
     assert lib.poll_status().wait_giveups == 0
+
+
+def test_extent_checking_mode_catches_buffers_that_are_too_small(dev):
+    """With the debug knob check_extents = 1 every device range an operator will touch is checked against the allocation
+    that holds the pointer, before anything is launched: an output (or input) one element short is an argument error
+    that names the argument, and the guard bytes behind it stay untouched."""
+    import ctypes as C
+    import torch
+    from ane_b200 import lib
+    L = lib.load()
+    B, Cn, S = 2, 64, 40
+    nbytes = B * Cn * S * 4
+    bufs = {k: L.ane_cuda_alloc(nbytes) for k in ("x", "out", "f")}
+    short = L.ane_cuda_alloc(nbytes - 4)
+    w = L.ane_cuda_alloc(Cn * 4)
+    assert all(bufs.values()) and short and w
+    ptr = lambda b: L.ane_cuda_devptr(b)
+    st = None
+    lib.set_tuning("check_extents", 1)
+    try:
+        assert L.ane_cuda_rmsnorm_dev(st, lib.F32, B, Cn, S, ptr(bufs["out"]), ptr(bufs["x"]), ptr(w), C.c_float(1e-5)) == lib.OK
+        assert L.ane_cuda_rmsnorm_dev(st, lib.F32, B, Cn, S, ptr(short), ptr(bufs["x"]), ptr(w), C.c_float(1e-5)) == lib.ERR_INVALID
+        assert b"out" in L.ane_cuda_last_error() and b"bytes" in L.ane_cuda_last_error()
+        assert L.ane_cuda_rmsnorm_dev(st, lib.F32, B, Cn, S, ptr(bufs["out"]), ptr(short), ptr(w), C.c_float(1e-5)) == lib.ERR_INVALID
+        assert L.ane_cuda_rmsnorm_dev(st, lib.F32, B, Cn + 1, S, ptr(bufs["out"]), ptr(bufs["x"]), ptr(w), C.c_float(1e-5)) == lib.ERR_INVALID   # w too small too
+        n = B * Cn * S
+        assert L.ane_cuda_residual_dev(st, lib.F32, n, ptr(bufs["out"]), ptr(bufs["x"]), ptr(bufs["f"]), C.c_float(0.5)) == lib.OK
+        assert L.ane_cuda_residual_dev(st, lib.F32, n, ptr(bufs["out"]), ptr(bufs["x"]), ptr(short), C.c_float(0.5)) == lib.ERR_INVALID
+        assert L.ane_cuda_swiglu_dev(st, lib.F32, n + 1, ptr(bufs["out"]), ptr(bufs["x"]), ptr(bufs["f"])) == lib.ERR_INVALID
+        assert L.ane_cuda_qknorm_rope_dev(st, lib.F32, B, 1, Cn, S, ptr(short), ptr(bufs["x"]), ptr(w), C.c_float(1e-6), C.c_float(1e4), 0) == lib.ERR_INVALID
+        host = (C.c_float * 4)()
+        assert L.ane_cuda_residual_dev(st, lib.F32, 4, ptr(bufs["out"]), C.cast(host, C.c_void_p), ptr(bufs["f"]), C.c_float(0.5)) == lib.ERR_INVALID   # not device memory
+        # a torch tensor inside the caching allocator's segment: the check sees the segment, so an in-range view passes
+        t = torch.zeros(B, Cn, S, device="cuda")
+        assert L.ane_cuda_rmsnorm_dev(torch.cuda.current_stream().cuda_stream, lib.F32, B, Cn, S, t.data_ptr(), t.data_ptr(), ptr(w), C.c_float(1e-5)) == lib.OK
+    finally:
+        lib.clear_tuning("check_extents")
+    # off again: the same short buffer is not looked at (and the call below stays inside it)
+    assert L.ane_cuda_residual_dev(st, lib.F32, n - 1, ptr(short), ptr(bufs["x"]), ptr(bufs["f"]), C.c_float(0.5)) == lib.OK
+    torch.cuda.synchronize()
+    for b in list(bufs.values()) + [short, w]:
+        L.ane_cuda_free(b)
