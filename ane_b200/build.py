@@ -50,7 +50,7 @@ def _stale(target: str, deps: list[str]) -> bool:
 
 def _compile(src: str, verbose: bool) -> tuple[str, str]:
     obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
-    cmd = [_nvcc(), *ARCH, *NVCC_FLAGS, "-c", src, "-o", obj]
+    cmd = [_nvcc(), *ARCH, *NVCC_FLAGS, *os.environ.get("ANE_NVCC_EXTRA", "").split(), "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     r = subprocess.run(cmd, capture_output=True, text=True)

@@ -15,6 +15,9 @@
 
 #include <cooperative_groups.h>
 
+#ifndef ANE_NORM_BWD_U
+#define ANE_NORM_BWD_U 4
+#endif
 namespace ane {
 
 namespace cgx = cooperative_groups;
@@ -285,7 +288,7 @@ rmsnorm_bwd_cluster_kernel(T *dx, float *__restrict__ partial, const T *dy, cons
     constexpr int R = ST_THREADS / LG;
     constexpr int TW = LG * VEC;
     constexpr int NW = ST_THREADS / 32;
-    constexpr int U = 4;
+    constexpr int U = ANE_NORM_BWD_U;
     static_assert(TW <= ST_THREADS, "one thread per token for the exchange");
     extern __shared__ uint4 strip[];                 // [NBUF buffers][x: [part][LG], dy: [part][LG]], then dw accumulators float[part]
     __shared__ __align__(16) float red[2][NW][TW];
