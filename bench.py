@@ -533,11 +533,14 @@ def run_ours(args):
                                 lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0,
                                 staging=symmetric_buffer(RegionShardedAdam.staging_floats(edges, world), device),
                                 deferred_broadcast=not args.no_deferred_broadcast)
+        exchange = (f"peer memory: every rank owns a share of every layer group; the gradients of {len(groups) - 1} of {len(groups)} groups are pushed "
+                    "to their owners by the copy engines (side stream) while the rest of the backward pass runs and are added from local "
+                    "memory in rank order, the last group, embedding and norm weights are read from the peers by the reduce kernel")
         if not args.no_deferred_broadcast:
             exchange += ("; Adam writes the new weights locally, the norm weights are copied to the peers at once and the matrices and the "
                          "embedding table by the copy engines beside the next step's operator chain (landed before the next optimizer step)")
-        exchange += (f"; every rank owns a share of every layer group, and the gradients of {len(groups) - 1} of {len(groups)} groups are pushed to "
-                     "their owners by the copy engines (side stream) while the rest of the backward pass runs")
+        else:
+            exchange += "; the Adam kernel stores the new weights to every rank"
 
     def step():
         params.zero_produced_grads()
