@@ -524,23 +524,27 @@ def run_ours(args):
     # group of layers can run while the remaining groups are computed.  Every rank owns a share of every group.
     groups, region_of_group = None, None
     if world > 1 and peer_ptrs is not None and args.overlap_groups > 1 and not args.early_reduce:
-        groups = chain.capture_segments(args.overlap_groups) if use_graph else chain.layer_groups(args.overlap_groups)
-        per_layer = cfg.matrix_params_per_layer()
-        edges = sorted({lo_ * per_layer for _, lo_ in groups} | {params.n_matrix, params.n_padded})
-        region_of_group = [edges.index(lo_ * per_layer) for _, lo_ in groups]
-        from ane_b200.sharded import symmetric_buffer
-        opt = RegionShardedAdam(params.w, params.g, params.m, params.v, params.n_decay, params.n, world, rank, peer_ptrs, edges,
-                                lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0,
-                                staging=symmetric_buffer(RegionShardedAdam.staging_floats(edges, world), device),
-                                deferred_broadcast=not args.no_deferred_broadcast)
-        exchange = (f"peer memory: every rank owns a share of every layer group; the gradients of {len(groups) - 1} of {len(groups)} groups are pushed "
-                    "to their owners by the copy engines (side stream) while the rest of the backward pass runs and are added from local "
-                    "memory in rank order, the last group, embedding and norm weights are read from the peers by the reduce kernel")
-        if not args.no_deferred_broadcast:
-            exchange += ("; Adam writes the new weights locally, the norm weights are copied to the peers at once and the matrices and the "
-                         "embedding table by the copy engines beside the next step's operator chain (landed before the next optimizer step)")
-        else:
-            exchange += "; the Adam kernel stores the new weights to every rank"
+        try:
+            groups = chain.capture_segments(args.overlap_groups) if use_graph else chain.layer_groups(args.overlap_groups)
+            per_layer = cfg.matrix_params_per_layer()
+            edges = sorted({lo_ * per_layer for _, lo_ in groups} | {params.n_matrix, params.n_padded})
+            region_of_group = [edges.index(lo_ * per_layer) for _, lo_ in groups]
+            from ane_b200.sharded import symmetric_buffer
+            opt = RegionShardedAdam(params.w, params.g, params.m, params.v, params.n_decay, params.n, world, rank, peer_ptrs, edges,
+                                    lr=3e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, clip=1.0,
+                                    staging=symmetric_buffer(RegionShardedAdam.staging_floats(edges, world), device),
+                                    deferred_broadcast=not args.no_deferred_broadcast)
+            exchange = (f"peer memory: every rank owns a share of every layer group; the gradients of {len(groups) - 1} of {len(groups)} groups are pushed "
+                        "to their owners by the copy engines (side stream) while the rest of the backward pass runs and are added from local "
+                        "memory in rank order, the last group, embedding and norm weights are read from the peers by the reduce kernel")
+            if not args.no_deferred_broadcast:
+                exchange += ("; Adam writes the new weights locally, the norm weights are copied to the peers at once and the matrices and the "
+                             "embedding table by the copy engines beside the next step's operator chain (landed before the next optimizer step)")
+            else:
+                exchange += "; the Adam kernel stores the new weights to every rank"
+        except Exception as exc:       # staging memory or graph capture unavailable: the one-slice peer form computes the same step
+            groups, region_of_group = None, None
+            exchange += f" (exchange beside the backward pass unavailable: {str(exc)[:120]})"
 
     def step():
         params.zero_produced_grads()
