@@ -45,3 +45,41 @@ def test_product_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 src = open(os.path.join(dirpath, f), errors="replace").read()
                 assert "oracle" not in src, os.path.join(dirpath, f)
+
+
+def test_host_mirrors_refuse_arrays_that_do_not_match_their_size_arguments():
+    """The reference's functions trust the caller with the sizes; the Python mirrors check every array against them before
+    anything reaches C (no GPU needed: the check comes first)."""
+    import numpy as np
+    import pytest
+    import torch
+    from ane_b200 import cpu_ops, host_ops
+    x, w = np.zeros((8, 4), np.float32), np.ones(8, np.float32)
+    with pytest.raises(ValueError, match="out"):
+        cpu_ops.rmsnorm(np.zeros((8, 3), np.float32), x, w, 8, 4)
+    with pytest.raises(ValueError, match="w"):
+        cpu_ops.rmsnorm(np.zeros_like(x), x, np.ones(7, np.float32), 8, 4)
+    with pytest.raises(TypeError):
+        cpu_ops.rmsnorm(np.zeros_like(x), x.astype(np.float64), w, 8, 4)
+    with pytest.raises(TypeError):
+        cpu_ops.rmsnorm(np.zeros_like(x), x.T, w, 4, 8)                       # not C-contiguous
+    with pytest.raises(ValueError):
+        cpu_ops.rmsnorm(np.zeros_like(x), x, w, 8, 0)
+    with pytest.raises(ValueError, match="targets"):
+        cpu_ops.cross_entropy_loss(np.zeros((5, 4), np.float32), np.zeros((5, 4), np.float32), np.zeros(3, np.uint16), 5, 4)
+    with pytest.raises(ValueError, match="head width"):
+        cpu_ops.rope_backward_inplace(np.zeros((12, 4), np.float32), 4, 12, 5)
+    st = cpu_ops.AdamState(8)
+    with pytest.raises(ValueError, match="g"):
+        cpu_ops.adam_update(np.zeros(8, np.float32), np.zeros(9, np.float32), st, 1, 1e-3, 0.9, 0.999, 1e-8)
+    with pytest.raises(ValueError, match="from 1"):
+        cpu_ops.adam_update(np.zeros(8, np.float32), np.zeros(8, np.float32), st, 0, 1e-3, 0.9, 0.999, 1e-8)
+    t = torch.zeros(2, 8, 4)
+    with pytest.raises(ValueError, match="out"):
+        host_ops.rmsnorm(torch.zeros(2, 8, 3), t, torch.ones(8))
+    with pytest.raises(ValueError, match="w"):
+        host_ops.rmsnorm(torch.zeros(2, 8, 4), t, torch.ones(9))
+    with pytest.raises(ValueError, match="heads"):
+        host_ops.qknorm_rope(torch.zeros(2, 8, 4), t, torch.ones(3), 3)
+    with pytest.raises(ValueError, match="dy"):
+        host_ops.rmsnorm_bwd(torch.zeros(2, 8, 4), torch.zeros(8), torch.zeros(2, 8, 4, dtype=torch.bfloat16), t, torch.ones(8))
