@@ -83,3 +83,24 @@ def test_host_mirrors_refuse_arrays_that_do_not_match_their_size_arguments():
         host_ops.qknorm_rope(torch.zeros(2, 8, 4), t, torch.ones(3), 3)
     with pytest.raises(ValueError, match="dy"):
         host_ops.rmsnorm_bwd(torch.zeros(2, 8, 4), torch.zeros(8), torch.zeros(2, 8, 4, dtype=torch.bfloat16), t, torch.ones(8))
+
+
+def test_chain_and_library_memory_calls_refuse_to_run_before_init():
+    import ctypes as C
+    import torch
+    if torch.cuda.is_available():
+        return
+    L = lib.load()
+    assert not L.ane_cuda_chain_create(None, 1, None)
+    assert b"ane_cuda_init" in L.ane_cuda_last_error()
+    assert L.ane_cuda_chain_step(None, None) == lib.ERR_NOT_INIT
+    assert L.ane_cuda_chain_sync(None) == lib.ERR_NOT_INIT
+    assert L.ane_cuda_chain_h2d_bytes(None) == 0 and L.ane_cuda_chain_d2h_bytes(None) == 0
+    assert not L.ane_cuda_chain_compute_stream(None)
+    L.ane_cuda_chain_destroy(None)                                   # a null chain is ignored
+    for rc in (L.ane_cuda_reserve_workspace(1 << 20), L.ane_cuda_freeze(1), L.ane_cuda_release_caches(),
+               L.ane_cuda_zero_dev(None, None, 16), L.ane_cuda_copy_dev(None, None, None, 16)):
+        assert rc == lib.ERR_NOT_INIT
+    sz = C.c_size_t()
+    assert L.ane_cuda_ckpt_tensor_offset(None, 0, 0, 0, C.byref(sz), C.byref(sz)) == lib.ERR_INVALID
+    assert L.ane_cuda_ckpt_flat_decay_count(None) == 0

@@ -177,3 +177,18 @@ def test_a_rank_that_leaves_between_steps_is_detected_not_waited_for():
     assert out[0][0] == "detected", out[0]
     assert out[0][1] < 60.0               # within the group's timeout, not forever
     assert out[0][3]                      # the failed step did not half-update this rank's own slice
+
+
+def test_layer_groups_cover_the_layers_in_backward_order():
+    """LayerChain.layer_groups: the groups tile the layers exactly, top layers first, for any group count; together with
+    RegionShardedAdam.partition this fixes which gradients a rank pushes after which part of the backward pass."""
+    from ane_b200.layer_chain import ChainConfig, LayerChain
+    for layers in (1, 5, 28):
+        ch = LayerChain.__new__(LayerChain)
+        ch.cfg = ChainConfig(layers=layers)
+        for n in (1, 2, 7, 28, 40):
+            groups = ch.layer_groups(n)
+            assert len(groups) == min(n, layers)
+            assert groups[0][0] == layers - 1 and groups[-1][1] == 0
+            assert all(hi >= lo for hi, lo in groups)
+            assert all(groups[i][1] == groups[i + 1][0] + 1 for i in range(len(groups) - 1))
