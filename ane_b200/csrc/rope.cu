@@ -449,7 +449,7 @@ struct ItemMap {
     }
 };
 
-template <typename T, int RPT, bool ROPE, int NST, bool TILED = false>
+template <typename T, int RPT, bool ROPE, int NST, bool TILED = false, bool PIPE = true>
 __global__ void __launch_bounds__(QK_THREADS)
 qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap, const float *__restrict__ w, int heads,
                   int S, int tiles_per_seq, int ntiles, float eps, ane_cuda_status *status,
@@ -510,6 +510,51 @@ qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap,
     for (int k = 0; k < RPT; k++) wc[k] = __ldg(w + rg * RPT + k);
     V<VEC> cs[RPT / 2], sn[RPT / 2];
 
+    // Scale, rotate and store the rows `r` of an item whose reciprocal norms are in tot[buf].
+    auto finish_item = [&](const Raw<T, VEC> (&r)[RPT], int b, int h, int t, int buf) {
+        const V<VEC> rr = lanes_from_smem<VEC>(&tot[buf][lg * VEC]);
+        V<VEC> v[RPT];
+#pragma unroll
+        for (int k = 0; k < RPT; k++) v[k] = vscale(vmul(r[k].get(), rr), wc[k]);
+        if (ROPE) {
+#pragma unroll
+            for (int p = 0; p < RPT / 2; p++) {
+                const V<VEC> a = v[2 * p], bb = v[2 * p + 1];
+                v[2 * p] = vsub(vmul(a, cs[p]), vmul(bb, sn[p]));
+                v[2 * p + 1] = vfma(a, sn[p], vmul(bb, cs[p]));
+            }
+        }
+        // out_ratio > 1: the result is written to the `out_ratio` query heads that share this KV head (the tiled
+        // layout of a grouped-query model, training_dynamic/io.h:330-337, as an index map instead of a copy)
+        const int n_out = TILED ? out_ratio : 1;
+        for (int q = 0; q < n_out; q++) {
+            const size_t o = TILED ? ((size_t)b * heads * out_ratio + (size_t)h * out_ratio + q) * hstep + (size_t)(rg * RPT) * S + t
+                                   : (size_t)b * heads * hstep + h * hstep + (size_t)(rg * RPT) * S + t;
+#pragma unroll
+            for (int k = 0; k < RPT; k++) {
+                Raw<T, VEC> ro;
+                ro.put(v[k]);
+                ro.store_stream(out + o + (size_t)k * S);
+            }
+        }
+    };
+    auto load_table = [&](int t) {
+#pragma unroll
+        for (int p = 0; p < RPT / 2; p++) {
+            cs[p] = table_lanes<VEC>(cosT + (size_t)(rg * (RPT / 2) + p) * S + t);
+            sn[p] = table_lanes<VEC>(sinT + (size_t)(rg * (RPT / 2) + p) * S + t);
+        }
+    };
+
+    // PIPE: one block barrier per item instead of two.  Iteration j reads item j from its stage and publishes its partial
+    // sums; after the barrier the reciprocal norms of item j are made, and item j-1 -- whose rows are still in registers and
+    // whose norms were made one barrier ago -- is scaled, rotated and stored.  The loads and sums of one item thus overlap the
+    // arithmetic and stores of the one before it.  red / tot alternate between two buffers, which the single barrier per
+    // item keeps apart (a buffer is rewritten two barriers after it was last read).
+    Raw<T, VEC> rp[RPT];
+    int pb = 0, phd = 0, pt = 0, pbuf = 0;
+    bool pactive = false;
+
     for (int j = 0; j < n_items; j++) {
         const int tl = ctl, h = ch;
         im.next(j + 1, ctl, ch);
@@ -517,13 +562,8 @@ qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap,
         const int t = (tl % tiles_per_seq) * TW + lg * VEC;
         const bool active = t < S;
         const int s = j % NST, buf = j & 1;
-        if (ROPE && (h == 0 || j == 0 || j == im.n_full) && active) {
-#pragma unroll
-            for (int p = 0; p < RPT / 2; p++) {
-                cs[p] = table_lanes<VEC>(cosT + (size_t)(rg * (RPT / 2) + p) * S + t);
-                sn[p] = table_lanes<VEC>(sinT + (size_t)(rg * (RPT / 2) + p) * S + t);
-            }
-        }
+        const bool new_tile = h == 0 || j == 0 || j == im.n_full;
+        if (!PIPE && ROPE && new_tile && active) load_table(t);
         if (!mbar_wait_bounded(&full[s], (uint32_t)(j / NST) & 1u, test.wait_limit)) atomicExch(&give_up, 1);
         const T *tile = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES);
         Raw<T, VEC> r[RPT];
@@ -546,34 +586,20 @@ qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap,
             const float sum = block_column_sum<QK_R, TW, QK_THREADS>(&red[buf][0][0], threadIdx.x);
             if (threadIdx.x % P == 0) tot[buf][threadIdx.x / P] = 1.0f / sqrtf(__fadd_rn(__fmul_rn(sum, invd), eps));
         }
-        __syncthreads();
-        if (active) {
-            const V<VEC> rr = lanes_from_smem<VEC>(&tot[buf][lg * VEC]);
-            V<VEC> v[RPT];
+        if (PIPE) {
+            if (j > 0 && pactive) finish_item(rp, pb, phd, pt, pbuf);
+            if (ROPE && new_tile && active) load_table(t);       // the table of item j's tile: used one iteration later
 #pragma unroll
-            for (int k = 0; k < RPT; k++) v[k] = vscale(vmul(r[k].get(), rr), wc[k]);
-            if (ROPE) {
-#pragma unroll
-                for (int p = 0; p < RPT / 2; p++) {
-                    const V<VEC> a = v[2 * p], bb = v[2 * p + 1];
-                    v[2 * p] = vsub(vmul(a, cs[p]), vmul(bb, sn[p]));
-                    v[2 * p + 1] = vfma(a, sn[p], vmul(bb, cs[p]));
-                }
-            }
-            // out_ratio > 1: the result is written to the `out_ratio` query heads that share this KV head (the tiled
-            // layout of a grouped-query model, training_dynamic/io.h:330-337, as an index map instead of a copy)
-            const int n_out = TILED ? out_ratio : 1;
-            for (int r = 0; r < n_out; r++) {
-                const size_t o = TILED ? ((size_t)b * heads * out_ratio + (size_t)h * out_ratio + r) * hstep + (size_t)(rg * RPT) * S + t
-                                       : (size_t)b * heads * hstep + h * hstep + (size_t)(rg * RPT) * S + t;
-#pragma unroll
-                for (int k = 0; k < RPT; k++) {
-                    Raw<T, VEC> ro;
-                    ro.put(v[k]);
-                    ro.store_stream(out + o + (size_t)k * S);
-                }
-            }
+            for (int k = 0; k < RPT; k++) rp[k] = r[k];
+            pb = b; phd = h; pt = t; pbuf = buf; pactive = active;
+        } else {
+            __syncthreads();
+            if (active) finish_item(r, b, h, t, buf);
         }
+    }
+    if (PIPE && n_items > 0) {
+        __syncthreads();                                   // the norms of the last item
+        if (pactive) finish_item(rp, pb, phd, pt, pbuf);
     }
 }
 
@@ -1024,9 +1050,11 @@ static int launch_qk_fwd(cudaStream_t st, int B, int heads, int hd, int S, void 
         if (int rc = make_bcs_tensor_map(&xmap, sizeof(T) == 4 ? ANE_F32 : (std::is_same<T, __half>::value ? ANE_F16 : ANE_BF16), x, B,
                                          heads * hd, S, QK_LG * VEC, hd)) return rc;
         const int ntiles = B * tps;
+        const bool pipe = tuning("qk_fwd_pipe", 1) != 0;      // one barrier per item (default) or two
 #define ANE_QKF_TMA(RPTv, NSTv)                                                                                      \
         do {                                                                                                         \
-            auto k = out_ratio > 1 ? qk_fwd_tma_kernel<T, RPTv, ROPE, NSTv, true> : qk_fwd_tma_kernel<T, RPTv, ROPE, NSTv, false>; \
+            auto k = out_ratio > 1 ? (pipe ? qk_fwd_tma_kernel<T, RPTv, ROPE, NSTv, true, true> : qk_fwd_tma_kernel<T, RPTv, ROPE, NSTv, true, false>) \
+                                   : (pipe ? qk_fwd_tma_kernel<T, RPTv, ROPE, NSTv, false, true> : qk_fwd_tma_kernel<T, RPTv, ROPE, NSTv, false, false>); \
             const size_t smem = (size_t)NSTv * (RPTv * QK_R) * (QK_LG * VEC) * sizeof(T) + 128;                             \
             ANE_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));           \
             int per_sm = 0;                                                                                          \
