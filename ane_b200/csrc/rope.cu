@@ -19,6 +19,9 @@ int rmsnorm_bwd_any(cudaStream_t st, ane_dtype dtype, int B, int C, int S, void 
                     const void *x, const float *w, const void *add, float eps, unsigned flags);
 
 constexpr int QK_THREADS = 256;
+#ifndef ANE_QK_BWD_PIPE_DEFAULT
+#define ANE_QK_BWD_PIPE_DEFAULT 1
+#endif
 
 // ------------------------------------------------------------------ cos / sin table
 // theta(t, i) = (pos0 + t) * freq[i] depends on neither the head nor the sequence, but evaluating
@@ -607,7 +610,7 @@ qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap,
 // KV head h); the GQ tiles of a head are added in fp32, in head order, and rounded once to T before anything else
 // uses them -- exactly what gqa_reduce followed by this operator computes (training_dynamic/io.h:340-351,
 // train.m:653-656), without the reduced tensor ever crossing HBM.
-template <typename T, int RPT, bool ROPE, int NST, int GQ = 1>
+template <typename T, int RPT, bool ROPE, int NST, int GQ = 1, bool PIPE = false>
 __global__ void __launch_bounds__(QK_THREADS, 2)
 qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_constant__ CUtensorMap dymap,
                   const __grid_constant__ CUtensorMap xmap, const float *__restrict__ w, int heads, int S, int tiles_per_seq,
@@ -677,6 +680,66 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
     for (int k = 0; k < RPT; k++) { wc[k] = __ldg(w + rg * RPT + k); dwacc[k] = 0.0f; }
     V<VEC> cs[RPT / 2], sn[RPT / 2];
 
+    // x and (summed) dy rows of pair p of a staged item, dy already rotated back
+    auto load_pair = [&](const T *xt, const T *dt, int p, V<VEC> &x0, V<VEC> &x1, V<VEC> &g0, V<VEC> &g1) {
+        Raw<T, VEC> a0, a1, c0, c1;
+        a0.load(xt + (rg * RPT + 2 * p) * TW + lg * VEC);
+        a1.load(xt + (rg * RPT + 2 * p + 1) * TW + lg * VEC);
+        c0.load(dt + (rg * RPT + 2 * p) * TW + lg * VEC);
+        c1.load(dt + (rg * RPT + 2 * p + 1) * TW + lg * VEC);
+        x0 = a0.get();
+        x1 = a1.get();
+        g0 = c0.get();
+        g1 = c1.get();
+        if (ROPE) {       // g = rope^-1(dy): (a cos + b sin, -a sin + b cos)   cpu_ops.h:178-181
+            const V<VEC> a = g0, bb = g1;
+            g0 = vfma(a, cs[p], vmul(bb, sn[p]));
+            g1 = vsub(vmul(bb, cs[p]), vmul(a, sn[p]));
+        }
+    };
+    // Sweep 2 of the item staged in stage `s`, whose (rrms, coef) are in tot[buf]: dx and the dw partial sums.  It reads the
+    // tile again from shared memory and redoes the inverse rotation (a few packed operations) -- sweep 1 keeps nothing but
+    // the two sums, and the register file then allows two blocks per SM.
+    auto sweep2 = [&](int s, int buf, int b, int h, int t) {
+        const T *xt = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES);
+        const T *dt = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES + TILE_BYTES);
+        const V<VEC> rr = lanes_from_smem<VEC>(&tot[buf][0][lg * VEC]);
+        const V<VEC> coef = lanes_from_smem<VEC>(&tot[buf][1][lg * VEC]);
+        const size_t o = (size_t)b * heads * hstep + h * hstep + (size_t)(rg * RPT) * S + t;
+#pragma unroll
+        for (int p = 0; p < RPT / 2; p++) {
+            V<VEC> xv[2], g[2];
+            load_pair(xt, dt, p, xv[0], xv[1], g[0], g[1]);
+#pragma unroll
+            for (int q = 0; q < 2; q++) {
+                const int k = 2 * p + q;
+                V<VEC> ov;
+                if (exact) ov = vmul(vsub(vscale(g[q], wc[k]), vmul(xv[q], coef)), rr);
+                else ov = vscale(vmul(vsub(g[q], vmul(xv[q], coef)), rr), wc[k]);
+                dwacc[k] += vmul(vmul(g[q], xv[q]), rr).hsum();
+                Raw<T, VEC> ro;
+                ro.put(ov);
+                ro.store_stream(dx + o + (size_t)k * S);
+            }
+        }
+    };
+    auto load_table = [&](int t) {
+#pragma unroll
+        for (int p = 0; p < RPT / 2; p++) {
+            cs[p] = table_lanes<VEC>(cosT + (size_t)(rg * (RPT / 2) + p) * S + t);
+            sn[p] = table_lanes<VEC>(sinT + (size_t)(rg * (RPT / 2) + p) * S + t);
+        }
+    };
+
+    // PIPE: sweep 2 of item j-1 runs AFTER sweep 1 of item j, behind the same barrier, so an item costs one block barrier
+    // instead of two and the loads and sums of one item overlap the arithmetic and stores of the one before it.  Both sweeps
+    // use the cos / sin values of their token tile, which live in registers once: where item j opens a new token tile, item
+    // j-1 is finished first (one extra barrier per tile).  A stage is refilled one barrier after its item's sweep 2.
+    int pend_s = 0, pend_buf = 0, pend_b = 0, pend_h = 0, pend_t = 0;     // item whose sweep 2 is still to run
+    bool pend = false, pend_active = false;
+    int freed = -1;                      // thread 0: every item <= freed has had its sweep 2 run by all threads (as of the last barrier)
+    int next_issue = n_items < NST ? n_items : NST;
+
     for (int j = 0; j < n_items; j++) {
         const int tl = ctl, h = ch;
         im.next(j + 1, ctl, ch);
@@ -684,13 +747,15 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
         const int t = (tl % tiles_per_seq) * TW + lg * VEC;
         const bool active = t < S;
         const int s = j % NST, buf = j & 1;
-        if (ROPE && (h == 0 || j == 0 || j == im.n_full) && active) {
-#pragma unroll
-            for (int p = 0; p < RPT / 2; p++) {
-                cs[p] = table_lanes<VEC>(cosT + (size_t)(rg * (RPT / 2) + p) * S + t);
-                sn[p] = table_lanes<VEC>(sinT + (size_t)(rg * (RPT / 2) + p) * S + t);
-            }
+        const bool new_tile = h == 0 || j == 0 || j == im.n_full;
+        bool flushed = false;
+        if (PIPE && pend && ROPE && new_tile) {       // finish item j-1 with its own tile's cos / sin before they are replaced
+            __syncthreads();                           // its (rrms, coef)
+            if (pend_active) sweep2(pend_s, pend_buf, pend_b, pend_h, pend_t);
+            pend = false;
+            flushed = true;
         }
+        if (ROPE && new_tile && active) load_table(t);
         if (!mbar_wait_bounded(&full[s], (uint32_t)(j / NST) & 1u, test.wait_limit)) atomicExch(&give_up, 1);
         const T *xt = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES);
         T *dt = reinterpret_cast<T *>(stages + (size_t)s * STAGE_BYTES + TILE_BYTES);
@@ -711,30 +776,11 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
                 a.store(dt + e);
             }
         }
-        // Sweep 1 keeps nothing but the two sums; sweep 2 reads the tile again from shared memory and
-        // redoes the inverse rotation (a few packed operations) -- the register file then allows two
-        // blocks per SM.
-        auto load_pair = [&](int p, V<VEC> &x0, V<VEC> &x1, V<VEC> &g0, V<VEC> &g1) {
-            Raw<T, VEC> a0, a1, c0, c1;
-            a0.load(xt + (rg * RPT + 2 * p) * TW + lg * VEC);
-            a1.load(xt + (rg * RPT + 2 * p + 1) * TW + lg * VEC);
-            c0.load(dt + (rg * RPT + 2 * p) * TW + lg * VEC);
-            c1.load(dt + (rg * RPT + 2 * p + 1) * TW + lg * VEC);
-            x0 = a0.get();
-            x1 = a1.get();
-            g0 = c0.get();
-            g1 = c1.get();
-            if (ROPE) {       // g = rope^-1(dy): (a cos + b sin, -a sin + b cos)   cpu_ops.h:178-181
-                const V<VEC> a = g0, bb = g1;
-                g0 = vfma(a, cs[p], vmul(bb, sn[p]));
-                g1 = vsub(vmul(bb, cs[p]), vmul(a, sn[p]));
-            }
-        };
         V<VEC> ss = V<VEC>::splat(0.0f), dot = V<VEC>::splat(0.0f);
 #pragma unroll
         for (int p = 0; p < RPT / 2; p++) {
             V<VEC> x0, x1, g0, g1;
-            load_pair(p, x0, x1, g0, g1);
+            load_pair(xt, dt, p, x0, x1, g0, g1);
             ss = vfma(x0, x0, ss);
             ss = vfma(x1, x1, ss);
             dot = vfma_s(vmul(g0, x0), wc[2 * p], dot);
@@ -746,12 +792,18 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
             lanes_to_smem<VEC>(&red[buf][0][threadIdx.x >> 5][lg * VEC], ss);
             lanes_to_smem<VEC>(&red[buf][1][threadIdx.x >> 5][lg * VEC], dot);
         }
-        __syncthreads();                                   // every thread has left sweep 2 of item j-1
+        __syncthreads();                                   // sweep 1 of item j published; every sweep 2 issued before it is done
         if (*(volatile int *)&give_up) {
             if (threadIdx.x == 0) { atomicAdd(&status->wait_giveups, 1); drain(j); }
             break;
         }
-        if (threadIdx.x == 0 && j >= 1 && j - 1 + NST < n_items) { fence_proxy_async(); issue(j - 1 + NST); }   // refill the stage of item j-1
+        if (threadIdx.x == 0) {
+            // PIPE: sweep 2 of item j-1 runs after this barrier, so items <= j-2 are done (item j-1 too when it was flushed);
+            // otherwise sweep 2 of item j-1 ran before this barrier
+            freed = PIPE ? (flushed ? j - 1 : j - 2) : j - 1;
+            if (next_issue < n_items && next_issue - NST <= freed) { fence_proxy_async(); }
+            while (next_issue < n_items && next_issue - NST <= freed) issue(next_issue++);
+        }
         {
             constexpr int P = QK_THREADS / TW;
             const float s0 = block_column_sum<NWARP, TW, QK_THREADS>(&red[buf][0][0][0], threadIdx.x);
@@ -764,28 +816,17 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
                 tot[buf][1][threadIdx.x / P] = s1 * r2;
             }
         }
-        __syncthreads();
-        if (active) {
-            const V<VEC> rr = lanes_from_smem<VEC>(&tot[buf][0][lg * VEC]);
-            const V<VEC> coef = lanes_from_smem<VEC>(&tot[buf][1][lg * VEC]);
-            const size_t o = (size_t)b * heads * hstep + h * hstep + (size_t)(rg * RPT) * S + t;
-#pragma unroll
-            for (int p = 0; p < RPT / 2; p++) {
-                V<VEC> xv[2], g[2];
-                load_pair(p, xv[0], xv[1], g[0], g[1]);
-#pragma unroll
-                for (int q = 0; q < 2; q++) {
-                    const int k = 2 * p + q;
-                    V<VEC> ov;
-                    if (exact) ov = vmul(vsub(vscale(g[q], wc[k]), vmul(xv[q], coef)), rr);
-                    else ov = vscale(vmul(vsub(g[q], vmul(xv[q], coef)), rr), wc[k]);
-                    dwacc[k] += vmul(vmul(g[q], xv[q]), rr).hsum();
-                    Raw<T, VEC> ro;
-                    ro.put(ov);
-                    ro.store_stream(dx + o + (size_t)k * S);
-                }
-            }
+        if (PIPE) {
+            if (pend && pend_active) sweep2(pend_s, pend_buf, pend_b, pend_h, pend_t);      // item j-1 (same token tile: same cos / sin)
+            pend = true; pend_s = s; pend_buf = buf; pend_b = b; pend_h = h; pend_t = t; pend_active = active;
+        } else {
+            __syncthreads();
+            if (active) sweep2(s, buf, b, h, t);
         }
+    }
+    if (PIPE && pend && !*(volatile int *)&give_up) {
+        __syncthreads();                                   // the (rrms, coef) of the last item
+        if (pend_active) sweep2(pend_s, pend_buf, pend_b, pend_h, pend_t);
     }
 #pragma unroll
     for (int k = 0; k < RPT; k++) {
@@ -1098,9 +1139,10 @@ static int launch_qk_bwd(cudaStream_t st, int B, int heads, int hd, int S, void 
         CUtensorMap xmap, dymap;
         if (int rc = make_bcs_tensor_map(&xmap, dte, x, B, heads * hd, S, QK_LG * VEC, hd)) return rc;
         if (int rc = make_bcs_tensor_map(&dymap, dte, dy, B, heads * hd, S, QK_LG * VEC, hd)) return rc;
+        const bool pipe_b = tuning("qk_bwd_pipe", ANE_QK_BWD_PIPE_DEFAULT) != 0;      // one barrier per item, or two
 #define ANE_QKB_TMA(RPTv, NSTv)                                                                                      \
         do {                                                                                                         \
-            auto k = qk_bwd_tma_kernel<T, RPTv, ROPE, NSTv>;                                                          \
+            auto k = pipe_b ? qk_bwd_tma_kernel<T, RPTv, ROPE, NSTv, 1, true> : qk_bwd_tma_kernel<T, RPTv, ROPE, NSTv, 1, false>; \
             const size_t smem = (size_t)NSTv * 2 * (RPTv * QK_R) * (QK_LG * VEC) * sizeof(T) + 128;                         \
             ANE_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));           \
             int per_sm = 0;                                                                                          \

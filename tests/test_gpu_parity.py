@@ -338,9 +338,19 @@ def test_qknorm_and_fusions_bwd(dev, oracle, B, heads, hd, S, dt, exact):
 QK_ROUNDS = [(10, 16, 128, 2048), (19, 8, 128, 2048), (5, 16, 128, 2048 + 64 + 8), (12, 12, 64, 2048), (38, 2, 128, 2048)]
 
 
+@pytest.mark.parametrize("pipe", [0, 1])
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
 @pytest.mark.parametrize("B,heads,hd,S", QK_ROUNDS)
-def test_qk_kernels_over_several_rounds_fwd(dev, oracle, B, heads, hd, S, dt):
+def test_qk_kernels_over_several_rounds_fwd(dev, oracle, B, heads, hd, S, dt, pipe):
+    from ane_b200 import lib
+    lib.set_tuning("qk_fwd_pipe", pipe)                  # one block barrier per item, or two
+    try:
+        _qk_rounds_fwd(dev, oracle, B, heads, hd, S, dt)
+    finally:
+        lib.clear_tuning("qk_fwd_pipe")
+
+
+def _qk_rounds_fwd(dev, oracle, B, heads, hd, S, dt):
     from ane_b200 import lib
     r = gi.rng(53)
     x = gi.normal(r, (B, heads * hd, S))
@@ -354,10 +364,21 @@ def test_qk_kernels_over_several_rounds_fwd(dev, oracle, B, heads, hd, S, dt):
     assert lib.poll_status().wait_giveups == 0
 
 
+@pytest.mark.parametrize("pipe", [0, 1])
 @pytest.mark.parametrize("exact", [False, True])
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
 @pytest.mark.parametrize("B,heads,hd,S", QK_ROUNDS)
-def test_qk_kernels_over_several_rounds_bwd(dev, oracle, B, heads, hd, S, dt, exact):
+def test_qk_kernels_over_several_rounds_bwd(dev, oracle, B, heads, hd, S, dt, exact, pipe):
+    torch = _torch()
+    from ane_b200 import lib
+    lib.set_tuning("qk_bwd_pipe", pipe)                  # one block barrier per item, or two
+    try:
+        _qk_rounds_bwd(dev, oracle, B, heads, hd, S, dt, exact)
+    finally:
+        lib.clear_tuning("qk_bwd_pipe")
+
+
+def _qk_rounds_bwd(dev, oracle, B, heads, hd, S, dt, exact):
     torch = _torch()
     from ane_b200 import lib
     r = gi.rng(54)
@@ -903,7 +924,7 @@ def test_c_chain_object_equals_python_host_chain(dev):
 ALT_KNOBS = [
     ("norm_fwd", 0), ("norm_fwd", 2), ("norm_fwd", 3), ("norm_fwd", 4), ("norm_fwd", 6),
     ("norm_bwd", 0), ("norm_bwd", 8), ("norm_bwd", 9), ("norm_bwd", 10), ("norm_bwd", 11), ("norm_bwd", 12),
-    ("qk_fwd", 0), ("qk_fwd", 1), ("qk_fwd", 4), ("qk_bwd", 0), ("qk_bwd", 4),
+    ("qk_fwd", 0), ("qk_fwd", 1), ("qk_fwd", 4), ("qk_bwd", 0), ("qk_bwd", 4), ("qk_fwd_pipe", 0), ("qk_bwd_pipe", 0), ("qk_bwd_pipe", 1),
     ("rope_lg", 8), ("rope_table", 0), ("embed_tiled", 0), ("embed_rows", 0), ("embed_sort", 1), ("xent_cluster", 1), ("xent_lg", 4), ("xent_lg", 8), ("xent_lg", 32), ("xent_split", 1), ("xent_split", 2), ("xent_split", 8),
 ]
 
