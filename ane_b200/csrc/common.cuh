@@ -213,11 +213,18 @@ template <int N> struct V {
     }
     __device__ __forceinline__ float get(int j) const { return (j & 1) ? p[j >> 1].y : p[j >> 1].x; }
     __device__ __forceinline__ void set(int j, float v) { if (j & 1) p[j >> 1].y = v; else p[j >> 1].x = v; }
+    // Sum of the N lanes in a fixed tree order: packed adds halve the pair count each step, the last pair is added
+    // across.  (N / 2 must be a power of two: 2, 4 or 8 lanes in every use.)
     __device__ __forceinline__ float hsum() const {
-        float s = 0.0f;
+        float2 t[N / 2];
 #pragma unroll
-        for (int i = 0; i < N / 2; i++) { s += p[i].x; s += p[i].y; }
-        return s;
+        for (int i = 0; i < N / 2; i++) t[i] = p[i];
+#pragma unroll
+        for (int w = N / 4; w >= 1; w >>= 1) {
+#pragma unroll
+            for (int i = 0; i < w; i++) t[i] = f2_add(t[i], t[i + w]);
+        }
+        return t[0].x + t[0].y;
     }
 };
 template <> struct V<1> {
