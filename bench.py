@@ -706,12 +706,14 @@ def run_ours(args):
                                f"memory inside the timed region ({(h2d + d2h) / dt / 1e9:.1f} GB/s over PCIe, both directions); "
                                "PCIe-bound.  python_chain_value: the same step driven by ane_b200.host_chain.HostLayerChain over torch streams"}
         torch.cuda.empty_cache()
-        if world > 1:       # how much of the per-rank PCIe rate is left when all ranks copy at once, operators aside
-            dist.barrier()
+        if True:            # how much of the per-rank PCIe rate is left when all ranks copy at once, operators aside
+            if world > 1:
+                dist.barrier()
             r = torch.tensor([pcie_copy_only(torch, device)], device=device)
             lo_, hi_ = r.clone(), r.clone()
-            dist.all_reduce(lo_, op=dist.ReduceOp.MIN)
-            dist.all_reduce(hi_, op=dist.ReduceOp.MAX)
+            if world > 1:
+                dist.all_reduce(lo_, op=dist.ReduceOp.MIN)
+                dist.all_reduce(hi_, op=dist.ReduceOp.MAX)
             line["e2e"]["copy_only_GBps_per_rank_min_max"] = [round(float(lo_[0]), 1), round(float(hi_[0]), 1)]
             line["e2e"]["chain_GBps_per_rank"] = round((h2d + d2h) / dt / 1e9, 1)
             try:

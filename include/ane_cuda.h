@@ -22,7 +22,8 @@
  *
  * There is no CPU fallback: every operator runs on the GPU or returns an error.
  * Threading: one host thread per device at a time (the reference's operators are likewise
- * never re-entered concurrently, training/training_dynamic/train.m:727-749).
+ * never re-entered concurrently, training/training_dynamic/train.m:727-749).  Which thread that is
+ * may change between calls; the text behind ane_cuda_last_error() is kept per thread.
  */
 #ifndef ANE_CUDA_H
 #define ANE_CUDA_H

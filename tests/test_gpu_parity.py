@@ -737,6 +737,38 @@ def test_buffers_and_errors(dev):
     assert lib.launch_count() == before
 
 
+def test_another_host_thread_may_take_over_and_errors_stay_with_their_thread(dev, oracle):
+    """The header's threading contract: one host thread at a time, any thread.  A worker thread that runs while the main
+    thread waits gets the same bits as the main thread, and the text of an error made on the worker is the worker's:
+    the main thread's last error is not overwritten (training/training_dynamic/train.m:727-749 -- the reference's
+    operators are called from one thread at a time too)."""
+    import threading
+    from ane_b200 import lib
+    L = lib.load()
+    x = gi.normal(gi.rng(71), (3, 96, 40))
+    w = (1.0 + 0.02 * gi.normal(gi.rng(72), (96,))).astype(np.float32)
+    xt, _ = up(x)
+    wt, _ = up(w)
+    here = down(dev.rmsnorm(xt, wt))
+    assert L.ane_cuda_rmsnorm_dev(None, 7, 1, 8, 8, 1, 1, 1, C.c_float(1e-5)) == lib.ERR_INVALID
+    mine = L.ane_cuda_last_error()
+    box = {}
+
+    def worker():
+        box["out"] = down(dev.rmsnorm(xt, wt))
+        box["rc"] = L.ane_cuda_rope_dev(None, lib.F32, 1, 12, 8, 5, 1, 1, C.c_float(1e4), 0, 0)
+        box["err"] = L.ane_cuda_last_error()
+
+    th = threading.Thread(target=worker)
+    th.start()
+    th.join()
+    assert np.array_equal(box["out"], here)
+    assert box["rc"] == lib.ERR_INVALID and box["err"] and box["err"] != mine
+    assert L.ane_cuda_last_error() == mine
+    ref = np.stack([oracle.rmsnorm(x[b], w) for b in range(x.shape[0])])
+    assert rel_err(here, ref) <= TOL32
+
+
 # ------------------------------------------------------------------ benchmark sizes: size-independent properties
 def test_full_size_properties(dev):
     """Qwen3 shapes at S = 2048 in bf16: RoPE forward then inverse returns the input (to bf16
