@@ -60,6 +60,32 @@ void embed_side_release();
 #define ANE_CUDA_TRY(expr) do { cudaError_t e__ = (expr); if (e__ != cudaSuccess) return ::ane::fail(ANE_CUDA_ERR_CUDA, "%s: %s failed: %s", __func__, #expr, cudaGetErrorString(e__)); } while (0)
 #define ANE_LAUNCH_OK(n) do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) return ::ane::fail(ANE_CUDA_ERR_CUDA, "%s: kernel launch failed: %s", __func__, cudaGetErrorString(e__)); ::ane::note_launch(n); } while (0)
 
+// Programmatic dependent launch.  A kernel started through launch_dep() may be placed on the SMs while the kernel before
+// it on the stream is still draining its last blocks: its blocks run their own set-up (index arithmetic, barrier
+// initialisation) and then stop in dep_sync() until that kernel has completed and its memory is visible.  Rule for every
+// kernel launched this way: NO access to global memory before dep_sync(), and every thread calls it.  dep_sync() then lets
+// the kernel after this one be placed in turn, so at most one kernel ever waits behind the running one.  Launched the plain
+// way (<<<>>>, or knob "dep_launch" = 0) both instructions do nothing.
+__device__ __forceinline__ void dep_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+static inline void launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = tuning("dep_launch", 1) != 0 ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);      // the error, if any, is picked up by ANE_LAUNCH_OK
+}
+
 static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 static inline size_t dtype_size(ane_dtype d) { return d == ANE_F32 ? 4 : 2; }
 static inline bool dtype_ok(ane_dtype d) { return d == ANE_F32 || d == ANE_BF16 || d == ANE_F16; }
@@ -344,6 +370,7 @@ __global__ void __launch_bounds__(256) column_sum_add_kernel(float *__restrict__
     const int per = (rows + 7) / 8;
     const int r0 = sl * per, r1 = r0 + per < rows ? r0 + per : rows;
     float s = 0.0f;
+    dep_sync();
     if (c < cols) {
         int r = r0;
         for (; r + 8 <= r1; r += 8) {

@@ -23,6 +23,7 @@ __global__ void __launch_bounds__(EW_THREADS)
 ew_vec_kernel(EwPtrs<NIN, NOUT> p, size_t n_vec, int n_tail, Op op) {
     constexpr int VEC = Elt<T>::VEC;
     const size_t base = (size_t)blockIdx.x * (EW_THREADS * EW_UNROLL) + threadIdx.x;
+    dep_sync();
     Raw<T, VEC> r[EW_UNROLL][NIN];
 #pragma unroll
     for (int u = 0; u < EW_UNROLL; u++) {
@@ -95,7 +96,7 @@ static int launch_ew(cudaStream_t st, const EwPtrs<NIN, NOUT> &p, size_t n, Op o
         size_t blocks = (n_vec + (size_t)EW_THREADS * EW_UNROLL - 1) / ((size_t)EW_THREADS * EW_UNROLL);
         if (blocks == 0) blocks = 1;
         if (blocks > 0x7fffffffull) return fail(ANE_CUDA_ERR_UNSUPPORTED, "element count %zu too large", n);
-        ew_vec_kernel<T, NIN, NOUT, Op><<<(unsigned)blocks, EW_THREADS, 0, st>>>(p, n_vec, n_tail, op);
+        launch_dep(ew_vec_kernel<T, NIN, NOUT, Op>, dim3((unsigned)blocks), dim3(EW_THREADS), 0, st, p, n_vec, n_tail, op);
     } else {
         size_t blocks = (n + EW_THREADS - 1) / EW_THREADS;
         if (blocks > 148 * 32) blocks = 148 * 32;

@@ -230,8 +230,8 @@ static int launch_rmsnorm_fwd(cudaStream_t st, int B, int C, int S, void *out, v
 #define ANE_FWD_RR(LGv, THv, NVv)                                                                                   \
         do {                                                                                                        \
             const int tps_ = (S + (LGv) * VEC - 1) / ((LGv) * VEC);                                                  \
-            rmsnorm_fwd_rr_kernel<T, LGv, THv, NVv, FUSE_RES><<<(unsigned)(B * tps_), THv, 0, st>>>(                 \
-                (T *)out, (T *)x2, (const T *)x, (const T *)f, w, C, S, tps_, alpha, eps);                          \
+            launch_dep(rmsnorm_fwd_rr_kernel<T, LGv, THv, NVv, FUSE_RES>, dim3((unsigned)(B * tps_)), dim3(THv), 0, st, \
+                       (T *)out, (T *)x2, (const T *)x, (const T *)f, w, C, S, tps_, alpha, eps);                   \
             ANE_LAUNCH_OK(1);                                                                                       \
             return ANE_CUDA_OK;                                                                                     \
         } while (0)
@@ -252,7 +252,7 @@ static int launch_rmsnorm_fwd(cudaStream_t st, int B, int C, int S, void *out, v
             const size_t smem = (size_t)C * LGs * 16;
             auto k_ = rmsnorm_fwd_st_kernel<T, LGs, FUSE_RES>;
             ANE_CUDA_TRY(cudaFuncSetAttribute(k_, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            k_<<<(unsigned)(B * tps_), ST_THREADS, smem, st>>>((T *)out, (T *)x2, (const T *)x, (const T *)f, w, C, S, tps_, alpha, eps);
+            launch_dep(k_, dim3((unsigned)(B * tps_)), dim3(ST_THREADS), smem, st, (T *)out, (T *)x2, (const T *)x, (const T *)f, w, C, S, tps_, alpha, eps);
             ANE_LAUNCH_OK(1);
             return ANE_CUDA_OK;
         }
@@ -315,8 +315,8 @@ static int launch_rmsnorm_bwd_cluster(cudaStream_t st, int B, int C, int S, void
     const int ngroups = max_clusters < ntiles ? max_clusters : ntiles;
     float *partial = static_cast<float *>(workspace((size_t)ngroups * C * sizeof(float)));
     if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", ngroups, C);
-    k_<<<(unsigned)(CL * ngroups), ST_THREADS, smem_st, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags);
-    column_sum_add_kernel<><<<(C + 31) / 32, 256, 0, st>>>(dw, partial, ngroups, C);
+    launch_dep(k_, dim3((unsigned)(CL * ngroups)), dim3(ST_THREADS), smem_st, st, (T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags);
+    launch_dep(column_sum_add_kernel<>, dim3((C + 31) / 32), dim3(256), 0, st, dw, (const float *)partial, ngroups, C);
     ANE_LAUNCH_OK(2);
     return ANE_CUDA_OK;
 }
@@ -366,8 +366,8 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
             if (npairs > ntiles) npairs = ntiles;
             partial = static_cast<float *>(workspace((size_t)npairs * C * sizeof(float)));
             if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", npairs, C);
-            k_<<<(unsigned)(2 * npairs), ST_THREADS, smem_st, st>>>((T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags);
-            column_sum_add_kernel<><<<(C + 31) / 32, 256, 0, st>>>(dw, partial, npairs, C);
+            launch_dep(k_, dim3((unsigned)(2 * npairs)), dim3(ST_THREADS), smem_st, st, (T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags);
+            launch_dep(column_sum_add_kernel<>, dim3((C + 31) / 32), dim3(256), 0, st, dw, (const float *)partial, npairs, C);
             ANE_LAUNCH_OK(2);
             return ANE_CUDA_OK;
         }

@@ -32,6 +32,7 @@ rmsnorm_fwd_rr_kernel(T *out, T *x2out, const T *x, const T *f, const float *__r
 
     Raw<T, VEC> r[NV];
     V<VEC> ss = V<VEC>::splat(0.0f);
+    dep_sync();
 
     if (!FUSE_RES) {
 #pragma unroll

@@ -47,6 +47,7 @@ rmsnorm_fwd_st_kernel(T *out, T *x2out, const T *x, const T *f, const float *__r
     const int t = (blockIdx.x % tiles_per_seq) * TW + lg * VEC;
     const bool active = t < S;
     const size_t base = (size_t)b * C * S + t;
+    dep_sync();
 
     if (active)
         for (int c = rg; c < C; c += R) cp_async16(&strip[c * LG + lg], x + base + (size_t)c * S);
@@ -146,6 +147,7 @@ rmsnorm_bwd_pair_kernel(T *dx, float *__restrict__ partial, const T *dy, const T
 
     for (int c = threadIdx.x; c < Cn; c += ST_THREADS) dwacc[c] = 0.0f;
     __syncthreads();
+    dep_sync();
 
     // The strips are software-pipelined across tiles without any extra barrier: a strip entry is only ever touched
     // by the thread that copied it, so as soon as sweep 2 has read an entry the same thread issues the copy of the
@@ -309,6 +311,7 @@ rmsnorm_bwd_cluster_kernel(T *dx, float *__restrict__ partial, const T *dy, cons
 
     for (int c = threadIdx.x; c < Cn; c += ST_THREADS) dwacc[c] = 0.0f;
     __syncthreads();
+    dep_sync();
 
     auto tile_base = [&](int tile, bool &act) -> size_t {
         const int b = tile / tiles_per_seq;

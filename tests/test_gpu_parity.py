@@ -957,7 +957,7 @@ ALT_KNOBS = [
     ("norm_fwd", 0), ("norm_fwd", 2), ("norm_fwd", 3), ("norm_fwd", 4), ("norm_fwd", 6),
     ("norm_bwd", 0), ("norm_bwd", 8), ("norm_bwd", 9), ("norm_bwd", 10), ("norm_bwd", 11), ("norm_bwd", 12),
     ("qk_fwd", 0), ("qk_fwd", 1), ("qk_fwd", 4), ("qk_bwd", 0), ("qk_bwd", 4), ("qk_fwd_pipe", 0), ("qk_bwd_pipe", 0), ("qk_bwd_pipe", 1),
-    ("rope_lg", 8), ("rope_table", 0), ("embed_tiled", 0), ("embed_rows", 0), ("embed_sort", 1), ("xent_cluster", 1), ("xent_lg", 4), ("xent_lg", 8), ("xent_lg", 32), ("xent_split", 1), ("xent_split", 2), ("xent_split", 8),
+    ("dep_launch", 0), ("rope_lg", 8), ("rope_table", 0), ("embed_tiled", 0), ("embed_rows", 0), ("embed_sort", 1), ("xent_cluster", 1), ("xent_lg", 4), ("xent_lg", 8), ("xent_lg", 32), ("xent_split", 1), ("xent_split", 2), ("xent_split", 8),
 ]
 
 
@@ -1027,6 +1027,75 @@ def test_alternate_kernels_match_the_oracle(dev, oracle, knob, value):
         assert lib.poll_status().wait_giveups == 0
     finally:
         lib.clear_tuning(knob)
+
+
+class _DependentChain:
+    """Operators that hand their results to each other in place, back to back on one stream: every launch reads what the
+    launch before it wrote and overwrites what an earlier one read."""
+
+    def __init__(self, torch, B=32, Cn=1024, S=2048, hd=128):
+        self.torch, self.hd = torch, hd
+        gen = torch.Generator(device="cuda").manual_seed(4242)
+        self.x0 = torch.randn(B, Cn, S, device="cuda", generator=gen).bfloat16()
+        self.f0 = torch.randn(B, Cn, S, device="cuda", generator=gen).bfloat16()
+        self.w = (1.0 + 0.02 * torch.randn(Cn, device="cuda", generator=gen)).float()
+        self.wq = (1.0 + 0.1 * torch.randn(hd, device="cuda", generator=gen)).float()
+        self.x, self.f = self.x0.clone(), self.f0.clone()
+        self.dw, self.dwq = torch.zeros(Cn, device="cuda"), torch.zeros(hd, device="cuda")
+        self.x2, self.x2n, self.g, self.h, self.q, self.dq = (torch.empty_like(self.x0) for _ in range(6))
+
+    def reset(self):
+        self.x.copy_(self.x0)
+        self.f.copy_(self.f0)
+        self.dw.zero_()
+        self.dwq.zero_()
+
+    def run(self, dev, rounds):
+        for _ in range(rounds):
+            dev.residual_rmsnorm(self.x, self.f, self.w, 0.3, x2=self.x2, x2norm=self.x2n)
+            dev.swiglu(self.x2n, self.x2, out=self.g)
+            dev.qknorm_rope(self.g, self.wq, self.hd, 1e-6, 1e6, 0, out=self.q)
+            dev.rope_qknorm_bwd(self.q, self.g, self.wq, self.dwq, self.hd, 1e-6, 1e6, 0, out=self.dq)
+            dev.swiglu_bwd(self.x2n, self.x2, self.dq, dh1=self.h, dh3=self.f)   # f is overwritten: the next round's residual reads it
+            dev.rmsnorm_bwd(self.h, self.x2, self.w, self.dw, add=self.q, out=self.x)   # x too
+            dev.scale(self.x, 0.05, out=self.x)                                 # keeps the loop bounded
+
+    def results(self):
+        self.torch.cuda.synchronize()
+        return [t.clone() for t in (self.x, self.f, self.x2, self.x2n, self.g, self.h, self.q, self.dq, self.dw, self.dwq)]
+
+
+def test_dependent_launches_give_the_bits_of_plain_launches(dev):
+    """The chain's kernels are started as programmatic dependent launches (the next kernel is placed while the running one
+    drains, and stops before its first global access until that one is complete).  A kernel that touched global memory too
+    early would read or overwrite data of the launch before it: the same in-place operator sequence must end with the same
+    bits whether the launches are dependent (default) or plain (knob dep_launch = 0), eagerly and as a replayed graph."""
+    torch = _torch()
+    from ane_b200 import lib
+    ch = _DependentChain(torch)
+    lib.set_tuning("dep_launch", 0)
+    try:
+        ch.run(dev, 5)
+        plain = ch.results()
+    finally:
+        lib.clear_tuning("dep_launch")
+    assert all(bool(torch.isfinite(t.float()).all()) for t in plain)
+    assert float(plain[0].float().abs().max()) > 0.0 and float(plain[8].abs().max()) > 0.0
+    for _ in range(2):
+        ch.reset()
+        ch.run(dev, 5)
+        for a, b in zip(ch.results(), plain):
+            assert torch.equal(a, b)
+    # the same launches as nodes of one graph (dependent edges between kernel nodes), replayed
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ch.run(dev, 5)
+    for _ in range(2):
+        ch.reset()
+        graph.replay()
+        for a, b in zip(ch.results(), plain):
+            assert torch.equal(a, b)
+    assert lib.poll_status().wait_giveups == 0
 
 
 @pytest.mark.parametrize("nranks,n,lo", [(1, 1000, 0), (2, 4099, 8), (4, 1 << 16, 1 << 14), (8, 33, 3), (3, 70001, 4)])
