@@ -96,7 +96,7 @@ static int launch_ew(cudaStream_t st, const EwPtrs<NIN, NOUT> &p, size_t n, Op o
         size_t blocks = (n_vec + (size_t)EW_THREADS * EW_UNROLL - 1) / ((size_t)EW_THREADS * EW_UNROLL);
         if (blocks == 0) blocks = 1;
         if (blocks > 0x7fffffffull) return fail(ANE_CUDA_ERR_UNSUPPORTED, "element count %zu too large", n);
-        launch_dep(ew_vec_kernel<T, NIN, NOUT, Op>, dim3((unsigned)blocks), dim3(EW_THREADS), 0, st, p, n_vec, n_tail, op);
+        launch_dep(DEP_EW, ew_vec_kernel<T, NIN, NOUT, Op>, dim3((unsigned)blocks), dim3(EW_THREADS), 0, st, p, n_vec, n_tail, op);
     } else {
         size_t blocks = (n + EW_THREADS - 1) / EW_THREADS;
         if (blocks > 148 * 32) blocks = 148 * 32;

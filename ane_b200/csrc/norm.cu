@@ -230,7 +230,7 @@ static int launch_rmsnorm_fwd(cudaStream_t st, int B, int C, int S, void *out, v
 #define ANE_FWD_RR(LGv, THv, NVv)                                                                                   \
         do {                                                                                                        \
             const int tps_ = (S + (LGv) * VEC - 1) / ((LGv) * VEC);                                                  \
-            launch_dep(rmsnorm_fwd_rr_kernel<T, LGv, THv, NVv, FUSE_RES>, dim3((unsigned)(B * tps_)), dim3(THv), 0, st, \
+            launch_dep(DEP_NORM_FWD, rmsnorm_fwd_rr_kernel<T, LGv, THv, NVv, FUSE_RES>, dim3((unsigned)(B * tps_)), dim3(THv), 0, st, \
                        (T *)out, (T *)x2, (const T *)x, (const T *)f, w, C, S, tps_, alpha, eps);                   \
             ANE_LAUNCH_OK(1);                                                                                       \
             return ANE_CUDA_OK;                                                                                     \
@@ -252,7 +252,7 @@ static int launch_rmsnorm_fwd(cudaStream_t st, int B, int C, int S, void *out, v
             const size_t smem = (size_t)C * LGs * 16;
             auto k_ = rmsnorm_fwd_st_kernel<T, LGs, FUSE_RES>;
             ANE_CUDA_TRY(cudaFuncSetAttribute(k_, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            launch_dep(k_, dim3((unsigned)(B * tps_)), dim3(ST_THREADS), smem, st, (T *)out, (T *)x2, (const T *)x, (const T *)f, w, C, S, tps_, alpha, eps);
+            launch_dep(DEP_NORM_FWD, k_, dim3((unsigned)(B * tps_)), dim3(ST_THREADS), smem, st, (T *)out, (T *)x2, (const T *)x, (const T *)f, w, C, S, tps_, alpha, eps);
             ANE_LAUNCH_OK(1);
             return ANE_CUDA_OK;
         }
@@ -315,8 +315,8 @@ static int launch_rmsnorm_bwd_cluster(cudaStream_t st, int B, int C, int S, void
     const int ngroups = max_clusters < ntiles ? max_clusters : ntiles;
     float *partial = static_cast<float *>(workspace((size_t)ngroups * C * sizeof(float)));
     if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", ngroups, C);
-    launch_dep(k_, dim3((unsigned)(CL * ngroups)), dim3(ST_THREADS), smem_st, st, (T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags);
-    launch_dep(column_sum_add_kernel<>, dim3((C + 31) / 32), dim3(256), 0, st, dw, (const float *)partial, ngroups, C);
+    launch_dep(DEP_NORM_BWD, k_, dim3((unsigned)(CL * ngroups)), dim3(ST_THREADS), smem_st, st, (T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags);
+    launch_dep(DEP_COLSUM, column_sum_add_kernel<>, dim3((C + 31) / 32), dim3(256), 0, st, dw, (const float *)partial, ngroups, C);
     ANE_LAUNCH_OK(2);
     return ANE_CUDA_OK;
 }
@@ -366,8 +366,8 @@ static int launch_rmsnorm_bwd(cudaStream_t st, int B, int C, int S, void *dx, fl
             if (npairs > ntiles) npairs = ntiles;
             partial = static_cast<float *>(workspace((size_t)npairs * C * sizeof(float)));
             if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rmsnorm_bwd: no scratch for %d x %d partials", npairs, C);
-            launch_dep(k_, dim3((unsigned)(2 * npairs)), dim3(ST_THREADS), smem_st, st, (T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags);
-            launch_dep(column_sum_add_kernel<>, dim3((C + 31) / 32), dim3(256), 0, st, dw, (const float *)partial, npairs, C);
+            launch_dep(DEP_NORM_BWD, k_, dim3((unsigned)(2 * npairs)), dim3(ST_THREADS), smem_st, st, (T *)dx, partial, (const T *)dy, (const T *)x, w, (const T *)add, C, S, tps_, ntiles, eps, flags);
+            launch_dep(DEP_COLSUM, column_sum_add_kernel<>, dim3((C + 31) / 32), dim3(256), 0, st, dw, (const float *)partial, npairs, C);
             ANE_LAUNCH_OK(2);
             return ANE_CUDA_OK;
         }

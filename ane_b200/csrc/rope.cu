@@ -1007,12 +1007,12 @@ static int launch_qk_bwd_gqa(cudaStream_t st, int B, int heads, int ratio, int h
         if (grid > ntiles) grid = ntiles;                                                                            \
         partial = static_cast<float *>(workspace((size_t)grid * hd * sizeof(float)));                                \
         if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "rope_qknorm_bwd_gqa: no scratch");                            \
-        launch_dep(k, dim3((unsigned)grid), dim3(QK_THREADS), smem, st, (T *)dx, partial, dymap, xmap, w, heads, S, tps, ntiles, eps, flags, ctx().status, cosT, sinT, ring_test()); \
+        launch_dep(DEP_QK, k, dim3((unsigned)grid), dim3(QK_THREADS), smem, st, (T *)dx, partial, dymap, xmap, w, heads, S, tps, ntiles, eps, flags, ctx().status, cosT, sinT, ring_test()); \
     } while (0)
     if (hd == 128) { if (ratio == 2) ANE_QKB_GQA(4, 2); else ANE_QKB_GQA(4, 4); }
     else { if (ratio == 2) ANE_QKB_GQA(2, 2); else ANE_QKB_GQA(2, 4); }
 #undef ANE_QKB_GQA
-    launch_dep(column_sum_add_kernel<>, dim3((hd + 31) / 32), dim3(256), 0, st, dw, (const float *)partial, grid, hd);
+    launch_dep(DEP_COLSUM, column_sum_add_kernel<>, dim3((hd + 31) / 32), dim3(256), 0, st, dw, (const float *)partial, grid, hd);
     ANE_LAUNCH_OK(2);
     return ANE_CUDA_OK;
 }
@@ -1104,7 +1104,7 @@ static int launch_qk_fwd(cudaStream_t st, int B, int heads, int hd, int S, void 
             if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, QK_THREADS, smem) != cudaSuccess || per_sm < 1) per_sm = 1; \
             int g = per_sm * ctx().sm_count;                                                                         \
             if (g > ntiles) g = ntiles;                                                                              \
-            launch_dep(k, dim3((unsigned)g), dim3(QK_THREADS), smem, st, (T *)out, xmap, w, heads, S, tps, ntiles, eps, ctx().status, cosT, sinT, out_ratio, ring_test()); \
+            launch_dep(DEP_QK, k, dim3((unsigned)g), dim3(QK_THREADS), smem, st, (T *)out, xmap, w, heads, S, tps, ntiles, eps, ctx().status, cosT, sinT, out_ratio, ring_test()); \
         } while (0)
         if (hd == 128) { if (hb == 3) ANE_QKF_TMA(4, 3); else if (hb == 4) ANE_QKF_TMA(4, 4); else ANE_QKF_TMA(4, 6); }
         else { if (hb == 3) ANE_QKF_TMA(2, 3); else if (hb == 4) ANE_QKF_TMA(2, 4); else ANE_QKF_TMA(2, 6); }
@@ -1153,12 +1153,12 @@ static int launch_qk_bwd(cudaStream_t st, int B, int heads, int hd, int S, void 
             if (grid > ntiles) grid = ntiles;                                                                        \
             partial = static_cast<float *>(workspace((size_t)grid * hd * sizeof(float)));                            \
             if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "qknorm_bwd: no scratch");                                 \
-            launch_dep(k, dim3((unsigned)grid), dim3(QK_THREADS), smem, st, (T *)dx, partial, dymap, xmap, w, heads, S, tps, ntiles, eps, flags, ctx().status, cosT, sinT, ring_test()); \
+            launch_dep(DEP_QK, k, dim3((unsigned)grid), dim3(QK_THREADS), smem, st, (T *)dx, partial, dymap, xmap, w, heads, S, tps, ntiles, eps, flags, ctx().status, cosT, sinT, ring_test()); \
         } while (0)
         if (hd == 128) { if (hb == 3) ANE_QKB_TMA(4, 3); else ANE_QKB_TMA(4, 4); }
         else { if (hb == 3) ANE_QKB_TMA(2, 3); else ANE_QKB_TMA(2, 4); }
 #undef ANE_QKB_TMA
-        launch_dep(column_sum_add_kernel<>, dim3((hd + 31) / 32), dim3(256), 0, st, dw, (const float *)partial, grid, hd);
+        launch_dep(DEP_COLSUM, column_sum_add_kernel<>, dim3((hd + 31) / 32), dim3(256), 0, st, dw, (const float *)partial, grid, hd);
         ANE_LAUNCH_OK(2);
         return ANE_CUDA_OK;
     }

@@ -957,7 +957,7 @@ ALT_KNOBS = [
     ("norm_fwd", 0), ("norm_fwd", 2), ("norm_fwd", 3), ("norm_fwd", 4), ("norm_fwd", 6),
     ("norm_bwd", 0), ("norm_bwd", 8), ("norm_bwd", 9), ("norm_bwd", 10), ("norm_bwd", 11), ("norm_bwd", 12),
     ("qk_fwd", 0), ("qk_fwd", 1), ("qk_fwd", 4), ("qk_bwd", 0), ("qk_bwd", 4), ("qk_fwd_pipe", 0), ("qk_bwd_pipe", 0), ("qk_bwd_pipe", 1),
-    ("dep_launch", 0), ("rope_lg", 8), ("rope_table", 0), ("embed_tiled", 0), ("embed_rows", 0), ("embed_sort", 1), ("xent_cluster", 1), ("xent_lg", 4), ("xent_lg", 8), ("xent_lg", 32), ("xent_split", 1), ("xent_split", 2), ("xent_split", 8),
+    ("dep_launch", 31), ("rope_lg", 8), ("rope_table", 0), ("embed_tiled", 0), ("embed_rows", 0), ("embed_sort", 1), ("xent_cluster", 1), ("xent_lg", 4), ("xent_lg", 8), ("xent_lg", 32), ("xent_split", 1), ("xent_split", 2), ("xent_split", 8),
 ]
 
 
@@ -969,7 +969,7 @@ def test_alternate_kernels_match_the_oracle(dev, oracle, knob, value):
     lib.set_tuning(knob, value)
     try:
         dt = "bf16"
-        if knob.startswith("norm"):
+        if knob.startswith("norm") or knob == "dep_launch":
             B, Cn, S = 3, 1024, 128
             x, w, dy = gi.cfg1(seed=21, B=B, dim=Cn, seq=S)
             f = gi.normal(gi.rng(7), (B, Cn, S))
@@ -988,7 +988,7 @@ def test_alternate_kernels_match_the_oracle(dev, oracle, knob, value):
             rdx, rdw = oracle.rmsnorm_bwd(dyr, xr, w)
             assert close(down(dx), oracle.add(rdx, fr), dt)
             assert rel_err(down(dw), rdw) <= 1e-4
-        elif knob.startswith("qk") or knob == "rope_lg":
+        if knob.startswith("qk") or knob in ("rope_lg", "rope_table", "dep_launch"):
             B, heads, hd, S = 2, 4, 128, 256
             q = gi.normal(gi.rng(8), (B, heads * hd, S))
             dq = gi.normal(gi.rng(9), (B, heads * hd, S))
@@ -1003,7 +1003,7 @@ def test_alternate_kernels_match_the_oracle(dev, oracle, knob, value):
             rdx, rdw = oracle.rope_qknorm_bwd(dqr, qr, wq, hd, eps=1e-6, base=1e6)
             assert close(down(dx), rdx, dt)
             assert rel_err(down(dwq), rdw) <= 1e-4
-        elif knob.startswith("embed"):
+        if knob.startswith("embed"):
             V, D, B, S = 300, 256, 2, 64
             table = gi.normal(gi.rng(11), (V, D), 0.02)
             tok = gi.rng(12).integers(0, V, (B, S)).astype(np.int32)
@@ -1016,7 +1016,7 @@ def test_alternate_kernels_match_the_oracle(dev, oracle, knob, value):
             dev.embed_backward(dE, x, tokd)
             rdE, _ = oracle.embed_backward(np.zeros((V, D), np.float32), rx, tok)
             assert np.array_equal(down(dE), rdE)                # same additions in the same order
-        else:
+        if knob.startswith("xent"):
             B, V, S = 2, 8192, 128
             logits = gi.normal(gi.rng(13), (B, V, S), 2.0)
             tg = gi.rng(14).integers(0, V, (B, S)).astype(np.int32)
@@ -1066,19 +1066,23 @@ class _DependentChain:
 
 
 def test_dependent_launches_give_the_bits_of_plain_launches(dev):
-    """The chain's kernels are started as programmatic dependent launches (the next kernel is placed while the running one
-    drains, and stops before its first global access until that one is complete).  A kernel that touched global memory too
-    early would read or overwrite data of the launch before it: the same in-place operator sequence must end with the same
-    bits whether the launches are dependent (default) or plain (knob dep_launch = 0), eagerly and as a replayed graph."""
+    """Knob dep_launch starts the chain's kernels as programmatic dependent launches (the next kernel is placed while the
+    running one drains, and stops before its first global access until that one is complete).  A kernel that touched global
+    memory too early would read or overwrite data of the launch before it: the same in-place operator sequence must end with
+    the same bits whether the launches are plain (default) or dependent (all kernel classes), eagerly and as a replayed graph."""
     torch = _torch()
     from ane_b200 import lib
     ch = _DependentChain(torch)
-    lib.set_tuning("dep_launch", 0)
+    ch.run(dev, 5)
+    plain = ch.results()
+    lib.set_tuning("dep_launch", 31)
     try:
-        ch.run(dev, 5)
-        plain = ch.results()
+        _dependent_launch_checks(dev, torch, lib, ch, plain)
     finally:
         lib.clear_tuning("dep_launch")
+
+
+def _dependent_launch_checks(dev, torch, lib, ch, plain):
     assert all(bool(torch.isfinite(t.float()).all()) for t in plain)
     assert float(plain[0].float().abs().max()) > 0.0 and float(plain[8].abs().max()) > 0.0
     for _ in range(2):
