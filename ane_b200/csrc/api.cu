@@ -253,6 +253,7 @@ void ane_cuda_shutdown(void) {
     pipe_destroy();
     rope_tables_release();
     embed_side_release();
+    qk_side_release();
     if (c.ws) cudaFree(c.ws);
     for (void *p : g_retired) cudaFree(p);
     g_retired.clear();

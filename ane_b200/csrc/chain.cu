@@ -76,8 +76,8 @@ static int chain_fwd_layer(ANECudaChain *ch, int l) {
     const auto &c = ch->c;
     const auto &p = ch->p;
     const int r = l % ch->R, B = ch->B;
-    CH_TRY(ane_cuda_qknorm_rope_dev(ch->s_c, c.dtype, B, c.heads, c.head_dim, c.seq, ch->q_r[r], ch->q[l], p.q_w + (size_t)l * c.head_dim, c.qk_eps, c.rope_base, 0));
-    CH_TRY(ane_cuda_qknorm_rope_dev(ch->s_c, c.dtype, B, c.kv_heads, c.head_dim, c.seq, ch->k_r[r], ch->k[l], p.k_w + (size_t)l * c.head_dim, c.qk_eps, c.rope_base, 0));
+    CH_TRY(ane_cuda_qknorm_rope_pair_dev(ch->s_c, c.dtype, B, c.heads, c.kv_heads, c.head_dim, c.seq, ch->q_r[r], ch->k_r[r], ch->q[l], ch->k[l],
+                                         p.q_w + (size_t)l * c.head_dim, p.k_w + (size_t)l * c.head_dim, c.qk_eps, c.rope_base, 0));
     CH_TRY(ane_cuda_residual_rmsnorm_dev(ch->s_c, c.dtype, B, c.dim, c.seq, ch->x2[l], ch->x2norm[r], ch->layer_in[l], ch->o_out[l],
                                          p.ffn_w + (size_t)l * c.dim, c.alpha, c.eps));                                     // train.m:460-461
     CH_TRY(ane_cuda_swiglu_dev(ch->s_c, c.dtype, (size_t)B * c.hidden * c.seq, ch->gate[r], ch->h1[l], ch->h3[l]));
@@ -96,10 +96,9 @@ static int chain_bwd_layer(ANECudaChain *ch, int l, int &cur) {
     CH_TRY(ane_cuda_swiglu_bwd_dev(ch->s_c, c.dtype, (size_t)B * c.hidden * c.seq, ch->dh1[r], ch->dh3[r], ch->h1[l], ch->h3[l], ch->dsilu[r]));   // train.m:537-554
     CH_TRY(ane_cuda_rmsnorm_bwd_dev(ch->s_c, c.dtype, B, c.dim, c.seq, ch->dx2, p.ffn_g + (size_t)l * c.dim, ch->dx_ffn[r], ch->x2[l],
                                     p.ffn_w + (size_t)l * c.dim, dyc, c.eps, c.norm_bwd_flags));                             // train.m:588-590
-    CH_TRY(ane_cuda_rope_qknorm_bwd_dev(ch->s_c, c.dtype, B, c.heads, c.head_dim, c.seq, ch->dq[r], p.q_g + (size_t)l * c.head_dim, ch->dq_in[r],
-                                        ch->q[l], p.q_w + (size_t)l * c.head_dim, c.qk_eps, c.rope_base, 0, c.norm_bwd_flags));
-    CH_TRY(ane_cuda_rope_qknorm_bwd_dev(ch->s_c, c.dtype, B, c.kv_heads, c.head_dim, c.seq, ch->dk[r], p.k_g + (size_t)l * c.head_dim, ch->dk_in[r],
-                                        ch->k[l], p.k_w + (size_t)l * c.head_dim, c.qk_eps, c.rope_base, 0, c.norm_bwd_flags));
+    CH_TRY(ane_cuda_rope_qknorm_bwd_pair_dev(ch->s_c, c.dtype, B, c.heads, c.kv_heads, c.head_dim, c.seq, ch->dq[r], ch->dk[r],
+                                             p.q_g + (size_t)l * c.head_dim, p.k_g + (size_t)l * c.head_dim, ch->dq_in[r], ch->dk_in[r], ch->q[l], ch->k[l],
+                                             p.q_w + (size_t)l * c.head_dim, p.k_w + (size_t)l * c.head_dim, c.qk_eps, c.rope_base, 0, c.norm_bwd_flags));
     CH_TRY(ane_cuda_rmsnorm_bwd_dev(ch->s_c, c.dtype, B, c.dim, c.seq, nxt, p.att_g + (size_t)l * c.dim, ch->dx_attn[r], ch->layer_in[l],
                                     p.att_w + (size_t)l * c.dim, ch->dx2, c.eps, c.norm_bwd_flags));                         // train.m:719-722
     cur = 1 - cur;

@@ -54,6 +54,8 @@ int tuning(const char *name, int dflt);
 void rope_tables_release();
 // Destroys the side stream and events of the embedding scatter-add (embed.cu).
 void embed_side_release();
+// Destroys the side stream and events of the Q / K pair operators (rope.cu).
+void qk_side_release();
 
 #define ANE_REQUIRE_INIT() do { if (!::ane::ctx().inited) return ::ane::fail(ANE_CUDA_ERR_NOT_INIT, "%s: call ane_cuda_init first", __func__); } while (0)
 #define ANE_REQUIRE(cond, ...) do { if (!(cond)) return ::ane::fail(ANE_CUDA_ERR_INVALID, __VA_ARGS__); } while (0)

@@ -11,6 +11,7 @@
 
 #include <math.h>
 #include <type_traits>
+#include <initializer_list>
 
 namespace ane {
 
@@ -1068,6 +1069,36 @@ static int qk_persistent_grid(KernelT kernel, int ntiles) {
     return (int)g;
 }
 
+// Q and K of one layer side by side (the *_pair entry points): the two launches of the ring kernel run at the same time,
+// on the caller's stream and on a stream of the library, each on its share of the persistent grid (16 : 8 heads -> two
+// thirds and one third of the blocks), so the pair pays one ramp and one tail instead of two.  The shares add up to no more
+// than the blocks that are resident at once: neither launch waits for a second wave.
+struct QkShare { int num = 1, den = 1; float *partial = nullptr; };
+static QkShare g_share;      // set by the pair entry points around the launches they make (one host thread at a time)
+static inline int share_grid(int g) {
+    const long long s = (long long)g * g_share.num / g_share.den;
+    return s < 1 ? 1 : (int)s;
+}
+struct QkSide { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; bool ok = false; };
+static QkSide g_qk_side;
+static QkSide *qk_side() {
+    if (g_qk_side.ok) return &g_qk_side;
+    if (cudaStreamCreateWithFlags(&g_qk_side.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&g_qk_side.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&g_qk_side.join, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    g_qk_side.ok = true;
+    return &g_qk_side;
+}
+void qk_side_release() {
+    if (g_qk_side.stream) cudaStreamDestroy(g_qk_side.stream);
+    if (g_qk_side.fork) cudaEventDestroy(g_qk_side.fork);
+    if (g_qk_side.join) cudaEventDestroy(g_qk_side.join);
+    g_qk_side = QkSide();
+}
+
 template <typename T, bool ROPE>
 static bool qk_fast_ok(int hd, int S, const void *a, const void *b, const void *c) {
     constexpr int VEC = Elt<T>::VEC;
@@ -1102,7 +1133,7 @@ static int launch_qk_fwd(cudaStream_t st, int B, int heads, int hd, int S, void 
             ANE_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));           \
             int per_sm = 0;                                                                                          \
             if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, QK_THREADS, smem) != cudaSuccess || per_sm < 1) per_sm = 1; \
-            int g = per_sm * ctx().sm_count;                                                                         \
+            int g = share_grid(per_sm * ctx().sm_count);                                                             \
             if (g > ntiles) g = ntiles;                                                                              \
             launch_dep(DEP_QK, k, dim3((unsigned)g), dim3(QK_THREADS), smem, st, (T *)out, xmap, w, heads, S, tps, ntiles, eps, ctx().status, cosT, sinT, out_ratio, ring_test()); \
         } while (0)
@@ -1149,9 +1180,9 @@ static int launch_qk_bwd(cudaStream_t st, int B, int heads, int hd, int S, void 
             ANE_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));           \
             int per_sm = 0;                                                                                          \
             if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, QK_THREADS, smem) != cudaSuccess || per_sm < 1) per_sm = 1; \
-            grid = per_sm * ctx().sm_count;                                                                          \
+            grid = share_grid(per_sm * ctx().sm_count);                                                              \
             if (grid > ntiles) grid = ntiles;                                                                        \
-            partial = static_cast<float *>(workspace((size_t)grid * hd * sizeof(float)));                            \
+            partial = g_share.partial ? g_share.partial : static_cast<float *>(workspace((size_t)grid * hd * sizeof(float))); \
             if (!partial) return fail(ANE_CUDA_ERR_NOMEM, "qknorm_bwd: no scratch");                                 \
             launch_dep(DEP_QK, k, dim3((unsigned)grid), dim3(QK_THREADS), smem, st, (T *)dx, partial, dymap, xmap, w, heads, S, tps, ntiles, eps, flags, ctx().status, cosT, sinT, ring_test()); \
         } while (0)
@@ -1322,6 +1353,70 @@ int ane_cuda_rope_qknorm_bwd_dev(void *stream, ane_dtype dtype, int B, int heads
     // other head widths and unaligned shapes
     ANE_DISPATCH_DTYPE(dtype, T, return (launch_qk_rope_bwd_generic<T>(st, B, heads, hd, S, dx, dw, dy, x, w, eps, pos0, flags, fq)));
     return ANE_CUDA_OK;
+}
+
+// ---- Q and K of one layer in one call
+static bool pair_side_by_side(ane_dtype dtype, int hd, int S, const char *stage_knob, std::initializer_list<const void *> ptrs) {
+    if (tuning("qk_pair", 1) == 0 || tuning(stage_knob, 3) < 3) return false;
+    if (!(hd == 128 || hd == 64) || !dtype_ok(dtype) || S % (16 / (int)dtype_size(dtype)) != 0) return false;
+    for (const void *p : ptrs)
+        if (!aligned16(p)) return false;
+    return true;
+}
+
+int ane_cuda_qknorm_rope_pair_dev(void *stream, ane_dtype dtype, int B, int heads_q, int heads_k, int hd, int S, void *out_q,
+                                  void *out_k, const void *q, const void *k, const float *wq, const float *wk, float eps,
+                                  float base, int pos0) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(out_q && out_k && q && k && wq && wk, "%s: null pointer", __func__);
+    if (int rc = check_qk(__func__, B, heads_q, hd, S)) return rc;
+    if (int rc = check_qk(__func__, B, heads_k, hd, S)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    QkSide *side = pair_side_by_side(dtype, hd, S, "qk_fwd", {out_q, out_k, q, k}) ? qk_side() : nullptr;
+    if (!side) {
+        if (int rc = ane_cuda_qknorm_rope_dev(stream, dtype, B, heads_q, hd, S, out_q, q, wq, eps, base, pos0)) return rc;
+        return ane_cuda_qknorm_rope_dev(stream, dtype, B, heads_k, hd, S, out_k, k, wk, eps, base, pos0);
+    }
+    ANE_CUDA_TRY(cudaEventRecord(side->fork, st));
+    ANE_CUDA_TRY(cudaStreamWaitEvent(side->stream, side->fork, 0));
+    g_share = QkShare{heads_q, heads_q + heads_k, nullptr};
+    int rc = ane_cuda_qknorm_rope_dev(stream, dtype, B, heads_q, hd, S, out_q, q, wq, eps, base, pos0);
+    g_share = QkShare{heads_k, heads_q + heads_k, nullptr};
+    const int rc2 = ane_cuda_qknorm_rope_dev(side->stream, dtype, B, heads_k, hd, S, out_k, k, wk, eps, base, pos0);
+    g_share = QkShare();
+    // the side stream rejoins the caller's stream whatever happened (a capture must not end with a forked stream)
+    cudaEventRecord(side->join, side->stream);
+    cudaStreamWaitEvent(st, side->join, 0);
+    return rc ? rc : rc2;
+}
+
+int ane_cuda_rope_qknorm_bwd_pair_dev(void *stream, ane_dtype dtype, int B, int heads_q, int heads_k, int hd, int S, void *dq,
+                                      void *dk, float *dwq, float *dwk, const void *dyq, const void *dyk, const void *q,
+                                      const void *k, const float *wq, const float *wk, float eps, float base, int pos0,
+                                      unsigned flags) {
+    ANE_REQUIRE_INIT();
+    ANE_REQUIRE(dq && dk && dwq && dwk && dyq && dyk && q && k && wq && wk, "%s: null pointer", __func__);
+    if (int rc = check_qk(__func__, B, heads_q, hd, S)) return rc;
+    if (int rc = check_qk(__func__, B, heads_k, hd, S)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    QkSide *side = pair_side_by_side(dtype, hd, S, "qk_bwd", {dq, dk, dyq, dyk, q, k}) ? qk_side() : nullptr;
+    // one scratch range for both launches' dw partials: they run at the same time
+    const size_t rows = (size_t)8 * ctx().sm_count;
+    float *partial = side ? static_cast<float *>(workspace(2 * rows * hd * sizeof(float))) : nullptr;
+    if (!side || !partial) {
+        if (int rc = ane_cuda_rope_qknorm_bwd_dev(stream, dtype, B, heads_q, hd, S, dq, dwq, dyq, q, wq, eps, base, pos0, flags)) return rc;
+        return ane_cuda_rope_qknorm_bwd_dev(stream, dtype, B, heads_k, hd, S, dk, dwk, dyk, k, wk, eps, base, pos0, flags);
+    }
+    ANE_CUDA_TRY(cudaEventRecord(side->fork, st));
+    ANE_CUDA_TRY(cudaStreamWaitEvent(side->stream, side->fork, 0));
+    g_share = QkShare{heads_q, heads_q + heads_k, partial};
+    int rc = ane_cuda_rope_qknorm_bwd_dev(stream, dtype, B, heads_q, hd, S, dq, dwq, dyq, q, wq, eps, base, pos0, flags);
+    g_share = QkShare{heads_k, heads_q + heads_k, partial + rows * hd};
+    const int rc2 = ane_cuda_rope_qknorm_bwd_dev(side->stream, dtype, B, heads_k, hd, S, dk, dwk, dyk, k, wk, eps, base, pos0, flags);
+    g_share = QkShare();
+    cudaEventRecord(side->join, side->stream);
+    cudaStreamWaitEvent(st, side->join, 0);
+    return rc ? rc : rc2;
 }
 
 }  // extern "C"

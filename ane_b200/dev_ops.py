@@ -129,6 +129,34 @@ def rope_qknorm_bwd(dy, x, w, dw, hd, eps=1e-6, base=1e6, pos0=0, exact=False, o
     return out
 
 
+def qknorm_rope_pair(q, k, wq, wk, hd, eps=1e-6, base=1e6, pos0=0, out_q=None, out_k=None):
+    """qknorm_rope of Q and of K of one layer in one call (side by side on the GPU where the shapes allow it)."""
+    out_q = torch.empty_like(q) if out_q is None else out_q
+    out_k = torch.empty_like(k) if out_k is None else out_k
+    B, Cq, S = _bcs(q)
+    Bk, Ck, Sk = _bcs(k)
+    if (Bk, Sk) != (B, S) or _dt(k) != _dt(q):
+        raise ValueError("q and k must agree in batch, sequence length and dtype")
+    _l.check(_l.load().ane_cuda_qknorm_rope_pair_dev(_stream(), _dt(q), B, Cq // hd, Ck // hd, hd, S, _p(out_q), _p(out_k),
+                                                    _p(q), _p(k), _p(wq), _p(wk), eps, base, pos0))
+    return out_q, out_k
+
+
+def rope_qknorm_bwd_pair(dyq, dyk, q, k, wq, wk, dwq, dwk, hd, eps=1e-6, base=1e6, pos0=0, exact=False, out_q=None, out_k=None):
+    """rope_qknorm_bwd of Q and of K of one layer in one call; dwq / dwk are accumulated into."""
+    out_q = torch.empty_like(q) if out_q is None else out_q
+    out_k = torch.empty_like(k) if out_k is None else out_k
+    B, Cq, S = _bcs(q)
+    Bk, Ck, Sk = _bcs(k)
+    if (Bk, Sk) != (B, S) or _dt(k) != _dt(q):
+        raise ValueError("q and k must agree in batch, sequence length and dtype")
+    _l.check(_l.load().ane_cuda_rope_qknorm_bwd_pair_dev(_stream(), _dt(q), B, Cq // hd, Ck // hd, hd, S, _p(out_q), _p(out_k),
+                                                        _p(dwq), _p(dwk), _p(dyq), _p(dyk), _p(q), _p(k), _p(wq), _p(wk),
+                                                        eps, base, pos0,
+                                                        _l.NORM_BWD_EXACT if exact else _l.NORM_BWD_REFERENCE))
+    return out_q, out_k
+
+
 def embed_lookup(table, tokens, out=None, zero_oor=False):
     """table [V, D], tokens [B, S] (int32 or uint16 bits) -> x [B, D, S] of table's dtype."""
     B, S = tokens.shape

@@ -233,8 +233,9 @@ class LayerChain:
         c, p = self.cfg, self.p
         r = L % self.R
         x = self.layer_in[L]
-        ops.qknorm_rope(self.q[L], p.norm_w("q", L), c.head_dim, c.qk_eps, c.rope_base, 0, out=self.q_r[r])
-        ops.qknorm_rope(self.k[L], p.norm_w("k", L), c.head_dim, c.qk_eps, c.rope_base, 0, out=self.k_r[r])
+        # Q and K in one call: the two launches share the GPU instead of following each other
+        ops.qknorm_rope_pair(self.q[L], self.k[L], p.norm_w("q", L), p.norm_w("k", L), c.head_dim, c.qk_eps, c.rope_base, 0,
+                             out_q=self.q_r[r], out_k=self.k_r[r])
         ops.residual_rmsnorm(x, self.o_out[L], p.norm_w("ffn", L), c.alpha, c.eps, x2=self.x2[L], x2norm=self.x2norm[r])
         ops.swiglu(self.h1[L], self.h3[L], out=self.gate[r])
         # x_next = x2 + alpha*ffn (train.m:497) fused with the norm that reads it next: the next layer's attention
@@ -276,10 +277,9 @@ class LayerChain:
         self._maybe_time("swiglu_bwd", lambda: ops.swiglu_bwd(self.h1[L], self.h3[L], self.dsilu[r], dh1=self.dh1[r], dh3=self.dh3[r]))
         ops.rmsnorm_bwd(self.dx_ffn[r], self.x2[L], p.norm_w("ffn", L), p.norm_w("ffn", L, grad=True), add=dy, eps=c.eps,
                         exact=ex, out=self.dx2)
-        ops.rope_qknorm_bwd(self.dq_in[r], self.q[L], p.norm_w("q", L), p.norm_w("q", L, grad=True), c.head_dim,
-                            c.qk_eps, c.rope_base, 0, exact=ex, out=self.dq[r])
-        ops.rope_qknorm_bwd(self.dk_in[r], self.k[L], p.norm_w("k", L), p.norm_w("k", L, grad=True), c.head_dim,
-                            c.qk_eps, c.rope_base, 0, exact=ex, out=self.dk[r])
+        ops.rope_qknorm_bwd_pair(self.dq_in[r], self.dk_in[r], self.q[L], self.k[L], p.norm_w("q", L), p.norm_w("k", L),
+                                 p.norm_w("q", L, grad=True), p.norm_w("k", L, grad=True), c.head_dim, c.qk_eps, c.rope_base, 0,
+                                 exact=ex, out_q=self.dq[r], out_k=self.dk[r])
         nxt = self.dy[1 - self._cur]
         ops.rmsnorm_bwd(self.dx_attn[r], self.layer_in[L], p.norm_w("att", L), p.norm_w("att", L, grad=True), add=self.dx2,
                         eps=c.eps, exact=ex, out=nxt)

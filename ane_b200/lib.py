@@ -107,6 +107,8 @@ PROTOTYPES = {
     "ane_cuda_qknorm_bwd_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _u]),
     "ane_cuda_qknorm_rope_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _f, _f, _i]),
     "ane_cuda_rope_qknorm_bwd_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _u]),
+    "ane_cuda_qknorm_rope_pair_dev": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i]),
+    "ane_cuda_rope_qknorm_bwd_pair_dev": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _f, _i, _u]),
     "ane_cuda_embed_lookup_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _u]),
     "ane_cuda_embed_backward_dev": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i]),
     "ane_cuda_cross_entropy_dev": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _f]),

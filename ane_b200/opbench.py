@@ -92,6 +92,17 @@ def _cases(torch, ops, device, M, shape=None):
         (wq, dwq), k, dk, ko = head_w(), mk(KVD, n=2 * NSET), mk(KVD, n=2 * NSET), mk(KVD, n=2 * NSET)
         return (lambda i: ops.rope_qknorm_bwd(dk[i % (2 * NSET)], k[i % (2 * NSET)], wq, dwq, HD, out=ko[i % (2 * NSET)])), 3 * KVD * T * e, 20
 
+    # Q and K of one layer in one call (what the layer chain issues): bytes of the Q and the K operator together
+    def qknorm_rope_pair():
+        (wq, _), q, qo, k, ko = head_w(), mk(QD), mk(QD), mk(KVD), mk(KVD)
+        return (lambda i: ops.qknorm_rope_pair(q[i % NSET], k[i % NSET], wq, wq, HD, out_q=qo[i % NSET], out_k=ko[i % NSET])), 2 * (QD + KVD) * T * e, 20
+
+    def rope_qknorm_bwd_pair():
+        (wq, dwq), q, dq, qo, k, dk, ko = head_w(), mk(QD), mk(QD), mk(QD), mk(KVD), mk(KVD), mk(KVD)
+        dwk = torch.zeros_like(dwq)
+        return (lambda i: ops.rope_qknorm_bwd_pair(dq[i % NSET], dk[i % NSET], q[i % NSET], k[i % NSET], wq, wq, dwq, dwk, HD,
+                                                   out_q=qo[i % NSET], out_k=ko[i % NSET])), 3 * (QD + KVD) * T * e, 20
+
     # embedding: batch sequences of 2048 tokens, table [151936, 1024] bf16
     def _embed_common():
         Be = M
@@ -191,6 +202,7 @@ def _cases(torch, ops, device, M, shape=None):
         "residual_rmsnorm": residual_rmsnorm, "residual": residual, "swiglu": swiglu, "swiglu_bwd": swiglu_bwd,
         "rope": rope, "qknorm_rope(Q)": qknorm_rope, "rope_qknorm_bwd(Q)": rope_qknorm_bwd,
         "qknorm_rope(K)": qknorm_rope_k, "rope_qknorm_bwd(K)": rope_qknorm_bwd_k,
+        "qknorm_rope(Q+K)": qknorm_rope_pair, "rope_qknorm_bwd(Q+K)": rope_qknorm_bwd_pair,
         "embed_lookup": embed_lookup, "embed_backward": embed_backward,
         "cross_entropy": cross_entropy, "cross_entropy_compact": cross_entropy_compact, "cross_entropy_9200": cross_entropy_9200,
         "adam": adam, "grad_norm_sq": grad_norm_sq,

@@ -256,6 +256,21 @@ int ane_cuda_qknorm_rope_dev(void *stream, ane_dtype dtype, int B, int heads, in
 int ane_cuda_rope_qknorm_bwd_dev(void *stream, ane_dtype dtype, int B, int heads, int hd, int S,
                                  void *dx, float *dw, const void *dy, const void *x, const float *w,
                                  float eps, float base, int pos0, unsigned flags);
+/* Q and K of one layer in one call: the two operators above applied to q [B][heads_q*hd][S] with wq and to k
+ * [B][heads_k*hd][S] with wk.  The outputs (and dq, dk) carry the bits of the two separate calls; dwq / dwk are the same
+ * sums added in another fixed order (bit-stable from call to call).  For head widths 64 and 128 with 16-byte aligned rows
+ * the two launches run at the same time, each on its share of the GPU (heads_q : heads_k), K on a stream of the library
+ * that is forked from and joined to the caller's stream inside the call (also under stream capture); other shapes, or knob
+ * "qk_pair" = 0, make the two calls one after the other.  Same positions (pos0) and head width for both, as in a
+ * transformer layer (no counterpart in the reference, which has no QK-norm: the RoPE of Q and K of a layer is one loop
+ * there, training/training_dynamic/cpu_ops.h:168-184 called for dq and dk at train.m:659-660). */
+int ane_cuda_qknorm_rope_pair_dev(void *stream, ane_dtype dtype, int B, int heads_q, int heads_k, int hd, int S,
+                                  void *out_q, void *out_k, const void *q, const void *k, const float *wq,
+                                  const float *wk, float eps, float base, int pos0);
+int ane_cuda_rope_qknorm_bwd_pair_dev(void *stream, ane_dtype dtype, int B, int heads_q, int heads_k, int hd, int S,
+                                      void *dq, void *dk, float *dwq, float *dwk, const void *dyq, const void *dyk,
+                                      const void *q, const void *k, const float *wq, const float *wk, float eps,
+                                      float base, int pos0, unsigned flags);
 /* a9: x[b][d][t] = table[tok[b][t]][d] (bit-exact copy; table has the same dtype as x).
  * flags: ANE_OOR_SKIP (default) or ANE_OOR_ZERO.  stories_cpu_ops.h:112-120 */
 int ane_cuda_embed_lookup_dev(void *stream, ane_dtype dtype, ane_idtype idtype, int B, int D, int S,

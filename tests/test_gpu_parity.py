@@ -364,6 +364,85 @@ def _qk_rounds_fwd(dev, oracle, B, heads, hd, S, dt):
     assert lib.poll_status().wait_giveups == 0
 
 
+# Q and K of one layer in one call: (B, heads_q, heads_k, hd, S) -- one block round and several, a ragged last round, both head
+# widths, a shape the side-by-side form does not cover (hd 32: the two calls run one after the other)
+QK_PAIRS = [(2, 4, 2, 128, 256), (10, 16, 8, 128, 2048), (5, 16, 8, 128, 2048 + 64 + 8), (7, 12, 4, 64, 2048), (3, 3, 1, 128, 520),
+            (2, 4, 2, 32, 96)]
+
+
+@pytest.mark.parametrize("pair", [1, 0])
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("B,hq,hk,hd,S", QK_PAIRS)
+def test_qk_pair_equals_the_two_calls_and_the_oracle(dev, oracle, B, hq, hk, hd, S, dt, pair):
+    """ane_cuda_qknorm_rope_pair_dev / ane_cuda_rope_qknorm_bwd_pair_dev: outputs and dx carry the bits of the separate
+    calls (and match the oracle), dw matches the oracle and is bit-stable from call to call; knob qk_pair = 0 makes the
+    two calls one after the other."""
+    torch = _torch()
+    from ane_b200 import lib
+    r = gi.rng(97)
+    q, k = gi.normal(r, (B, hq * hd, S)), gi.normal(r, (B, hk * hd, S))
+    dyq, dyk = gi.normal(r, (B, hq * hd, S)), gi.normal(r, (B, hk * hd, S))
+    wq, wk = gi.normal(r, (hd,), 0.05, 1.0), gi.normal(r, (hd,), 0.05, 1.0)
+    (qd, qr), (kd, kr), (dyqd, dyqr), (dykd, dykr) = up(q, dt), up(k, dt), up(dyq, dt), up(dyk, dt)
+    wqd, wkd = up(wq)[0], up(wk)[0]
+    lib.poll_status(reset=True)
+    lib.set_tuning("qk_pair", pair)
+    try:
+        oq, ok = dev.qknorm_rope_pair(qd, kd, wqd, wkd, hd, 1e-6, 1e6, 0)
+        dwq, dwk = torch.zeros(hd, device="cuda"), torch.zeros(hd, device="cuda")
+        dq, dk = dev.rope_qknorm_bwd_pair(dyqd, dykd, qd, kd, wqd, wkd, dwq, dwk, hd, 1e-6, 1e6, 0)
+        dwq2, dwk2 = torch.zeros(hd, device="cuda"), torch.zeros(hd, device="cuda")
+        dq2, dk2 = dev.rope_qknorm_bwd_pair(dyqd, dykd, qd, kd, wqd, wkd, dwq2, dwk2, hd, 1e-6, 1e6, 0)
+    finally:
+        lib.clear_tuning("qk_pair")
+    assert torch.equal(oq, dev.qknorm_rope(qd, wqd, hd, 1e-6, 1e6, 0)) and torch.equal(ok, dev.qknorm_rope(kd, wkd, hd, 1e-6, 1e6, 0))
+    sq, sk = torch.zeros(hd, device="cuda"), torch.zeros(hd, device="cuda")
+    assert torch.equal(dq, dev.rope_qknorm_bwd(dyqd, qd, wqd, sq, hd, 1e-6, 1e6, 0))
+    assert torch.equal(dk, dev.rope_qknorm_bwd(dykd, kd, wkd, sk, hd, 1e-6, 1e6, 0))
+    assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dwq, dwq2) and torch.equal(dwk, dwk2)
+    assert close(down(oq), oracle.qknorm_rope(qr, wq, hd, 1e-6, 1e6, 0), dt) and close(down(ok), oracle.qknorm_rope(kr, wk, hd, 1e-6, 1e6, 0), dt)
+    rdq, rdwq = oracle.rope_qknorm_bwd(dyqr, qr, wq, hd, eps=1e-6, base=1e6)
+    rdk, rdwk = oracle.rope_qknorm_bwd(dykr, kr, wk, hd, eps=1e-6, base=1e6)
+    assert close(down(dq), rdq, dt) and close(down(dk), rdk, dt)
+    dwtol = TOL32 if dt == "f32" else 1e-4
+    assert rel_err(down(dwq), rdwq) <= dwtol and rel_err(down(dwk), rdwk) <= dwtol
+    assert rel_err(down(sq), rdwq) <= dwtol and rel_err(down(sk), rdwk) <= dwtol
+    assert lib.poll_status().wait_giveups == 0
+
+
+def test_qk_pair_in_a_replayed_graph(dev):
+    """The pair forks to a stream of the library and joins again inside the call: captured into a graph, the replay gives
+    the bits of the eager call."""
+    torch = _torch()
+    B, hq, hk, hd, S = 6, 16, 8, 128, 1024
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn(B, hq * hd, S, device="cuda", generator=gen).bfloat16()
+    k = torch.randn(B, hk * hd, S, device="cuda", generator=gen).bfloat16()
+    dyq, dyk = torch.randn_like(q), torch.randn_like(k)
+    wq = (1 + 0.1 * torch.randn(hd, device="cuda", generator=gen)).float()
+    wk = (1 + 0.1 * torch.randn(hd, device="cuda", generator=gen)).float()
+    oq, ok, dq, dk = torch.empty_like(q), torch.empty_like(k), torch.empty_like(q), torch.empty_like(k)
+    dwq, dwk = torch.zeros(hd, device="cuda"), torch.zeros(hd, device="cuda")
+
+    def run():
+        dev.qknorm_rope_pair(q, k, wq, wk, hd, out_q=oq, out_k=ok)
+        dev.rope_qknorm_bwd_pair(dyq, dyk, oq, ok, wq, wk, dwq, dwk, hd, out_q=dq, out_k=dk)
+
+    run()
+    torch.cuda.synchronize()
+    want = [t.clone() for t in (oq, ok, dq, dk, dwq, dwk)]
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run()
+    for _ in range(2):
+        for t in (oq, ok, dq, dk, dwq, dwk):
+            t.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        for a, b in zip((oq, ok, dq, dk, dwq, dwk), want):
+            assert torch.equal(a, b)
+
+
 @pytest.mark.parametrize("pipe", [0, 1])
 @pytest.mark.parametrize("exact", [False, True])
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
