@@ -230,13 +230,57 @@ def time_op(torch, builder, peak_gbs, iters=None, warmup=5):
             "frac_8TBs": round(gbs / NOMINAL_HBM_GBS, 3), "bytes": nbytes}
 
 
-def per_op_table(torch, ops, device, peak_gbs, batch=32, only=None, iters=None, warmup=5, shape=None):
+def sustain_op(torch, builder, peak_gbs, seconds):
+    """The operator launched back to back for `seconds`, with the board power and the SM clock sampled through NVML every
+    50 ms (the first third of the samples, while the clocks settle, is dropped).  A 20-launch timing shows what the kernel does
+    at the clock the GPU happens to hold; this shows what it does once the 1000 W power cap has set the clock -- the state a
+    long training step runs in -- and what a byte costs in energy (power x time / algorithmic bytes)."""
+    import threading
+    import time
+    import pynvml
+    pynvml.nvmlInit()
+    handle = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+    fn, nbytes, _ = builder()
+    for i in range(10):
+        fn(i)
+    torch.cuda.synchronize()
+    samples, stop = [], threading.Event()
+
+    def sampler():
+        while not stop.is_set():
+            samples.append((pynvml.nvmlDeviceGetPowerUsage(handle) / 1000.0, pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+            time.sleep(0.05)
+
+    th = threading.Thread(target=sampler)
+    th.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n, t0 = 0, time.perf_counter()
+    e0.record()
+    while time.perf_counter() - t0 < seconds:
+        for i in range(200):
+            fn(n + i)
+        n += 200
+        torch.cuda.synchronize()
+    e1.record()
+    torch.cuda.synchronize()
+    stop.set()
+    th.join()
+    ms = e0.elapsed_time(e1) / n
+    kept = samples[len(samples) // 3:] or samples or [(0.0, 0)]
+    watts = sum(p for p, _ in kept) / len(kept)
+    mhz = sorted(c for _, c in kept)[len(kept) // 2]
+    gbs = nbytes / ms / 1e6
+    return {"ms": round(ms, 4), "GB/s": round(gbs, 1), "frac_measured": round(gbs / peak_gbs, 3), "frac_8TBs": round(gbs / NOMINAL_HBM_GBS, 3),
+            "power_w": round(watts), "sm_mhz": mhz, "pJ_per_byte": round(watts * ms * 1e-3 / nbytes * 1e12, 1), "launches": n, "bytes": nbytes}
+
+
+def per_op_table(torch, ops, device, peak_gbs, batch=32, only=None, iters=None, warmup=5, shape=None, sustain=0.0):
     """Achieved GB/s per operator on benchmark-sized bf16 tensors (algorithmic bytes / time)."""
     res = {}
     for name, builder in _cases(torch, ops, device, batch, shape).items():
         if only and name not in only:
             continue
-        res[name] = time_op(torch, builder, peak_gbs, iters, warmup)
+        res[name] = sustain_op(torch, builder, peak_gbs, sustain) if sustain > 0 else time_op(torch, builder, peak_gbs, iters, warmup)
         torch.cuda.empty_cache()
     return res
 
@@ -274,6 +318,8 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--peak-gbs", type=float, default=None, help="roofline denominator (default: MEASURED_PEAKS.json)")
     ap.add_argument("--tuning", default="", help="comma-separated knob=value pairs")
+    ap.add_argument("--sustain", type=float, default=0.0, help="launch every operator back to back for this many seconds and "
+                    "report time, board power, SM clock and energy per byte under the power cap instead of the 20-launch timing")
     a = ap.parse_args(argv)
     import torch
     from . import dev_ops as ops, lib
@@ -291,8 +337,8 @@ def main(argv=None):
     shape = {k: v for k, v in (("dim", a.dim), ("hidden", a.hidden), ("seq", a.seq), ("sets", a.sets)) if v}
     if a.dtype:
         shape["dtype"] = getattr(torch, a.dtype)
-    table = per_op_table(torch, ops, torch.device("cuda:0"), peak, a.batch, a.op, a.iters, a.warmup, shape or None)
-    print(json.dumps({"batch": a.batch, "peak_gbs": peak, "peak_kind": kind, "ops": table}))
+    table = per_op_table(torch, ops, torch.device("cuda:0"), peak, a.batch, a.op, a.iters, a.warmup, shape or None, a.sustain)
+    print(json.dumps({"batch": a.batch, "peak_gbs": peak, "peak_kind": kind, "sustain_s": a.sustain, "ops": table}))
 
 
 if __name__ == "__main__":

@@ -233,7 +233,9 @@ int ane_cuda_scale_dev(void *stream, ane_dtype dtype, size_t n, void *out, const
 int ane_cuda_residual_rmsnorm_dev(void *stream, ane_dtype dtype, int B, int C, int S,
                                   void *x2, void *x2norm, const void *x, const void *f, const float *w,
                                   float alpha, float eps);
-/* a4: out = h1*sigmoid(h1)*h3                                          forward.h:101,149-151 */
+/* a4: out = h1*sigmoid(h1)*h3                                          forward.h:101,149-151
+ * The sigmoid of a4 / a5 comes from the hardware's exp2 and reciprocal approximations (relative error below 1e-6; values
+ * under 2^-126, i.e. h1 < -87.3, become zero); tuning knob "swiglu_exact" = 1 selects expf and an IEEE division. */
 int ane_cuda_swiglu_dev(void *stream, ane_dtype dtype, size_t n, void *out, const void *h1, const void *h3);
 /* a5: dh1, dh3 from h1, h3, dsilu in one pass                          train.m:537-554 */
 int ane_cuda_swiglu_bwd_dev(void *stream, ane_dtype dtype, size_t n, void *dh1, void *dh3,

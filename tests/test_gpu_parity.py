@@ -214,6 +214,36 @@ def test_elementwise(dev, oracle, n, off, dt):
     assert close(down(g1), r1, dt) and close(down(g3), r3, dt)
 
 
+@pytest.mark.parametrize("exact", [0, 1])
+def test_swiglu_over_the_whole_exponent_range(dev, oracle, exact):
+    """SwiGLU forward and backward with h1 from -100 to 100 (exp(-h1) from 0 to overflow), both forms of the sigmoid: the
+    default one from the hardware's ex2 / rcp approximations and the literal expf-and-division one (knob swiglu_exact).
+    Element by element within 1e-5 of the oracle (train.m:537-554, forward.h:101), no NaN where the oracle has none.  The
+    default form flushes a sigmoid below the normal range (h1 < -87.3: values under 1.2e-38) to zero, hence the absolute
+    floor of 1e-34 on products of such a value with h1, h3 and d."""
+    from ane_b200 import lib
+    r = gi.rng(23)
+    h1 = np.concatenate([np.linspace(-100, 100, 20001), gi.normal(r, (12000,), 3.0), [0.0, -0.0, 88.7, -88.7, 104.0, -104.0]]).astype(np.float32)
+    h3 = gi.normal(r, h1.shape)
+    d = gi.normal(r, h1.shape)
+    lib.set_tuning("swiglu_exact", exact)
+    try:
+        out = down(dev.swiglu(up(h1)[0], up(h3)[0]))
+        g1, g3 = (down(t) for t in dev.swiglu_bwd(up(h1)[0], up(h3)[0], up(d)[0]))
+    finally:
+        lib.clear_tuning("swiglu_exact")
+    r1, r3 = oracle.swiglu_bwd(h1, h3, d)
+    # dh1 = (d*h3) * sig * (1 + h1*(1 - sig)) cancels near h1 = -1.278: its error is measured against the size of its terms
+    with np.errstate(over="ignore"):
+        sig = 1.0 / (1.0 + np.exp(-h1.astype(np.float64)))
+    terms1 = np.abs(d.astype(np.float64) * h3) * sig * (1.0 + np.abs(h1) * (1.0 - sig))
+    ro = oracle.swiglu(h1, h3)
+    for got, ref, size in ((out, ro, np.abs(ro)), (g1, r1, terms1), (g3, r3, np.abs(r3))):
+        assert np.array_equal(np.isnan(got), np.isnan(ref))
+        ok = np.abs(got.astype(np.float64) - ref) <= 1e-5 * size + 1e-34
+        assert ok.all(), (int((~ok).sum()), h1[~ok][:5], got[~ok][:5], ref[~ok][:5])
+
+
 def test_residual_alpha_of_the_reference(dev, oracle):
     """alpha = 1/sqrt(2*NLAYERS) (train.m:188) and alpha = 1 (train_large.m:427): bit-exact."""
     _, _, _, x, f = gi.cfg2()
@@ -1036,7 +1066,7 @@ ALT_KNOBS = [
     ("norm_fwd", 0), ("norm_fwd", 2), ("norm_fwd", 3), ("norm_fwd", 4), ("norm_fwd", 6),
     ("norm_bwd", 0), ("norm_bwd", 8), ("norm_bwd", 9), ("norm_bwd", 10), ("norm_bwd", 11), ("norm_bwd", 12),
     ("qk_fwd", 0), ("qk_fwd", 1), ("qk_fwd", 4), ("qk_bwd", 0), ("qk_bwd", 4), ("qk_fwd_pipe", 0), ("qk_bwd_pipe", 0), ("qk_bwd_pipe", 1),
-    ("dep_launch", 31), ("rope_lg", 8), ("rope_table", 0), ("embed_tiled", 0), ("embed_rows", 0), ("embed_sort", 1), ("xent_cluster", 1), ("xent_reverse", 0), ("xent_lg", 4), ("xent_lg", 8), ("xent_lg", 32), ("xent_split", 1), ("xent_split", 2), ("xent_split", 8),
+    ("dep_launch", 31), ("swiglu_exact", 1), ("rope_lg", 8), ("rope_table", 0), ("embed_tiled", 0), ("embed_rows", 0), ("embed_sort", 1), ("xent_cluster", 1), ("xent_reverse", 0), ("xent_lg", 4), ("xent_lg", 8), ("xent_lg", 32), ("xent_split", 1), ("xent_split", 2), ("xent_split", 8),
 ]
 
 
@@ -1082,6 +1112,14 @@ def test_alternate_kernels_match_the_oracle(dev, oracle, knob, value):
             rdx, rdw = oracle.rope_qknorm_bwd(dqr, qr, wq, hd, eps=1e-6, base=1e6)
             assert close(down(dx), rdx, dt)
             assert rel_err(down(dwq), rdw) <= 1e-4
+        if knob.startswith("swiglu"):
+            arrs = [gi.normal(gi.rng(31 + i), (3 * 3072 * 64 + 5,)) for i in range(3)]
+            for sdt in ("bf16", "f32"):
+                (h1d, h1), (h3d, h3), (dd, d) = [up(a, sdt) for a in arrs]
+                assert close(down(dev.swiglu(h1d, h3d)), oracle.swiglu(h1, h3), sdt)
+                g1, g3 = dev.swiglu_bwd(h1d, h3d, dd)
+                r1, r3 = oracle.swiglu_bwd(h1, h3, d)
+                assert close(down(g1), r1, sdt) and close(down(g3), r3, sdt)
         if knob.startswith("embed"):
             V, D, B, S = 300, 256, 2, 64
             table = gi.normal(gi.rng(11), (V, D), 0.02)
