@@ -560,14 +560,18 @@ qk_fwd_tma_kernel(T *__restrict__ out, const __grid_constant__ CUtensorMap xmap,
     int pb = 0, phd = 0, pt = 0, pbuf = 0;
     bool pactive = false;
 
+    int b = 0, t = 0;                    // sequence and first token of the current tile: one division per tile, not per item
+    bool active = false;
     for (int j = 0; j < n_items; j++) {
         const int tl = ctl, h = ch;
         im.next(j + 1, ctl, ch);
-        const int b = tl / tiles_per_seq;
-        const int t = (tl % tiles_per_seq) * TW + lg * VEC;
-        const bool active = t < S;
         const int s = j % NST, buf = j & 1;
         const bool new_tile = h == 0 || j == 0 || j == im.n_full;
+        if (new_tile) {
+            b = tl / tiles_per_seq;
+            t = (tl - b * tiles_per_seq) * TW + lg * VEC;
+            active = t < S;
+        }
         if (!PIPE && ROPE && new_tile && active) load_table(t);
         if (!mbar_wait_bounded(&full[s], (uint32_t)(j / NST) & 1u, test.wait_limit)) atomicExch(&give_up, 1);
         const T *tile = reinterpret_cast<const T *>(stages + (size_t)s * STAGE_BYTES);
@@ -743,14 +747,18 @@ qk_bwd_tma_kernel(T *__restrict__ dx, float *__restrict__ partial, const __grid_
     int freed = -1;                      // thread 0: every item <= freed has had its sweep 2 run by all threads (as of the last barrier)
     int next_issue = n_items < NST ? n_items : NST;
 
+    int b = 0, t = 0;                    // sequence and first token of the current tile: one division per tile, not per item
+    bool active = false;
     for (int j = 0; j < n_items; j++) {
         const int tl = ctl, h = ch;
         im.next(j + 1, ctl, ch);
-        const int b = tl / tiles_per_seq;
-        const int t = (tl % tiles_per_seq) * TW + lg * VEC;
-        const bool active = t < S;
         const int s = j % NST, buf = j & 1;
         const bool new_tile = h == 0 || j == 0 || j == im.n_full;
+        if (new_tile) {
+            b = tl / tiles_per_seq;
+            t = (tl - b * tiles_per_seq) * TW + lg * VEC;
+            active = t < S;
+        }
         bool flushed = false;
         if (PIPE && pend && ROPE && new_tile) {       // finish item j-1 with its own tile's cos / sin before they are replaced
             __syncthreads();                           // its (rrms, coef)
