@@ -38,7 +38,7 @@ if ROOT not in sys.path:
 TOTAL_SEQS = 256
 FALLBACK_HBM_GBS = 6650.0
 NOMINAL_HBM_GBS = 8000.0
-SWIGLU_BWD_DRAM_BYTES_PER_ALGORITHMIC_BYTE = 0.956
+SWIGLU_BWD_DRAM_BYTES_PER_ALGORITHMIC_BYTE = 0.953
 
 
 def parse_args():
@@ -624,7 +624,7 @@ def run_ours(args):
                 "peak": peak_gbs, "peak_kind": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650",
                 "unit": "GB/s", "frac": round(achieved / peak_gbs, 4), "frac_of_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
                 "traffic": None, "launch_ms": round(k_ms, 4), "launches_timed": len(ev), "algorithmic_bytes_per_launch": k_bytes}
-    # DRAM bytes of this kernel from one profiler capture at 16 sequences (dram__bytes_read + dram__bytes_write = 0.956 of
+    # DRAM bytes of this kernel from one profiler capture at 16 sequences (dram__bytes_read + dram__bytes_write = 0.953 of
     # its algorithmic bytes: the inputs are read exactly once, part of the output is still in L2 when the kernel ends);
     # a streaming kernel's traffic grows in proportion to the elements moved, so the ratio carries to this launch size.
     roofline["traffic"] = int(SWIGLU_BWD_DRAM_BYTES_PER_ALGORITHMIC_BYTE * k_bytes)
