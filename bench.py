@@ -635,7 +635,9 @@ def run_ours(args):
     if roofline["frac"] > 1.0:
         roofline["note"] = ("frac > 1: the denominator is a measured plain copy (read + write), not a hardware limit; this kernel reads three "
                             "streams and writes two, part of its output is still in L2 when it ends (frac_dram), and its clocks under "
-                            "load differ from those of the peak measurement")
+                            "load differ from those of the peak measurement.  Launched back to back for seconds under the 1000 W cap a "
+                            "three-stream copy on this board sustains 6.8 TB/s (146 pJ per byte; python -m ane_b200.opbench --sustain), "
+                            "which is the ceiling of a long step")
 
     chain_bytes = tokens * (cfg.layers * cfg.bytes_per_token_layer() + cfg.bytes_per_token_ends()) + 28 * params.n + 4 * params.n
     line = {
